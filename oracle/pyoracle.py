@@ -1,0 +1,268 @@
+"""ctypes binding of the CPU oracle (oracle/liboracle.so) -- TEST INFRASTRUCTURE, NOT PRODUCT.
+
+Only the test-suite, the smoke check and the benchmark's CPU-baseline leg import this
+module.  Arrays are numpy; fp16 data travels as numpy float16 viewed as uint16.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile oracle.cpp with the Makefile beside it (no-op when up to date)."""
+    src_mtime = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("oracle.cpp", "oracle.h"))
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < src_mtime:
+        subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.orc_f16_to_f32.restype = C.c_float
+        _lib.orc_f16_to_f32.argtypes = [C.c_uint16]
+        _lib.orc_f32_to_f16.restype = C.c_uint16
+        _lib.orc_f32_to_f16.argtypes = [C.c_float]
+        _lib.orc_max_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a, dtype=None):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
+    if dtype is not None:
+        assert a.dtype == dtype, (a.dtype, dtype)
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.int32)
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())
+
+
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    f = lib().orc_f32_to_f16
+    return np.array([f(float(v)) for v in x.ravel()], dtype=np.uint16).reshape(x.shape)
+
+
+def round_f16(x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib().orc_round_to_f16(_p(x), _p(out), C.c_int64(x.size))
+    return out
+
+
+def fill_normal(shape, seed: int, sigma: float = 1.0, round_to_f16: bool = True) -> np.ndarray:
+    out = np.empty(shape, dtype=np.float32)
+    lib().orc_fill_normal(_p(out), C.c_int64(out.size), C.c_uint64(seed), C.c_float(sigma), C.c_int(int(round_to_f16)))
+    return out
+
+
+def permutation(n: int, seed: int) -> np.ndarray:
+    out = np.empty(n, dtype=np.int32)
+    lib().orc_permutation(_p(out), C.c_int32(n), C.c_uint64(seed))
+    return out
+
+
+def uniform_int(n: int, lo: int, hi: int, seed: int) -> np.ndarray:
+    out = np.empty(n, dtype=np.int32)
+    lib().orc_uniform_int(_p(out), C.c_int32(n), C.c_int32(lo), C.c_int32(hi), C.c_uint64(seed))
+    return out
+
+
+def default_inv_freq(theta: float, rotary_dim: int) -> np.ndarray:
+    out = np.empty(rotary_dim // 2, dtype=np.float32)
+    lib().orc_default_inv_freq(C.c_float(theta), C.c_int(rotary_dim), _p(out))
+    return out
+
+
+def yarn_inv_freq(theta, rotary_dim, factor, original_context, beta_fast, beta_slow) -> np.ndarray:
+    out = np.empty(rotary_dim // 2, dtype=np.float32)
+    lib().orc_yarn_inv_freq(C.c_float(theta), C.c_int(rotary_dim), C.c_float(factor), C.c_float(original_context),
+                            C.c_float(beta_fast), C.c_float(beta_slow), _p(out))
+    return out
+
+
+def qk_norm_rope(x, norm_weight, inv_freq, rotary_dim, position_offset, eps=1e-6, factor=1.0, positions=None):
+    """x [B,T,H,D] -> same shape.  positions (int32 [B]) overrides position_offset per batch row."""
+    x = _f32(x)
+    B, T, H, D = x.shape
+    out = np.empty_like(x)
+    w = _f32(norm_weight)
+    inv_freq = _f32(inv_freq)
+    if positions is None:
+        lib().orc_qk_norm_rope_half_split(_p(x), _p(w), _p(inv_freq), _p(out), C.c_int64(B * T * H), C.c_int(T),
+                                          C.c_int(H), C.c_int(D), C.c_int(rotary_dim), C.c_int(position_offset),
+                                          C.c_float(eps), C.c_float(factor))
+    else:
+        pos = _i32(positions)
+        lib().orc_qk_norm_rope_half_split_pos(_p(x), _p(w), _p(inv_freq), _p(out), C.c_int(B), C.c_int(T), C.c_int(H),
+                                              C.c_int(D), C.c_int(rotary_dim), _p(pos), C.c_float(eps),
+                                              C.c_float(factor))
+    return out
+
+
+def rope_slice_glm(x, position_offset, theta):
+    x = _f32(x)
+    B, T, H, R = x.shape
+    out = np.empty_like(x)
+    lib().orc_rope_slice_glm(_p(x), _p(out), C.c_int(B), C.c_int(T), C.c_int(H), C.c_int(R), C.c_int(position_offset),
+                             C.c_float(theta))
+    return out
+
+
+def mla_kv_postprocess(x, norm_weight, tokens, latent_dim, rope_dim, position_offset, theta, eps):
+    x = _f32(x)
+    rows = x.size // (latent_dim + rope_dim)
+    lat = np.empty((rows, latent_dim), dtype=np.float32)
+    rope = np.empty((rows, rope_dim), dtype=np.float32)
+    w = _f32(norm_weight)
+    lib().orc_mla_kv_postprocess(_p(x), _p(w), _p(lat), _p(rope), C.c_int64(rows), C.c_int(tokens),
+                                 C.c_int(latent_dim), C.c_int(rope_dim), C.c_int(position_offset), C.c_float(theta),
+                                 C.c_float(eps))
+    return lat, rope
+
+
+def gqa_ring_attention(q, k, v, gate, cached_k, cached_v, past_tokens, stored_tokens, capacity, sliding_window=0,
+                       fuse_append=True):
+    """q [B,T,Hq,D]; k,v [B,T,Hkv,D]; cached_* uint16 [B,capacity,Hkv,D] (modified in place)."""
+    q, k, v, gate = _f32(q), _f32(k), _f32(v), _f32(gate)
+    B, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    out = np.empty_like(q)
+    lib().orc_gqa_ring_attention(_p(q), _p(k), _p(v), _p(gate), _p(cached_k, np.uint16), _p(cached_v, np.uint16),
+                                 _p(out), C.c_int(B), C.c_int(Hq), C.c_int(Hkv), C.c_int(D), C.c_int(T),
+                                 C.c_int(past_tokens), C.c_int(stored_tokens), C.c_int(capacity),
+                                 C.c_int(sliding_window), C.c_int(int(fuse_append)))
+    return out
+
+
+def test_cpu_gqa(q, k, v, gate, q_heads, kv_heads, head_dim, sliding_window=0, last_only=False):
+    q, k, v, gate = _f32(q), _f32(k), _f32(v), _f32(gate)
+    tokens = k.size // (kv_heads * head_dim)
+    out = np.empty((q_heads, head_dim) if last_only else (tokens, q_heads, head_dim), dtype=np.float32)
+    lib().orc_test_cpu_gqa(_p(q), _p(k), _p(v), _p(gate), _p(out), C.c_int(tokens), C.c_int(q_heads),
+                           C.c_int(kv_heads), C.c_int(head_dim), C.c_int(sliding_window), C.c_int(int(last_only)))
+    return out
+
+
+def gqa_ring_decode_segmented(q, k, v, gate, cached_k, cached_v, past_tokens, cached_start, cached_count, capacity,
+                              segment_tokens):
+    q, k, v, gate = _f32(q), _f32(k), _f32(v), _f32(gate)
+    B, Hq, D = q.shape[0], q.shape[-2], q.shape[-1]
+    Hkv = k.shape[-2]
+    out = np.empty((B, Hq, D), dtype=np.float32)
+    lib().orc_gqa_ring_decode_segmented(_p(q), _p(k), _p(v), _p(gate), _p(cached_k, np.uint16),
+                                        _p(cached_v, np.uint16), _p(out), C.c_int(B), C.c_int(Hq), C.c_int(Hkv),
+                                        C.c_int(D), C.c_int(past_tokens), C.c_int(cached_start),
+                                        C.c_int(cached_count), C.c_int(capacity), C.c_int(segment_tokens))
+    return out
+
+
+def gqa_paged_attention(q, k, v, gate, k_pool, v_pool, page_table, past_tokens, page_size, sliding_window=0,
+                        fuse_append=True, scale=0.0, threads=0):
+    """q [B,T,Hq,D]; k,v [B,T,Hkv,D] f32; pools uint16 [pages,Hkv,P,D] (modified in place when appending)."""
+    q, k, v, gate = _f32(q), _f32(k), _f32(v), _f32(gate)
+    B, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    pt = _i32(page_table)
+    past = _i32(past_tokens)
+    out = np.empty_like(q)
+    lib().orc_gqa_paged_attention(_p(q), _p(k), _p(v), _p(gate), _p(k_pool, np.uint16), _p(v_pool, np.uint16), _p(pt),
+                                  C.c_int(pt.shape[1]), _p(past), _p(out), C.c_int(B), C.c_int(Hq), C.c_int(Hkv),
+                                  C.c_int(D), C.c_int(page_size), C.c_int(T), C.c_int(sliding_window),
+                                  C.c_int(int(fuse_append)), C.c_float(scale), C.c_int(threads))
+    return out
+
+
+def linearize_paged(pool, page_table, tokens, page_size):
+    pt = _i32(page_table)
+    B = pt.shape[0]
+    _, Hkv, P, D = pool.shape
+    out = np.empty((B, Hkv, tokens, D), dtype=np.uint16)
+    lib().orc_linearize_paged(_p(pool, np.uint16), _p(pt), C.c_int(pt.shape[1]), _p(out), C.c_int(B), C.c_int(Hkv),
+                              C.c_int(tokens), C.c_int(page_size), C.c_int(D))
+    return out
+
+
+def paged_decode_mha_f16(q, paged_k, cur_k, paged_v, cur_v, past_tokens, page_size):
+    q, cur_k, cur_v = _f32(q), _f32(cur_k), _f32(cur_v)
+    B, H, D = q.shape
+    Dv = cur_v.shape[-1]
+    out = np.empty((B, H, Dv), dtype=np.float32)
+    lib().orc_paged_decode_mha_f16(_p(q), _p(paged_k, np.uint16), _p(cur_k), _p(paged_v, np.uint16), _p(cur_v),
+                                   _p(out), C.c_int(B), C.c_int(H), C.c_int(past_tokens), C.c_int(page_size),
+                                   C.c_int(D), C.c_int(Dv))
+    return out
+
+
+def q8_0_heads_matvec(weights: np.ndarray, x, heads, in_features, out_features):
+    x = _f32(x)
+    rows = x.size // (heads * in_features)
+    out = np.empty((rows, heads, out_features), dtype=np.float32)
+    w = np.ascontiguousarray(weights, dtype=np.uint8)
+    lib().orc_q8_0_heads_matvec(_p(w), _p(x), _p(out), C.c_int64(rows), C.c_int(heads), C.c_int(in_features),
+                                C.c_int(out_features))
+    return out
+
+
+def mla_absorbed_f32(q_latent, q_rope, paged_latent, cur_latent, paged_rope, cur_rope, batch, heads, q_tokens,
+                     past_tokens, page_size, latent_dim, rope_dim, scale_dim):
+    a = [_f32(t) for t in (q_latent, q_rope, paged_latent, cur_latent, paged_rope, cur_rope)]
+    out = np.empty((batch, q_tokens, heads, latent_dim), dtype=np.float32)
+    lib().orc_mla_absorbed_f32(_p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(a[5]), _p(out), C.c_int(batch),
+                               C.c_int(heads), C.c_int(q_tokens), C.c_int(past_tokens), C.c_int(page_size),
+                               C.c_int(latent_dim), C.c_int(rope_dim), C.c_int(scale_dim))
+    return out
+
+
+def mla_absorbed_paged(q, cur_rows, pool, page_table, past_tokens, page_size, latent_dim, rope_dim, scale,
+                       fuse_append=True, threads=0):
+    """q [B,T,H,L+R] f32; cur_rows [B,T,L+R] f32; pool uint16 [pages,P,L+R]."""
+    q, cur_rows = _f32(q), _f32(cur_rows)
+    B, T, H, _ = q.shape
+    pt = _i32(page_table)
+    past = _i32(past_tokens)
+    out = np.empty((B, T, H, latent_dim), dtype=np.float32)
+    lib().orc_mla_absorbed_paged(_p(q), _p(cur_rows), _p(pool, np.uint16), _p(pt), C.c_int(pt.shape[1]), _p(past),
+                                 _p(out), C.c_int(B), C.c_int(H), C.c_int(T), C.c_int(page_size), C.c_int(latent_dim),
+                                 C.c_int(rope_dim), C.c_float(scale), C.c_int(int(fuse_append)), C.c_int(threads))
+    return out
+
+
+def causal_mha(q, k_nope, k_rope, v, scale, rows=None, threads=0):
+    """q [T,H,dn+dr]; k_nope [T,H,dn]; k_rope [T,dr] or None; v [T,H,dv]; rows int32 list or None."""
+    q, k_nope, v = _f32(q), _f32(k_nope), _f32(v)
+    T, H, dqk = q.shape
+    dn = k_nope.shape[2]
+    dr = dqk - dn
+    kr = _f32(k_rope) if dr else None
+    dv = v.shape[2]
+    r = _i32(rows) if rows is not None else None
+    n = len(r) if r is not None else T
+    out = np.empty((n, H, dv), dtype=np.float32)
+    lib().orc_causal_mha(_p(q), _p(k_nope), _p(kr), _p(v), _p(out), C.c_int(T), C.c_int(H), C.c_int(dn), C.c_int(dr),
+                         C.c_int(dv), C.c_float(scale), _p(r), C.c_int(n), C.c_int(threads))
+    return out
