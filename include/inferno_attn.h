@@ -1,0 +1,212 @@
+/* inferno_attn.h -- C ABI of the B200 (sm_100a) attention backend.
+ *
+ * This is the boundary a `CudaBackend` implementation of the reference's
+ * `trait Backend` (crates/backend/src/backend.rs:711) binds over FFI for the attention
+ * path: fused RoPE + KV-append, paged GQA decode, causal GQA prefill, absorbed-MLA
+ * decode and causal MLA prefill.  Plain pointers and sizes only; every pointer named
+ * "device" is a CUDA device pointer on the context's GPU.
+ *
+ * Conventions
+ *   - every op returns int32_t: INF_OK (0), INF_UNSUPPORTED (1, the reference's
+ *     `Ok(None)`: "this backend has no device path for these arguments",
+ *     backend.rs:1054-1056) or a negative INF_E_* mirroring `common::Error`
+ *     (crates/common/src/error.rs:7-52).  inf_last_error() returns the message.
+ *   - all shape / length / dtype checks run on the host before any launch, like the
+ *     reference's validate_execution (crates/backend/src/metal/f16_attention.rs:602-680);
+ *     nothing aborts and no kernel traps.
+ *   - ops are enqueued on the context's stream and return without synchronising;
+ *     dependent ops need no host sync (the guarantee Metal hazard tracking gives the
+ *     reference, crates/backend/src/metal/batch.rs:14-17).  inf_flush() waits.
+ *   - there is no CPU fallback: without a CUDA device the context cannot be created.
+ *   - a context is used from one thread at a time (the reference serialises through a
+ *     mutex around its open command buffer, metal/batch.rs:34-55).
+ *
+ * KV layout in HBM (generalises crates/cache/src/paged.rs:40-72 and the kernel formula
+ * kernels/attention_kernels.metal:377-379 from the identity page map to a page table):
+ *   GQA pools   K and V: fp16 [num_pages][kv_heads][page_size][head_dim]
+ *   MLA pool    fp16 [num_pages][page_size][latent_dim + rope_dim]   (512 + 64)
+ *   page table  int32 [batch][max_pages]: logical token n of sequence b lives in page
+ *               page_table[b][n / page_size] at slot n % page_size
+ */
+#ifndef INFERNO_ATTN_H
+#define INFERNO_ATTN_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define INF_OK 0
+#define INF_UNSUPPORTED 1
+#define INF_E_BACKEND (-1)  /* Error::Backend: CUDA failure, device status word set */
+#define INF_E_SHAPE (-2)    /* Error::ShapeMismatch */
+#define INF_E_CONFIG (-3)   /* Error::Config */
+#define INF_E_CACHE (-4)    /* Error::Cache: page table / capacity problems */
+#define INF_E_DTYPE (-5)    /* unsupported dtype */
+#define INF_E_ARG (-6)      /* null pointer, bad handle */
+
+#define INF_DTYPE_F32 0
+#define INF_DTYPE_F16 1
+
+typedef struct inf_ctx inf_ctx;
+
+/* ---- context, memory, ordering ------------------------------------------------ */
+/* MetalBackend::new / from_device (backend.rs:2175-2260).  `stream` is a cudaStream_t to
+ * enqueue on, or NULL for a stream owned by the context. */
+int32_t inf_ctx_create(int32_t device_ordinal, void* stream, inf_ctx** out);
+int32_t inf_ctx_destroy(inf_ctx* ctx);
+const char* inf_last_error(inf_ctx* ctx);
+/* device_values_supported (backend.rs:1060). */
+int32_t inf_device_values_supported(inf_ctx* ctx);
+/* device_flush (backend.rs:1066): wait for the stream, then report the device status word
+ * (bounded waits that gave up, page ids out of range) as INF_E_BACKEND. */
+int32_t inf_flush(inf_ctx* ctx);
+/* device_submit (backend.rs:1072): launches are already asynchronous; checks arguments only. */
+int32_t inf_submit(inf_ctx* ctx);
+/* device_alloc_f32/f16_tensor (backend.rs:1098/1104), device_upload_f32_tensor (:1086),
+ * device_upload_f32_tensor_as_f16 (:1092), device_copy_same_dtype (:1110),
+ * device_download_f32_tensor (:1136). */
+int32_t inf_alloc(inf_ctx* ctx, size_t bytes, void** device_out);
+int32_t inf_free(inf_ctx* ctx, void* device_ptr);
+int32_t inf_upload(inf_ctx* ctx, void* device_dst, const void* host_src, size_t bytes);
+int32_t inf_upload_f32_as_f16(inf_ctx* ctx, void* device_dst_f16, const float* host_src, size_t count);
+int32_t inf_download(inf_ctx* ctx, void* host_dst, const void* device_src, size_t bytes);
+int32_t inf_copy(inf_ctx* ctx, void* device_dst, const void* device_src, size_t bytes);
+int32_t inf_memset_zero(inf_ctx* ctx, void* device_dst, size_t bytes);
+
+/* ---- descriptors ---------------------------------------------------------------- */
+/* DeviceRopeTable (backend.rs:239-244), built by prepare_rope_table (backend.rs:1227):
+ * inverse frequencies for the half-split convention plus the factor multiplied into cos/sin. */
+typedef struct inf_rope_table {
+    const float* inv_freq; /* device, rotary_dim / 2 entries */
+    int32_t rotary_dim;    /* 64 or 128 (metal/rope.rs:472-487) */
+    float attention_factor;
+} inf_rope_table;
+int32_t inf_rope_table_create(inf_ctx* ctx, const float* host_inv_freq, int32_t count, int32_t rotary_dim,
+                              float attention_factor, inf_rope_table* out);
+int32_t inf_rope_table_destroy(inf_ctx* ctx, inf_rope_table* table);
+
+/* The paged replacement of LagunaF16KvCache (backend.rs:297-314): caller-owned pools. */
+typedef struct inf_kv_pool {
+    void* k; /* device fp16 [num_pages][kv_heads][page_size][head_dim] */
+    void* v;
+    int32_t num_pages, page_size, kv_heads, head_dim;
+} inf_kv_pool;
+/* prepare_laguna_f16_kv_cache (backend.rs:1322): allocates and zero-fills both pools. */
+int32_t inf_kv_pool_create(inf_ctx* ctx, int32_t num_pages, int32_t page_size, int32_t kv_heads, int32_t head_dim,
+                           inf_kv_pool* out);
+int32_t inf_kv_pool_destroy(inf_ctx* ctx, inf_kv_pool* pool);
+
+/* The paged replacement of DevicePagedKvView for the MLA latent layout (backend.rs:543-553;
+ * latent in view.k, rope tail in view.v, metal/attention.rs:1147-1155): one fused row. */
+typedef struct inf_mla_pool {
+    void* rows; /* device fp16 [num_pages][page_size][latent_dim + rope_dim] */
+    int32_t num_pages, page_size, latent_dim, rope_dim;
+} inf_mla_pool;
+int32_t inf_mla_pool_create(inf_ctx* ctx, int32_t num_pages, int32_t page_size, int32_t latent_dim,
+                            int32_t rope_dim, inf_mla_pool* out);
+int32_t inf_mla_pool_destroy(inf_ctx* ctx, inf_mla_pool* pool);
+
+/* Page table of a batch.  `lens` has the meaning each op states.  The host mirrors are
+ * optional: when given, every entry a launch can touch is range-checked on the host first
+ * (INF_E_CACHE); kernels additionally refuse out-of-range pages and raise the status word. */
+typedef struct inf_page_table {
+    const int32_t* pages; /* device int32 [batch][max_pages] */
+    const int32_t* lens;  /* device int32 [batch] */
+    int32_t batch, max_pages;
+    const int32_t* host_pages; /* optional host copy of pages */
+    const int32_t* host_lens;  /* optional host copy of lens  */
+} inf_page_table;
+
+/* ---- RoPE and KV append ----------------------------------------------------------- */
+/* laguna_qk_rms_norm_rope_pair_device (backend.rs:1252; kernel rope_kernels.metal:167):
+ * per-head RMSNorm (weight NULL = no norm) then half-split RoPE, f32 in / f32 out.
+ * q [batch, tokens, q_heads, head_dim], k [batch, tokens, kv_heads, head_dim]. */
+int32_t inf_laguna_qk_rms_norm_rope_pair(inf_ctx* ctx, const float* q, const float* k, const float* q_norm_weight,
+                                         const float* k_norm_weight, float eps, int32_t position_offset,
+                                         const inf_rope_table* rope, int32_t batch, int32_t tokens, int32_t q_heads,
+                                         int32_t kv_heads, int32_t head_dim, float* q_out, float* k_out);
+
+/* Fused RoPE + KV-append: the rope kernel above fused with the cache append of
+ * f16_attention_kernels.metal:131-143 / :512-544.  Row t of sequence b sits at position
+ * lens[b] + t (lens = tokens already cached).  q/k/v are device f32 or fp16 (in_dtype);
+ * q_out receives the roped queries as fp16 [batch, tokens, q_heads, head_dim] (the layout
+ * the attention kernels read); K (roped) and V are written RNE-fp16 into their pages.
+ * k_roped_f32_out is optional (NULL): the roped keys in f32, as the reference returns them. */
+int32_t inf_rope_append_gqa(inf_ctx* ctx, const void* q, const void* k, const void* v, int32_t in_dtype,
+                            const float* q_norm_weight, const float* k_norm_weight, float eps,
+                            const inf_rope_table* rope, const inf_kv_pool* pool, const inf_page_table* table,
+                            int32_t tokens, int32_t q_heads, void* q_out_f16, float* k_roped_f32_out);
+
+/* rope_slice_device (backend.rs:1866; kernel rope_kernels.metal:5): GLM interleaved-pair RoPE,
+ * f32 [batch, tokens, heads, rope_dim]. */
+int32_t inf_rope_slice(inf_ctx* ctx, const float* input, float* output, int32_t batch, int32_t tokens, int32_t heads,
+                       int32_t rope_dim, int32_t position_offset, float theta);
+
+/* mla_kv_postprocess_device (backend.rs:1895; kernel norm_kernels.metal:52) fused with the append
+ * the reference does by downloading rows and blitting them into the paged window
+ * (crates/runtime/src/lib.rs:3696-3795, 4963-5045).  input f32 [batch, tokens, latent+rope];
+ * row t of sequence b is post-processed at position lens[b] + t and stored RNE-fp16 at that
+ * logical slot.  latent_out / rope_out (f32, optional) are the reference's two outputs. */
+int32_t inf_mla_kv_postprocess_append(inf_ctx* ctx, const float* input, const float* norm_weight, float eps,
+                                      float theta, const inf_mla_pool* pool, const inf_page_table* table,
+                                      int32_t tokens, float* latent_out, float* rope_out);
+
+/* ---- attention ---------------------------------------------------------------------- */
+/* Paged GQA decode, split-KV (kernels f16_attention_kernels.metal:325-510, generalised to pages):
+ * q fp16 [batch, q_heads, head_dim]; lens[b] = visible keys including the current token, which
+ * has already been appended.  sliding_window 0 = full.  gate (f32 [batch, q_heads], optional)
+ * applies softplus(gate) like the reference.  scale <= 0 means 1/sqrt(head_dim).
+ * max_len >= max(lens) sizes the grid; split_chunk keys per partial (multiple of 64).
+ * out: [batch, q_heads, head_dim] in out_dtype. */
+int32_t inf_gqa_decode_paged(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
+                             int32_t q_heads, int32_t max_len, int32_t split_chunk, int32_t sliding_window,
+                             const float* gate, float scale, void* out, int32_t out_dtype);
+/* Bytes of scratch inf_gqa_decode_paged needs for these sizes (the context grows its own). */
+size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t max_len,
+                                      int32_t split_chunk);
+
+/* Causal GQA prefill over pages (kernel f16_attention_kernels.metal:153-316, generalised):
+ * q fp16 [batch, tokens, q_heads, head_dim]; lens[b] = keys cached BEFORE this chunk; the chunk's
+ * K/V have already been appended at lens[b]..lens[b]+tokens-1.  Row t sees keys
+ * [max(0, p+1-window), p], p = lens[b] + t.  out [batch, tokens, q_heads, head_dim]. */
+int32_t inf_gqa_prefill_paged(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
+                              int32_t tokens, int32_t q_heads, int32_t sliding_window, const float* gate, float scale,
+                              void* out, int32_t out_dtype);
+
+/* laguna_gated_gqa_f16_attention_device (backend.rs:1350) as one call: f32 q/k/v (already roped),
+ * f32 gate, append then attend.  lens[b] = tokens cached before the call; the caller advances its
+ * host counters afterwards, like commit_append (backend.rs:5400).  max_len >= max(lens) + tokens. */
+int32_t inf_laguna_gated_gqa_f16_attention(inf_ctx* ctx, const float* q, const float* k, const float* v,
+                                           const float* gate, const inf_kv_pool* pool, const inf_page_table* table,
+                                           int32_t tokens, int32_t q_heads, int32_t max_len, int32_t sliding_window,
+                                           float* out);
+
+/* Absorbed-MLA decode (kernel attention_kernels.metal:465-603; q8_0_absorbed_mla_device backend.rs:1982
+ * without its K_b / V_b projections): q fp16 [batch, tokens, heads, latent+rope] = q_latent || q_rope;
+ * lens[b] = cached rows BEFORE this call's `tokens` rows, which have already been appended; row t sees
+ * rows 0..lens[b]+t.  scale = 1/sqrt(scale_dim).  out [batch, tokens, heads, latent_dim]. */
+int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool,
+                                const inf_page_table* table, int32_t tokens, int32_t heads, int32_t max_len,
+                                float scale, void* out, int32_t out_dtype);
+
+/* Causal attention over expanded heads = the reference's MLA prefill
+ * (causal_sequence_attention_device backend.rs:2028; kernel attention_kernels.metal:723).
+ * fp16 tensors with element strides: q [tokens][heads][nope+rope], k_nope [tokens][heads][nope],
+ * k_rope [tokens][rope] shared by all heads (layout_kernels.metal:166-182), v [tokens][heads][v_dim].
+ * *_ts / *_hs are token and head strides in elements (innermost stride 1). */
+int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs, const void* k_nope,
+                               int64_t kn_ts, int64_t kn_hs, const void* k_rope, int64_t kr_ts, const void* v,
+                               int64_t v_ts, int64_t v_hs, int32_t tokens, int32_t heads, int32_t nope_dim,
+                               int32_t rope_dim, int32_t v_dim, float scale, void* out, int64_t o_ts, int64_t o_hs,
+                               int32_t out_dtype);
+
+/* paged_kv_contiguous_device (backend.rs:2040; kernel layout_kernels.metal:205): gather logical rows
+ * of one pool out of its pages: out fp16 [batch][kv_heads][tokens][head_dim]. */
+int32_t inf_linearize_paged(inf_ctx* ctx, const void* pool_f16, const inf_kv_pool* shape,
+                            const inf_page_table* table, int32_t tokens, void* out_f16);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

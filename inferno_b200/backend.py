@@ -1,0 +1,260 @@
+"""Host-side mirror of the reference's backend operator surface for the attention path.
+
+`CudaBackend` plays the role of the reference's `MetalBackend` (crates/backend/src/backend.rs:2175)
+for the methods of `trait Backend` that lie on the attention path; method names follow the trait.
+Every method is a thin shim over one C-ABI call of libinferno_attn.so.  torch is used for device
+memory and stream plumbing only: tensors are handed to the library as raw device pointers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import lib as L
+from .lib import InfernoError
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "device tensors must be contiguous CUDA tensors"
+    return C.c_void_p(t.data_ptr())
+
+
+@dataclass
+class KvPool:
+    """Caller-owned paged K/V storage: fp16 [num_pages, kv_heads, page_size, head_dim] each."""
+    k: torch.Tensor
+    v: torch.Tensor
+    desc: L.KvPool
+
+    @property
+    def page_size(self):
+        return self.desc.page_size
+
+
+@dataclass
+class MlaPool:
+    """Caller-owned paged latent storage: fp16 [num_pages, page_size, latent_dim + rope_dim]."""
+    rows: torch.Tensor
+    desc: L.MlaPool
+
+
+@dataclass
+class PageTable:
+    pages: torch.Tensor  # int32 [batch, max_pages] on the device
+    lens: torch.Tensor   # int32 [batch] on the device
+    desc: L.PageTable
+    host_pages: Optional[torch.Tensor] = None
+    host_lens: Optional[torch.Tensor] = None
+
+
+class CudaBackend:
+    def __init__(self, device: int = 0, stream: Optional[torch.cuda.Stream] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("CudaBackend needs a CUDA device: there is no CPU fallback")
+        self._lib = L.load()
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        self.stream = stream if stream is not None else torch.cuda.current_stream(self.device)
+        h = C.c_void_p()
+        rc = self._lib.inf_ctx_create(device, C.c_void_p(self.stream.cuda_stream), C.byref(h))
+        if rc != L.INF_OK:
+            raise InfernoError(rc, "inf_ctx_create failed (is this an sm_100 GPU?)")
+        self._ctx = h
+        self._keep = []
+
+    def close(self):
+        if getattr(self, "_ctx", None):
+            self._lib.inf_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ helpers
+    def _check(self, rc: int):
+        if rc == L.INF_OK:
+            return True
+        if rc == L.INF_UNSUPPORTED:
+            return None  # the reference's Ok(None)
+        raise InfernoError(rc, self._lib.inf_last_error(self._ctx).decode())
+
+    def device_values_supported(self) -> bool:  # backend.rs:1060
+        return bool(self._lib.inf_device_values_supported(self._ctx))
+
+    def device_flush(self):  # backend.rs:1066
+        self._check(self._lib.inf_flush(self._ctx))
+
+    def device_submit(self):  # backend.rs:1072
+        self._check(self._lib.inf_submit(self._ctx))
+
+    def device_upload_f32_tensor(self, host: torch.Tensor) -> torch.Tensor:  # backend.rs:1086
+        host = host.contiguous().float()
+        out = torch.empty(host.shape, dtype=torch.float32, device=self.device)
+        self._check(self._lib.inf_upload(self._ctx, _ptr(out), C.c_void_p(host.data_ptr()), host.numel() * 4))
+        return out
+
+    def device_upload_f32_tensor_as_f16(self, host: torch.Tensor) -> torch.Tensor:  # backend.rs:1092
+        host = host.contiguous().float()
+        out = torch.empty(host.shape, dtype=torch.float16, device=self.device)
+        self._check(self._lib.inf_upload_f32_as_f16(self._ctx, _ptr(out), C.c_void_p(host.data_ptr()), host.numel()))
+        return out
+
+    def device_download_f32_tensor(self, dev: torch.Tensor) -> torch.Tensor:  # backend.rs:1136
+        assert dev.dtype == torch.float32
+        out = torch.empty(dev.shape, dtype=torch.float32)
+        self._check(self._lib.inf_download(self._ctx, C.c_void_p(out.data_ptr()), _ptr(dev), dev.numel() * 4))
+        return out
+
+    # ------------------------------------------------------------------ descriptors
+    def prepare_rope_table(self, inv_freq, rotary_dim: int, attention_factor: float) -> L.RopeTable:  # backend.rs:1227
+        host = torch.as_tensor(inv_freq, dtype=torch.float32).contiguous()
+        t = L.RopeTable()
+        self._check(self._lib.inf_rope_table_create(self._ctx, C.c_void_p(host.data_ptr()), host.numel(), rotary_dim,
+                                                    attention_factor, C.byref(t)))
+        return t
+
+    def prepare_kv_pool(self, num_pages: int, page_size: int, kv_heads: int, head_dim: int = 128) -> KvPool:
+        """prepare_laguna_f16_kv_cache (backend.rs:1322) for the paged layout; zero-filled."""
+        if page_size <= 0 or page_size % 16:
+            raise InfernoError(L.INF_E_CACHE, f"page_size must be a positive multiple of 16, got {page_size}")
+        if head_dim != 128:
+            raise InfernoError(L.INF_E_SHAPE, f"head_dim must be 128, got {head_dim}")
+        k = torch.zeros((num_pages, kv_heads, page_size, head_dim), dtype=torch.float16, device=self.device)
+        v = torch.zeros_like(k)
+        return KvPool(k, v, L.KvPool(k.data_ptr(), v.data_ptr(), num_pages, page_size, kv_heads, head_dim))
+
+    def prepare_mla_pool(self, num_pages: int, page_size: int = 64, latent_dim: int = 512, rope_dim: int = 64) -> MlaPool:
+        if page_size != 64:
+            raise InfernoError(L.INF_E_CACHE, f"MLA page_size must be 64, got {page_size}")
+        if latent_dim != 512 or rope_dim != 64:
+            raise InfernoError(L.INF_E_SHAPE, "MLA rows must be 512 + 64 wide")
+        rows = torch.zeros((num_pages, page_size, latent_dim + rope_dim), dtype=torch.float16, device=self.device)
+        return MlaPool(rows, L.MlaPool(rows.data_ptr(), num_pages, page_size, latent_dim, rope_dim))
+
+    def page_table(self, pages, lens, validate_on_host: bool = True) -> PageTable:
+        """pages int32 [batch, max_pages], lens int32 [batch]; host or device tensors."""
+        pages_t = torch.as_tensor(pages, dtype=torch.int32)
+        lens_t = torch.as_tensor(lens, dtype=torch.int32)
+        hp = pages_t.cpu().contiguous() if validate_on_host else None
+        hl = lens_t.cpu().contiguous() if validate_on_host else None
+        dp = pages_t.to(self.device).contiguous()
+        dl = lens_t.to(self.device).contiguous()
+        desc = L.PageTable(dp.data_ptr(), dl.data_ptr(), dp.shape[0], dp.shape[1],
+                           hp.data_ptr() if hp is not None else None, hl.data_ptr() if hl is not None else None)
+        return PageTable(dp, dl, desc, hp, hl)
+
+    # ------------------------------------------------------------------ RoPE + append
+    def laguna_qk_rms_norm_rope_pair_device(self, q, k, q_norm, k_norm, eps, position_offset, table):  # backend.rs:1252
+        B, T, Hq, D = q.shape
+        Hkv = k.shape[2]
+        q_out, k_out = torch.empty_like(q), torch.empty_like(k)
+        ok = self._check(self._lib.inf_laguna_qk_rms_norm_rope_pair(
+            self._ctx, _ptr(q), _ptr(k), _ptr(q_norm), _ptr(k_norm), eps, position_offset, C.byref(table), B, T, Hq,
+            Hkv, D, _ptr(q_out), _ptr(k_out)))
+        return (q_out, k_out) if ok else None
+
+    def rope_append_gqa(self, q, k, v, rope, pool: KvPool, table: PageTable, q_norm=None, k_norm=None, eps=1e-6,
+                        want_k_f32=False):
+        """Fused per-head RMSNorm + half-split RoPE + paged KV append.  Returns roped q (fp16)."""
+        B, T, Hq, D = q.shape
+        if q.dtype != k.dtype or q.dtype != v.dtype or q.dtype not in (torch.float32, torch.float16):
+            raise InfernoError(L.INF_E_DTYPE, "q/k/v must share dtype f32 or f16")
+        dt = L.DTYPE_F32 if q.dtype == torch.float32 else L.DTYPE_F16
+        q_out = torch.empty((B, T, Hq, D), dtype=torch.float16, device=self.device)
+        k_f32 = torch.empty(k.shape, dtype=torch.float32, device=self.device) if want_k_f32 else None
+        self._check(self._lib.inf_rope_append_gqa(
+            self._ctx, _ptr(q), _ptr(k), _ptr(v), dt, _ptr(q_norm), _ptr(k_norm), eps,
+            C.byref(rope) if rope is not None else None, C.byref(pool.desc), C.byref(table.desc), T, Hq, _ptr(q_out),
+            _ptr(k_f32)))
+        return (q_out, k_f32) if want_k_f32 else q_out
+
+    def rope_slice_device(self, x, rope_dim, position_offset, theta):  # backend.rs:1866
+        B, T, H, R = x.shape
+        out = torch.empty_like(x)
+        self._check(self._lib.inf_rope_slice(self._ctx, _ptr(x), _ptr(out), B, T, H, rope_dim, position_offset, theta))
+        return out
+
+    def mla_kv_postprocess_device(self, x, norm_weight, eps, theta, pool: MlaPool, table: PageTable, want_outputs=True):
+        """mla_kv_postprocess_device (backend.rs:1895) fused with the paged append."""
+        B, T, W = x.shape
+        lat = torch.empty((B, T, pool.desc.latent_dim), dtype=torch.float32, device=self.device) if want_outputs else None
+        rope = torch.empty((B, T, pool.desc.rope_dim), dtype=torch.float32, device=self.device) if want_outputs else None
+        self._check(self._lib.inf_mla_kv_postprocess_append(self._ctx, _ptr(x), _ptr(norm_weight), eps, theta,
+                                                            C.byref(pool.desc), C.byref(table.desc), T, _ptr(lat),
+                                                            _ptr(rope)))
+        return lat, rope
+
+    # ------------------------------------------------------------------ attention
+    def gqa_decode_paged(self, q_f16, pool: KvPool, table: PageTable, max_len: int, split_chunk: int = 512,
+                         sliding_window: int = 0, gate=None, scale: float = 0.0, out_dtype=torch.float32, out=None):
+        B, Hq, D = q_f16.shape
+        if out is None:
+            out = torch.empty((B, Hq, D), dtype=out_dtype, device=self.device)
+        dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
+        ok = self._check(self._lib.inf_gqa_decode_paged(self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc),
+                                                        Hq, max_len, split_chunk, sliding_window, _ptr(gate), scale,
+                                                        _ptr(out), dt))
+        return out if ok else None
+
+    def gqa_prefill_paged(self, q_f16, pool: KvPool, table: PageTable, sliding_window: int = 0, gate=None,
+                          scale: float = 0.0, out_dtype=torch.float16, out=None):
+        B, T, Hq, D = q_f16.shape
+        if out is None:
+            out = torch.empty((B, T, Hq, D), dtype=out_dtype, device=self.device)
+        dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
+        ok = self._check(self._lib.inf_gqa_prefill_paged(self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc),
+                                                         T, Hq, sliding_window, _ptr(gate), scale, _ptr(out), dt))
+        return out if ok else None
+
+    def laguna_gated_gqa_f16_attention_device(self, q, k, v, gate, pool: KvPool, table: PageTable, max_len: int,
+                                              sliding_window: int = 0):  # backend.rs:1350
+        B, T, Hq, D = q.shape
+        out = torch.empty((B, T, Hq, D), dtype=torch.float32, device=self.device)
+        ok = self._check(self._lib.inf_laguna_gated_gqa_f16_attention(
+            self._ctx, _ptr(q), _ptr(k), _ptr(v), _ptr(gate), C.byref(pool.desc), C.byref(table.desc), T, Hq, max_len,
+            sliding_window, _ptr(out)))
+        return out if ok else None
+
+    def mla_decode_absorbed(self, q_f16, pool: MlaPool, table: PageTable, max_len: int, scale: float,
+                            out_dtype=torch.float32, out=None):
+        B, T, H, W = q_f16.shape
+        if out is None:
+            out = torch.empty((B, T, H, pool.desc.latent_dim), dtype=out_dtype, device=self.device)
+        dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
+        ok = self._check(self._lib.inf_mla_decode_absorbed(self._ctx, _ptr(q_f16), C.byref(pool.desc),
+                                                           C.byref(table.desc), T, H, max_len, scale, _ptr(out), dt))
+        return out if ok else None
+
+    def causal_sequence_attention_device(self, q, k_nope, k_rope, v, scale: float, out_dtype=torch.float16):
+        """causal_sequence_attention_device (backend.rs:2028) for MLA prefill: q [T,H,dn+dr], k_nope [T,H,dn],
+        k_rope [T,dr] shared by the heads (or None), v [T,H,dv]; any token/head strides, unit inner stride."""
+        T, H, dqk = q.shape
+        dn = k_nope.shape[2]
+        dr = dqk - dn
+        dv = v.shape[2]
+        out = torch.empty((T, H, dv), dtype=out_dtype, device=self.device)
+        dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
+        for t in (q, k_nope, v) + ((k_rope,) if k_rope is not None else ()):
+            assert t.stride(-1) == 1 and t.dtype == torch.float16
+        ok = self._check(self._lib.inf_mla_prefill_causal(
+            self._ctx, C.c_void_p(q.data_ptr()), q.stride(0), q.stride(1), C.c_void_p(k_nope.data_ptr()),
+            k_nope.stride(0), k_nope.stride(1), C.c_void_p(k_rope.data_ptr()) if k_rope is not None else None,
+            k_rope.stride(0) if k_rope is not None else 0, C.c_void_p(v.data_ptr()), v.stride(0), v.stride(1), T, H,
+            dn, dr, dv, scale, _ptr(out), out.stride(0), out.stride(1), dt))
+        return out if ok else None
+
+    def paged_kv_contiguous_device(self, which: torch.Tensor, pool: KvPool, table: PageTable, tokens: int):
+        """paged_kv_contiguous_device (backend.rs:2040): gather [batch, kv_heads, tokens, head_dim] out of the pages."""
+        B = table.desc.batch
+        out = torch.empty((B, pool.desc.kv_heads, tokens, pool.desc.head_dim), dtype=torch.float16, device=self.device)
+        self._check(self._lib.inf_linearize_paged(self._ctx, _ptr(which), C.byref(pool.desc), C.byref(table.desc),
+                                                  tokens, _ptr(out)))
+        return out

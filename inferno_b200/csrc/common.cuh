@@ -1,0 +1,84 @@
+// Host-side plumbing shared by every translation unit of the library: the context
+// object behind inf_ctx, error reporting, scratch memory, and TMA descriptor creation.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/inferno_attn.h"
+
+// Bits of the device status word (ctx->status[0]); kernels OR them in and keep going safely.
+#define INF_STATUS_WAIT_TIMEOUT 1  // a bounded mbarrier wait gave up
+#define INF_STATUS_BAD_PAGE 2      // a page id outside the pool was refused
+#define INF_STATUS_BAD_LEN 4       // a length that does not fit the page table
+
+typedef CUresult (*inf_tmap_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct inf_tmap_key {
+    const void* base;
+    uint64_t dims[3];
+    uint64_t strides[2];
+    uint32_t box[3];
+    uint32_t rank;
+    bool operator==(const inf_tmap_key& o) const {
+        if (base != o.base || rank != o.rank) return false;
+        for (int i = 0; i < 3; ++i)
+            if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+        return strides[0] == o.strides[0] && strides[1] == o.strides[1];
+    }
+};
+
+struct inf_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    int sm_count = 0;
+    std::string err;
+    void* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int* status = nullptr;       // device int32[4]
+    int* host_status = nullptr;  // pinned int32[4]
+    inf_tmap_encode_fn encode = nullptr;
+    std::vector<std::pair<inf_tmap_key, CUtensorMap>> tmaps;
+    uint32_t func_attr_done = 0;  // one bit per kernel whose dynamic shared-memory limit has been raised
+};
+
+int inf_fail(inf_ctx* ctx, int code, const char* fmt, ...);
+// Grows (never shrinks) the context's scratch buffer.  Allocation is synchronous with respect to
+// the stream: the old buffer is released only after the stream has drained.
+int inf_ensure_workspace(inf_ctx* ctx, size_t bytes);
+// fp16 tiled tensor map with the 128-byte swizzle, rank 2 or 3.  dims/strides innermost first;
+// strides in bytes for dims 1..rank-1.
+int inf_make_tmap(inf_ctx* ctx, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                  const uint32_t* box, CUtensorMap* out);
+
+#define INF_CHECK_CTX(ctx) \
+    do {                   \
+        if (!(ctx)) return INF_E_ARG; \
+    } while (0)
+
+#define INF_CUDA(ctx, call)                                                                              \
+    do {                                                                                                 \
+        cudaError_t e__ = (call);                                                                        \
+        if (e__ != cudaSuccess)                                                                          \
+            return inf_fail(ctx, INF_E_BACKEND, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), \
+                            __FILE__, __LINE__);                                                         \
+    } while (0)
+
+#define INF_LAUNCH_CHECK(ctx, name)                                                                  \
+    do {                                                                                             \
+        cudaError_t e__ = cudaGetLastError();                                                        \
+        if (e__ != cudaSuccess)                                                                      \
+            return inf_fail(ctx, INF_E_BACKEND, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+// Host-side range check of the page-table entries a launch may touch (needs the host mirrors).
+int inf_validate_table(inf_ctx* ctx, const inf_page_table* t, int num_pages, int page_size, int extra_tokens,
+                       const char* what);

@@ -1,0 +1,464 @@
+// Paged GQA decode: split-KV partial kernel + combine kernel.
+//
+// HBM-bound (6 flop per KV byte at 6 query heads per KV head), so the design is about
+// bytes in flight: one CTA per (sequence, KV head, chunk of keys); a producer warp streams
+// 16-token page tiles with TMA (one tensor map over the whole pool, the page id becomes a
+// row coordinate, 128-byte swizzle) through a 3-stage mbarrier ring; four consumer warps each
+// take one 16-key page tile of a stage, run QK^T and PV on mma.sync with all the query heads
+// of the group stacked into the 16 rows of the M dimension (K/V are read once per KV head,
+// not once per query head), and keep an online softmax in registers with quad shuffles.
+// The per-chunk (max, sum, acc) triples go to scratch; the combine kernel merges them,
+// applies softplus(gate)/sum and writes the output.
+//
+// CUDA cores alone cannot keep up with HBM here: 6.5 TB/s x 6 flop/B = 39 TFLOP/s of fp32
+// FMA plus as many fp16->fp32 conversions, against ~70 TFLOP/s peak; hence mma.sync.
+// Reference kernels: f16_attention_kernels.metal:325-510 (segmented partial + merge).
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+using namespace inf;
+
+namespace {
+
+constexpr int D = 128;
+constexpr int TILE_KEYS = 64;
+constexpr int STAGES = 3;
+constexpr int HALF_BYTES = TILE_KEYS * 128;       // one [64 keys][64 dims] swizzled block
+constexpr int STAGE_BYTES = 4 * HALF_BYTES;       // K lo, K hi, V lo, V hi
+constexpr int CONSUMER_WARPS = 4;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int MAX_CHUNK = 2048;
+constexpr float M_INIT = -1.0e30f;
+
+struct DecodeParams {
+    const __half* q;
+    const int* pages;
+    const int* lens;
+    int max_pages, q_heads, kv_heads, group, page_size, num_pages;
+    int chunk, window;
+    float scale_log2;
+    float* part_acc;
+    float* part_ml;
+    int max_chunks;
+    int* status;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                          DecodeParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES];
+    __shared__ int row_y[MAX_CHUNK / 16];
+    __shared__ float warp_m[CONSUMER_WARPS][16], warp_l[CONSUMER_WARPS][16];
+
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kv_len = p.lens[b];
+    if (kv_len <= 0) return;
+    const int win_start = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
+    const int first_chunk = win_start / p.chunk;
+    const int key_begin = (first_chunk + (int)blockIdx.x) * p.chunk;
+    if (key_begin >= kv_len) return;
+    const int key_end = min(kv_len, key_begin + p.chunk);
+    const int lo = max(key_begin, win_start);
+    const int tile0 = (lo - key_begin) / TILE_KEYS;
+    const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], CONSUMER_WARPS);
+        }
+        mbar_fence_init();
+    }
+    {
+        const int n_sub = (key_end - key_begin + 15) / 16;
+        const int oob_row = p.num_pages * p.kv_heads * p.page_size;  // outside the tensor: TMA fills zeros
+        for (int i = tid; i < n_sub; i += THREADS) {
+            int token = key_begin + i * 16;
+            int slot = token / p.page_size;
+            int y = oob_row;
+            if (slot < p.max_pages) {
+                int page = p.pages[(long long)b * p.max_pages + slot];
+                if (page >= 0 && page < p.num_pages)
+                    y = (page * p.kv_heads + kvh) * p.page_size + token % p.page_size;
+                else
+                    atomicOr(p.status, INF_STATUS_BAD_PAGE);
+            } else {
+                atomicOr(p.status, INF_STATUS_BAD_LEN);
+            }
+            row_y[i] = y;
+        }
+    }
+    __syncthreads();
+
+    float o[16][4];
+    float m_run[2] = {M_INIT, M_INIT}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+    if (warp == CONSUMER_WARPS) {
+        // ---------------- producer: one lane issues the TMA loads ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            for (int t = tile0; t < n_tiles; ++t) {
+                const int it = t - tile0, s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u)) {
+                    atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                    break;
+                }
+                const int remaining = key_end - (key_begin + t * TILE_KEYS);
+                const int nsub = min(4, (remaining + 15) / 16);
+                uint8_t* base = smem + s * STAGE_BYTES;
+                mbar_arrive_expect_tx(&full_bar[s], (uint32_t)nsub * 4u * 2048u);
+                for (int sub = 0; sub < nsub; ++sub) {
+                    const int y = row_y[t * 4 + sub];
+                    tma_load_2d(base + 0 * HALF_BYTES + sub * 2048, &tm_k, 0, y, &full_bar[s]);
+                    tma_load_2d(base + 1 * HALF_BYTES + sub * 2048, &tm_k, 64, y, &full_bar[s]);
+                    tma_load_2d(base + 2 * HALF_BYTES + sub * 2048, &tm_v, 0, y, &full_bar[s]);
+                    tma_load_2d(base + 3 * HALF_BYTES + sub * 2048, &tm_v, 64, y, &full_bar[s]);
+                }
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const int g = lane >> 2, qd = lane & 3;
+        // Q fragments: rows = query heads of this KV group (zero beyond the group)
+        uint32_t qa[8][4];
+        {
+            const __half* qb = p.q + ((long long)b * p.q_heads + (long long)kvh * p.group) * D;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                const int c0 = kk * 16 + qd * 2;
+                qa[kk][0] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0) : 0u;
+                qa[kk][1] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0) : 0u;
+                qa[kk][2] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0 + 8) : 0u;
+                qa[kk][3] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0 + 8) : 0u;
+            }
+        }
+        const uint32_t smem_base = smem_u32(smem);
+        for (int t = tile0; t < n_tiles; ++t) {
+            const int it = t - tile0, s = it % STAGES;
+            const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+            if (!mbar_wait(&full_bar[s], ph)) {
+                if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+            const int k0 = key_begin + t * TILE_KEYS + warp * 16;  // first key of this warp's page tile
+            bool wrote_smem = false;
+            if (k0 < key_end && k0 + 16 > lo) {
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
+                const bool edge = (k0 < lo) || (k0 + 16 > key_end);
+                if (edge) {
+                    // slots of a page past the sequence end may hold anything: zero those V rows so that
+                    // 0 * garbage cannot poison the accumulators
+                    for (int i = lane; i < 16 * 16; i += 32) {
+                        int r = i >> 4, ch = i & 15;
+                        int key = k0 + r;
+                        if (key < lo || key >= key_end) {
+                            uint8_t* dst = smem + s * STAGE_BYTES + (2 + (ch >> 3)) * HALF_BYTES +
+                                           (warp * 16 + r) * 128 + (ch & 7) * 16;
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                    wrote_smem = true;
+                    __syncwarp();
+                }
+                // ---- S = Q K^T for 16 keys
+                float sc[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+                {
+                    const int mat = lane >> 3, rin = lane & 7;
+                    const int krow = warp * 16 + (mat >> 1) * 8 + rin;
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const int dchunk = kk * 2 + (mat & 1);
+                        uint32_t r[4];
+                        ldsm_x4(stage + (dchunk >> 3) * HALF_BYTES + sw128_offset(krow, (dchunk & 7) * 8), r);
+                        mma_16816(sc[0], qa[kk], r[0], r[1]);
+                        mma_16816(sc[1], qa[kk], r[2], r[3]);
+                    }
+                }
+                // ---- online softmax (log2 domain); rows g and g+8
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sc[nt][e] *= p.scale_log2;
+                if (edge) {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            int key = k0 + nt * 8 + qd * 2 + (e & 1);
+                            if (key < lo || key >= key_end) sc[nt][e] = -INFINITY;
+                        }
+                }
+                float alpha[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float mx = fmaxf(fmaxf(sc[0][2 * h], sc[0][2 * h + 1]), fmaxf(sc[1][2 * h], sc[1][2 * h + 1]));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    float m_new = fmaxf(m_run[h], mx);
+                    alpha[h] = ex2_approx(m_run[h] - m_new);
+                    m_run[h] = m_new;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            float pv = ex2_approx(sc[nt][2 * h + e] - m_new);
+                            sc[nt][2 * h + e] = pv;
+                            sum += pv;
+                        }
+                    l_run[h] = l_run[h] * alpha[h] + sum;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    o[j][0] *= alpha[0];
+                    o[j][1] *= alpha[0];
+                    o[j][2] *= alpha[1];
+                    o[j][3] *= alpha[1];
+                }
+                // ---- O += P V
+                uint32_t pa[4];
+                pa[0] = pack_half2(sc[0][0], sc[0][1]);
+                pa[1] = pack_half2(sc[0][2], sc[0][3]);
+                pa[2] = pack_half2(sc[1][0], sc[1][1]);
+                pa[3] = pack_half2(sc[1][2], sc[1][3]);
+                {
+                    const int mat = lane >> 3, rin = lane & 7;
+                    const int vrow = warp * 16 + (mat & 1) * 8 + rin;
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) {
+                        const int dchunk = jj * 2 + (mat >> 1);
+                        uint32_t r[4];
+                        ldsm_x4_trans(stage + (2 + (dchunk >> 3)) * HALF_BYTES + sw128_offset(vrow, (dchunk & 7) * 8),
+                                      r);
+                        mma_16816(o[2 * jj], pa, r[0], r[1]);
+                        mma_16816(o[2 * jj + 1], pa, r[2], r[3]);
+                    }
+                }
+            }
+            if (wrote_smem) fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);
+        }
+        // row sums live spread over the quad
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+        }
+    }
+
+    // ---------------- merge the four warps through shared memory ----------------
+    __syncthreads();  // every load has landed and every ldmatrix has been issued: the ring is free
+    float* merge = reinterpret_cast<float*>(smem);  // [warp][16 rows][128]
+    if (warp < CONSUMER_WARPS) {
+        const int g = lane >> 2, qd = lane & 3;
+        float* mw = merge + warp * 16 * D;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            *reinterpret_cast<float2*>(mw + g * D + j * 8 + qd * 2) = make_float2(o[j][0], o[j][1]);
+            *reinterpret_cast<float2*>(mw + (g + 8) * D + j * 8 + qd * 2) = make_float2(o[j][2], o[j][3]);
+        }
+        if (qd == 0) {
+            warp_m[warp][g] = m_run[0];
+            warp_m[warp][g + 8] = m_run[1];
+            warp_l[warp][g] = l_run[0];
+            warp_l[warp][g + 8] = l_run[1];
+        }
+    }
+    __syncthreads();
+    if (tid < D) {
+        const long long prow0 = ((long long)b * p.max_chunks + blockIdx.x) * p.q_heads + (long long)kvh * p.group;
+        for (int r = 0; r < p.group; ++r) {
+            float M = fmaxf(fmaxf(warp_m[0][r], warp_m[1][r]), fmaxf(warp_m[2][r], warp_m[3][r]));
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; ++w) {
+                float sc = ex2_approx(warp_m[w][r] - M);
+                acc += sc * merge[(w * 16 + r) * D + tid];
+                L += sc * warp_l[w][r];
+            }
+            p.part_acc[(prow0 + r) * D + tid] = acc;
+            if (tid == 0) {
+                p.part_ml[(prow0 + r) * 2 + 0] = M;
+                p.part_ml[(prow0 + r) * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// kernels/fp8_attention_kernels.metal:56-64
+__device__ __forceinline__ float softplus_ref(float v) {
+    if (v > 20.0f) return v;
+    if (v < -20.0f) return expf(v);
+    return logf(1.0f + expf(v));
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(D)
+gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                          const int* __restrict__ lens, const float* __restrict__ gate, OutT* __restrict__ out,
+                          int q_heads, int max_chunks, int chunk, int window) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int kv_len = lens[b];
+    const long long orow = ((long long)b * q_heads + h) * D + d;
+    if (kv_len <= 0) {
+        out[orow] = OutT(0.f);
+        return;
+    }
+    const int win_start = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int first_chunk = win_start / chunk;
+    const int n = (kv_len + chunk - 1) / chunk - first_chunk;
+    float M = M_INIT, L = 0.f, acc = 0.f;
+    for (int c = 0; c < n; ++c) {
+        const long long prow = ((long long)b * max_chunks + c) * q_heads + h;
+        float m = part_ml[prow * 2], l = part_ml[prow * 2 + 1];
+        float a = part_acc[prow * D + d];
+        float Mn = fmaxf(M, m);
+        float s0 = ex2_approx(M - Mn), s1 = ex2_approx(m - Mn);
+        acc = acc * s0 + a * s1;
+        L = L * s0 + l * s1;
+        M = Mn;
+    }
+    float gain = (gate ? softplus_ref(gate[(long long)b * q_heads + h]) : 1.0f) / L;
+    out[orow] = OutT(acc * gain);
+}
+
+}  // namespace
+
+int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
+                          int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
+                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes);
+
+extern "C" size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t max_len,
+                                                 int32_t split_chunk) {
+    if (batch <= 0 || q_heads <= 0 || head_dim <= 0 || max_len <= 0 || split_chunk <= 0) return 0;
+    size_t max_chunks = (size_t)(max_len + split_chunk - 1) / split_chunk;
+    return (size_t)batch * max_chunks * q_heads * (head_dim + 2) * sizeof(float);
+}
+
+// Shared by the allocating entry point below and by callers that bring their own scratch.
+int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
+                          int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
+                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes) {
+    if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "gqa_decode: null pointer");
+    if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "gqa_decode: pool has no storage");
+    if (pool->head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: head_dim must be 128, got %d", pool->head_dim);
+    if (pool->page_size % 16 != 0) return inf_fail(ctx, INF_E_CACHE, "gqa_decode: page_size must be a multiple of 16");
+    if (q_heads <= 0 || q_heads % pool->kv_heads != 0)
+        return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: q_heads %d must be a positive multiple of kv_heads %d", q_heads,
+                        pool->kv_heads);
+    const int group = q_heads / pool->kv_heads;
+    if (group > 16) return INF_UNSUPPORTED;
+    if (split_chunk <= 0 || split_chunk % TILE_KEYS != 0 || split_chunk > MAX_CHUNK)
+        return inf_fail(ctx, INF_E_CONFIG, "gqa_decode: split_chunk must be a multiple of 64 in [64, 2048], got %d",
+                        split_chunk);
+    if (max_len <= 0) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: max_len must be positive");
+    if (sliding_window < 0) return inf_fail(ctx, INF_E_CONFIG, "gqa_decode: sliding_window must be >= 0");
+    if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
+        return inf_fail(ctx, INF_E_DTYPE, "gqa_decode: output dtype must be f32 or f16");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, 0, "gqa_decode");
+    if (rc != INF_OK) return rc;
+    if (table->host_lens)
+        for (int b = 0; b < table->batch; ++b)
+            if (table->host_lens[b] > max_len)
+                return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: sequence %d length %d exceeds max_len %d", b,
+                                table->host_lens[b], max_len);
+    // with a window only ceil(window/chunk)+1 chunks can be visible
+    int max_chunks = (max_len + split_chunk - 1) / split_chunk;
+    size_t need = inf_gqa_decode_workspace_bytes(table->batch, q_heads, D, max_len, split_chunk);
+    if (scratch_bytes < need)
+        return inf_fail(ctx, INF_E_ARG, "gqa_decode: scratch of %zu bytes is smaller than the %zu needed", scratch_bytes,
+                        need);
+
+    const uint64_t rows_total = (uint64_t)pool->num_pages * pool->kv_heads * pool->page_size;
+    uint64_t dims[2] = {(uint64_t)D, rows_total};
+    uint64_t strides[1] = {(uint64_t)D * 2};
+    uint32_t box[2] = {64, 16};
+    CUtensorMap tm_k, tm_v;
+    rc = inf_make_tmap(ctx, pool->k, 2, dims, strides, box, &tm_k);
+    if (rc != INF_OK) return rc;
+    rc = inf_make_tmap(ctx, pool->v, 2, dims, strides, box, &tm_v);
+    if (rc != INF_OK) return rc;
+
+    DecodeParams p;
+    p.q = (const __half*)q_f16;
+    p.pages = table->pages;
+    p.lens = table->lens;
+    p.max_pages = table->max_pages;
+    p.q_heads = q_heads;
+    p.kv_heads = pool->kv_heads;
+    p.group = group;
+    p.page_size = pool->page_size;
+    p.num_pages = pool->num_pages;
+    p.chunk = split_chunk;
+    p.window = sliding_window;
+    p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf((float)D)) * 1.4426950408889634f;
+    p.part_acc = (float*)scratch;
+    p.part_ml = p.part_acc + (size_t)table->batch * max_chunks * q_heads * D;
+    p.max_chunks = max_chunks;
+    p.status = ctx->status;
+
+    const size_t smem = STAGES * STAGE_BYTES + 1024;
+    if (!(ctx->func_attr_done & 1u)) {
+        INF_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem));
+        ctx->func_attr_done |= 1u;
+    }
+    dim3 grid(max_chunks, pool->kv_heads, table->batch);
+    gqa_decode_partial_kernel<<<grid, THREADS, smem, ctx->stream>>>(tm_k, tm_v, p);
+    INF_LAUNCH_CHECK(ctx, "gqa_decode_partial_kernel");
+    dim3 cgrid(q_heads, table->batch);
+    if (out_dtype == INF_DTYPE_F32)
+        gqa_decode_combine_kernel<float><<<cgrid, D, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens, gate,
+                                                                        (float*)out, q_heads, max_chunks, split_chunk,
+                                                                        sliding_window);
+    else
+        gqa_decode_combine_kernel<__half><<<cgrid, D, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens, gate,
+                                                                         (__half*)out, q_heads, max_chunks,
+                                                                         split_chunk, sliding_window);
+    INF_LAUNCH_CHECK(ctx, "gqa_decode_combine_kernel");
+    return INF_OK;
+}
+
+extern "C" int32_t inf_gqa_decode_paged(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                        const inf_page_table* table, int32_t q_heads, int32_t max_len,
+                                        int32_t split_chunk, int32_t sliding_window, const float* gate, float scale,
+                                        void* out, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    if (!table) return inf_fail(ctx, INF_E_ARG, "gqa_decode: null page table");
+    size_t need = inf_gqa_decode_workspace_bytes(table->batch, q_heads, D, max_len, split_chunk);
+    if (need == 0) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: sizes must be positive");
+    int rc = inf_ensure_workspace(ctx, need);
+    if (rc != INF_OK) return rc;
+    return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
+                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes);
+}

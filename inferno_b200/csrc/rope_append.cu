@@ -1,0 +1,350 @@
+// RoPE, per-head RMSNorm and KV-append kernels.
+//
+// Elementwise, HBM-bound work: one warp per head row, lanes stride the row so every
+// load and store of a warp is one contiguous segment, and the half-split rotation
+// partner (d +- rotary/2) always lives in the same lane.  Frequencies arrive as tables
+// computed on the host, so device powf never enters the angle.
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int D = 128;  // head_dim of the GQA path
+
+template <typename T>
+__device__ __forceinline__ float ld_as_f32(const T* p);
+template <>
+__device__ __forceinline__ float ld_as_f32<float>(const float* p) {
+    return *p;
+}
+template <>
+__device__ __forceinline__ float ld_as_f32<__half>(const __half* p) {
+    return __half2float(*p);
+}
+
+// rope_kernels.metal:167-229 for one row held as x[j] = row[lane + 32 j].
+__device__ __forceinline__ void norm_rope_row(float (&x)[4], int lane, const float* __restrict__ w,
+                                              const float* __restrict__ inv_freq, int rotary_dim, float position,
+                                              float eps, float factor) {
+    if (w) {
+        float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        float inv_rms = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = x[j] * w[lane + 32 * j] * inv_rms;
+    }
+    // rotary 64: pairs (lane, lane+32); rotary 128: pairs (lane, lane+64) and (lane+32, lane+96)
+    if (rotary_dim == 64) {
+        float angle = position * inv_freq[lane];
+        float c = cosf(angle) * factor, s = sinf(angle) * factor;
+        float a = x[0], b = x[1];
+        x[0] = a * c + (-b) * s;
+        x[1] = b * c + a * s;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float angle = position * inv_freq[lane + 32 * j];
+            float c = cosf(angle) * factor, s = sinf(angle) * factor;
+            float a = x[j], b = x[j + 2];
+            x[j] = a * c + (-b) * s;
+            x[j + 2] = b * c + a * s;
+        }
+    }
+}
+
+// laguna_qk_rms_norm_rope_pair_device: f32 in, f32 out, Q rows then K rows in one grid.
+__global__ void qk_norm_rope_pair_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                         const float* __restrict__ qw, const float* __restrict__ kw,
+                                         const float* __restrict__ inv_freq, float* __restrict__ q_out,
+                                         float* __restrict__ k_out, long long q_rows, long long k_rows, int tokens,
+                                         int q_heads, int kv_heads, int rotary_dim, int position_offset, float eps,
+                                         float factor) {
+    long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    if (row >= q_rows + k_rows) return;
+    bool is_q = row < q_rows;
+    long long r = is_q ? row : row - q_rows;
+    int heads = is_q ? q_heads : kv_heads;
+    const float* in = (is_q ? q : k) + r * D;
+    float* out = (is_q ? q_out : k_out) + r * D;
+    int token = (int)((r / heads) % tokens);
+    float x[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = in[lane + 32 * j];
+    norm_rope_row(x, lane, is_q ? qw : kw, inv_freq, rotary_dim, (float)(position_offset + token), eps, factor);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) out[lane + 32 * j] = x[j];
+}
+
+// Fused RoPE + append.  Row space: [Q rows | K rows | V rows].
+template <typename T>
+__global__ void rope_append_gqa_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                                       const float* __restrict__ qw, const float* __restrict__ kw,
+                                       const float* __restrict__ inv_freq, int rotary_dim, float factor, float eps,
+                                       __half* __restrict__ k_pool, __half* __restrict__ v_pool, int num_pages,
+                                       int page_size, const int* __restrict__ pages, const int* __restrict__ lens,
+                                       int max_pages, int tokens, int q_heads, int kv_heads,
+                                       __half* __restrict__ q_out, float* __restrict__ k_f32_out, long long q_rows,
+                                       long long kv_rows, int* __restrict__ status) {
+    long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    if (row >= q_rows + 2 * kv_rows) return;
+    int kind = row < q_rows ? 0 : (row < q_rows + kv_rows ? 1 : 2);
+    long long r = kind == 0 ? row : (kind == 1 ? row - q_rows : row - q_rows - kv_rows);
+    int heads = kind == 0 ? q_heads : kv_heads;
+    int head = (int)(r % heads);
+    int token = (int)((r / heads) % tokens);
+    int b = (int)(r / ((long long)heads * tokens));
+    int position = lens[b] + token;
+    const T* in = (kind == 0 ? q : (kind == 1 ? k : v)) + r * D;
+    float x[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = ld_as_f32<T>(in + lane + 32 * j);
+    if (kind != 2 && inv_freq)
+        norm_rope_row(x, lane, kind == 0 ? qw : kw, inv_freq, rotary_dim, (float)position, eps, factor);
+    if (kind == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q_out[r * D + lane + 32 * j] = __float2half_rn(x[j]);
+        return;
+    }
+    if (kind == 1 && k_f32_out) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) k_f32_out[r * D + lane + 32 * j] = x[j];
+    }
+    int slot = position / page_size;
+    if (position < 0 || slot >= max_pages) {
+        if (lane == 0) atomicOr(status, INF_STATUS_BAD_LEN);
+        return;
+    }
+    int page = pages[(long long)b * max_pages + slot];
+    if (page < 0 || page >= num_pages) {
+        if (lane == 0) atomicOr(status, INF_STATUS_BAD_PAGE);
+        return;
+    }
+    __half* dst = (kind == 1 ? k_pool : v_pool) +
+                  ((((long long)page * kv_heads + head) * page_size) + position % page_size) * D;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2half_rn(x[j]);
+}
+
+struct InvFreq64 {
+    float v[64];
+};
+
+// rope_kernels.metal:5-40: one thread per (even, odd) pair.
+__global__ void rope_slice_kernel(const float* __restrict__ in, float* __restrict__ out, long long pair_total,
+                                  int tokens, int heads, int rope_dim, int position_offset, InvFreq64 f) {
+    long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= pair_total) return;
+    int pair_count = rope_dim / 2;
+    int pair = (int)(gid % pair_count);
+    int token = (int)((gid / ((long long)pair_count * heads)) % tokens);
+    float angle = (float)(position_offset + token) * f.v[pair];
+    float c = cosf(angle), s = sinf(angle);
+    float2 eo = reinterpret_cast<const float2*>(in)[gid];
+    reinterpret_cast<float2*>(out)[gid] = make_float2(eo.x * c - eo.y * s, eo.x * s + eo.y * c);
+}
+
+// norm_kernels.metal:52-115 fused with the paged append.  One 128-thread block per token row.
+__global__ void __launch_bounds__(128)
+mla_postprocess_append_kernel(const float* __restrict__ in, const float* __restrict__ w, float eps, InvFreq64 f,
+                              __half* __restrict__ pool, int num_pages, int page_size, const int* __restrict__ pages,
+                              const int* __restrict__ lens, int max_pages, int tokens, int L, int R,
+                              float* __restrict__ latent_out, float* __restrict__ rope_out, int* __restrict__ status) {
+    long long row = blockIdx.x;
+    int tid = threadIdx.x;
+    int b = (int)(row / tokens), token = (int)(row % tokens);
+    const float* x = in + row * (L + R);
+    __shared__ float warp_sums[4];
+    float ss = 0.0f;
+    for (int d = tid; d < L; d += 128) ss += x[d] * x[d];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) warp_sums[tid >> 5] = ss;
+    __syncthreads();
+    float total = warp_sums[0] + warp_sums[1] + warp_sums[2] + warp_sums[3];
+    float norm_scale = rsqrtf(total / (float)L + eps);
+    int position = lens[b] + token;
+    int slot = position / page_size;
+    __half* dst = nullptr;
+    if (position < 0 || slot >= max_pages) {
+        if (tid == 0) atomicOr(status, INF_STATUS_BAD_LEN);
+    } else {
+        int page = pages[(long long)b * max_pages + slot];
+        if (page < 0 || page >= num_pages) {
+            if (tid == 0) atomicOr(status, INF_STATUS_BAD_PAGE);
+        } else {
+            dst = pool + ((long long)page * page_size + position % page_size) * (L + R);
+        }
+    }
+    for (int d = tid; d < L; d += 128) {
+        float y = x[d] * norm_scale * w[d];
+        if (latent_out) latent_out[row * L + d] = y;
+        if (dst) dst[d] = __float2half_rn(y);
+    }
+    for (int d = tid; d < R; d += 128) {
+        bool even = (d & 1) == 0;
+        float angle = (float)position * f.v[d >> 1];
+        float value = x[L + d], partner = x[L + (even ? d + 1 : d - 1)];
+        float rotated = even ? -partner : partner;
+        float y = value * cosf(angle) + rotated * sinf(angle);
+        if (rope_out) rope_out[row * R + d] = y;
+        if (dst) dst[L + d] = __float2half_rn(y);
+    }
+}
+
+// layout_kernels.metal:205-232 under a page table: one warp per (b, head, token) row of 128 halves.
+__global__ void linearize_paged_kernel(const __half* __restrict__ pool, const int* __restrict__ pages, int max_pages,
+                                       int num_pages, int kv_heads, int page_size, int tokens, long long rows,
+                                       __half* __restrict__ out, int* __restrict__ status) {
+    long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    int t = (int)(row % tokens);
+    int h = (int)((row / tokens) % kv_heads);
+    int b = (int)(row / ((long long)tokens * kv_heads));
+    int page = pages[(long long)b * max_pages + t / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (lane == 0) atomicOr(status, INF_STATUS_BAD_PAGE);
+        return;
+    }
+    const uint2* src =
+        reinterpret_cast<const uint2*>(pool + ((((long long)page * kv_heads + h) * page_size) + t % page_size) * D);
+    reinterpret_cast<uint2*>(out + row * D)[lane] = src[lane];
+}
+
+void host_inv_freq_glm(float theta, int rope_dim, InvFreq64* f) {
+    int pair_count = rope_dim / 2;
+    for (int p = 0; p < 64; ++p) f->v[p] = p < pair_count ? 1.0f / powf(theta, (float)p / (float)pair_count) : 0.0f;
+}
+
+int check_rope(inf_ctx* ctx, const inf_rope_table* rope) {
+    if (!rope->inv_freq) return inf_fail(ctx, INF_E_ARG, "rope table has no device frequencies");
+    if (rope->rotary_dim != 64 && rope->rotary_dim != 128)
+        return inf_fail(ctx, INF_E_BACKEND, "Laguna rotary dimension must be 64 or 128, got %d", rope->rotary_dim);
+    return INF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t inf_laguna_qk_rms_norm_rope_pair(inf_ctx* ctx, const float* q, const float* k, const float* qw,
+                                         const float* kw, float eps, int32_t position_offset,
+                                         const inf_rope_table* rope, int32_t batch, int32_t tokens, int32_t q_heads,
+                                         int32_t kv_heads, int32_t head_dim, float* q_out, float* k_out) {
+    INF_CHECK_CTX(ctx);
+    if (!q || !k || !rope || !q_out || !k_out) return inf_fail(ctx, INF_E_ARG, "qk_norm_rope_pair: null pointer");
+    if (head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "qk_norm_rope_pair: head_dim must be 128, got %d", head_dim);
+    if (batch <= 0 || tokens <= 0 || q_heads <= 0 || kv_heads <= 0)
+        return inf_fail(ctx, INF_E_SHAPE, "qk_norm_rope_pair: sizes must be positive");
+    int rc = check_rope(ctx, rope);
+    if (rc != INF_OK) return rc;
+    long long q_rows = (long long)batch * tokens * q_heads, k_rows = (long long)batch * tokens * kv_heads;
+    long long rows = q_rows + k_rows;
+    int blocks = (int)((rows + 7) / 8);
+    qk_norm_rope_pair_kernel<<<blocks, 256, 0, ctx->stream>>>(q, k, qw, kw, rope->inv_freq, q_out, k_out, q_rows,
+                                                              k_rows, tokens, q_heads, kv_heads, rope->rotary_dim,
+                                                              position_offset, eps, rope->attention_factor);
+    INF_LAUNCH_CHECK(ctx, "qk_norm_rope_pair_kernel");
+    return INF_OK;
+}
+
+int32_t inf_rope_append_gqa(inf_ctx* ctx, const void* q, const void* k, const void* v, int32_t in_dtype,
+                            const float* qw, const float* kw, float eps, const inf_rope_table* rope,
+                            const inf_kv_pool* pool, const inf_page_table* table, int32_t tokens, int32_t q_heads,
+                            void* q_out_f16, float* k_f32_out) {
+    INF_CHECK_CTX(ctx);
+    if (!q || !k || !v || !pool || !table || !q_out_f16) return inf_fail(ctx, INF_E_ARG, "rope_append_gqa: null pointer");
+    if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "rope_append_gqa: pool has no storage");
+    if (pool->head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "rope_append_gqa: head_dim must be 128");
+    if (tokens <= 0 || q_heads <= 0 || q_heads % pool->kv_heads != 0)
+        return inf_fail(ctx, INF_E_SHAPE, "rope_append_gqa: q_heads %d must be a positive multiple of kv_heads %d",
+                        q_heads, pool->kv_heads);
+    if (in_dtype != INF_DTYPE_F32 && in_dtype != INF_DTYPE_F16)
+        return inf_fail(ctx, INF_E_DTYPE, "rope_append_gqa: input dtype must be f32 or f16");
+    if (rope) {
+        int rc = check_rope(ctx, rope);
+        if (rc != INF_OK) return rc;
+    }
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "rope_append_gqa");
+    if (rc != INF_OK) return rc;
+    long long q_rows = (long long)table->batch * tokens * q_heads;
+    long long kv_rows = (long long)table->batch * tokens * pool->kv_heads;
+    long long rows = q_rows + 2 * kv_rows;
+    int blocks = (int)((rows + 7) / 8);
+    const float* inv = rope ? rope->inv_freq : nullptr;
+    int rd = rope ? rope->rotary_dim : 64;
+    float factor = rope ? rope->attention_factor : 1.0f;
+    if (in_dtype == INF_DTYPE_F32)
+        rope_append_gqa_kernel<float><<<blocks, 256, 0, ctx->stream>>>(
+            (const float*)q, (const float*)k, (const float*)v, qw, kw, inv, rd, factor, eps, (__half*)pool->k,
+            (__half*)pool->v, pool->num_pages, pool->page_size, table->pages, table->lens, table->max_pages, tokens,
+            q_heads, pool->kv_heads, (__half*)q_out_f16, k_f32_out, q_rows, kv_rows, ctx->status);
+    else
+        rope_append_gqa_kernel<__half><<<blocks, 256, 0, ctx->stream>>>(
+            (const __half*)q, (const __half*)k, (const __half*)v, qw, kw, inv, rd, factor, eps, (__half*)pool->k,
+            (__half*)pool->v, pool->num_pages, pool->page_size, table->pages, table->lens, table->max_pages, tokens,
+            q_heads, pool->kv_heads, (__half*)q_out_f16, k_f32_out, q_rows, kv_rows, ctx->status);
+    INF_LAUNCH_CHECK(ctx, "rope_append_gqa_kernel");
+    return INF_OK;
+}
+
+int32_t inf_rope_slice(inf_ctx* ctx, const float* input, float* output, int32_t batch, int32_t tokens, int32_t heads,
+                       int32_t rope_dim, int32_t position_offset, float theta) {
+    INF_CHECK_CTX(ctx);
+    if (!input || !output) return inf_fail(ctx, INF_E_ARG, "rope_slice: null pointer");
+    if (rope_dim <= 0 || (rope_dim & 1)) return inf_fail(ctx, INF_E_SHAPE, "rope_dim must be even, got %d", rope_dim);
+    if (rope_dim > 128) return inf_fail(ctx, INF_E_SHAPE, "rope_dim must be at most 128, got %d", rope_dim);
+    if (batch <= 0 || tokens <= 0 || heads <= 0) return inf_fail(ctx, INF_E_SHAPE, "rope_slice: sizes must be positive");
+    if (!(theta > 0.0f) || !isfinite(theta)) return inf_fail(ctx, INF_E_CONFIG, "rope theta must be positive");
+    InvFreq64 f;
+    host_inv_freq_glm(theta, rope_dim, &f);
+    long long pairs = (long long)batch * tokens * heads * (rope_dim / 2);
+    int blocks = (int)((pairs + 255) / 256);
+    rope_slice_kernel<<<blocks, 256, 0, ctx->stream>>>(input, output, pairs, tokens, heads, rope_dim, position_offset, f);
+    INF_LAUNCH_CHECK(ctx, "rope_slice_kernel");
+    return INF_OK;
+}
+
+int32_t inf_mla_kv_postprocess_append(inf_ctx* ctx, const float* input, const float* norm_weight, float eps,
+                                      float theta, const inf_mla_pool* pool, const inf_page_table* table,
+                                      int32_t tokens, float* latent_out, float* rope_out) {
+    INF_CHECK_CTX(ctx);
+    if (!input || !norm_weight || !pool || !table) return inf_fail(ctx, INF_E_ARG, "mla_kv_postprocess: null pointer");
+    if (!pool->rows) return inf_fail(ctx, INF_E_ARG, "mla_kv_postprocess: pool has no storage");
+    if (tokens <= 0) return inf_fail(ctx, INF_E_SHAPE, "mla_kv_postprocess: tokens must be positive");
+    if (pool->rope_dim > 128 || (pool->rope_dim & 1)) return inf_fail(ctx, INF_E_SHAPE, "rope_dim must be even and <= 128");
+    if (!(theta > 0.0f) || !isfinite(theta)) return inf_fail(ctx, INF_E_CONFIG, "rope theta must be positive");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "mla_kv_postprocess");
+    if (rc != INF_OK) return rc;
+    InvFreq64 f;
+    host_inv_freq_glm(theta, pool->rope_dim, &f);
+    long long rows = (long long)table->batch * tokens;
+    mla_postprocess_append_kernel<<<(unsigned)rows, 128, 0, ctx->stream>>>(
+        input, norm_weight, eps, f, (__half*)pool->rows, pool->num_pages, pool->page_size, table->pages, table->lens,
+        table->max_pages, tokens, pool->latent_dim, pool->rope_dim, latent_out, rope_out, ctx->status);
+    INF_LAUNCH_CHECK(ctx, "mla_postprocess_append_kernel");
+    return INF_OK;
+}
+
+int32_t inf_linearize_paged(inf_ctx* ctx, const void* pool_f16, const inf_kv_pool* shape, const inf_page_table* table,
+                            int32_t tokens, void* out_f16) {
+    INF_CHECK_CTX(ctx);
+    if (!pool_f16 || !shape || !table || !out_f16) return inf_fail(ctx, INF_E_ARG, "linearize_paged: null pointer");
+    if (shape->head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "linearize_paged: head_dim must be 128");
+    if (tokens <= 0 || tokens > table->max_pages * shape->page_size)
+        return inf_fail(ctx, INF_E_CACHE, "linearize_paged: %d tokens exceed the page table", tokens);
+    long long rows = (long long)table->batch * shape->kv_heads * tokens;
+    int blocks = (int)((rows + 7) / 8);
+    linearize_paged_kernel<<<blocks, 256, 0, ctx->stream>>>((const __half*)pool_f16, table->pages, table->max_pages,
+                                                            shape->num_pages, shape->kv_heads, shape->page_size, tokens,
+                                                            rows, (__half*)out_f16, ctx->status);
+    INF_LAUNCH_CHECK(ctx, "linearize_paged_kernel");
+    return INF_OK;
+}
+
+}  // extern "C"
