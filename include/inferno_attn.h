@@ -52,7 +52,8 @@ typedef struct inf_ctx inf_ctx;
 
 /* ---- context, memory, ordering ------------------------------------------------ */
 /* MetalBackend::new / from_device (backend.rs:2175-2260).  `stream` is a cudaStream_t to
- * enqueue on, or NULL for a stream owned by the context. */
+ * enqueue on, or NULL for a stream owned by the context (pass cudaStreamLegacy, (void*)1, to name
+ * the default stream). */
 int32_t inf_ctx_create(int32_t device_ordinal, void* stream, inf_ctx** out);
 int32_t inf_ctx_destroy(inf_ctx* ctx);
 const char* inf_last_error(inf_ctx* ctx);
@@ -63,6 +64,12 @@ int32_t inf_device_values_supported(inf_ctx* ctx);
 int32_t inf_flush(inf_ctx* ctx);
 /* device_submit (backend.rs:1072): launches are already asynchronous; checks arguments only. */
 int32_t inf_submit(inf_ctx* ctx);
+/* device_profile_boundary (backend.rs:1080; GPU time per command buffer, metal/batch.rs:161-170):
+ * while enabled, every op records a CUDA event pair around its dominant kernel.  inf_profile_read waits
+ * for the stream, returns the summed device time and launch count of the kernel called `kernel_name`
+ * since the last read, and forgets them. */
+int32_t inf_profile_enable(inf_ctx* ctx, int32_t on);
+int32_t inf_profile_read(inf_ctx* ctx, const char* kernel_name, double* total_ms, int32_t* launches);
 /* device_alloc_f32/f16_tensor (backend.rs:1098/1104), device_upload_f32_tensor (:1086),
  * device_upload_f32_tensor_as_f16 (:1092), device_copy_same_dtype (:1110),
  * device_download_f32_tensor (:1136). */

@@ -61,7 +61,9 @@ class CudaBackend:
         torch.cuda.set_device(self.device)
         self.stream = stream if stream is not None else torch.cuda.current_stream(self.device)
         h = C.c_void_p()
-        rc = self._lib.inf_ctx_create(device, C.c_void_p(self.stream.cuda_stream), C.byref(h))
+        # torch's default stream has handle 0, which the C ABI reads as "make your own": name the legacy
+        # default stream explicitly (cudaStreamLegacy == 1) so that torch ops and library ops stay ordered
+        rc = self._lib.inf_ctx_create(device, C.c_void_p(self.stream.cuda_stream or 1), C.byref(h))
         if rc != L.INF_OK:
             raise InfernoError(rc, "inf_ctx_create failed (is this an sm_100 GPU?)")
         self._ctx = h
@@ -94,6 +96,15 @@ class CudaBackend:
 
     def device_submit(self):  # backend.rs:1072
         self._check(self._lib.inf_submit(self._ctx))
+
+    def device_profile_boundary(self, enable: bool):  # backend.rs:1080
+        self._check(self._lib.inf_profile_enable(self._ctx, int(enable)))
+
+    def profile_read(self, kernel_name: str):
+        """(summed device milliseconds, launches) of one kernel since the last read."""
+        ms, n = C.c_double(), C.c_int32()
+        self._check(self._lib.inf_profile_read(self._ctx, kernel_name.encode(), C.byref(ms), C.byref(n)))
+        return ms.value, n.value
 
     def device_upload_f32_tensor(self, host: torch.Tensor) -> torch.Tensor:  # backend.rs:1086
         host = host.contiguous().float()

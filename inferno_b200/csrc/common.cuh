@@ -48,6 +48,30 @@ struct inf_ctx {
     inf_tmap_encode_fn encode = nullptr;
     std::vector<std::pair<inf_tmap_key, CUtensorMap>> tmaps;
     uint32_t func_attr_done = 0;  // one bit per kernel whose dynamic shared-memory limit has been raised
+    // optional per-kernel timing (inf_profile_enable): event pairs around named kernels
+    bool prof_on = false;
+    struct prof_rec {
+        const char* name;
+        cudaEvent_t a, b;
+    };
+    std::vector<prof_rec> prof;
+};
+
+// Records an event pair around one kernel launch when profiling is on; a no-op otherwise.
+struct inf_prof_scope {
+    inf_ctx* ctx;
+    cudaEvent_t a = nullptr, b = nullptr;
+    const char* name;
+    inf_prof_scope(inf_ctx* c, const char* n) : ctx(c), name(n) {
+        if (ctx->prof_on && cudaEventCreate(&a) == cudaSuccess && cudaEventCreate(&b) == cudaSuccess)
+            cudaEventRecord(a, ctx->stream);
+    }
+    ~inf_prof_scope() {
+        if (a && b) {
+            cudaEventRecord(b, ctx->stream);
+            ctx->prof.push_back({name, a, b});
+        }
+    }
 };
 
 int inf_fail(inf_ctx* ctx, int code, const char* fmt, ...);

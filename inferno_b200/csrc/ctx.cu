@@ -139,6 +139,10 @@ int32_t inf_ctx_destroy(inf_ctx* ctx) {
     INF_CHECK_CTX(ctx);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    for (auto& r : ctx->prof) {
+        cudaEventDestroy(r.a);
+        cudaEventDestroy(r.b);
+    }
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
@@ -163,6 +167,37 @@ int32_t inf_flush(inf_ctx* ctx) {
                         (s & INF_STATUS_BAD_PAGE) ? " page id outside the pool;" : "",
                         (s & INF_STATUS_BAD_LEN) ? " length beyond the page table;" : "");
     }
+    return INF_OK;
+}
+
+int32_t inf_profile_enable(inf_ctx* ctx, int32_t on) {
+    INF_CHECK_CTX(ctx);
+    ctx->prof_on = on != 0;
+    return INF_OK;
+}
+
+int32_t inf_profile_read(inf_ctx* ctx, const char* kernel_name, double* total_ms, int32_t* launches) {
+    INF_CHECK_CTX(ctx);
+    if (!kernel_name || !total_ms || !launches) return inf_fail(ctx, INF_E_ARG, "inf_profile_read: null pointer");
+    INF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    double sum = 0.0;
+    int n = 0;
+    for (size_t i = 0; i < ctx->prof.size();) {
+        if (strcmp(ctx->prof[i].name, kernel_name) == 0) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, ctx->prof[i].a, ctx->prof[i].b) == cudaSuccess) {
+                sum += ms;
+                ++n;
+            }
+            cudaEventDestroy(ctx->prof[i].a);
+            cudaEventDestroy(ctx->prof[i].b);
+            ctx->prof.erase(ctx->prof.begin() + i);
+        } else {
+            ++i;
+        }
+    }
+    *total_ms = sum;
+    *launches = n;
     return INF_OK;
 }
 

@@ -434,7 +434,10 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
         ctx->func_attr_done |= 1u;
     }
     dim3 grid(max_chunks, pool->kv_heads, table->batch);
-    gqa_decode_partial_kernel<<<grid, THREADS, smem, ctx->stream>>>(tm_k, tm_v, p);
+    {
+        inf_prof_scope prof(ctx, "gqa_decode_partial_kernel");
+        gqa_decode_partial_kernel<<<grid, THREADS, smem, ctx->stream>>>(tm_k, tm_v, p);
+    }
     INF_LAUNCH_CHECK(ctx, "gqa_decode_partial_kernel");
     dim3 cgrid(q_heads, table->batch);
     if (out_dtype == INF_DTYPE_F32)

@@ -61,6 +61,8 @@ SIGNATURES = {
     "inf_device_values_supported": (_I, [_P]),
     "inf_flush": (_I, [_P]),
     "inf_submit": (_I, [_P]),
+    "inf_profile_enable": (_I, [_P, _I]),
+    "inf_profile_read": (_I, [_P, C.c_char_p, C.POINTER(C.c_double), C.POINTER(_I)]),
     "inf_alloc": (_I, [_P, C.c_size_t, C.POINTER(_P)]),
     "inf_free": (_I, [_P, _P]),
     "inf_upload": (_I, [_P, _P, _P, C.c_size_t]),
