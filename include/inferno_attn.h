@@ -173,6 +173,30 @@ int32_t inf_gqa_decode_paged(inf_ctx* ctx, const void* q_f16, const inf_kv_pool*
 size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t max_len,
                                       int32_t split_chunk);
 
+/* inf_gqa_decode_paged for callers that must not allocate.  (No counterpart in the reference: its
+ * arena hands out a fresh partial buffer per call, crates/backend/src/metal/f16_attention.rs:471-478.)
+ *
+ * inf_gqa_decode_paged keeps the split-KV partials in a workspace that it grows with cudaMalloc when a
+ * call is larger than any before it.  A server that has given all free HBM to its KV pool, a decode
+ * loop that cannot take the device-wide stall inside cudaMalloc/cudaFree, or a host whose device memory
+ * is owned by another allocator can call this variant instead: same arguments, same result, but the
+ * partials live in an array of INF_GQA_DECODE_STATIC_SCRATCH_BYTES that is part of the library image
+ * (every GPU that loads the library holds it until the process exits), and the call performs no
+ * cudaMalloc, cudaFree or other device allocation.
+ *
+ *   - sizes whose partials (inf_gqa_decode_workspace_bytes) exceed the array are refused with
+ *     INF_E_CONFIG and a message naming both numbers; nothing is launched.
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call during set-up, before any stream capture.
+ *   - all calls, on every stream and context of the process, share the one array per GPU and it keeps
+ *     the previous call's contents (nothing in it needs clearing: each call overwrites what it reads).
+ *     Two calls that overlap on the same GPU race on it; keep them on one stream or order them. */
+#define INF_GQA_DECODE_STATIC_SCRATCH_BYTES (32u << 20)
+int32_t inf_gqa_decode_paged_static(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                    const inf_page_table* table, int32_t q_heads, int32_t max_len,
+                                    int32_t split_chunk, int32_t sliding_window, const float* gate, float scale,
+                                    void* out, int32_t out_dtype);
+
 /* Causal GQA prefill over pages (kernel f16_attention_kernels.metal:153-316, generalised):
  * q fp16 [batch, tokens, q_heads, head_dim]; lens[b] = keys cached BEFORE this chunk; the chunk's
  * K/V have already been appended at lens[b]..lens[b]+tokens-1.  Row t sees keys

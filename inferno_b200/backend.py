@@ -215,6 +215,21 @@ class CudaBackend:
                                                         _ptr(out), dt))
         return out if ok else None
 
+    def gqa_decode_paged_static(self, q_f16, pool: KvPool, table: PageTable, max_len: int, split_chunk: int = 512,
+                                sliding_window: int = 0, gate=None, scale: float = 0.0, out=None):
+        """gqa_decode_paged for callers that must not allocate device memory while decoding: the split-KV
+        partials go to the fixed array inside the library instead of a cudaMalloc'ed workspace.  `out` must be
+        supplied by the caller (allocating it here would defeat the purpose); sizes beyond the array raise
+        InfernoError(kind 'Config').  Calls that overlap on one GPU race on the shared array."""
+        B, Hq, D = q_f16.shape
+        if out is None:
+            raise InfernoError(L.INF_E_ARG, "gqa_decode_paged_static writes into a caller-provided `out`")
+        dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
+        ok = self._check(self._lib.inf_gqa_decode_paged_static(self._ctx, _ptr(q_f16), C.byref(pool.desc),
+                                                               C.byref(table.desc), Hq, max_len, split_chunk,
+                                                               sliding_window, _ptr(gate), scale, _ptr(out), dt))
+        return out if ok else None
+
     def gqa_prefill_paged(self, q_f16, pool: KvPool, table: PageTable, sliding_window: int = 0, gate=None,
                           scale: float = 0.0, out_dtype=torch.float16, out=None):
         B, T, Hq, D = q_f16.shape

@@ -465,3 +465,63 @@ extern "C" int32_t inf_gqa_decode_paged(inf_ctx* ctx, const void* q_f16, const i
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
                                  out, out_dtype, ctx->workspace, ctx->workspace_bytes);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode without any allocation.
+//
+// inf_gqa_decode_paged keeps its split-KV partials in the context's workspace, which it grows with
+// cudaMalloc whenever a call needs more than any earlier one did.  Some callers cannot afford that:
+// a serving loop that has already handed every free byte of HBM to its KV pool, so that a late
+// cudaMalloc may simply fail; a latency-bound decode loop, for which the device-wide synchronisation
+// hidden inside cudaMalloc / cudaFree is a stall in the middle of a token; a host whose device memory
+// belongs to another allocator and must not be touched behind its back.  For them the partials live
+// in the fixed array below, which is part of the library image: every GPU that loads the library
+// holds these INF_GQA_DECODE_STATIC_SCRATCH_BYTES until the process exits.
+//
+// In host code the name of a __device__ array is only a host-side stand-in, not a device address, so
+// the address is looked up once per device with cudaGetSymbolAddress (with that device current) and
+// that pointer is what the kernels receive.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[INF_GQA_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+void* g_static_scratch_ptr[MAX_DEVICES] = {};
+bool g_static_scratch_ready[MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" int32_t inf_gqa_decode_paged_static(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                               const inf_page_table* table, int32_t q_heads, int32_t max_len,
+                                               int32_t split_chunk, int32_t sliding_window, const float* gate,
+                                               float scale, void* out, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    if (!table) return inf_fail(ctx, INF_E_ARG, "gqa_decode_static: null page table");
+    const size_t need = inf_gqa_decode_workspace_bytes(table->batch, q_heads, D, max_len, split_chunk);
+    if (need == 0) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode_static: sizes must be positive");
+    if (need > (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES)
+        return inf_fail(ctx, INF_E_CONFIG,
+                        "gqa_decode_static: batch %d x %d chunks x %d heads needs %zu bytes of split-KV scratch, the "
+                        "built-in array holds %zu; use a larger split_chunk, a smaller batch, or inf_gqa_decode_paged",
+                        table->batch, (max_len + split_chunk - 1) / split_chunk, q_heads, need,
+                        (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES);
+    if (ctx->device < 0 || ctx->device >= MAX_DEVICES)
+        return inf_fail(ctx, INF_E_ARG, "gqa_decode_static: device ordinal %d is out of range", ctx->device);
+    if (!g_static_scratch_ready[ctx->device]) {
+        // first call on this device: resolve the array's device address with this device current
+        int current = -1;
+        INF_CUDA(ctx, cudaGetDevice(&current));
+        if (current != ctx->device) INF_CUDA(ctx, cudaSetDevice(ctx->device));
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+        if (current != ctx->device) cudaSetDevice(current);
+        if (e != cudaSuccess || !ptr)
+            return inf_fail(ctx, INF_E_BACKEND, "gqa_decode_static: cudaGetSymbolAddress failed: %s",
+                            cudaGetErrorString(e));
+        g_static_scratch_ptr[ctx->device] = ptr;
+        g_static_scratch_ready[ctx->device] = true;
+    }
+    // Nothing in the array has to start at zero: every partial the combine kernel reads is written
+    // by the partial kernel of the same call first.
+    return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
+                                 out, out_dtype, g_static_scratch_ptr[ctx->device],
+                                 (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES);
+}

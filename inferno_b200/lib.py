@@ -15,6 +15,7 @@ INF_OK = 0
 INF_UNSUPPORTED = 1
 INF_E_BACKEND, INF_E_SHAPE, INF_E_CONFIG, INF_E_CACHE, INF_E_DTYPE, INF_E_ARG = -1, -2, -3, -4, -5, -6
 DTYPE_F32, DTYPE_F16 = 0, 1
+GQA_DECODE_STATIC_SCRATCH_BYTES = 32 << 20
 
 ERROR_NAMES = {INF_E_BACKEND: "Backend", INF_E_SHAPE: "ShapeMismatch", INF_E_CONFIG: "Config", INF_E_CACHE: "Cache",
                INF_E_DTYPE: "DType", INF_E_ARG: "Argument"}
@@ -84,6 +85,8 @@ SIGNATURES = {
     "inf_mla_kv_postprocess_append": (_I, [_P, _P, _P, _F, _F, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _P, _P]),
     "inf_gqa_decode_paged": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _I, _P, _F, _P, _I]),
     "inf_gqa_decode_workspace_bytes": (C.c_size_t, [_I, _I, _I, _I, _I]),
+    "inf_gqa_decode_paged_static": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _I, _P, _F, _P,
+                                         _I]),
     "inf_gqa_prefill_paged": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _P, _F, _P, _I]),
     "inf_laguna_gated_gqa_f16_attention": (_I, [_P, _P, _P, _P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I,
                                                 _I, _I, _P]),
