@@ -1,0 +1,549 @@
+// Causal flash attention for prefill on tcgen05 / TMEM, fed by TMA.
+//
+// One CTA owns 128 query rows of one head.  Seven warps, specialised:
+//   warps 0-3  softmax + epilogue; thread r owns query row r and TMEM lane r
+//   warp 4     TMA producer for Q and the K tiles
+//   warp 5     allocates TMEM and issues every tcgen05.mma
+//   warp 6     TMA producer for the V tiles
+// Per 64-key tile:  S = Q K^T  (SS MMA, M128 N64, both operands K-major, 128-byte swizzle)
+//                   softmax in registers, P written back to TMEM as packed fp16 over its own S buffer
+//                   O += P V   (TS MMA, A = P from TMEM, B = V MN-major straight from its [key][dim] tile)
+// S is double-buffered in TMEM (columns 0-63 / 64-127, O in 128-255), so QK^T of tile j+1 is already
+// queued behind the tensor pipe while tile j is in softmax; O is rescaled lazily (only when a row
+// maximum grew by more than 2^8), so the accumulator stays in TMEM for the whole row of tiles.
+// 256 TMEM columns and <= 113 KB of shared memory per CTA: two CTAs share an SM and fill each other's
+// softmax bubbles.
+//
+// Two instantiations: paged GQA prefill (head_dim 128; K/V tiles are four 16-token page boxes
+// addressed through the page table; reference kernel f16_attention_kernels.metal:153-316) and dense
+// MLA prefill over expanded heads (qk 128+64 with the rope tail shared by all heads, v 128;
+// reference kernel attention_kernels.metal:723-968 with no past, K laid out as in
+// layout_kernels.metal:148-183).
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+using namespace inf;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 64;
+constexpr int NUM_THREADS = 224;
+constexpr float M_INIT = -1.0e30f;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t COL_S0 = 0, COL_S1 = 64, COL_O = 128;
+
+struct FlashParams {
+    int tokens, q_heads, kv_heads, group, batch;
+    const int* pages;
+    const int* lens;
+    int max_pages, page_size, num_pages;
+    int window;
+    float scale_log2;
+    const float* gate;  // [batch][tokens][q_heads] or null
+    void* out;
+    int out_f16;
+    long long o_ts, o_hs, o_bs;  // element strides of the output: token, head, batch
+    int* status;
+};
+
+// kernels/fp8_attention_kernels.metal:56-64
+__device__ __forceinline__ float softplus_ref(float v) {
+    if (v > 20.0f) return v;
+    if (v < -20.0f) return expf(v);
+    return logf(1.0f + expf(v));
+}
+
+template <int DQK, int DV, int KS, int VS>
+struct SmemLayout {
+    static constexpr int Q_BYTES = BM * DQK * 2;
+    static constexpr int K_BYTES = BN * DQK * 2;
+    static constexpr int V_BYTES = BN * DV * 2;
+    static constexpr int OFF_K = Q_BYTES;
+    static constexpr int OFF_V = OFF_K + KS * K_BYTES;
+    static constexpr int OFF_BAR = OFF_V + VS * V_BYTES;
+    static constexpr int TOTAL = OFF_BAR + 256;
+};
+
+template <int DQK, int DV, int KS, int VS, bool PAGED>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_k2, const __grid_constant__ CUtensorMap tm_v,
+                     FlashParams p) {
+    using L = SmemLayout<DQK, DV, KS, VS>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;
+    uint8_t* sK = smem + L::OFF_K;
+    uint8_t* sV = smem + L::OFF_V;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = k_full + KS;
+    uint64_t* v_full = k_empty + KS;
+    uint64_t* v_empty = v_full + VS;
+    uint64_t* s_full = v_empty + VS;  // [2]
+    uint64_t* p_full = s_full + 2;    // [2]
+    uint64_t* o_ready = p_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.x;
+    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;  // heaviest (latest) query tiles first
+    const int b = blockIdx.z;
+    const int q0 = qt * BM;
+    const int past = PAGED ? p.lens[b] : 0;
+    const int kv_total = past + p.tokens;
+    const int q_last = min(q0 + BM, p.tokens) - 1;
+    const int kt_end = (past + q_last + 1 + BN - 1) / BN;
+    const int lo_key = p.window > 0 ? max(0, past + q0 + 1 - p.window) : 0;
+    const int kt_begin = lo_key / BN;
+    const int n = kt_end - kt_begin;
+
+    if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
+        if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        return;
+    }
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < KS; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+        }
+        for (int i = 0; i < VS; ++i) {
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+        }
+        mbar_init(o_ready, 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = *tmem_slot;
+
+    if (warp == 4) {
+        // ------------------------------------------------ Q + K producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            mbar_arrive_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+            for (int blk = 0; blk < DQK / 64; ++blk)
+                tma_load_3d(sQ + blk * BM * 128, &tm_q, blk * 64, head, b * p.tokens + q0, q_full);
+        }
+        const int kvh = PAGED ? head / p.group : head;
+        const int oob_row = p.num_pages * p.kv_heads * p.page_size;
+        for (int j = 0; j < n; ++j) {
+            const int k0 = (kt_begin + j) * BN;
+            const int ks = j % KS;
+            int y = oob_row;
+            if (PAGED && lane < 4) {
+                const int token = k0 + lane * 16;
+                const int slot = token / p.page_size;
+                if (token < kv_total && slot < p.max_pages) {
+                    const int page = p.pages[(long long)b * p.max_pages + slot];
+                    if (page >= 0 && page < p.num_pages)
+                        y = (page * p.kv_heads + kvh) * p.page_size + token % p.page_size;
+                    else
+                        atomicOr(p.status, INF_STATUS_BAD_PAGE);
+                }
+            }
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&k_empty[ks], (((uint32_t)(j / KS)) & 1u) ^ 1u) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+            const int y0 = __shfl_sync(0xffffffffu, y, 0), y1 = __shfl_sync(0xffffffffu, y, 1);
+            const int y2 = __shfl_sync(0xffffffffu, y, 2), y3 = __shfl_sync(0xffffffffu, y, 3);
+            if (lane == 0) {
+                uint8_t* dst = sK + ks * L::K_BYTES;
+                mbar_arrive_expect_tx(&k_full[ks], L::K_BYTES);
+                if (PAGED) {
+                    const int ys[4] = {y0, y1, y2, y3};
+#pragma unroll
+                    for (int sub = 0; sub < 4; ++sub)
+#pragma unroll
+                        for (int blk = 0; blk < DQK / 64; ++blk)
+                            tma_load_2d(dst + blk * BN * 128 + sub * 2048, &tm_k, blk * 64, ys[sub], &k_full[ks]);
+                } else {
+                    // 128 no-rope dims of this head, then the 64-dim rope tail shared by every head
+                    tma_load_3d(dst, &tm_k, 0, head, k0, &k_full[ks]);
+                    tma_load_3d(dst + BN * 128, &tm_k, 64, head, k0, &k_full[ks]);
+                    if (DQK == 192) tma_load_2d(dst + 2 * BN * 128, &tm_k2, 0, k0, &k_full[ks]);
+                }
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------ V producer
+        if (lane == 0) tma_prefetch_desc(&tm_v);
+        const int kvh = PAGED ? head / p.group : head;
+        const int oob_row = p.num_pages * p.kv_heads * p.page_size;
+        for (int j = 0; j < n; ++j) {
+            const int k0 = (kt_begin + j) * BN;
+            const int vs = j % VS;
+            int y = oob_row;
+            if (PAGED && lane < 4) {
+                const int token = k0 + lane * 16;
+                const int slot = token / p.page_size;
+                if (token < kv_total && slot < p.max_pages) {
+                    const int page = p.pages[(long long)b * p.max_pages + slot];
+                    if (page >= 0 && page < p.num_pages) y = (page * p.kv_heads + kvh) * p.page_size + token % p.page_size;
+                }
+            }
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&v_empty[vs], (((uint32_t)(j / VS)) & 1u) ^ 1u) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+            const int y0 = __shfl_sync(0xffffffffu, y, 0), y1 = __shfl_sync(0xffffffffu, y, 1);
+            const int y2 = __shfl_sync(0xffffffffu, y, 2), y3 = __shfl_sync(0xffffffffu, y, 3);
+            if (lane == 0) {
+                uint8_t* dst = sV + vs * L::V_BYTES;
+                mbar_arrive_expect_tx(&v_full[vs], L::V_BYTES);
+                if (PAGED) {
+                    const int ys[4] = {y0, y1, y2, y3};
+#pragma unroll
+                    for (int sub = 0; sub < 4; ++sub)
+#pragma unroll
+                        for (int blk = 0; blk < DV / 64; ++blk)
+                            tma_load_2d(dst + blk * BN * 128 + sub * 2048, &tm_v, blk * 64, ys[sub], &v_full[vs]);
+                } else {
+#pragma unroll
+                    for (int blk = 0; blk < DV / 64; ++blk)
+                        tma_load_3d(dst + blk * BN * 128, &tm_v, blk * 64, head, k0, &v_full[vs]);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            const uint32_t idesc_qk = umma_idesc_f16(BM, BN, 0, 0);
+            const uint32_t idesc_pv = umma_idesc_f16(BM, DV, 0, 1);
+            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            bool ok = mbar_wait(q_full, 0);
+            auto issue_qk = [&](int j) {
+                const int ks = j % KS;
+                const uint32_t s_col = (j & 1) ? COL_S1 : COL_S0;
+#pragma unroll
+                for (int kk = 0; kk < DQK / 16; ++kk) {
+                    const uint64_t ad = umma_smem_desc(q_addr + (kk / 4) * BM * 128 + (kk % 4) * 32, 16, 1024, UMMA_SW128);
+                    const uint64_t bd =
+                        umma_smem_desc(k_addr + ks * L::K_BYTES + (kk / 4) * BN * 128 + (kk % 4) * 32, 16, 1024, UMMA_SW128);
+                    umma_ss(tbase + s_col, ad, bd, idesc_qk, kk > 0);
+                }
+                tc_commit(&s_full[j & 1]);
+                tc_commit(&k_empty[ks]);
+            };
+            if (ok) ok = mbar_wait(&k_full[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; ok && j < n; ++j) {
+                if (j + 1 < n) {
+                    ok = mbar_wait(&k_full[(j + 1) % KS], ((uint32_t)((j + 1) / KS)) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                ok = mbar_wait(&p_full[j & 1], ((uint32_t)(j >> 1)) & 1u);
+                if (!ok) break;
+                const int vs = j % VS;
+                ok = mbar_wait(&v_full[vs], ((uint32_t)(j / VS)) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t p_col = (j & 1) ? COL_S1 : COL_S0;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t bd = umma_smem_desc(v_addr + vs * L::V_BYTES + kk * 2048, BN * 128, 1024, UMMA_SW128);
+                    umma_ts(tbase + COL_O, tbase + p_col + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(&v_empty[vs]);
+                tc_commit(o_ready);
+            }
+            if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        }
+    } else {
+        // ------------------------------------------------ softmax + epilogue: thread = query row
+        const int r = tid;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        const int qpos = past + q0 + r;
+        float m_used = M_INIT, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n; ++j) {
+            const int k0 = (kt_begin + j) * BN;
+            const uint32_t buf_col = (j & 1) ? COL_S1 : COL_S0;
+            if (!mbar_wait(&s_full[j & 1], ((uint32_t)(j >> 1)) & 1u)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint32_t sraw[BN];
+            tmem_ld32(tbase + lane_addr + buf_col, sraw);
+            tmem_ld32(tbase + lane_addr + buf_col + 32, sraw + 32);
+            tc_wait_ld();
+            float x[BN];
+#pragma unroll
+            for (int i = 0; i < BN; ++i) x[i] = __uint_as_float(sraw[i]) * p.scale_log2;
+            const bool need_mask = (k0 + BN - 1 > past + q0) || (k0 + BN > kv_total) ||
+                                   (p.window > 0 && k0 < past + q0 + BM - p.window);
+            if (need_mask) {
+                const int first = p.window > 0 ? qpos + 1 - p.window : 0;
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const int key = k0 + i;
+                    if (key > qpos || key < first || key >= kv_total) x[i] = -INFINITY;
+                }
+            }
+            float mx = x[0];
+#pragma unroll
+            for (int i = 1; i < BN; ++i) mx = fmaxf(mx, x[i]);
+            const float m_cand = fmaxf(m_used, mx);
+            if (j == 0) {
+                m_used = m_cand;
+            } else {
+                const bool need = (m_cand - m_used) > RESCALE_THRESHOLD;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float alpha = ex2_approx(m_used - m_cand);
+                    m_used = m_cand;
+                    l *= alpha;
+                    if (!mbar_wait(o_ready, ((uint32_t)(j - 1)) & 1u)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < DV / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(tbase + lane_addr + COL_O + c * 32, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tbase + lane_addr + COL_O + c * 32, o);
+                    }
+                    tc_wait_st();
+                }
+            }
+            float sum = 0.f;
+            uint32_t packed[BN / 2];
+#pragma unroll
+            for (int i = 0; i < BN; i += 2) {
+                const float p0 = ex2_approx(x[i] - m_used), p1 = ex2_approx(x[i + 1] - m_used);
+                sum += p0 + p1;
+                packed[i / 2] = pack_half2(p0, p1);
+            }
+            l += sum;
+            tmem_st32(tbase + lane_addr + buf_col, packed);
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&p_full[j & 1]);
+        }
+        if (ok && !mbar_wait(o_ready, ((uint32_t)(n - 1)) & 1u)) ok = false;
+        if (!ok) {
+            if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        } else {
+            tc_fence_after();
+            const bool valid = (q0 + r) < p.tokens;
+            float gain = 1.0f / l;
+            if (p.gate && valid) gain *= softplus_ref(p.gate[((long long)b * p.tokens + q0 + r) * p.q_heads + head]);
+            const long long obase = (long long)b * p.o_bs + (long long)(q0 + r) * p.o_ts + (long long)head * p.o_hs;
+#pragma unroll
+            for (int c = 0; c < DV / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tbase + lane_addr + COL_O + c * 32, o);
+                tc_wait_ld();
+                if (valid) {
+                    if (p.out_f16) {
+                        __half* dst = reinterpret_cast<__half*>(p.out) + obase + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 v;
+                            v.x = pack_half2(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain);
+                            v.y = pack_half2(__uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                            v.z = pack_half2(__uint_as_float(o[i + 4]) * gain, __uint_as_float(o[i + 5]) * gain);
+                            v.w = pack_half2(__uint_as_float(o[i + 6]) * gain, __uint_as_float(o[i + 7]) * gain);
+                            *reinterpret_cast<uint4*>(dst + i) = v;
+                        }
+                    } else {
+                        float* dst = reinterpret_cast<float*>(p.out) + obase + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4*>(dst + i) =
+                                make_float4(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain,
+                                            __uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tbase, TMEM_COLS);
+}
+
+template <int DQK, int DV, int KS, int VS, bool PAGED>
+int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tk2,
+                 const CUtensorMap& tv, const FlashParams& p, const char* name) {
+    using L = SmemLayout<DQK, DV, KS, VS>;
+    auto kernel = flash_prefill_kernel<DQK, DV, KS, VS, PAGED>;
+    if (!(ctx->func_attr_done & attr_bit)) {
+        INF_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        ctx->func_attr_done |= attr_bit;
+    }
+    dim3 grid(p.q_heads, (p.tokens + BM - 1) / BM, p.batch);
+    {
+        inf_prof_scope prof(ctx, name);
+        kernel<<<grid, NUM_THREADS, L::TOTAL, ctx->stream>>>(tq, tk, tk2, tv, p);
+    }
+    INF_LAUNCH_CHECK(ctx, name);
+    return INF_OK;
+}
+
+}  // namespace
+
+// Shared with the fused operator entry point.
+int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
+                           int tokens, int q_heads, int sliding_window, const float* gate, float scale, void* out,
+                           int out_dtype) {
+    if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "gqa_prefill: null pointer");
+    if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "gqa_prefill: pool has no storage");
+    if (pool->head_dim != 128) return inf_fail(ctx, INF_E_SHAPE, "gqa_prefill: head_dim must be 128, got %d", pool->head_dim);
+    if (pool->page_size % 16 != 0) return inf_fail(ctx, INF_E_CACHE, "gqa_prefill: page_size must be a multiple of 16");
+    if (tokens <= 0) return inf_fail(ctx, INF_E_SHAPE, "gqa_prefill: tokens must be positive");
+    if (q_heads <= 0 || q_heads % pool->kv_heads != 0)
+        return inf_fail(ctx, INF_E_SHAPE, "gqa_prefill: q_heads %d must be a positive multiple of kv_heads %d", q_heads,
+                        pool->kv_heads);
+    if (sliding_window < 0) return inf_fail(ctx, INF_E_CONFIG, "gqa_prefill: sliding_window must be >= 0");
+    if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
+        return inf_fail(ctx, INF_E_DTYPE, "gqa_prefill: output dtype must be f32 or f16");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "gqa_prefill");
+    if (rc != INF_OK) return rc;
+
+    CUtensorMap tq, tk, tv;
+    {
+        uint64_t dims[3] = {128, (uint64_t)q_heads, (uint64_t)table->batch * tokens};
+        uint64_t strides[2] = {128 * 2, (uint64_t)q_heads * 128 * 2};
+        uint32_t box[3] = {64, 1, BM};
+        rc = inf_make_tmap(ctx, q_f16, 3, dims, strides, box, &tq);
+        if (rc != INF_OK) return rc;
+    }
+    {
+        uint64_t dims[2] = {128, (uint64_t)pool->num_pages * pool->kv_heads * pool->page_size};
+        uint64_t strides[1] = {128 * 2};
+        uint32_t box[2] = {64, 16};
+        rc = inf_make_tmap(ctx, pool->k, 2, dims, strides, box, &tk);
+        if (rc != INF_OK) return rc;
+        rc = inf_make_tmap(ctx, pool->v, 2, dims, strides, box, &tv);
+        if (rc != INF_OK) return rc;
+    }
+    FlashParams p{};
+    p.tokens = tokens;
+    p.q_heads = q_heads;
+    p.kv_heads = pool->kv_heads;
+    p.group = q_heads / pool->kv_heads;
+    p.batch = table->batch;
+    p.pages = table->pages;
+    p.lens = table->lens;
+    p.max_pages = table->max_pages;
+    p.page_size = pool->page_size;
+    p.num_pages = pool->num_pages;
+    p.window = sliding_window;
+    p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
+    p.gate = gate;
+    p.out = out;
+    p.out_f16 = out_dtype == INF_DTYPE_F16;
+    p.o_hs = 128;
+    p.o_ts = (long long)q_heads * 128;
+    p.o_bs = (long long)tokens * q_heads * 128;
+    p.status = ctx->status;
+    return launch_flash<128, 128, 2, 2, true>(ctx, 2u, tq, tk, tk, tv, p, "flash_prefill_gqa_kernel");
+}
+
+extern "C" int32_t inf_gqa_prefill_paged(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                         const inf_page_table* table, int32_t tokens, int32_t q_heads,
+                                         int32_t sliding_window, const float* gate, float scale, void* out,
+                                         int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    return inf_gqa_prefill_launch(ctx, q_f16, pool, table, tokens, q_heads, sliding_window, gate, scale, out,
+                                  out_dtype);
+}
+
+extern "C" int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs, const void* k_nope,
+                                          int64_t kn_ts, int64_t kn_hs, const void* k_rope, int64_t kr_ts,
+                                          const void* v, int64_t v_ts, int64_t v_hs, int32_t tokens, int32_t heads,
+                                          int32_t nope_dim, int32_t rope_dim, int32_t v_dim, float scale, void* out,
+                                          int64_t o_ts, int64_t o_hs, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    if (!q || !k_nope || !v || !out) return inf_fail(ctx, INF_E_ARG, "mla_prefill: null pointer");
+    if (tokens <= 0 || heads <= 0) return inf_fail(ctx, INF_E_SHAPE, "mla_prefill: sizes must be positive");
+    if (nope_dim != 128 || v_dim != 128 || (rope_dim != 64 && rope_dim != 0)) return INF_UNSUPPORTED;
+    if (rope_dim && !k_rope) return inf_fail(ctx, INF_E_ARG, "mla_prefill: null rope tail");
+    if (!(scale > 0.f)) return inf_fail(ctx, INF_E_CONFIG, "mla_prefill: scale must be positive");
+    if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
+        return inf_fail(ctx, INF_E_DTYPE, "mla_prefill: output dtype must be f32 or f16");
+    const int dqk = nope_dim + rope_dim;
+    CUtensorMap tq, tk, tk2, tv;
+    int rc;
+    {
+        uint64_t dims[3] = {(uint64_t)dqk, (uint64_t)heads, (uint64_t)tokens};
+        uint64_t strides[2] = {(uint64_t)q_hs * 2, (uint64_t)q_ts * 2};
+        uint32_t box[3] = {64, 1, BM};
+        rc = inf_make_tmap(ctx, q, 3, dims, strides, box, &tq);
+        if (rc != INF_OK) return rc;
+    }
+    {
+        uint64_t dims[3] = {(uint64_t)nope_dim, (uint64_t)heads, (uint64_t)tokens};
+        uint64_t strides[2] = {(uint64_t)kn_hs * 2, (uint64_t)kn_ts * 2};
+        uint32_t box[3] = {64, 1, BN};
+        rc = inf_make_tmap(ctx, k_nope, 3, dims, strides, box, &tk);
+        if (rc != INF_OK) return rc;
+    }
+    if (rope_dim) {
+        uint64_t dims[2] = {(uint64_t)rope_dim, (uint64_t)tokens};
+        uint64_t strides[1] = {(uint64_t)kr_ts * 2};
+        uint32_t box[2] = {64, BN};
+        rc = inf_make_tmap(ctx, k_rope, 2, dims, strides, box, &tk2);
+        if (rc != INF_OK) return rc;
+    } else {
+        tk2 = tk;
+    }
+    {
+        uint64_t dims[3] = {(uint64_t)v_dim, (uint64_t)heads, (uint64_t)tokens};
+        uint64_t strides[2] = {(uint64_t)v_hs * 2, (uint64_t)v_ts * 2};
+        uint32_t box[3] = {64, 1, BN};
+        rc = inf_make_tmap(ctx, v, 3, dims, strides, box, &tv);
+        if (rc != INF_OK) return rc;
+    }
+    FlashParams p{};
+    p.tokens = tokens;
+    p.q_heads = heads;
+    p.kv_heads = heads;
+    p.group = 1;
+    p.batch = 1;
+    p.window = 0;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.out = out;
+    p.out_f16 = out_dtype == INF_DTYPE_F16;
+    p.o_ts = o_ts;
+    p.o_hs = o_hs;
+    p.o_bs = 0;
+    p.status = ctx->status;
+    if (rope_dim) return launch_flash<192, 128, 2, 1, false>(ctx, 4u, tq, tk, tk2, tv, p, "flash_prefill_mla_kernel");
+    return launch_flash<128, 128, 2, 2, false>(ctx, 8u, tq, tk, tk2, tv, p, "flash_prefill_mha_kernel");
+}

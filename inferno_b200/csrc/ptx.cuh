@@ -40,16 +40,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  try_wait itself blocks for a hardware-defined slice, so the
-// bound is generous in wall-clock terms (seconds) yet always finite.
-#ifndef INF_SPIN_LIMIT
-#define INF_SPIN_LIMIT (1u << 24)
+// Bounded wait: gives up after INF_WAIT_LIMIT_NS of wall-clock time (default 2 s) so that a
+// lost arrival turns into an error status instead of a hung GPU.
+#ifndef INF_WAIT_LIMIT_NS
+#define INF_WAIT_LIMIT_NS 2000000000ull
 #endif
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < INF_SPIN_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > INF_WAIT_LIMIT_NS) return false;
     }
-    return false;
 }
 
 // ---------------------------------------------------------------- proxies
