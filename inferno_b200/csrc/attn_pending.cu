@@ -4,6 +4,4 @@ extern "C" {
 int32_t inf_laguna_gated_gqa_f16_attention(inf_ctx* ctx, const float*, const float*, const float*, const float*,
                                            const inf_kv_pool*, const inf_page_table*, int32_t, int32_t, int32_t,
                                            int32_t, float*) { INF_CHECK_CTX(ctx); return INF_UNSUPPORTED; }
-int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void*, const inf_mla_pool*, const inf_page_table*, int32_t,
-                                int32_t, int32_t, float, void*, int32_t) { INF_CHECK_CTX(ctx); return INF_UNSUPPORTED; }
 }

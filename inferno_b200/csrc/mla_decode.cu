@@ -1,0 +1,426 @@
+// Absorbed-MLA decode over the paged latent cache on tcgen05 / TMEM.
+//
+// All query heads of a token share one cached row (512 latent + 64 rope, fp16), so the heads are the
+// M dimension of the MMAs: S[64 heads x 64 keys] = Q[64 x 576] C^T, O[64 x 512] += P[64 x 64] C[:, :512],
+// and each cached byte is fetched from HBM once for all heads (the reference re-reads it per head,
+// attention_kernels.metal:465-603).  One CTA = (sequence, query token, 64-head block, split of the page
+// range).  A page (64 rows x 576) arrives as nine [64 x 64] TMA boxes with the 128-byte swizzle; the
+// same shared-memory bytes serve as the K-major B operand of QK^T and, columns 0-511, as the MN-major B
+// operand of PV.  M = 64 accumulators use 16 lanes of each TMEM quadrant, so the 512 output columns are
+// held as two interleaved halves (lane offset 0 and 16) over TMEM columns 0-255; S is double-buffered in
+// columns 256-383.  Softmax runs on lanes 0-15 of the four softmax warps, P goes to shared memory as the
+// K-major A operand, O is rescaled lazily.  Split partials (max, sum, O) are merged by a second kernel.
+//
+// Warps: 0-3 softmax/epilogue, 4 TMA producer, 5 TMEM allocation + MMA issue.
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+using namespace inf;
+
+namespace {
+
+constexpr int LAT = 512, ROPE = 64, ROW = LAT + ROPE;  // 576
+constexpr int PAGE = 64;
+constexpr int HB = 64;                                   // heads per CTA (MMA M)
+constexpr int NBLK = ROW / 64;                           // 9 column blocks
+constexpr int BLK_BYTES = 64 * 128;                      // one [64 rows][64 cols] swizzled block
+constexpr int TILE_BYTES = NBLK * BLK_BYTES;             // 73728: Q tile and KV page alike
+constexpr int NUM_THREADS = 192;
+constexpr float M_INIT = -1.0e30f;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_O = 0, COL_S0 = 256, COL_S1 = 320;
+
+constexpr int OFF_KV = TILE_BYTES;
+constexpr int OFF_P = OFF_KV + 2 * TILE_BYTES;
+constexpr int OFF_BAR = OFF_P + BLK_BYTES;
+constexpr int SMEM_TOTAL = OFF_BAR + 128;
+
+struct MlaParams {
+    const int* pages;
+    const int* lens;
+    int max_pages, num_pages;
+    int tokens, heads, head_blocks, batch;
+    int n_splits;
+    float scale_log2;
+    float* part_acc;  // [batch][tokens][n_splits][heads][512]
+    float* part_ml;   // [batch][tokens][n_splits][heads][2]
+    int* status;
+};
+
+__device__ __forceinline__ void split_range(int n_pages, int n_splits, int s, int& begin, int& end) {
+    const int per = (n_pages + n_splits - 1) / n_splits;
+    begin = min(n_pages, s * per);
+    end = min(n_pages, begin + per);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                          MlaParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;
+    uint8_t* sKV = smem + OFF_KV;
+    uint8_t* sP = smem + OFF_P;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* q_full = bars;
+    uint64_t* kv_full = bars + 1;   // [2]
+    uint64_t* kv_empty = bars + 3;  // [2]
+    uint64_t* s_full = bars + 5;    // [2]
+    uint64_t* p_full = bars + 7;
+    uint64_t* pv_done = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x;
+    const int t = blockIdx.y % p.tokens, hb = blockIdx.y / p.tokens;
+    const int b = blockIdx.z;
+    const int kv_len = p.lens[b] + t + 1;  // rows visible to this query token
+    const int n_pages = (kv_len + PAGE - 1) / PAGE;
+    int pg_begin, pg_end;
+    split_range(n_pages, p.n_splits, split, pg_begin, pg_end);
+    const int n = pg_end - pg_begin;
+    if (n <= 0) return;
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        return;
+    }
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+        }
+        mbar_init(p_full, 128);
+        mbar_init(pv_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = *tmem_slot;
+
+    if (warp == 4) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_kv);
+            mbar_arrive_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+            for (int blk = 0; blk < NBLK; ++blk)
+                tma_load_3d(sQ + blk * BLK_BYTES, &tm_q, blk * 64, hb * HB, b * p.tokens + t, q_full);
+            const int oob_row = p.num_pages * PAGE;
+            for (int j = 0; j < n; ++j) {
+                const int slot = pg_begin + j;
+                int y = oob_row;
+                if (slot < p.max_pages) {
+                    const int page = p.pages[(long long)b * p.max_pages + slot];
+                    if (page >= 0 && page < p.num_pages)
+                        y = page * PAGE;
+                    else
+                        atomicOr(p.status, INF_STATUS_BAD_PAGE);
+                } else {
+                    atomicOr(p.status, INF_STATUS_BAD_LEN);
+                }
+                const int st = j & 1;
+                if (!mbar_wait(&kv_empty[st], (((uint32_t)(j >> 1)) & 1u) ^ 1u)) {
+                    atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                    break;
+                }
+                mbar_arrive_expect_tx(&kv_full[st], TILE_BYTES);
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk)
+                    tma_load_2d(sKV + st * TILE_BYTES + blk * BLK_BYTES, &tm_kv, blk * 64, y, &kv_full[st]);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_qk = umma_idesc_f16(HB, PAGE, 0, 0);
+            const uint32_t idesc_pv = umma_idesc_f16(HB, 256, 0, 1);
+            const uint32_t q_addr = smem_u32(sQ), kv_addr = smem_u32(sKV), p_addr = smem_u32(sP);
+            auto issue_qk = [&](int j) {
+                const uint32_t s_col = (j & 1) ? COL_S1 : COL_S0;
+                const uint32_t tile = kv_addr + (j & 1) * TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < ROW / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
+                    umma_ss(tbase + s_col, umma_smem_desc(q_addr + off, 16, 1024, UMMA_SW128),
+                            umma_smem_desc(tile + off, 16, 1024, UMMA_SW128), idesc_qk, kk > 0);
+                }
+                tc_commit(&s_full[j & 1]);
+            };
+            bool ok = mbar_wait(q_full, 0);
+            if (ok) ok = mbar_wait(&kv_full[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; ok && j < n; ++j) {
+                if (j + 1 < n) {
+                    ok = mbar_wait(&kv_full[(j + 1) & 1], ((uint32_t)((j + 1) >> 1)) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                ok = mbar_wait(p_full, ((uint32_t)j) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tile = kv_addr + (j & 1) * TILE_BYTES;
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+#pragma unroll
+                    for (int kk = 0; kk < PAGE / 16; ++kk)
+                        umma_ss(tbase + COL_O + ((uint32_t)(half * 16) << 16),
+                                umma_smem_desc(p_addr + kk * 32, 16, 1024, UMMA_SW128),
+                                umma_smem_desc(tile + half * 4 * BLK_BYTES + kk * 2048, BLK_BYTES, 1024, UMMA_SW128),
+                                idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(&kv_empty[j & 1]);
+                tc_commit(pv_done);
+            }
+            if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        }
+    } else {
+        // ------------------------------------------------ softmax + epilogue
+        // lanes 0-15 of warp w own rows 16w..16w+15 of S and of O[:, 0:256]; lanes 16-31 own the same rows of
+        // O[:, 256:512] (the accumulator half that sits at TMEM lane offset 16).
+        const int row = warp * 16 + (lane & 15);
+        const bool s_owner = lane < 16;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        float m_used = M_INIT, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n; ++j) {
+            const uint32_t s_col = (j & 1) ? COL_S1 : COL_S0;
+            if (!mbar_wait(&s_full[j & 1], ((uint32_t)(j >> 1)) & 1u)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint32_t sraw[PAGE];
+            tmem_ld32(tbase + lane_addr + s_col, sraw);
+            tmem_ld32(tbase + lane_addr + s_col + 32, sraw + 32);
+            tc_wait_ld();
+            float x[PAGE];
+            const int k0 = (pg_begin + j) * PAGE;
+#pragma unroll
+            for (int i = 0; i < PAGE; ++i) {
+                x[i] = __uint_as_float(sraw[i]) * p.scale_log2;
+                if (k0 + i >= kv_len) x[i] = -INFINITY;
+            }
+            float mx = x[0];
+#pragma unroll
+            for (int i = 1; i < PAGE; ++i) mx = fmaxf(mx, x[i]);
+            if (!s_owner) mx = -INFINITY;
+            const float m_cand = fmaxf(m_used, mx);
+            float alpha = 1.0f;
+            bool rescale = false;
+            if (j == 0) {
+                m_used = m_cand;
+            } else {
+                rescale = __any_sync(0xffffffffu, s_owner && (m_cand - m_used) > RESCALE_THRESHOLD);
+                if (rescale) {
+                    alpha = ex2_approx(m_used - m_cand);
+                    m_used = m_cand;
+                    l *= alpha;
+                }
+            }
+            // P (and O) may only be touched once the previous tile's PV has drained
+            if (j > 0 && !mbar_wait(pv_done, ((uint32_t)(j - 1)) & 1u)) {
+                ok = false;
+                break;
+            }
+            if (rescale) {
+                alpha = __shfl_sync(0xffffffffu, alpha, lane & 15);
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < 256 / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(tbase + lane_addr + COL_O + c * 32, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tbase + lane_addr + COL_O + c * 32, o);
+                }
+                tc_wait_st();
+            }
+            if (s_owner) {
+                float sum = 0.f;
+#pragma unroll
+                for (int c = 0; c < PAGE / 8; ++c) {
+                    float pv[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        pv[i] = ex2_approx(x[c * 8 + i] - m_used);
+                        sum += pv[i];
+                    }
+                    uint4 v;
+                    v.x = pack_half2(pv[0], pv[1]);
+                    v.y = pack_half2(pv[2], pv[3]);
+                    v.z = pack_half2(pv[4], pv[5]);
+                    v.w = pack_half2(pv[6], pv[7]);
+                    *reinterpret_cast<uint4*>(sP + sw128_offset(row, c * 8)) = v;
+                }
+                l += sum;
+            }
+            fence_proxy_async_smem();  // P was written through the generic proxy, the MMA reads it through the async one
+            tc_fence_before();
+            mbar_arrive(p_full);
+        }
+        if (ok && !mbar_wait(pv_done, ((uint32_t)(n - 1)) & 1u)) ok = false;
+        if (!ok) {
+            if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        } else {
+            tc_fence_after();
+            const int head = hb * HB + row;
+            const long long prow =
+                ((((long long)b * p.tokens + t) * p.n_splits + split) * p.heads) + head;
+            const bool valid = head < p.heads;
+            float* dst = p.part_acc + prow * LAT + (lane >> 4) * 256;
+#pragma unroll
+            for (int c = 0; c < 256 / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tbase + lane_addr + COL_O + c * 32, o);
+                tc_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + c * 32 + i) =
+                            make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]),
+                                        __uint_as_float(o[i + 3]));
+                }
+            }
+            if (valid && s_owner) {
+                p.part_ml[prow * 2] = m_used;
+                p.part_ml[prow * 2 + 1] = l;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tbase, TMEM_COLS);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+mla_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                          const int* __restrict__ lens, OutT* __restrict__ out, int tokens, int heads, int n_splits) {
+    const int h = blockIdx.x, t = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
+    const int kv_len = lens[b] + t + 1;
+    const int n_pages = (kv_len + PAGE - 1) / PAGE;
+    float M = M_INIT, Lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_splits; ++s) {
+        int pb, pe;
+        split_range(n_pages, n_splits, s, pb, pe);
+        if (pe <= pb) continue;
+        const long long prow = ((((long long)b * tokens + t) * n_splits + s) * heads) + h;
+        const float m = part_ml[prow * 2], l = part_ml[prow * 2 + 1];
+        const float4 a = *reinterpret_cast<const float4*>(part_acc + prow * LAT + tid * 4);
+        const float Mn = fmaxf(M, m);
+        const float s0 = ex2_approx(M - Mn), s1 = ex2_approx(m - Mn);
+        acc.x = acc.x * s0 + a.x * s1;
+        acc.y = acc.y * s0 + a.y * s1;
+        acc.z = acc.z * s0 + a.z * s1;
+        acc.w = acc.w * s0 + a.w * s1;
+        Lsum = Lsum * s0 + l * s1;
+        M = Mn;
+    }
+    const float inv = 1.0f / Lsum;
+    OutT* dst = out + ((((long long)b * tokens + t) * heads) + h) * LAT + tid * 4;
+    dst[0] = OutT(acc.x * inv);
+    dst[1] = OutT(acc.y * inv);
+    dst[2] = OutT(acc.z * inv);
+    dst[3] = OutT(acc.w * inv);
+}
+
+}  // namespace
+
+extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool,
+                                           const inf_page_table* table, int32_t tokens, int32_t heads,
+                                           int32_t max_len, float scale, void* out, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "mla_decode: null pointer");
+    if (!pool->rows) return inf_fail(ctx, INF_E_ARG, "mla_decode: pool has no storage");
+    if (pool->latent_dim != LAT || pool->rope_dim != ROPE || pool->page_size != PAGE) return INF_UNSUPPORTED;
+    if (tokens <= 0 || heads <= 0 || max_len <= 0) return inf_fail(ctx, INF_E_SHAPE, "mla_decode: sizes must be positive");
+    if (!(scale > 0.f)) return inf_fail(ctx, INF_E_CONFIG, "mla_decode: scale must be positive");
+    if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
+        return inf_fail(ctx, INF_E_DTYPE, "mla_decode: output dtype must be f32 or f16");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, PAGE, tokens, "mla_decode");
+    if (rc != INF_OK) return rc;
+    if (table->host_lens)
+        for (int b = 0; b < table->batch; ++b)
+            if (table->host_lens[b] + tokens > max_len)
+                return inf_fail(ctx, INF_E_SHAPE, "mla_decode: sequence %d reaches %d rows, beyond max_len %d", b,
+                                table->host_lens[b] + tokens, max_len);
+    const int head_blocks = (heads + HB - 1) / HB;
+    const int max_pages_used = (max_len + PAGE - 1) / PAGE;
+    const int ctas_per_split = table->batch * tokens * head_blocks;
+    int n_splits = ctx->sm_count / ctas_per_split;
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > max_pages_used) n_splits = max_pages_used;
+    // even out: with `per` pages per split only ceil(pages/per) splits do work
+    const int per = (max_pages_used + n_splits - 1) / n_splits;
+    n_splits = (max_pages_used + per - 1) / per;
+
+    const size_t prows = (size_t)table->batch * tokens * n_splits * heads;
+    rc = inf_ensure_workspace(ctx, prows * (LAT + 2) * sizeof(float));
+    if (rc != INF_OK) return rc;
+
+    CUtensorMap tq, tkv;
+    {
+        uint64_t dims[3] = {(uint64_t)ROW, (uint64_t)heads, (uint64_t)table->batch * tokens};
+        uint64_t strides[2] = {(uint64_t)ROW * 2, (uint64_t)heads * ROW * 2};
+        uint32_t box[3] = {64, (uint32_t)HB, 1};
+        rc = inf_make_tmap(ctx, q_f16, 3, dims, strides, box, &tq);
+        if (rc != INF_OK) return rc;
+    }
+    {
+        uint64_t dims[2] = {(uint64_t)ROW, (uint64_t)pool->num_pages * PAGE};
+        uint64_t strides[1] = {(uint64_t)ROW * 2};
+        uint32_t box[2] = {64, (uint32_t)PAGE};
+        rc = inf_make_tmap(ctx, pool->rows, 2, dims, strides, box, &tkv);
+        if (rc != INF_OK) return rc;
+    }
+    MlaParams p{};
+    p.pages = table->pages;
+    p.lens = table->lens;
+    p.max_pages = table->max_pages;
+    p.num_pages = pool->num_pages;
+    p.tokens = tokens;
+    p.heads = heads;
+    p.head_blocks = head_blocks;
+    p.batch = table->batch;
+    p.n_splits = n_splits;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.part_acc = (float*)ctx->workspace;
+    p.part_ml = p.part_acc + prows * LAT;
+    p.status = ctx->status;
+    if (!(ctx->func_attr_done & 16u)) {
+        INF_CUDA(ctx, cudaFuncSetAttribute(mla_decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SMEM_TOTAL));
+        ctx->func_attr_done |= 16u;
+    }
+    dim3 grid(n_splits, tokens * head_blocks, table->batch);
+    {
+        inf_prof_scope prof(ctx, "mla_decode_partial_kernel");
+        mla_decode_partial_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tq, tkv, p);
+    }
+    INF_LAUNCH_CHECK(ctx, "mla_decode_partial_kernel");
+    dim3 cgrid(heads, tokens, table->batch);
+    if (out_dtype == INF_DTYPE_F32)
+        mla_decode_combine_kernel<float><<<cgrid, 128, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
+                                                                         (float*)out, tokens, heads, n_splits);
+    else
+        mla_decode_combine_kernel<__half><<<cgrid, 128, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
+                                                                          (__half*)out, tokens, heads, n_splits);
+    INF_LAUNCH_CHECK(ctx, "mla_decode_combine_kernel");
+    return INF_OK;
+}
