@@ -160,10 +160,9 @@ class GqaDecodeB32:
         self.hout.copy_(self.out, non_blocking=True)
 
     # ---- CPU arm: the oracle on host arrays of the same shapes
-    @staticmethod
-    def cpu_sample(rank=0, max_sequences=32):
+    def cpu_sample(self, rank=0, max_sequences=32):
         from oracle import pyoracle as orc
-        c = GqaDecodeB32
+        c = self
         lens = decode_lens(rank, c.B)[:max_sequences]
         pages = (lens + c.P - 1) // c.P
         num_pages = int(pages.sum()) + 8
@@ -192,8 +191,229 @@ class GqaDecodeB32:
         return run, units, f"{len(lens)} of 32 sequences, all heads, full contexts"
 
 
-WORKLOADS = {w.name: w for w in (GqaDecodeB32,)}
-EXTRA_WORKLOADS: list = []  # measured in the same run and reported under "workloads"
+
+class MlaDecode:
+    """Absorbed-MLA decode, batch 1, 64 heads over the paged 512+64 latent (second benchmark configuration)."""
+    metric, unit, bound = "mla_decode_hbm_gbs", "GB/s", "hbm"
+    kernel = "mla_decode_partial_kernel"
+    launches_per_step = 3  # post-process + append, split partial, combine
+    H, L, R, P = 64, 512, 64, 64
+    max_steps = 400
+
+    def __init__(self, be, rank, ctx_len):
+        import torch
+        self.torch, self.be, self.ctx_len = torch, be, ctx_len
+        self.name = f"mla_decode_{ctx_len // 1024}k"
+        row_bytes = (self.L + self.R) * 2
+        self.n_caches = max(2, int(np.ceil(320e6 / (ctx_len * row_bytes))))  # rotate through > L2 worth of caches
+        pages_per = (ctx_len + self.P - 1) // self.P
+        num_pages = self.n_caches * pages_per + 8
+        g = torch.Generator(device="cpu").manual_seed(SEED + 21 + rank)
+        perm = torch.randperm(num_pages, generator=g).to(torch.int32)
+        self.pool = be.prepare_mla_pool(num_pages)
+        gd = torch.Generator(device=be.device).manual_seed(SEED + 22 + rank)
+        self.pool.rows.normal_(0, 0.5, generator=gd)
+        self.tables = [be.page_table(perm[i * pages_per:(i + 1) * pages_per].view(1, -1), [ctx_len - 1],
+                                     validate_on_host=False) for i in range(self.n_caches)]
+        self.q = torch.randn((1, 1, self.H, self.L + self.R), generator=gd, device=be.device, dtype=torch.float16)
+        self.x = torch.randn((1, 1, self.L + self.R), generator=gd, device=be.device, dtype=torch.float32)
+        self.w = torch.ones((self.L,), device=be.device, dtype=torch.float32)
+        self.out = torch.empty((1, 1, self.H, self.L), dtype=torch.float32, device=be.device)
+        self.hq, self.hx = self.q.cpu().pin_memory(), self.x.cpu().pin_memory()
+        self.hout = torch.empty(self.out.shape, dtype=torch.float32).pin_memory()
+        self.scale = 1.0 / float(np.sqrt(192.0))
+        self.i = 0
+        self.units_per_step = float(ctx_len) * row_bytes
+        self.flops_per_step = 2.0 * self.H * (self.L + self.R + self.L) * ctx_len
+        self.h2d = self.hq.numel() * 2 + self.hx.numel() * 4
+        self.d2h = self.hout.numel() * 4
+        self.config = {"workload": self.name, "batch": 1, "heads": self.H, "latent_dim": self.L, "rope_dim": self.R,
+                       "context": ctx_len, "page_size": self.P, "kv_sigma": 0.5, "scale": "1/sqrt(192)",
+                       "kv_bytes_per_step": int(self.units_per_step), "flops_per_step": self.flops_per_step,
+                       "l2": f"rotates through {self.n_caches} distinct caches ({self.n_caches * ctx_len * row_bytes / 1e6:.0f} MB > L2)",
+                       "sharding": "replicas"}
+
+    def step(self):
+        t = self.tables[self.i % self.n_caches]
+        self.i += 1
+        self.be.mla_kv_postprocess_device(self.x, self.w, 1e-6, 1.0e7, self.pool, t, want_outputs=False)
+        self.be.mla_decode_absorbed(self.q, self.pool, t, self.ctx_len, self.scale, out=self.out)
+
+    def step_e2e(self):
+        self.q.copy_(self.hq, non_blocking=True)
+        self.x.copy_(self.hx, non_blocking=True)
+        self.step()
+        self.hout.copy_(self.out, non_blocking=True)
+
+    def cpu_sample(self):
+        from oracle import pyoracle as orc
+        n, W = self.ctx_len, self.L + self.R
+        table = np.random.RandomState(SEED + 23).permutation((n + self.P - 1) // self.P).astype(np.int32)[None]
+        pool = np.resize(np.random.RandomState(SEED + 24).standard_normal(1 << 20).astype(np.float16).view(np.uint16),
+                         table.size * self.P * W).reshape(-1, self.P, W)
+        q = orc.fill_normal((1, 1, self.H, W), SEED + 25)
+        cur = orc.fill_normal((1, 1, W), SEED + 26, 0.5)
+        run = lambda: orc.mla_absorbed_paged(q, cur, pool, table, [n - 1], self.P, self.L, self.R, self.scale)
+        return run, self.units_per_step, "whole workload (1 sequence, 64 heads, full context)"
+
+
+class GqaPrefill2k:
+    """Causal GQA prefill, one 2048-token prompt, 48 q / 8 kv heads, fused RoPE + KV-append (fourth configuration).
+    With N > 1 ranks the heads are sharded (48/N query heads with their 8/N KV heads per rank) and the output is
+    all-gathered over NCCL: strong scaling."""
+    name = "gqa_prefill_2k"
+    metric, unit, bound = "gqa_prefill_tflops", "TFLOP/s", "tensor"
+    kernel = "flash_prefill_gqa_kernel"
+    launches_per_step = 2  # rope+append, flash prefill
+    T, Hq, Hkv, D, P, THETA = 2048, 48, 8, 128, 16, 500000.0
+    max_steps = 400
+    N_SETS = 8
+
+    def __init__(self, be, rank, world=1, dist=None):
+        import torch
+        self.torch, self.be, self.world, self.dist = torch, be, world, dist
+        self.hq_local, self.hkv_local = self.Hq // world, self.Hkv // world
+        pages = self.T // self.P
+        gd = torch.Generator(device=be.device).manual_seed(SEED + 31 + rank)
+        inv = 1.0 / np.power(np.float32(self.THETA), (2 * np.arange(32)).astype(np.float32) / np.float32(64))
+        self.rope = be.prepare_rope_table(inv.astype(np.float32), 64, 1.0)
+        self.sets = []
+        for i in range(self.N_SETS):  # distinct inputs and pools per iteration: more than L2 in rotation
+            pool = be.prepare_kv_pool(pages + 4, self.P, self.hkv_local, self.D)
+            perm = torch.randperm(pages + 4, generator=torch.Generator().manual_seed(SEED + 32 + i)).to(torch.int32)
+            table = be.page_table(perm[:pages].view(1, -1), [0], validate_on_host=False)
+            q = torch.randn((1, self.T, self.hq_local, self.D), generator=gd, device=be.device, dtype=torch.float16)
+            k = torch.randn((1, self.T, self.hkv_local, self.D), generator=gd, device=be.device, dtype=torch.float16)
+            v = torch.randn((1, self.T, self.hkv_local, self.D), generator=gd, device=be.device, dtype=torch.float16)
+            self.sets.append((pool, table, q, k, v))
+        self.out = torch.empty((1, self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device)
+        self.gathered = torch.empty((world, self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device) if world > 1 else None
+        q, k, v = self.sets[0][2:]
+        self.hq, self.hk, self.hv = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
+        self.hout = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
+        self.i = 0
+        total_flops = 4.0 * self.D * self.Hq * self.T * (self.T + 1) / 2
+        self.units_per_step = total_flops / world  # per rank; summed over ranks by the harness
+        self.h2d = sum(t.numel() * 2 for t in (self.hq, self.hk, self.hv))
+        self.d2h = self.hout.numel() * 2
+        set_mb = (self.T * (self.hq_local + 2 * self.hkv_local) * self.D * 2 * 2) / 1e6
+        self.config = {"workload": self.name, "tokens": self.T, "q_heads": self.Hq, "kv_heads": self.Hkv,
+                       "head_dim": self.D, "page_size": self.P, "rope_theta": self.THETA, "causal": True,
+                       "flops_per_step": total_flops, "append_bytes_per_step": self.T * self.Hkv * self.D * 2 * 2,
+                       "l2": f"rotates through {self.N_SETS} distinct input sets and pools ({self.N_SETS * set_mb:.0f} MB)",
+                       "sharding": "heads" if world > 1 else "none", "collective": "nccl all_gather of the output" if world > 1 else None}
+
+    def step(self):
+        pool, table, q, k, v = self.sets[self.i % self.N_SETS]
+        self.i += 1
+        q16 = self.be.rope_append_gqa(q, k, v, self.rope, pool, table)
+        self.be.gqa_prefill_paged(q16, pool, table, out=self.out)
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.gathered, self.out)
+
+    def step_e2e(self):
+        pool, table, q, k, v = self.sets[self.i % self.N_SETS]
+        q.copy_(self.hq, non_blocking=True)
+        k.copy_(self.hk, non_blocking=True)
+        v.copy_(self.hv, non_blocking=True)
+        self.step()
+        self.hout.copy_(self.out, non_blocking=True)
+
+    def cpu_sample(self):
+        from oracle import pyoracle as orc
+        c = self
+        q = orc.fill_normal((1, c.T, c.Hq, c.D), SEED + 33)
+        k = orc.fill_normal((1, c.T, c.Hkv, c.D), SEED + 34)
+        v = orc.fill_normal((1, c.T, c.Hkv, c.D), SEED + 35)
+        inv = orc.default_inv_freq(c.THETA, 64)
+        pages = c.T // c.P
+        table = np.random.RandomState(SEED + 36).permutation(pages).astype(np.int32)[None]
+        kp = np.zeros((pages, c.Hkv, c.P, c.D), np.uint16)
+        vp = np.zeros_like(kp)
+
+        def run():
+            qr = orc.qk_norm_rope(q, None, inv, 64, 0)
+            kr = orc.qk_norm_rope(k, None, inv, 64, 0)
+            return orc.gqa_paged_attention(qr, kr, v, None, kp, vp, table, [0], c.P)
+
+        return run, 4.0 * c.D * c.Hq * c.T * (c.T + 1) / 2, "whole workload (2048 tokens, 48 heads)"
+
+
+class MlaPrefill32k:
+    """Causal MLA prefill, 32768-token prompt, 64 heads, qk 128+64, v 128 (fifth configuration).  With N > 1
+    ranks the heads are sharded 64/N per rank and the [32768, 64, 128] output is all-gathered over NCCL."""
+    name = "mla_prefill_32k"
+    metric, unit, bound = "mla_prefill_tflops", "TFLOP/s", "tensor"
+    kernel = "flash_prefill_mla_kernel"
+    launches_per_step = 1
+    T, H = 32768, 64
+    max_steps = 3
+
+    def __init__(self, be, rank, world=1, dist=None):
+        import torch
+        self.torch, self.be, self.world, self.dist = torch, be, world, dist
+        hl = self.H // world
+        self.hl = hl
+        gd = torch.Generator(device=be.device).manual_seed(SEED + 41 + rank)
+        self.q = torch.randn((self.T, hl, 192), generator=gd, device=be.device, dtype=torch.float16)
+        self.kn = torch.randn((self.T, hl, 128), generator=gd, device=be.device, dtype=torch.float16)
+        self.kr = torch.randn((self.T, 64), generator=gd, device=be.device, dtype=torch.float16)
+        self.v = torch.randn((self.T, hl, 128), generator=gd, device=be.device, dtype=torch.float16)
+        self.gathered = torch.empty((world, self.T, hl, 128), dtype=torch.float16, device=be.device) if world > 1 else None
+        self.host = [t.cpu().pin_memory() for t in (self.q, self.kn, self.kr, self.v)]
+        self.hout = torch.empty((self.T, hl, 128), dtype=torch.float16).pin_memory()
+        self.scale = 1.0 / float(np.sqrt(192.0))
+        total_flops = self.T * (self.T + 1) / 2 * self.H * 2.0 * (192 + 128)
+        self.units_per_step = total_flops / world
+        self.h2d = sum(t.numel() * 2 for t in self.host)
+        self.d2h = self.hout.numel() * 2
+        self.out = None
+        self.config = {"workload": self.name, "tokens": self.T, "heads": self.H, "qk_dim": 192, "v_dim": 128,
+                       "causal": True, "flops_per_step": total_flops,
+                       "l2": "inputs larger than L2 (2.4 GB of Q/K/V)", "sharding": "heads" if world > 1 else "none",
+                       "collective": "nccl all_gather of the output" if world > 1 else None}
+
+    def step(self):
+        self.out = self.be.causal_sequence_attention_device(self.q, self.kn, self.kr, self.v, self.scale)
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.gathered, self.out)
+
+    def step_e2e(self):
+        for d, h in zip((self.q, self.kn, self.kr, self.v), self.host):
+            d.copy_(h, non_blocking=True)
+        self.step()
+        self.hout.copy_(self.out, non_blocking=True)
+
+    def cpu_sample(self):
+        from oracle import pyoracle as orc
+        T, H = self.T, 8  # 8 of the 64 heads, 48 sampled rows with their full causal key ranges
+        rows = np.sort(np.random.RandomState(SEED + 42).randint(0, T, size=48)).astype(np.int32)
+        blk = np.random.RandomState(SEED + 43).standard_normal(1 << 22).astype(np.float16).astype(np.float32)
+        q = np.resize(blk, T * H * 192).reshape(T, H, 192)
+        kn = np.resize(blk[::-1], T * H * 128).reshape(T, H, 128)
+        kr = np.resize(blk[7:], T * 64).reshape(T, 64)
+        v = np.resize(blk[13:], T * H * 128).reshape(T, H, 128)
+        flops = float(np.sum(rows.astype(np.int64) + 1)) * H * 2.0 * (192 + 128)
+        run = lambda: orc.causal_mha(q, kn, kr, v, self.scale, rows=rows)
+        return run, flops, "48 sampled query rows x 8 of 64 heads, full causal key ranges (sampled)"
+
+
+def make_workload(name, be, rank, world=1, dist=None):
+    if name == "gqa_decode_b32":
+        return GqaDecodeB32(be, rank)
+    if name == "mla_decode_4k":
+        return MlaDecode(be, rank, 4096)
+    if name == "mla_decode_32k":
+        return MlaDecode(be, rank, 32768)
+    if name == "gqa_prefill_2k":
+        return GqaPrefill2k(be, rank, world, dist)
+    if name == "mla_prefill_32k":
+        return MlaPrefill32k(be, rank, world, dist)
+    raise KeyError(name)
+
+
+WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "gqa_prefill_2k", "mla_prefill_32k"]
+STRONG = {"gqa_prefill_2k", "mla_prefill_32k"}  # head-sharded with an all-gather; the others replicate/shard by sequence
 
 
 # ----------------------------------------------------------------------------- measurement
@@ -235,24 +455,27 @@ def kernel_time(be, torch, wl, steps):
     return (ms / n) if n else None, n
 
 
-def cpu_baseline(wl_cls, budget_s=12.0):
+def cpu_baseline(wl, budget_s=12.0):
+    """The oracle (a scalar port of the reference kernels) on all host threads, on a bounded sample."""
     from oracle import pyoracle as orc
-    run, units, sample = wl_cls.cpu_sample()
+    run, units, sample = wl.cpu_sample()
     t0 = time.perf_counter()
     run()
     first = time.perf_counter() - t0
-    reps = max(1, min(8, int(budget_s / max(first, 1e-3)) - 1))
+    reps = max(0, min(6, int(budget_s / max(first, 1e-3)) - 1))
     best = first
     for _ in range(reps):
         t0 = time.perf_counter()
         run()
         best = min(best, time.perf_counter() - t0)
-    scale = 1e-9 if wl_cls.unit == "GB/s" else 1e-12
-    return {"value": units / best * scale, "unit": wl_cls.unit, "cores": orc.max_threads(), "kind": "port",
+    scale = 1e-9 if wl.unit == "GB/s" else 1e-12
+    return {"value": units / best * scale, "unit": wl.unit, "cores": orc.max_threads(), "kind": "port",
             "sample": sample, "seconds_per_pass": best}
 
 
 def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, profile_steps=100):
+    steps = max(1, min(steps, getattr(wl, "max_steps", steps)))
+    profile_steps = max(1, min(profile_steps, getattr(wl, "max_steps", profile_steps)))
     ms = timed(torch, dist, world, wl.step, steps, warmup)
     ms_e2e = timed(torch, dist, world, wl.step_e2e, steps, warmup)
     units = wl.units_per_step
@@ -266,19 +489,23 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
     value = total_units * steps / (ms * 1e-3) * scale
     e2e = total_units * steps / (ms_e2e * 1e-3) * scale
     k_ms, k_n = kernel_time(be, torch, wl, profile_steps)
-    peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops"] * 1.0
+    peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops"]
     achieved = units / (k_ms * 1e-3) * scale if k_ms else None
-    res = {"metric": wl.metric, "value": value, "unit": wl.unit, "ms_per_step": ms / steps,
+    roof = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if wl.bound == "hbm" else "TFLOP/s",
+            "frac": (achieved / peak) if achieved else None, "traffic": getattr(wl, "traffic", None),
+            "kernel": wl.kernel, "kernel_ms": k_ms, "kernel_launches_timed": k_n,
+            "peak_source": f"{peaks['source']} ({'copy bandwidth' if wl.bound == 'hbm' else 'cuBLAS bf16 burst'})"}
+    if wl.bound == "hbm" and hasattr(wl, "flops_per_step") and k_ms:
+        roof["tensor_tflops"] = wl.flops_per_step / (k_ms * 1e-3) * 1e-12
+        roof["tensor_frac_of_burst_peak"] = roof["tensor_tflops"] / peaks["tflops"]
+    if wl.bound == "tensor" and achieved and peaks.get("tflops_sustained"):
+        roof["frac_of_sustained_peak"] = achieved / peaks["tflops_sustained"]
+    res = {"metric": wl.metric, "value": value, "unit": wl.unit, "steps": steps, "ms_per_step": ms / steps,
            "e2e": {"value": e2e, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                    "ms_per_step": ms_e2e / steps},
-           "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak,
-                        "unit": "GB/s" if wl.bound == "hbm" else "TFLOP/s",
-                        "frac": (achieved / peak) if achieved else None, "traffic": getattr(wl, "traffic", None),
-                        "kernel": wl.kernel, "kernel_ms": k_ms, "kernel_launches_timed": k_n,
-                        "peak_source": f"{peaks['source']} ({'copy bandwidth' if wl.bound == 'hbm' else 'cuBLAS bf16 burst'})"},
-           "gpu_launches": wl.launches_per_step * steps, "config": wl.config}
+           "roofline": roof, "gpu_launches": wl.launches_per_step * steps, "config": wl.config}
     if with_cpu and rank == 0:
-        res["cpu_baseline"] = cpu_baseline(type(wl))
+        res["cpu_baseline"] = cpu_baseline(wl)
     return res
 
 
@@ -293,49 +520,65 @@ def run_ours(args):
     be = CudaBackend(local_rank if world > 1 else 0)
     peaks = load_peaks()
     sampler = ClockSampler(local_rank if world > 1 else 0) if rank == 0 else None
-    wl = WORKLOADS[args.workload](be, rank)
+    wl = make_workload(args.workload, be, rank, world, dist)
     head = measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
                    with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps)
     extras = []
-    if not args.no_extras:
-        for cls in EXTRA_WORKLOADS:
-            if cls.name == args.workload:
+    if args.extras or (world == 1 and not args.no_extras):
+        for name in WORKLOAD_NAMES:
+            if name == args.workload:
                 continue
             del wl
             torch.cuda.empty_cache()
-            wl = cls(be, rank)
-            extras.append(measure(be, torch, dist, world, rank, wl, min(args.steps, cls.max_steps), args.warmup, peaks,
-                                  with_cpu=False, profile_steps=min(args.profile_steps, cls.max_steps)))
+            wl = make_workload(name, be, rank, world, dist)
+            extras.append(measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
+                                  with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps))
     be.device_flush()
     clocks = sampler.stop() if sampler else None
     if rank == 0:
         line = {"metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-                "data": "synthetic", "config": head["config"], "e2e": head["e2e"], "roofline": head["roofline"],
-                "gpu_launches": head["gpu_launches"], "clocks": clocks}
+                "steps": head["steps"], "warmup": args.warmup, "ms_per_step": head["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong" if args.workload in STRONG else "weak",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": head["config"],
+                "e2e": head["e2e"], "roofline": head["roofline"], "gpu_launches": head["gpu_launches"],
+                "clocks": clocks}
         if "cpu_baseline" in head:
             line["cpu_baseline"] = head["cpu_baseline"]
         if extras:
-            line["workloads"] = [{k: e[k] for k in ("metric", "value", "unit", "ms_per_step", "e2e", "roofline", "config")}
-                                 for e in extras]
+            keys = ("metric", "value", "unit", "steps", "ms_per_step", "e2e", "roofline", "gpu_launches", "config",
+                    "cpu_baseline")
+            line["workloads"] = [{k: e[k] for k in keys if k in e} for e in extras]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+class _NoBackend:
+    """The CPU arm builds workload objects only for their cpu_sample(); it never touches a device."""
+
+
 def run_reference(args):
-    """The CPU arm: the oracle port on all host threads; rank 0 only."""
+    """The CPU arm: the oracle port on all host threads; rank 0 only, the other ranks exit at once."""
     rank, _, world = dist_env()
     if rank != 0:
         return
     from oracle import pyoracle as orc
-    cls = WORKLOADS[args.workload]
-    run, units, sample = cls.cpu_sample()
-    for _ in range(min(args.warmup, 1)):
+    protos = {"gqa_decode_b32": GqaDecodeB32, "mla_decode_4k": MlaDecode, "mla_decode_32k": MlaDecode,
+              "gqa_prefill_2k": GqaPrefill2k, "mla_prefill_32k": MlaPrefill32k}
+    cls = protos[args.workload]
+    wl = cls.__new__(cls)  # no device set-up: only the shape constants and cpu_sample() are used
+    if cls is MlaDecode:
+        wl.ctx_len = 4096 if args.workload.endswith("4k") else 32768
+        wl.scale = 1.0 / float(np.sqrt(192.0))
+        wl.units_per_step = float(wl.ctx_len) * (wl.L + wl.R) * 2
+    if cls is MlaPrefill32k:
+        wl.scale = 1.0 / float(np.sqrt(192.0))
+    run, units, sample = wl.cpu_sample()
+    warm = min(args.warmup, 1)
+    for _ in range(warm):
         run()
-    steps = max(1, min(args.steps, 10))
+    steps = max(1, min(args.steps, 5))
     t0 = time.perf_counter()
     for _ in range(steps):
         run()
@@ -343,10 +586,11 @@ def run_reference(args):
     scale = 1e-9 if cls.unit == "GB/s" else 1e-12
     value = units * steps / dt * scale
     line = {"impl": "reference", "metric": cls.metric, "value": value, "unit": cls.unit, "n_gpus": world,
-            "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": cls.name, "sample": sample,
-                       "note": "reference is Rust + Metal and cannot be built here; this is the scalar CPU port of its kernels"},
+            "steps": steps, "warmup": warm, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+            "scaling": "strong" if args.workload in STRONG else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "sample": sample,
+                       "note": "the reference is Rust + Metal and cannot be built here; this is the scalar CPU port of its kernels"},
             "cpu_baseline": {"value": value, "unit": cls.unit, "cores": orc.max_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": cls.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -358,9 +602,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="gqa_decode_b32", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="gqa_decode_b32", choices=WORKLOAD_NAMES)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--extras", action="store_true", help="also measure the other workloads of the path (default at N=1)")
+    ap.add_argument("--no-extras", action="store_true", help="only the selected workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiler runs)")
     ap.add_argument("--profile-steps", type=int, default=100, help="launches timed per kernel for the roofline")
     args = ap.parse_args()
