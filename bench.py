@@ -398,7 +398,7 @@ class MlaPrefill32k:
         return run, flops, "48 sampled query rows x 8 of 64 heads, full causal key ranges (sampled)"
 
 
-def make_workload(name, be, rank, world=1, dist=None):
+def make_workload(name, be, rank, world=1, dist=None, tokens=0):
     if name == "gqa_decode_b32":
         return GqaDecodeB32(be, rank)
     if name == "mla_decode_4k":
@@ -408,7 +408,14 @@ def make_workload(name, be, rank, world=1, dist=None):
     if name == "gqa_prefill_2k":
         return GqaPrefill2k(be, rank, world, dist)
     if name == "mla_prefill_32k":
-        return MlaPrefill32k(be, rank, world, dist)
+        wl = MlaPrefill32k.__new__(MlaPrefill32k)
+        if tokens:
+            wl.T = tokens  # smaller prompt for profiler captures; the name in `config` reflects it
+        wl.__init__(be, rank, world, dist)
+        if tokens:
+            wl.config["workload"] = f"mla_prefill_{tokens}"
+            wl.max_steps = 50
+        return wl
     raise KeyError(name)
 
 
@@ -520,7 +527,7 @@ def run_ours(args):
     be = CudaBackend(local_rank if world > 1 else 0)
     peaks = load_peaks()
     sampler = ClockSampler(local_rank if world > 1 else 0) if rank == 0 else None
-    wl = make_workload(args.workload, be, rank, world, dist)
+    wl = make_workload(args.workload, be, rank, world, dist, args.tokens)
     head = measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
                    with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps)
     extras = []
@@ -606,6 +613,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extras", action="store_true", help="also measure the other workloads of the path (default at N=1)")
     ap.add_argument("--no-extras", action="store_true", help="only the selected workload")
+    ap.add_argument("--tokens", type=int, default=0, help="prompt length override for mla_prefill_32k (profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiler runs)")
     ap.add_argument("--profile-steps", type=int, default=100, help="launches timed per kernel for the roofline")
     args = ap.parse_args()

@@ -1,24 +1,28 @@
 // Causal flash attention for prefill on tcgen05 / TMEM, fed by TMA.
 //
-// One CTA owns 128 query rows of one head.  Seven warps, specialised:
-//   warps 0-3  softmax + epilogue; thread r owns query row r and TMEM lane r
-//   warp 4     TMA producer for Q and the K tiles
-//   warp 5     allocates TMEM and issues every tcgen05.mma
-//   warp 6     TMA producer for the V tiles
-// Per 64-key tile:  S = Q K^T  (SS MMA, M128 N64, both operands K-major, 128-byte swizzle)
-//                   softmax in registers, P written back to TMEM as packed fp16 over its own S buffer
-//                   O += P V   (TS MMA, A = P from TMEM, B = V MN-major straight from its [key][dim] tile)
-// S is double-buffered in TMEM (columns 0-63 / 64-127, O in 128-255), so QK^T of tile j+1 is already
-// queued behind the tensor pipe while tile j is in softmax; O is rescaled lazily (only when a row
-// maximum grew by more than 2^8), so the accumulator stays in TMEM for the whole row of tiles.
-// 256 TMEM columns and <= 113 KB of shared memory per CTA: two CTAs share an SM and fill each other's
-// softmax bubbles.
+// One CTA per SM runs TWO query streams of 128 rows each against one shared ring of K/V tiles, so
+// every K/V tile is fetched once for 256 query rows and the tensor pipe always has the other
+// stream's MMAs to run while one stream is in softmax.  The two streams are either two query heads
+// of the same KV group at the same rows (GQA: identical causal structure, perfectly balanced) or
+// two consecutive 128-row tiles of one head (MHA / MLA prefill).
 //
-// Two instantiations: paged GQA prefill (head_dim 128; K/V tiles are four 16-token page boxes
-// addressed through the page table; reference kernel f16_attention_kernels.metal:153-316) and dense
-// MLA prefill over expanded heads (qk 128+64 with the rope tail shared by all heads, v 128;
-// reference kernel attention_kernels.metal:723-968 with no past, K laid out as in
-// layout_kernels.metal:148-183).
+// Twelve warps, specialised:
+//   warps 0-3   softmax + epilogue of stream 0; thread r owns query row r and TMEM lane r
+//   warps 4-7   the same for stream 1
+//   warp 8      TMA producer for Q and the K tiles
+//   warp 9      allocates TMEM and issues every tcgen05.mma
+//   warp 10     TMA producer for the V tiles            (warp 11 only pads the third warpgroup)
+// Per stream and 64-key tile:  S = Q K^T  (SS MMA, M128 N64, both operands K-major, 128-byte swizzle)
+//                              softmax in registers, P written back to TMEM as packed fp16 over its S buffer
+//                              O += P V   (TS MMA, A = P from TMEM, B = V MN-major from its [key][dim] tile)
+// TMEM: 256 columns per stream (S double-buffered in 0-63 / 64-127, O in 128-255).  O is rescaled lazily
+// (only when a row maximum grew by more than 2^8).  The K/V ring is 5 (GQA) or 3 (MLA) tiles deep,
+// enough to cover L2/HBM latency at one tile per ~1000 cycles.
+//
+// Two instantiations: paged GQA prefill (head_dim 128; a K/V tile is four 16-token page boxes addressed
+// through the page table; reference kernel f16_attention_kernels.metal:153-316) and dense MLA prefill
+// over expanded heads (qk 128+64 with the rope tail shared by all heads, v 128; reference kernel
+// attention_kernels.metal:723-968 with no past, K laid out as in layout_kernels.metal:148-183).
 #include <cuda_fp16.h>
 #include <math.h>
 
@@ -31,14 +35,15 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BN = 64;
-constexpr int NUM_THREADS = 224;
+constexpr int NUM_THREADS = 384;
 constexpr float M_INIT = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
-constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t COL_S0 = 0, COL_S1 = 64, COL_O = 128;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t STREAM_COLS = 256, COL_S0 = 0, COL_S1 = 64, COL_O = 128;
 
 struct FlashParams {
     int tokens, q_heads, kv_heads, group, batch;
+    int pair_heads;  // 1: streams are heads (2c, 2c+1) at the same rows; 0: streams are row tiles (2c, 2c+1) of one head
     const int* pages;
     const int* lens;
     int max_pages, page_size, num_pages;
@@ -60,17 +65,21 @@ __device__ __forceinline__ float softplus_ref(float v) {
 
 template <int DQK, int DV, int KS, int VS>
 struct SmemLayout {
-    static constexpr int Q_BYTES = BM * DQK * 2;
+    static constexpr int Q_BYTES = BM * DQK * 2;  // per stream
     static constexpr int K_BYTES = BN * DQK * 2;
     static constexpr int V_BYTES = BN * DV * 2;
-    static constexpr int OFF_K = Q_BYTES;
+    static constexpr int OFF_K = 2 * Q_BYTES;
     static constexpr int OFF_V = OFF_K + KS * K_BYTES;
     static constexpr int OFF_BAR = OFF_V + VS * V_BYTES;
-    static constexpr int TOTAL = OFF_BAR + 256;
+    static constexpr int TOTAL = OFF_BAR + 512;
+};
+
+struct Stream {
+    int head, q0, kt_begin, kt_end;  // key-tile range [kt_begin, kt_end); empty when the stream has no rows
 };
 
 template <int DQK, int DV, int KS, int VS, bool PAGED>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_k2, const __grid_constant__ CUtensorMap tm_v,
                      FlashParams p) {
@@ -80,28 +89,43 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint8_t* sK = smem + L::OFF_K;
     uint8_t* sV = smem + L::OFF_V;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-    uint64_t* q_full = bars;
-    uint64_t* k_full = bars + 1;
-    uint64_t* k_empty = k_full + KS;
-    uint64_t* v_full = k_empty + KS;
-    uint64_t* v_empty = v_full + VS;
-    uint64_t* s_full = v_empty + VS;  // [2]
-    uint64_t* p_full = s_full + 2;    // [2]
-    uint64_t* o_ready = p_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
+    uint64_t* q_full = bars;            // [1]
+    uint64_t* k_full = bars + 1;        // [KS]
+    uint64_t* k_empty = k_full + KS;    // [KS]
+    uint64_t* v_full = k_empty + KS;    // [VS]
+    uint64_t* v_empty = v_full + VS;    // [VS]
+    uint64_t* s_full = v_empty + VS;    // [2 streams][2 buffers]
+    uint64_t* p_full = s_full + 4;      // [2][2]
+    uint64_t* o_ready = p_full + 4;     // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int head = blockIdx.x;
-    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;  // heaviest (latest) query tiles first
     const int b = blockIdx.z;
-    const int q0 = qt * BM;
     const int past = PAGED ? p.lens[b] : 0;
     const int kv_total = past + p.tokens;
-    const int q_last = min(q0 + BM, p.tokens) - 1;
-    const int kt_end = (past + q_last + 1 + BN - 1) / BN;
-    const int lo_key = p.window > 0 ? max(0, past + q0 + 1 - p.window) : 0;
-    const int kt_begin = lo_key / BN;
-    const int n = kt_end - kt_begin;
+    const int qtile = (int)gridDim.y - 1 - (int)blockIdx.y;  // heaviest (latest) query rows first
+
+    Stream st[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        st[s].head = p.pair_heads ? 2 * (int)blockIdx.x + s : (int)blockIdx.x;
+        st[s].q0 = p.pair_heads ? qtile * BM : (2 * qtile + s) * BM;
+        if (st[s].q0 < p.tokens && st[s].head < p.q_heads) {
+            const int q_last = min(st[s].q0 + BM, p.tokens) - 1;
+            st[s].kt_end = (past + q_last + 1 + BN - 1) / BN;
+            const int lo_key = p.window > 0 ? max(0, past + st[s].q0 + 1 - p.window) : 0;
+            st[s].kt_begin = lo_key / BN;
+        } else {
+            st[s].kt_begin = st[s].kt_end = 0;
+        }
+    }
+    const bool act0 = st[0].kt_end > st[0].kt_begin, act1 = st[1].kt_end > st[1].kt_begin;
+    if (!act0 && !act1) return;
+    const int kt_lo = act0 && act1 ? min(st[0].kt_begin, st[1].kt_begin) : (act0 ? st[0].kt_begin : st[1].kt_begin);
+    const int kt_hi = act0 && act1 ? max(st[0].kt_end, st[1].kt_end) : (act0 ? st[0].kt_end : st[1].kt_end);
+    const int n = kt_hi - kt_lo;
+    // both streams of a CTA read the same KV head (pair_heads pairs lie inside one KV group)
+    const int kvh = PAGED ? st[act0 ? 0 : 1].head / p.group : st[act0 ? 0 : 1].head;
 
     if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
         if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
@@ -117,14 +141,15 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
         }
-        mbar_init(o_ready, 1);
+        mbar_init(&o_ready[0], 1);
+        mbar_init(&o_ready[1], 1);
         mbar_fence_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
@@ -133,20 +158,23 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------ Q + K producer
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
-            mbar_arrive_expect_tx(q_full, L::Q_BYTES);
+            mbar_arrive_expect_tx(q_full, (uint32_t)((act0 ? 1 : 0) + (act1 ? 1 : 0)) * L::Q_BYTES);
 #pragma unroll
-            for (int blk = 0; blk < DQK / 64; ++blk)
-                tma_load_3d(sQ + blk * BM * 128, &tm_q, blk * 64, head, b * p.tokens + q0, q_full);
+            for (int s = 0; s < 2; ++s)
+                if (st[s].kt_end > st[s].kt_begin)
+#pragma unroll
+                    for (int blk = 0; blk < DQK / 64; ++blk)
+                        tma_load_3d(sQ + s * L::Q_BYTES + blk * BM * 128, &tm_q, blk * 64, st[s].head,
+                                    b * p.tokens + st[s].q0, q_full);
         }
-        const int kvh = PAGED ? head / p.group : head;
         const int oob_row = p.num_pages * p.kv_heads * p.page_size;
         for (int j = 0; j < n; ++j) {
-            const int k0 = (kt_begin + j) * BN;
+            const int k0 = (kt_lo + j) * BN;
             const int ks = j % KS;
             int y = oob_row;
             if (PAGED && lane < 4) {
@@ -181,19 +209,18 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             tma_load_2d(dst + blk * BN * 128 + sub * 2048, &tm_k, blk * 64, ys[sub], &k_full[ks]);
                 } else {
                     // 128 no-rope dims of this head, then the 64-dim rope tail shared by every head
-                    tma_load_3d(dst, &tm_k, 0, head, k0, &k_full[ks]);
-                    tma_load_3d(dst + BN * 128, &tm_k, 64, head, k0, &k_full[ks]);
+                    tma_load_3d(dst, &tm_k, 0, kvh, k0, &k_full[ks]);
+                    tma_load_3d(dst + BN * 128, &tm_k, 64, kvh, k0, &k_full[ks]);
                     if (DQK == 192) tma_load_2d(dst + 2 * BN * 128, &tm_k2, 0, k0, &k_full[ks]);
                 }
             }
         }
-    } else if (warp == 6) {
+    } else if (warp == 10) {
         // ------------------------------------------------ V producer
         if (lane == 0) tma_prefetch_desc(&tm_v);
-        const int kvh = PAGED ? head / p.group : head;
         const int oob_row = p.num_pages * p.kv_heads * p.page_size;
         for (int j = 0; j < n; ++j) {
-            const int k0 = (kt_begin + j) * BN;
+            const int k0 = (kt_lo + j) * BN;
             const int vs = j % VS;
             int y = oob_row;
             if (PAGED && lane < 4) {
@@ -226,30 +253,39 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 } else {
 #pragma unroll
                     for (int blk = 0; blk < DV / 64; ++blk)
-                        tma_load_3d(dst + blk * BN * 128, &tm_v, blk * 64, head, k0, &v_full[vs]);
+                        tma_load_3d(dst + blk * BN * 128, &tm_v, blk * 64, kvh, k0, &v_full[vs]);
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------ MMA issuer (one thread)
         if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc_f16(BM, BN, 0, 0);
             const uint32_t idesc_pv = umma_idesc_f16(BM, DV, 0, 1);
             const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            bool ok = mbar_wait(q_full, 0);
+            // tile j of the CTA is local tile (kt_lo + j - kt_begin) of a stream, if inside its range
+            auto local = [&](int s, int j) { return kt_lo + j - st[s].kt_begin; };
+            auto active = [&](int s, int j) { return kt_lo + j >= st[s].kt_begin && kt_lo + j < st[s].kt_end; };
             auto issue_qk = [&](int j) {
                 const int ks = j % KS;
-                const uint32_t s_col = (j & 1) ? COL_S1 : COL_S0;
 #pragma unroll
-                for (int kk = 0; kk < DQK / 16; ++kk) {
-                    const uint64_t ad = umma_smem_desc(q_addr + (kk / 4) * BM * 128 + (kk % 4) * 32, 16, 1024, UMMA_SW128);
-                    const uint64_t bd =
-                        umma_smem_desc(k_addr + ks * L::K_BYTES + (kk / 4) * BN * 128 + (kk % 4) * 32, 16, 1024, UMMA_SW128);
-                    umma_ss(tbase + s_col, ad, bd, idesc_qk, kk > 0);
+                for (int s = 0; s < 2; ++s) {
+                    if (!active(s, j)) continue;
+                    const int jl = local(s, j);
+                    const uint32_t s_col = s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
+#pragma unroll
+                    for (int kk = 0; kk < DQK / 16; ++kk) {
+                        const uint64_t ad = umma_smem_desc(q_addr + s * L::Q_BYTES + (kk / 4) * BM * 128 + (kk % 4) * 32,
+                                                           16, 1024, UMMA_SW128);
+                        const uint64_t bd = umma_smem_desc(k_addr + ks * L::K_BYTES + (kk / 4) * BN * 128 + (kk % 4) * 32,
+                                                           16, 1024, UMMA_SW128);
+                        umma_ss(tbase + s_col, ad, bd, idesc_qk, kk > 0);
+                    }
+                    tc_commit(&s_full[s * 2 + (jl & 1)]);
                 }
-                tc_commit(&s_full[j & 1]);
                 tc_commit(&k_empty[ks]);
             };
+            bool ok = mbar_wait(q_full, 0);
             if (ok) ok = mbar_wait(&k_full[0], 0);
             if (ok) {
                 tc_fence_after();
@@ -262,131 +298,145 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     tc_fence_after();
                     issue_qk(j + 1);
                 }
-                ok = mbar_wait(&p_full[j & 1], ((uint32_t)(j >> 1)) & 1u);
-                if (!ok) break;
                 const int vs = j % VS;
                 ok = mbar_wait(&v_full[vs], ((uint32_t)(j / VS)) & 1u);
                 if (!ok) break;
-                tc_fence_after();
-                const uint32_t p_col = (j & 1) ? COL_S1 : COL_S0;
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t bd = umma_smem_desc(v_addr + vs * L::V_BYTES + kk * 2048, BN * 128, 1024, UMMA_SW128);
-                    umma_ts(tbase + COL_O, tbase + p_col + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                for (int s = 0; s < 2; ++s) {
+                    if (!active(s, j)) continue;
+                    const int jl = local(s, j);
+                    ok = mbar_wait(&p_full[s * 2 + (jl & 1)], ((uint32_t)(jl >> 1)) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t p_col = s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; ++kk) {
+                        const uint64_t bd = umma_smem_desc(v_addr + vs * L::V_BYTES + kk * 2048, BN * 128, 1024, UMMA_SW128);
+                        umma_ts(tbase + s * STREAM_COLS + COL_O, tbase + p_col + kk * 8, bd, idesc_pv,
+                                (jl > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&o_ready[s]);
                 }
+                if (!ok) break;
                 tc_commit(&v_empty[vs]);
-                tc_commit(o_ready);
             }
             if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
         }
-    } else {
-        // ------------------------------------------------ softmax + epilogue: thread = query row
-        const int r = tid;
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        const int qpos = past + q0 + r;
-        float m_used = M_INIT, l = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n; ++j) {
-            const int k0 = (kt_begin + j) * BN;
-            const uint32_t buf_col = (j & 1) ? COL_S1 : COL_S0;
-            if (!mbar_wait(&s_full[j & 1], ((uint32_t)(j >> 1)) & 1u)) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            uint32_t sraw[BN];
-            tmem_ld32(tbase + lane_addr + buf_col, sraw);
-            tmem_ld32(tbase + lane_addr + buf_col + 32, sraw + 32);
-            tc_wait_ld();
-            float x[BN];
-#pragma unroll
-            for (int i = 0; i < BN; ++i) x[i] = __uint_as_float(sraw[i]) * p.scale_log2;
-            const bool need_mask = (k0 + BN - 1 > past + q0) || (k0 + BN > kv_total) ||
-                                   (p.window > 0 && k0 < past + q0 + BM - p.window);
-            if (need_mask) {
-                const int first = p.window > 0 ? qpos + 1 - p.window : 0;
-#pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const int key = k0 + i;
-                    if (key > qpos || key < first || key >= kv_total) x[i] = -INFINITY;
+    } else if (warp < 8) {
+        // ------------------------------------------------ softmax + epilogue: thread = query row of its stream
+        const int s = warp >> 2;
+        const Stream me = st[s];
+        const int n_s = me.kt_end - me.kt_begin;
+        if (n_s > 0) {
+            const int r = tid & 127;
+            const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+            const uint32_t col0 = tbase + lane_addr + s * STREAM_COLS;
+            const int qpos = past + me.q0 + r;
+            float m_used = M_INIT, l = 0.f;
+            bool ok = true;
+            for (int j = 0; j < n_s; ++j) {
+                const int k0 = (me.kt_begin + j) * BN;
+                const uint32_t buf_col = (j & 1) ? COL_S1 : COL_S0;
+                if (!mbar_wait(&s_full[s * 2 + (j & 1)], ((uint32_t)(j >> 1)) & 1u)) {
+                    ok = false;
+                    break;
                 }
-            }
-            float mx = x[0];
-#pragma unroll
-            for (int i = 1; i < BN; ++i) mx = fmaxf(mx, x[i]);
-            const float m_cand = fmaxf(m_used, mx);
-            if (j == 0) {
-                m_used = m_cand;
-            } else {
-                const bool need = (m_cand - m_used) > RESCALE_THRESHOLD;
-                if (__any_sync(0xffffffffu, need)) {
-                    const float alpha = ex2_approx(m_used - m_cand);
-                    m_used = m_cand;
-                    l *= alpha;
-                    if (!mbar_wait(o_ready, ((uint32_t)(j - 1)) & 1u)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < DV / 32; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(tbase + lane_addr + COL_O + c * 32, o);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tbase + lane_addr + COL_O + c * 32, o);
-                    }
-                    tc_wait_st();
-                }
-            }
-            float sum = 0.f;
-            uint32_t packed[BN / 2];
-#pragma unroll
-            for (int i = 0; i < BN; i += 2) {
-                const float p0 = ex2_approx(x[i] - m_used), p1 = ex2_approx(x[i + 1] - m_used);
-                sum += p0 + p1;
-                packed[i / 2] = pack_half2(p0, p1);
-            }
-            l += sum;
-            tmem_st32(tbase + lane_addr + buf_col, packed);
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(&p_full[j & 1]);
-        }
-        if (ok && !mbar_wait(o_ready, ((uint32_t)(n - 1)) & 1u)) ok = false;
-        if (!ok) {
-            if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
-        } else {
-            tc_fence_after();
-            const bool valid = (q0 + r) < p.tokens;
-            float gain = 1.0f / l;
-            if (p.gate && valid) gain *= softplus_ref(p.gate[((long long)b * p.tokens + q0 + r) * p.q_heads + head]);
-            const long long obase = (long long)b * p.o_bs + (long long)(q0 + r) * p.o_ts + (long long)head * p.o_hs;
-#pragma unroll
-            for (int c = 0; c < DV / 32; ++c) {
-                uint32_t o[32];
-                tmem_ld32(tbase + lane_addr + COL_O + c * 32, o);
+                tc_fence_after();
+                uint32_t sraw[BN];
+                tmem_ld32(col0 + buf_col, sraw);
+                tmem_ld32(col0 + buf_col + 32, sraw + 32);
                 tc_wait_ld();
-                if (valid) {
-                    if (p.out_f16) {
-                        __half* dst = reinterpret_cast<__half*>(p.out) + obase + c * 32;
+                const bool need_mask = (k0 + BN - 1 > past + me.q0) || (k0 + BN > kv_total) ||
+                                       (p.window > 0 && k0 < past + me.q0 + BM - p.window);
+                if (need_mask) {
+                    const int first = p.window > 0 ? qpos + 1 - p.window : 0;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 v;
-                            v.x = pack_half2(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain);
-                            v.y = pack_half2(__uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
-                            v.z = pack_half2(__uint_as_float(o[i + 4]) * gain, __uint_as_float(o[i + 5]) * gain);
-                            v.w = pack_half2(__uint_as_float(o[i + 6]) * gain, __uint_as_float(o[i + 7]) * gain);
-                            *reinterpret_cast<uint4*>(dst + i) = v;
+                    for (int i = 0; i < BN; ++i) {
+                        const int key = k0 + i;
+                        if (key > qpos || key < first || key >= kv_total) sraw[i] = 0xff800000u;  // -inf
+                    }
+                }
+                float mx = __uint_as_float(sraw[0]);
+#pragma unroll
+                for (int i = 1; i < BN; ++i) mx = fmaxf(mx, __uint_as_float(sraw[i]));
+                const float m_cand = fmaxf(m_used, mx * p.scale_log2);  // scale > 0, so max and scale commute
+                if (j == 0) {
+                    m_used = m_cand;
+                } else {
+                    const bool need = (m_cand - m_used) > RESCALE_THRESHOLD;
+                    if (__any_sync(0xffffffffu, need)) {
+                        const float alpha = ex2_approx(m_used - m_cand);
+                        m_used = m_cand;
+                        l *= alpha;
+                        if (!mbar_wait(&o_ready[s], ((uint32_t)(j - 1)) & 1u)) {
+                            ok = false;
+                            break;
                         }
-                    } else {
-                        float* dst = reinterpret_cast<float*>(p.out) + obase + c * 32;
+                        tc_fence_after();
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<float4*>(dst + i) =
-                                make_float4(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain,
-                                            __uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                        for (int c = 0; c < DV / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_ld32(col0 + COL_O + c * 32, o);
+                            tc_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(col0 + COL_O + c * 32, o);
+                        }
+                        tc_wait_st();
+                    }
+                }
+                float sum = 0.f;
+                uint32_t packed[BN / 2];
+                const float neg_m = -m_used;
+#pragma unroll
+                for (int i = 0; i < BN; i += 2) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[i]), p.scale_log2, neg_m));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[i + 1]), p.scale_log2, neg_m));
+                    sum += p0 + p1;
+                    packed[i / 2] = pack_half2(p0, p1);
+                }
+                l += sum;
+                tmem_st32(col0 + buf_col, packed);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(&p_full[s * 2 + (j & 1)]);
+            }
+            if (ok && !mbar_wait(&o_ready[s], ((uint32_t)(n_s - 1)) & 1u)) ok = false;
+            if (!ok) {
+                if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+            } else {
+                tc_fence_after();
+                const bool valid = (me.q0 + r) < p.tokens;
+                float gain = 1.0f / l;
+                if (p.gate && valid)
+                    gain *= softplus_ref(p.gate[((long long)b * p.tokens + me.q0 + r) * p.q_heads + me.head]);
+                const long long obase =
+                    (long long)b * p.o_bs + (long long)(me.q0 + r) * p.o_ts + (long long)me.head * p.o_hs;
+#pragma unroll
+                for (int c = 0; c < DV / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(col0 + COL_O + c * 32, o);
+                    tc_wait_ld();
+                    if (valid) {
+                        if (p.out_f16) {
+                            __half* dst = reinterpret_cast<__half*>(p.out) + obase + c * 32;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 v;
+                                v.x = pack_half2(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain);
+                                v.y = pack_half2(__uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                                v.z = pack_half2(__uint_as_float(o[i + 4]) * gain, __uint_as_float(o[i + 5]) * gain);
+                                v.w = pack_half2(__uint_as_float(o[i + 6]) * gain, __uint_as_float(o[i + 7]) * gain);
+                                *reinterpret_cast<uint4*>(dst + i) = v;
+                            }
+                        } else {
+                            float* dst = reinterpret_cast<float*>(p.out) + obase + c * 32;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)
+                                *reinterpret_cast<float4*>(dst + i) =
+                                    make_float4(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain,
+                                                __uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                        }
                     }
                 }
             }
@@ -394,19 +444,21 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tbase, TMEM_COLS);
+    if (warp == 9) tmem_dealloc(tbase, TMEM_COLS);
 }
 
 template <int DQK, int DV, int KS, int VS, bool PAGED>
 int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tk2,
                  const CUtensorMap& tv, const FlashParams& p, const char* name) {
     using L = SmemLayout<DQK, DV, KS, VS>;
+    static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA per SM");
     auto kernel = flash_prefill_kernel<DQK, DV, KS, VS, PAGED>;
     if (!(ctx->func_attr_done & attr_bit)) {
         INF_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         ctx->func_attr_done |= attr_bit;
     }
-    dim3 grid(p.q_heads, (p.tokens + BM - 1) / BM, p.batch);
+    const int q_tiles = (p.tokens + BM - 1) / BM;
+    dim3 grid(p.pair_heads ? p.q_heads / 2 : p.q_heads, p.pair_heads ? q_tiles : (q_tiles + 1) / 2, p.batch);
     {
         inf_prof_scope prof(ctx, name);
         kernel<<<grid, NUM_THREADS, L::TOTAL, ctx->stream>>>(tq, tk, tk2, tv, p);
@@ -457,6 +509,7 @@ int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* p
     p.q_heads = q_heads;
     p.kv_heads = pool->kv_heads;
     p.group = q_heads / pool->kv_heads;
+    p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
     p.batch = table->batch;
     p.pages = table->pages;
     p.lens = table->lens;
@@ -472,7 +525,7 @@ int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* p
     p.o_ts = (long long)q_heads * 128;
     p.o_bs = (long long)tokens * q_heads * 128;
     p.status = ctx->status;
-    return launch_flash<128, 128, 2, 2, true>(ctx, 2u, tq, tk, tk, tv, p, "flash_prefill_gqa_kernel");
+    return launch_flash<128, 128, 5, 5, true>(ctx, 2u, tq, tk, tk, tv, p, "flash_prefill_gqa_kernel");
 }
 
 extern "C" int32_t inf_gqa_prefill_paged(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
@@ -535,6 +588,7 @@ extern "C" int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q
     p.q_heads = heads;
     p.kv_heads = heads;
     p.group = 1;
+    p.pair_heads = 0;
     p.batch = 1;
     p.window = 0;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -544,6 +598,6 @@ extern "C" int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q
     p.o_hs = o_hs;
     p.o_bs = 0;
     p.status = ctx->status;
-    if (rope_dim) return launch_flash<192, 128, 2, 1, false>(ctx, 4u, tq, tk, tk2, tv, p, "flash_prefill_mla_kernel");
-    return launch_flash<128, 128, 2, 2, false>(ctx, 8u, tq, tk, tk2, tv, p, "flash_prefill_mha_kernel");
+    if (rope_dim) return launch_flash<192, 128, 3, 3, false>(ctx, 4u, tq, tk, tk2, tv, p, "flash_prefill_mla_kernel");
+    return launch_flash<128, 128, 5, 5, false>(ctx, 8u, tq, tk, tk2, tv, p, "flash_prefill_mha_kernel");
 }
