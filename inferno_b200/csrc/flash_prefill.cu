@@ -259,27 +259,32 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
     } else if (warp == 9) {
         // ------------------------------------------------ MMA issuer (one thread)
+        // Everything this thread does between two MMAs delays the tensor pipe, so descriptors are kept as
+        // precomputed 32-bit words that only receive compile-time offsets, and ring indices and phases are
+        // carried incrementally instead of being recomputed with divisions.
         if (lane == 0) {
-            const uint32_t idesc_qk = umma_idesc_f16(BM, BN, 0, 0);
-            const uint32_t idesc_pv = umma_idesc_f16(BM, DV, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            // tile j of the CTA is local tile (kt_lo + j - kt_begin) of a stream, if inside its range
-            auto local = [&](int s, int j) { return kt_lo + j - st[s].kt_begin; };
-            auto active = [&](int s, int j) { return kt_lo + j >= st[s].kt_begin && kt_lo + j < st[s].kt_end; };
-            auto issue_qk = [&](int j) {
-                const int ks = j % KS;
+            constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, 0, 0);
+            constexpr uint32_t idesc_pv = umma_idesc_f16(BM, DV, 0, 1);
+            constexpr uint32_t hi_k = umma_desc_hi(1024, UMMA_SW128);
+            const uint32_t q_lo[2] = {umma_desc_lo(smem_u32(sQ), 16), umma_desc_lo(smem_u32(sQ) + L::Q_BYTES, 16)};
+            const uint32_t k_lo0 = umma_desc_lo(smem_u32(sK), 16);
+            const uint32_t v_lo0 = umma_desc_lo(smem_u32(sV), BN * 128);
+            // per stream: first CTA tile index and tile count, so that "active" and "local index" are cheap
+            const int first[2] = {st[0].kt_begin - kt_lo, st[1].kt_begin - kt_lo};
+            const int count[2] = {st[0].kt_end - st[0].kt_begin, st[1].kt_end - st[1].kt_begin};
+            auto issue_qk = [&](int j, int ks) {
+                const uint32_t k_lo = k_lo0 + (uint32_t)ks * (L::K_BYTES >> 4);
 #pragma unroll
                 for (int s = 0; s < 2; ++s) {
-                    if (!active(s, j)) continue;
-                    const int jl = local(s, j);
-                    const uint32_t s_col = s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
+                    const int jl = j - first[s];
+                    if (jl < 0 || jl >= count[s]) continue;
+                    const uint32_t s_col = tbase + s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
 #pragma unroll
                     for (int kk = 0; kk < DQK / 16; ++kk) {
-                        const uint64_t ad = umma_smem_desc(q_addr + s * L::Q_BYTES + (kk / 4) * BM * 128 + (kk % 4) * 32,
-                                                           16, 1024, UMMA_SW128);
-                        const uint64_t bd = umma_smem_desc(k_addr + ks * L::K_BYTES + (kk / 4) * BN * 128 + (kk % 4) * 32,
-                                                           16, 1024, UMMA_SW128);
-                        umma_ss(tbase + s_col, ad, bd, idesc_qk, kk > 0);
+                        const uint32_t a_off = ((kk / 4) * BM * 128 + (kk % 4) * 32) >> 4;
+                        const uint32_t b_off = ((kk / 4) * BN * 128 + (kk % 4) * 32) >> 4;
+                        umma_ss(s_col, umma_desc_pack(q_lo[s] + a_off, hi_k), umma_desc_pack(k_lo + b_off, hi_k),
+                                idesc_qk, kk > 0 ? 1u : 0u);
                     }
                     tc_commit(&s_full[s * 2 + (jl & 1)]);
                 }
@@ -289,36 +294,53 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (ok) ok = mbar_wait(&k_full[0], 0);
             if (ok) {
                 tc_fence_after();
-                issue_qk(0);
+                issue_qk(0, 0);
             }
+            int ks_next = KS > 1 ? 1 : 0;
+            uint32_t k_phase = KS > 1 ? 0u : 1u;  // phase of the stage that tile j+1 lands in
+            int vs = 0;
+            uint32_t v_phase = 0u;
             for (int j = 0; ok && j < n; ++j) {
                 if (j + 1 < n) {
-                    ok = mbar_wait(&k_full[(j + 1) % KS], ((uint32_t)((j + 1) / KS)) & 1u);
+                    ok = mbar_wait(&k_full[ks_next], k_phase);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_qk(j + 1);
+                    issue_qk(j + 1, ks_next);
+                    if (++ks_next == KS) {
+                        ks_next = 0;
+                        k_phase ^= 1u;
+                    }
                 }
-                const int vs = j % VS;
-                ok = mbar_wait(&v_full[vs], ((uint32_t)(j / VS)) & 1u);
+                ok = mbar_wait(&v_full[vs], v_phase);
                 if (!ok) break;
+                const uint32_t v_lo = v_lo0 + (uint32_t)vs * (L::V_BYTES >> 4);
 #pragma unroll
                 for (int s = 0; s < 2; ++s) {
-                    if (!active(s, j)) continue;
-                    const int jl = local(s, j);
+                    const int jl = j - first[s];
+                    if (jl < 0 || jl >= count[s]) continue;
                     ok = mbar_wait(&p_full[s * 2 + (jl & 1)], ((uint32_t)(jl >> 1)) & 1u);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t p_col = s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
+                    const uint32_t o_col = tbase + s * STREAM_COLS + COL_O;
+                    const uint32_t p_col = tbase + s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
+                    if (jl == 0) {
 #pragma unroll
-                    for (int kk = 0; kk < BN / 16; ++kk) {
-                        const uint64_t bd = umma_smem_desc(v_addr + vs * L::V_BYTES + kk * 2048, BN * 128, 1024, UMMA_SW128);
-                        umma_ts(tbase + s * STREAM_COLS + COL_O, tbase + p_col + kk * 8, bd, idesc_pv,
-                                (jl > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < BN / 16; ++kk)
+                            umma_ts(o_col, p_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv,
+                                    kk > 0 ? 1u : 0u);
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < BN / 16; ++kk)
+                            umma_ts(o_col, p_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv, 1u);
                     }
                     tc_commit(&o_ready[s]);
                 }
                 if (!ok) break;
                 tc_commit(&v_empty[vs]);
+                if (++vs == VS) {
+                    vs = 0;
+                    v_phase ^= 1u;
+                }
             }
             if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
         }
@@ -356,9 +378,14 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         if (key > qpos || key < first || key >= kv_total) sraw[i] = 0xff800000u;  // -inf
                     }
                 }
-                float mx = __uint_as_float(sraw[0]);
+                // row maximum: eight independent chains, then a short tree (keeps the dependent path short)
+                float mxs[8];
 #pragma unroll
-                for (int i = 1; i < BN; ++i) mx = fmaxf(mx, __uint_as_float(sraw[i]));
+                for (int i = 0; i < 8; ++i) mxs[i] = __uint_as_float(sraw[i]);
+#pragma unroll
+                for (int i = 8; i < BN; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(sraw[i]));
+                const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                                       fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
                 const float m_cand = fmaxf(m_used, mx * p.scale_log2);  // scale > 0, so max and scale commute
                 if (j == 0) {
                     m_used = m_cand;
@@ -385,18 +412,22 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         tc_wait_st();
                     }
                 }
-                float sum = 0.f;
-                uint32_t packed[BN / 2];
+                // exponentials in two halves of 32 keys; each half of P is stored as soon as it is packed
                 const float neg_m = -m_used;
+                float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int i = 0; i < BN; i += 2) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[i]), p.scale_log2, neg_m));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[i + 1]), p.scale_log2, neg_m));
-                    sum += p0 + p1;
-                    packed[i / 2] = pack_half2(p0, p1);
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[half * 32 + i]), p.scale_log2, neg_m));
+                        const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[half * 32 + i + 1]), p.scale_log2, neg_m));
+                        sums[(i >> 1) & 3] += p0 + p1;
+                        packed[i / 2] = pack_half2(p0, p1);
+                    }
+                    tmem_st16(col0 + buf_col + half * 16, packed);
                 }
-                l += sum;
-                tmem_st32(col0 + buf_col, packed);
+                l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&p_full[s * 2 + (j & 1)]);

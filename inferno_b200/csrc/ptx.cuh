@@ -137,6 +137,21 @@ __host__ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint
 }
 constexpr uint32_t UMMA_SW128 = 2;
 
+// The same descriptor split into its two 32-bit words, for issue loops that only ever change the
+// start address: lo = address and LBO, hi = SBO, version and swizzle mode.  Adding (bytes >> 4) to
+// `lo` moves the start address (shared memory is < 256 KB, so the 14-bit field cannot overflow).
+__host__ __device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes, uint32_t layout) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | ((layout & 7u) << 29);
+}
+__device__ __forceinline__ uint64_t umma_desc_pack(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // Instruction descriptor for kind::f16 with fp16 A/B and fp32 accumulation.
 //   a_mn / b_mn: 0 = K-major operand, 1 = MN-major operand.
 __host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t M, uint32_t N, uint32_t a_mn, uint32_t b_mn) {
