@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libinferno_attn.so")
+LIB_PATH = os.environ.get("INFERNO_ATTN_LIB") or os.path.join(_HERE, "libinferno_attn.so")  # env: an alternative build
 
 INF_OK = 0
 INF_UNSUPPORTED = 1
