@@ -287,7 +287,7 @@ class GqaPrefill2k:
             v = torch.randn((1, self.T, self.hkv_local, self.D), generator=gd, device=be.device, dtype=torch.float16)
             self.sets.append((pool, table, q, k, v))
         self.out = torch.empty((1, self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device)
-        self.gathered = torch.empty((world, self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device) if world > 1 else None
+        self.gathered = torch.empty((world * self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device) if world > 1 else None
         q, k, v = self.sets[0][2:]
         self.hq, self.hk, self.hv = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
         self.hout = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
@@ -309,7 +309,7 @@ class GqaPrefill2k:
         q16 = self.be.rope_append_gqa(q, k, v, self.rope, pool, table)
         self.be.gqa_prefill_paged(q16, pool, table, out=self.out)
         if self.world > 1:
-            self.dist.all_gather_into_tensor(self.gathered, self.out)
+            self.dist.all_gather_into_tensor(self.gathered, self.out.view(self.T, self.hq_local, self.D))
 
     def step_e2e(self):
         pool, table, q, k, v = self.sets[self.i % self.N_SETS]
@@ -359,7 +359,7 @@ class MlaPrefill32k:
         self.kn = torch.randn((self.T, hl, 128), generator=gd, device=be.device, dtype=torch.float16)
         self.kr = torch.randn((self.T, 64), generator=gd, device=be.device, dtype=torch.float16)
         self.v = torch.randn((self.T, hl, 128), generator=gd, device=be.device, dtype=torch.float16)
-        self.gathered = torch.empty((world, self.T, hl, 128), dtype=torch.float16, device=be.device) if world > 1 else None
+        self.gathered = torch.empty((world * self.T, hl, 128), dtype=torch.float16, device=be.device) if world > 1 else None
         self.host = [t.cpu().pin_memory() for t in (self.q, self.kn, self.kr, self.v)]
         self.hout = torch.empty((self.T, hl, 128), dtype=torch.float16).pin_memory()
         self.scale = 1.0 / float(np.sqrt(192.0))

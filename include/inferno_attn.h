@@ -125,6 +125,31 @@ typedef struct inf_page_table {
     const int32_t* host_lens;  /* optional host copy of lens  */
 } inf_page_table;
 
+/* ---- host-side page bookkeeping (no device work) --------------------------------------------- */
+/* The logical-token -> (physical page, offset) map of the reference's PagedKvCache
+ * (crates/cache/src/paged.rs:40-72: token_location, append_prefill :176, append_decode :185,
+ * page_stats :135) for many sequences over one shared pool.  Pages come from a free list; the arrays
+ * returned by inf_paged_index_arrays are what a caller uploads as inf_page_table.pages / .lens (and may
+ * pass as the host mirrors).  Checkpoint / restore is the paged form of checkpoint_laguna_f16_kv_cache /
+ * restore_laguna_f16_kv_cache_checkpoint (backend.rs:1336-1348): pages are immutable once full, so a
+ * checkpoint is a remembered length and restoring frees the pages mapped since. */
+typedef struct inf_paged_index inf_paged_index;
+int32_t inf_paged_index_create(int32_t num_pages, int32_t page_size, int32_t max_seqs, int32_t max_pages_per_seq,
+                               inf_paged_index** out);
+int32_t inf_paged_index_destroy(inf_paged_index* index);
+const char* inf_paged_index_last_error(inf_paged_index* index);
+int32_t inf_paged_index_append(inf_paged_index* index, int32_t seq, int32_t tokens, int32_t* start_position,
+                               int32_t* allocated_pages);
+int32_t inf_paged_index_locate(inf_paged_index* index, int32_t seq, int32_t token, int32_t* page, int32_t* offset);
+int32_t inf_paged_index_len(inf_paged_index* index, int32_t seq);
+int32_t inf_paged_index_page_count(inf_paged_index* index, int32_t seq);
+int32_t inf_paged_index_free_pages(inf_paged_index* index);
+int32_t inf_paged_index_release(inf_paged_index* index, int32_t seq);
+int32_t inf_paged_index_checkpoint(inf_paged_index* index, int32_t seq);
+int32_t inf_paged_index_restore(inf_paged_index* index, int32_t seq);
+int32_t inf_paged_index_arrays(inf_paged_index* index, const int32_t** pages, const int32_t** lens,
+                               int32_t* max_seqs, int32_t* max_pages);
+
 /* ---- RoPE and KV append ----------------------------------------------------------- */
 /* laguna_qk_rms_norm_rope_pair_device (backend.rs:1252; kernel rope_kernels.metal:167):
  * per-head RMSNorm (weight NULL = no norm) then half-split RoPE, f32 in / f32 out.
@@ -231,6 +256,16 @@ int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q_ts, int64_
                                int64_t v_ts, int64_t v_hs, int32_t tokens, int32_t heads, int32_t nope_dim,
                                int32_t rope_dim, int32_t v_dim, float scale, void* out, int64_t o_ts, int64_t o_hs,
                                int32_t out_dtype);
+
+/* paged_decode_attention_resident_device (backend.rs:1966; kernel attention_kernels.metal:339-457): MHA decode
+ * over the GLM expanded layout, fp16 cache [page_count][batch][heads][page_size][dim] in identity page
+ * order (page = key / page_size), plus one current token given in f32.  q, cur_k [batch, heads, head_dim],
+ * cur_v [batch, heads, value_dim]; out f32 [batch, heads, value_dim].  head_dim and value_dim are
+ * multiples of 32 up to 256.  Scale is 1/sqrt(head_dim). */
+int32_t inf_paged_decode_attention_resident(inf_ctx* ctx, const float* q, const void* paged_k_f16, const float* cur_k,
+                                            const void* paged_v_f16, const float* cur_v, int32_t batch, int32_t heads,
+                                            int32_t past_tokens, int32_t page_size, int32_t head_dim,
+                                            int32_t value_dim, float* out);
 
 /* paged_kv_contiguous_device (backend.rs:2040; kernel layout_kernels.metal:205): gather logical rows
  * of one pool out of its pages: out fp16 [batch][kv_heads][tokens][head_dim]. */

@@ -277,6 +277,17 @@ class CudaBackend:
             dn, dr, dv, scale, _ptr(out), out.stride(0), out.stride(1), dt))
         return out if ok else None
 
+    def paged_decode_attention_resident_device(self, q, paged_k, cur_k, paged_v, cur_v, past_tokens: int, page_size: int):
+        """paged_decode_attention_resident_device (backend.rs:1966): GLM MHA decode, q/cur_k [B,H,D] f32,
+        cur_v [B,H,Dv] f32, caches fp16 [pages,B,H,P,D] / [pages,B,H,P,Dv] in identity page order."""
+        B, H, D = q.shape
+        Dv = cur_v.shape[-1]
+        out = torch.empty((B, H, Dv), dtype=torch.float32, device=self.device)
+        ok = self._check(self._lib.inf_paged_decode_attention_resident(
+            self._ctx, _ptr(q), _ptr(paged_k) if paged_k is not None else None, _ptr(cur_k),
+            _ptr(paged_v) if paged_v is not None else None, _ptr(cur_v), B, H, past_tokens, page_size, D, Dv, _ptr(out)))
+        return out if ok else None
+
     def paged_kv_contiguous_device(self, which: torch.Tensor, pool: KvPool, table: PageTable, tokens: int):
         """paged_kv_contiguous_device (backend.rs:2040): gather [batch, kv_heads, tokens, head_dim] out of the pages."""
         B = table.desc.batch

@@ -39,6 +39,7 @@ struct DecodeParams {
     const int* lens;
     int max_pages, q_heads, kv_heads, group, page_size, num_pages;
     int chunk, window;
+    int len_add;  // added to lens[b]: lets a caller that counts cached rows before the current token reuse its table
     float scale_log2;
     float* part_acc;
     float* part_ml;
@@ -74,7 +75,7 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
 
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kv_len = p.lens[b];
+    const int kv_len = p.lens[b] + p.len_add;
     if (kv_len <= 0) return;
     const int win_start = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
     const int first_chunk = win_start / p.chunk;
@@ -326,9 +327,9 @@ template <typename OutT>
 __global__ void __launch_bounds__(D)
 gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, const float* __restrict__ gate, OutT* __restrict__ out,
-                          int q_heads, int max_chunks, int chunk, int window) {
+                          int q_heads, int max_chunks, int chunk, int window, int len_add) {
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-    const int kv_len = lens[b];
+    const int kv_len = lens[b] + len_add;
     const long long orow = ((long long)b * q_heads + h) * D + d;
     if (kv_len <= 0) {
         out[orow] = OutT(0.f);
@@ -356,7 +357,7 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
 
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
-                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes);
+                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add);
 
 extern "C" size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t max_len,
                                                  int32_t split_chunk) {
@@ -368,7 +369,7 @@ extern "C" size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads,
 // Shared by the allocating entry point below and by callers that bring their own scratch.
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
-                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes) {
+                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add) {
     if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "gqa_decode: null pointer");
     if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "gqa_decode: pool has no storage");
     if (pool->head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: head_dim must be 128, got %d", pool->head_dim);
@@ -385,11 +386,11 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     if (sliding_window < 0) return inf_fail(ctx, INF_E_CONFIG, "gqa_decode: sliding_window must be >= 0");
     if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
         return inf_fail(ctx, INF_E_DTYPE, "gqa_decode: output dtype must be f32 or f16");
-    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, 0, "gqa_decode");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, len_add, "gqa_decode");
     if (rc != INF_OK) return rc;
     if (table->host_lens)
         for (int b = 0; b < table->batch; ++b)
-            if (table->host_lens[b] > max_len)
+            if (table->host_lens[b] + len_add > max_len)
                 return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: sequence %d length %d exceeds max_len %d", b,
                                 table->host_lens[b], max_len);
     // with a window only ceil(window/chunk)+1 chunks can be visible
@@ -421,6 +422,7 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     p.num_pages = pool->num_pages;
     p.chunk = split_chunk;
     p.window = sliding_window;
+    p.len_add = len_add;
     p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf((float)D)) * 1.4426950408889634f;
     p.part_acc = (float*)scratch;
     p.part_ml = p.part_acc + (size_t)table->batch * max_chunks * q_heads * D;
@@ -443,11 +445,11 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     if (out_dtype == INF_DTYPE_F32)
         gqa_decode_combine_kernel<float><<<cgrid, D, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens, gate,
                                                                         (float*)out, q_heads, max_chunks, split_chunk,
-                                                                        sliding_window);
+                                                                        sliding_window, len_add);
     else
         gqa_decode_combine_kernel<__half><<<cgrid, D, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens, gate,
                                                                          (__half*)out, q_heads, max_chunks,
-                                                                         split_chunk, sliding_window);
+                                                                         split_chunk, sliding_window, len_add);
     INF_LAUNCH_CHECK(ctx, "gqa_decode_combine_kernel");
     return INF_OK;
 }
@@ -463,7 +465,7 @@ extern "C" int32_t inf_gqa_decode_paged(inf_ctx* ctx, const void* q_f16, const i
     int rc = inf_ensure_workspace(ctx, need);
     if (rc != INF_OK) return rc;
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
-                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes);
+                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -523,5 +525,5 @@ extern "C" int32_t inf_gqa_decode_paged_static(inf_ctx* ctx, const void* q_f16, 
     // by the partial kernel of the same call first.
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
                                  out, out_dtype, g_static_scratch_ptr[ctx->device],
-                                 (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES);
+                                 (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES, 0);
 }

@@ -94,6 +94,19 @@ SIGNATURES = {
     "inf_mla_prefill_causal": (_I, [_P, _P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P, _L,
                                     _L, _I]),
     "inf_linearize_paged": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _P]),
+    "inf_paged_decode_attention_resident": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "inf_paged_index_create": (_I, [_I, _I, _I, _I, C.POINTER(_P)]),
+    "inf_paged_index_destroy": (_I, [_P]),
+    "inf_paged_index_last_error": (C.c_char_p, [_P]),
+    "inf_paged_index_append": (_I, [_P, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
+    "inf_paged_index_locate": (_I, [_P, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
+    "inf_paged_index_len": (_I, [_P, _I]),
+    "inf_paged_index_page_count": (_I, [_P, _I]),
+    "inf_paged_index_free_pages": (_I, [_P]),
+    "inf_paged_index_release": (_I, [_P, _I]),
+    "inf_paged_index_checkpoint": (_I, [_P, _I]),
+    "inf_paged_index_restore": (_I, [_P, _I]),
+    "inf_paged_index_arrays": (_I, [_P, C.POINTER(_P), C.POINTER(_P), C.POINTER(_I), C.POINTER(_I)]),
 }
 
 _lib = None
