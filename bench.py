@@ -138,6 +138,7 @@ class GqaDecodeB32:
         self.hq, self.hk, self.hv = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
         self.hout = torch.empty((self.B, self.Hq, self.D), dtype=torch.float32).pin_memory()
         self.max_len = int(self.lens.max())
+        self.i = 0
         self.units_per_step = float(self.lens.astype(np.int64).sum()) * self.Hkv * self.D * 2 * 2  # KV bytes
         self.h2d = sum(t.numel() * t.element_size() for t in (self.hq, self.hk, self.hv))
         self.d2h = self.hout.numel() * 4
@@ -223,6 +224,7 @@ class MlaDecode:
         self.hout = torch.empty(self.out.shape, dtype=torch.float32).pin_memory()
         self.scale = 1.0 / float(np.sqrt(192.0))
         self.i = 0
+        self.n_variants = self.n_caches
         self.units_per_step = float(ctx_len) * row_bytes
         self.flops_per_step = 2.0 * self.H * (self.L + self.R + self.L) * ctx_len
         self.h2d = self.hq.numel() * 2 + self.hx.numel() * 4
@@ -292,6 +294,7 @@ class GqaPrefill2k:
         self.hq, self.hk, self.hv = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
         self.hout = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
         self.i = 0
+        self.n_variants = self.N_SETS
         total_flops = 4.0 * self.D * self.Hq * self.T * (self.T + 1) / 2
         self.units_per_step = total_flops / world  # per rank; summed over ranks by the harness
         self.h2d = sum(t.numel() * 2 for t in (self.hq, self.hk, self.hv))
@@ -312,7 +315,7 @@ class GqaPrefill2k:
             self.dist.all_gather_into_tensor(self.gathered, self.out.view(self.T, self.hq_local, self.D))
 
     def step_e2e(self):
-        pool, table, q, k, v = self.sets[self.i % self.N_SETS]
+        pool, table, q, k, v = self.sets[self.i % self.N_SETS]  # the same set step() is about to use
         q.copy_(self.hq, non_blocking=True)
         k.copy_(self.hk, non_blocking=True)
         v.copy_(self.hv, non_blocking=True)
@@ -368,6 +371,7 @@ class MlaPrefill32k:
         self.h2d = sum(t.numel() * 2 for t in self.host)
         self.d2h = self.hout.numel() * 2
         self.out = None
+        self.i = 0
         self.config = {"workload": self.name, "tokens": self.T, "heads": self.H, "qk_dim": 192, "v_dim": 128,
                        "causal": True, "flops_per_step": total_flops,
                        "l2": "inputs larger than L2 (2.4 GB of Q/K/V)", "sharding": "heads" if world > 1 else "none",
@@ -428,6 +432,23 @@ def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
+class GraphedStep:
+    """A workload step captured into CUDA graphs, one per input set the workload rotates through, so that a
+    launch-bound step costs one driver call instead of one per kernel."""
+
+    def __init__(self, be, wl, fn_name):
+        self.n = getattr(wl, "n_variants", 1)
+        self.graphs = []
+        for v in range(self.n):
+            wl.i = v
+            self.graphs.append(be.capture_graph(getattr(wl, fn_name)))
+        self.k = 0
+
+    def __call__(self):
+        self.graphs[self.k % self.n].replay()
+        self.k += 1
+
+
 def timed(torch, dist, world, fn, steps, warmup):
     """W warm-up steps, then K steps between barrier + synchronize, device time by CUDA events, max over ranks."""
     for _ in range(warmup):
@@ -480,11 +501,19 @@ def cpu_baseline(wl, budget_s=12.0):
             "sample": sample, "seconds_per_pass": best}
 
 
-def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, profile_steps=100):
+def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, profile_steps=100, use_graph=True):
     steps = max(1, min(steps, getattr(wl, "max_steps", steps)))
     profile_steps = max(1, min(profile_steps, getattr(wl, "max_steps", profile_steps)))
-    ms = timed(torch, dist, world, wl.step, steps, warmup)
-    ms_e2e = timed(torch, dist, world, wl.step_e2e, steps, warmup)
+    if use_graph:
+        for _ in range(2):
+            wl.step()
+            wl.step_e2e()
+        step, step_e2e = GraphedStep(be, wl, "step"), GraphedStep(be, wl, "step_e2e")
+    else:
+        step, step_e2e = wl.step, wl.step_e2e
+    wl.config["launch"] = "cuda graph replay (one per input set)" if use_graph else "eager"
+    ms = timed(torch, dist, world, step, steps, warmup)
+    ms_e2e = timed(torch, dist, world, step_e2e, steps, warmup)
     units = wl.units_per_step
     if world > 1:
         t = torch.tensor([units], dtype=torch.float64, device="cuda")
@@ -528,8 +557,10 @@ def run_ours(args):
     peaks = load_peaks()
     sampler = ClockSampler(local_rank if world > 1 else 0) if rank == 0 else None
     wl = make_workload(args.workload, be, rank, world, dist, args.tokens)
+    graph_ok = lambda name: not args.no_graph and not (world > 1 and name in STRONG)  # NCCL stays eager
     head = measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
-                   with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps)
+                   with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps,
+                   use_graph=graph_ok(args.workload))
     extras = []
     if args.extras or (world == 1 and not args.no_extras):
         for name in WORKLOAD_NAMES:
@@ -539,7 +570,8 @@ def run_ours(args):
             torch.cuda.empty_cache()
             wl = make_workload(name, be, rank, world, dist)
             extras.append(measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
-                                  with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps))
+                                  with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps,
+                                  use_graph=graph_ok(name)))
     be.device_flush()
     clocks = sampler.stop() if sampler else None
     if rank == 0:
@@ -614,6 +646,7 @@ def main():
     ap.add_argument("--extras", action="store_true", help="also measure the other workloads of the path (default at N=1)")
     ap.add_argument("--no-extras", action="store_true", help="only the selected workload")
     ap.add_argument("--tokens", type=int, default=0, help="prompt length override for mla_prefill_32k (profiler captures)")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiler runs)")
     ap.add_argument("--profile-steps", type=int, default=100, help="launches timed per kernel for the roofline")
     args = ap.parse_args()

@@ -56,6 +56,11 @@ typedef struct inf_ctx inf_ctx;
  * the default stream). */
 int32_t inf_ctx_create(int32_t device_ordinal, void* stream, inf_ctx** out);
 int32_t inf_ctx_destroy(inf_ctx* ctx);
+/* Re-target the context at another cudaStream_t (NULL is not accepted; (void*)1 names the default stream).
+ * Pending work stays on the old stream.  A caller that captures a decode step into a CUDA graph points the
+ * context at its capture stream first; the scratch workspace must already be large enough (run the step
+ * once before capturing) because growing it allocates. */
+int32_t inf_ctx_set_stream(inf_ctx* ctx, void* stream);
 const char* inf_last_error(inf_ctx* ctx);
 /* device_values_supported (backend.rs:1060). */
 int32_t inf_device_values_supported(inf_ctx* ctx);

@@ -69,6 +69,29 @@ class CudaBackend:
         self._ctx = h
         self._keep = []
 
+    def set_stream(self, stream: torch.cuda.Stream):
+        """Enqueue subsequent ops on `stream` (e.g. the capture stream of a CUDA graph)."""
+        self._check(self._lib.inf_ctx_set_stream(self._ctx, C.c_void_p(stream.cuda_stream or 1)))
+        self.stream = stream
+
+    def capture_graph(self, fn, warmup: int = 2):
+        """Run `fn` (a sequence of backend ops with fixed arguments) a few times, then capture it into a CUDA
+        graph.  Returns the graph; `graph.replay()` re-launches the whole step with one driver call."""
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        old = self.stream
+        with torch.cuda.stream(side):
+            self.set_stream(side)
+            for _ in range(warmup):
+                fn()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        self.set_stream(old)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        return graph
+
     def close(self):
         if getattr(self, "_ctx", None):
             self._lib.inf_ctx_destroy(self._ctx)

@@ -151,6 +151,18 @@ int32_t inf_ctx_destroy(inf_ctx* ctx) {
     return INF_OK;
 }
 
+int32_t inf_ctx_set_stream(inf_ctx* ctx, void* stream) {
+    INF_CHECK_CTX(ctx);
+    if (!stream) return inf_fail(ctx, INF_E_ARG, "inf_ctx_set_stream: null stream");
+    if (ctx->own_stream) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+        ctx->own_stream = false;
+    }
+    ctx->stream = (cudaStream_t)stream;
+    return INF_OK;
+}
+
 const char* inf_last_error(inf_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 
 int32_t inf_device_values_supported(inf_ctx* ctx) { return ctx ? 1 : 0; }

@@ -1,7 +1,8 @@
 // Paged GQA decode: split-KV partial kernel + combine kernel.
 //
 // HBM-bound (6 flop per KV byte at 6 query heads per KV head), so the design is about
-// bytes in flight: one CTA per (sequence, KV head, chunk of keys); a producer warp streams
+// bytes in flight: one CTA per (sequence, KV head, run of up to 2048 keys = several split-KV
+// chunks); a producer warp streams
 // 16-token page tiles with TMA (one tensor map over the whole pool, the page id becomes a
 // row coordinate, 128-byte swizzle) through a 3-stage mbarrier ring; four consumer warps each
 // take one 16-key page tile of a stage, run QK^T and PV on mma.sync with all the query heads
@@ -39,6 +40,7 @@ struct DecodeParams {
     const int* lens;
     int max_pages, q_heads, kv_heads, group, page_size, num_pages;
     int chunk, window;
+    int chunks_per_cta;  // consecutive chunks one CTA streams (chunks_per_cta * chunk <= 2048)
     int len_add;  // added to lens[b]: lets a caller that counts cached rows before the current token reuse its table
     float scale_log2;
     float* part_acc;
@@ -64,14 +66,18 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// One CTA streams a RUN of consecutive chunks of one (sequence, KV head): the producer warp keeps the TMA ring
+// full across chunk boundaries while the consumers finish a chunk (merge the four warps, write its partial) and
+// start the next, so the per-chunk prologue and epilogue no longer drain the loads in flight.  Partials are still
+// one (max, sum, acc) triple per chunk of `chunk` keys, exactly what the combine kernel expects.
 __global__ void __launch_bounds__(THREADS, 2)
 gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           DecodeParams p) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES];
     __shared__ int row_y[MAX_CHUNK / 16];
     __shared__ float warp_m[CONSUMER_WARPS][16], warp_l[CONSUMER_WARPS][16];
+    float* merge = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);  // [warp][group rows][128], not in the ring
 
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -79,12 +85,15 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     if (kv_len <= 0) return;
     const int win_start = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
     const int first_chunk = win_start / p.chunk;
-    const int key_begin = (first_chunk + (int)blockIdx.x) * p.chunk;
-    if (key_begin >= kv_len) return;
-    const int key_end = min(kv_len, key_begin + p.chunk);
-    const int lo = max(key_begin, win_start);
-    const int tile0 = (lo - key_begin) / TILE_KEYS;
-    const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
+    const int cpc = p.chunks_per_cta;
+    const int run_chunk0 = (int)blockIdx.x * cpc;  // chunk index relative to first_chunk
+    const int run_begin = (first_chunk + run_chunk0) * p.chunk;
+    if (run_begin >= kv_len) return;
+    const int run_end = min(kv_len, run_begin + cpc * p.chunk);
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        return;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -94,10 +103,10 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
         mbar_fence_init();
     }
     {
-        const int n_sub = (key_end - key_begin + 15) / 16;
+        const int n_sub = (run_end - run_begin + 15) / 16;
         const int oob_row = p.num_pages * p.kv_heads * p.page_size;  // outside the tensor: TMA fills zeros
         for (int i = tid; i < n_sub; i += THREADS) {
-            int token = key_begin + i * 16;
+            int token = run_begin + i * 16;
             int slot = token / p.page_size;
             int y = oob_row;
             if (slot < p.max_pages) {
@@ -114,63 +123,89 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     }
     __syncthreads();
 
-    float o[16][4];
-    float m_run[2] = {M_INIT, M_INIT}, l_run[2] = {0.f, 0.f};
-#pragma unroll
-    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-
+    // Both roles walk the same sequence of tiles: for every chunk of the run, the tiles that hold visible keys.
+    // `it` counts tiles across the whole run and drives the ring stage and phase.
     if (warp == CONSUMER_WARPS) {
         // ---------------- producer: one lane issues the TMA loads ----------------
         if (lane == 0) {
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            for (int t = tile0; t < n_tiles; ++t) {
-                const int it = t - tile0, s = it % STAGES;
-                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                if (!mbar_wait(&empty_bar[s], ph ^ 1u)) {
-                    atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
-                    break;
-                }
-                const int remaining = key_end - (key_begin + t * TILE_KEYS);
-                const int nsub = min(4, (remaining + 15) / 16);
-                uint8_t* base = smem + s * STAGE_BYTES;
-                mbar_arrive_expect_tx(&full_bar[s], (uint32_t)nsub * 4u * 2048u);
-                for (int sub = 0; sub < nsub; ++sub) {
-                    const int y = row_y[t * 4 + sub];
-                    tma_load_2d(base + 0 * HALF_BYTES + sub * 2048, &tm_k, 0, y, &full_bar[s]);
-                    tma_load_2d(base + 1 * HALF_BYTES + sub * 2048, &tm_k, 64, y, &full_bar[s]);
-                    tma_load_2d(base + 2 * HALF_BYTES + sub * 2048, &tm_v, 0, y, &full_bar[s]);
-                    tma_load_2d(base + 3 * HALF_BYTES + sub * 2048, &tm_v, 64, y, &full_bar[s]);
+            int it = 0;
+            bool ok = true;
+            for (int cc = 0; cc < cpc && ok; ++cc) {
+                const int key_begin = run_begin + cc * p.chunk;
+                if (key_begin >= kv_len) break;
+                const int key_end = min(kv_len, key_begin + p.chunk);
+                const int lo = max(key_begin, win_start);
+                const int tile0 = (lo - key_begin) / TILE_KEYS;
+                const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
+                for (int t = tile0; t < n_tiles; ++t, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1u)) {
+                        atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    const int remaining = key_end - (key_begin + t * TILE_KEYS);
+                    const int nsub = min(4, (remaining + 15) / 16);
+                    uint8_t* base = smem + s * STAGE_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[s], (uint32_t)nsub * 4u * 2048u);
+                    const int sub0 = (key_begin - run_begin) / 16 + t * 4;
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const int y = row_y[sub0 + sub];
+                        tma_load_2d(base + 0 * HALF_BYTES + sub * 2048, &tm_k, 0, y, &full_bar[s]);
+                        tma_load_2d(base + 1 * HALF_BYTES + sub * 2048, &tm_k, 64, y, &full_bar[s]);
+                        tma_load_2d(base + 2 * HALF_BYTES + sub * 2048, &tm_v, 0, y, &full_bar[s]);
+                        tma_load_2d(base + 3 * HALF_BYTES + sub * 2048, &tm_v, 64, y, &full_bar[s]);
+                    }
                 }
             }
         }
-    } else {
-        // ---------------- consumers ----------------
-        const int g = lane >> 2, qd = lane & 3;
-        // Q fragments: rows = query heads of this KV group (zero beyond the group)
-        uint32_t qa[8][4];
-        {
-            const __half* qb = p.q + ((long long)b * p.q_heads + (long long)kvh * p.group) * D;
+        return;  // the producer takes no part in the consumers' named barriers
+    }
+
+    // ---------------- consumers ----------------
+    const int g = lane >> 2, qd = lane & 3;
+    // Q fragments: rows = query heads of this KV group (zero beyond the group)
+    uint32_t qa[8][4];
+    {
+        const __half* qb = p.q + ((long long)b * p.q_heads + (long long)kvh * p.group) * D;
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-                const int c0 = kk * 16 + qd * 2;
-                qa[kk][0] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0) : 0u;
-                qa[kk][1] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0) : 0u;
-                qa[kk][2] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0 + 8) : 0u;
-                qa[kk][3] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0 + 8) : 0u;
-            }
+        for (int kk = 0; kk < 8; ++kk) {
+            const int c0 = kk * 16 + qd * 2;
+            qa[kk][0] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0) : 0u;
+            qa[kk][1] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0) : 0u;
+            qa[kk][2] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0 + 8) : 0u;
+            qa[kk][3] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0 + 8) : 0u;
         }
-        const uint32_t smem_base = smem_u32(smem);
-        for (int t = tile0; t < n_tiles; ++t) {
-            const int it = t - tile0, s = it % STAGES;
+    }
+    const uint32_t smem_base = smem_u32(smem);
+    int it = 0;
+    bool failed = false;
+    for (int cc = 0; cc < cpc; ++cc) {
+        const int key_begin = run_begin + cc * p.chunk;
+        if (key_begin >= kv_len) break;  // uniform over the CTA
+        const int key_end = min(kv_len, key_begin + p.chunk);
+        const int lo = max(key_begin, win_start);
+        const int tile0 = (lo - key_begin) / TILE_KEYS;
+        const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
+
+        float o[16][4];
+        float m_run[2] = {M_INIT, M_INIT}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+        for (int t = tile0; t < n_tiles; ++t, ++it) {
+            const int s = it % STAGES;
             const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-            if (!mbar_wait(&full_bar[s], ph)) {
+            if (!failed && !mbar_wait(&full_bar[s], ph)) {
                 if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
-                break;
+                failed = true;
             }
             const int k0 = key_begin + t * TILE_KEYS + warp * 16;  // first key of this warp's page tile
             bool wrote_smem = false;
-            if (k0 < key_end && k0 + 16 > lo) {
+            if (!failed && k0 < key_end && k0 + 16 > lo) {
                 const uint32_t stage = smem_base + s * STAGE_BYTES;
                 const bool edge = (k0 < lo) || (k0 + 16 > key_end);
                 if (edge) {
@@ -275,44 +310,43 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
             l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
             l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
         }
-    }
-
-    // ---------------- merge the four warps through shared memory ----------------
-    __syncthreads();  // every load has landed and every ldmatrix has been issued: the ring is free
-    float* merge = reinterpret_cast<float*>(smem);  // [warp][16 rows][128]
-    if (warp < CONSUMER_WARPS) {
-        const int g = lane >> 2, qd = lane & 3;
-        float* mw = merge + warp * 16 * D;
+        // ---------------- merge the four warps of this chunk through their own shared-memory buffer ----------------
+        {
+            float* mw = merge + warp * p.group * D;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            *reinterpret_cast<float2*>(mw + g * D + j * 8 + qd * 2) = make_float2(o[j][0], o[j][1]);
-            *reinterpret_cast<float2*>(mw + (g + 8) * D + j * 8 + qd * 2) = make_float2(o[j][2], o[j][3]);
-        }
-        if (qd == 0) {
-            warp_m[warp][g] = m_run[0];
-            warp_m[warp][g + 8] = m_run[1];
-            warp_l[warp][g] = l_run[0];
-            warp_l[warp][g + 8] = l_run[1];
-        }
-    }
-    __syncthreads();
-    if (tid < D) {
-        const long long prow0 = ((long long)b * p.max_chunks + blockIdx.x) * p.q_heads + (long long)kvh * p.group;
-        for (int r = 0; r < p.group; ++r) {
-            float M = fmaxf(fmaxf(warp_m[0][r], warp_m[1][r]), fmaxf(warp_m[2][r], warp_m[3][r]));
-            float acc = 0.f, L = 0.f;
-#pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) {
-                float sc = ex2_approx(warp_m[w][r] - M);
-                acc += sc * merge[(w * 16 + r) * D + tid];
-                L += sc * warp_l[w][r];
+            for (int j = 0; j < 16; ++j) {
+                if (g < p.group) *reinterpret_cast<float2*>(mw + g * D + j * 8 + qd * 2) = make_float2(o[j][0], o[j][1]);
+                if (g + 8 < p.group)
+                    *reinterpret_cast<float2*>(mw + (g + 8) * D + j * 8 + qd * 2) = make_float2(o[j][2], o[j][3]);
             }
-            p.part_acc[(prow0 + r) * D + tid] = acc;
-            if (tid == 0) {
-                p.part_ml[(prow0 + r) * 2 + 0] = M;
-                p.part_ml[(prow0 + r) * 2 + 1] = L;
+            if (qd == 0) {
+                warp_m[warp][g] = m_run[0];
+                warp_m[warp][g + 8] = m_run[1];
+                warp_l[warp][g] = l_run[0];
+                warp_l[warp][g + 8] = l_run[1];
             }
         }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four consumer warps only
+        {
+            const long long prow0 =
+                ((long long)b * p.max_chunks + run_chunk0 + cc) * p.q_heads + (long long)kvh * p.group;
+            for (int r = 0; r < p.group; ++r) {
+                float M = fmaxf(fmaxf(warp_m[0][r], warp_m[1][r]), fmaxf(warp_m[2][r], warp_m[3][r]));
+                float acc = 0.f, L = 0.f;
+#pragma unroll
+                for (int w = 0; w < CONSUMER_WARPS; ++w) {
+                    float sc = ex2_approx(warp_m[w][r] - M);
+                    acc += sc * merge[(w * p.group + r) * D + tid];
+                    L += sc * warp_l[w][r];
+                }
+                p.part_acc[(prow0 + r) * D + tid] = acc;
+                if (tid == 0) {
+                    p.part_ml[(prow0 + r) * 2 + 0] = M;
+                    p.part_ml[(prow0 + r) * 2 + 1] = L;
+                }
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the merge buffer is free again
     }
 }
 
@@ -323,11 +357,15 @@ __device__ __forceinline__ float softplus_ref(float v) {
     return logf(1.0f + expf(v));
 }
 
+// Merge of the per-chunk partials.  The chunk weights are computed once in shared memory so that the
+// accumulation is a stream of independent coalesced loads.
 template <typename OutT>
 __global__ void __launch_bounds__(D)
 gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, const float* __restrict__ gate, OutT* __restrict__ out,
                           int q_heads, int max_chunks, int chunk, int window, int len_add) {
+    __shared__ float w[MAX_CHUNK / TILE_KEYS * 16];  // up to 512 chunks
+    __shared__ float red[4];
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int kv_len = lens[b] + len_add;
     const long long orow = ((long long)b * q_heads + h) * D + d;
@@ -337,19 +375,32 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
     }
     const int win_start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int first_chunk = win_start / chunk;
-    const int n = (kv_len + chunk - 1) / chunk - first_chunk;
-    float M = M_INIT, L = 0.f, acc = 0.f;
-    for (int c = 0; c < n; ++c) {
-        const long long prow = ((long long)b * max_chunks + c) * q_heads + h;
-        float m = part_ml[prow * 2], l = part_ml[prow * 2 + 1];
-        float a = part_acc[prow * D + d];
-        float Mn = fmaxf(M, m);
-        float s0 = ex2_approx(M - Mn), s1 = ex2_approx(m - Mn);
-        acc = acc * s0 + a * s1;
-        L = L * s0 + l * s1;
-        M = Mn;
+    const int n = (kv_len + chunk - 1) / chunk - first_chunk;  // <= 512, checked on the host
+    const long long prow0 = ((long long)b * max_chunks) * q_heads + h;
+    float mloc = M_INIT;
+    for (int c = d; c < n; c += D) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)c * q_heads) * 2]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+    if ((d & 31) == 0) red[d >> 5] = mloc;
+    __syncthreads();
+    const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    float lloc = 0.f;
+    for (int c = d; c < n; c += D) {
+        const float wc = ex2_approx(part_ml[(prow0 + (long long)c * q_heads) * 2] - M);
+        w[c] = wc;
+        lloc += wc * part_ml[(prow0 + (long long)c * q_heads) * 2 + 1];
     }
-    float gain = (gate ? softplus_ref(gate[(long long)b * q_heads + h]) : 1.0f) / L;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
+    if ((d & 31) == 0) red[d >> 5] = lloc;
+    __syncthreads();
+    const float L = red[0] + red[1] + red[2] + red[3];
+    const float* src = part_acc + prow0 * D + d;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < n; ++c) acc += w[c] * src[(long long)c * q_heads * D];
+    const float gain = (gate ? softplus_ref(gate[(long long)b * q_heads + h]) : 1.0f) / L;
     out[orow] = OutT(acc * gain);
 }
 
@@ -395,6 +446,9 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
                                 table->host_lens[b], max_len);
     // with a window only ceil(window/chunk)+1 chunks can be visible
     int max_chunks = (max_len + split_chunk - 1) / split_chunk;
+    if (max_chunks > 512)
+        return inf_fail(ctx, INF_E_CONFIG, "gqa_decode: %d chunks of %d keys exceed the 512 the combine step holds; "
+                        "use a larger split_chunk", max_chunks, split_chunk);
     size_t need = inf_gqa_decode_workspace_bytes(table->batch, q_heads, D, max_len, split_chunk);
     if (scratch_bytes < need)
         return inf_fail(ctx, INF_E_ARG, "gqa_decode: scratch of %zu bytes is smaller than the %zu needed", scratch_bytes,
@@ -427,15 +481,16 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     p.part_acc = (float*)scratch;
     p.part_ml = p.part_acc + (size_t)table->batch * max_chunks * q_heads * D;
     p.max_chunks = max_chunks;
+    p.chunks_per_cta = MAX_CHUNK / split_chunk;
     p.status = ctx->status;
 
-    const size_t smem = STAGES * STAGE_BYTES + 1024;
+    const size_t smem = STAGES * STAGE_BYTES + (size_t)CONSUMER_WARPS * group * D * sizeof(float);
     if (!(ctx->func_attr_done & 1u)) {
         INF_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)smem));
+                                           (int)(STAGES * STAGE_BYTES + CONSUMER_WARPS * 16 * D * sizeof(float))));
         ctx->func_attr_done |= 1u;
     }
-    dim3 grid(max_chunks, pool->kv_heads, table->batch);
+    dim3 grid((max_chunks + p.chunks_per_cta - 1) / p.chunks_per_cta, pool->kv_heads, table->batch);
     {
         inf_prof_scope prof(ctx, "gqa_decode_partial_kernel");
         gqa_decode_partial_kernel<<<grid, THREADS, smem, ctx->stream>>>(tm_k, tm_v, p);

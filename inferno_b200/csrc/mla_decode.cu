@@ -307,37 +307,51 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     if (warp == 5) tmem_dealloc(tbase, TMEM_COLS);
 }
 
+// Merge of the split partials.  One CTA per (head, token, quarter of the 512 output columns); the split
+// weights are computed once in shared memory, so the accumulation loop is a stream of independent
+// coalesced loads instead of a chain of dependent ones.
+constexpr int MAX_SPLITS = 1024;
+
 template <typename OutT>
 __global__ void __launch_bounds__(128)
 mla_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, OutT* __restrict__ out, int tokens, int heads, int n_splits) {
-    const int h = blockIdx.x, t = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
+    __shared__ float w[MAX_SPLITS];
+    __shared__ float red[4];
+    const int h = blockIdx.x, t = blockIdx.y % tokens, b = blockIdx.y / tokens, quarter = blockIdx.z;
+    const int tid = threadIdx.x;
     const int kv_len = lens[b] + t + 1;
     const int n_pages = (kv_len + PAGE - 1) / PAGE;
-    float M = M_INIT, Lsum = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < n_splits; ++s) {
-        int pb, pe;
-        split_range(n_pages, n_splits, s, pb, pe);
-        if (pe <= pb) continue;
-        const long long prow = ((((long long)b * tokens + t) * n_splits + s) * heads) + h;
-        const float m = part_ml[prow * 2], l = part_ml[prow * 2 + 1];
-        const float4 a = *reinterpret_cast<const float4*>(part_acc + prow * LAT + tid * 4);
-        const float Mn = fmaxf(M, m);
-        const float s0 = ex2_approx(M - Mn), s1 = ex2_approx(m - Mn);
-        acc.x = acc.x * s0 + a.x * s1;
-        acc.y = acc.y * s0 + a.y * s1;
-        acc.z = acc.z * s0 + a.z * s1;
-        acc.w = acc.w * s0 + a.w * s1;
-        Lsum = Lsum * s0 + l * s1;
-        M = Mn;
+    const int per = (n_pages + n_splits - 1) / n_splits;
+    const int n_valid = (n_pages + per - 1) / per;  // splits [0, n_valid) did work
+    const long long prow0 = (((long long)b * tokens + t) * n_splits) * heads + h;
+    // pass 1: global maximum
+    float mloc = M_INIT;
+    for (int s = tid; s < n_valid; s += 128) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)s * heads) * 2]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+    if ((tid & 31) == 0) red[tid >> 5] = mloc;
+    __syncthreads();
+    const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    // pass 2: weights and the normaliser
+    float lloc = 0.f;
+    for (int s = tid; s < n_valid; s += 128) {
+        const float ws = ex2_approx(part_ml[(prow0 + (long long)s * heads) * 2] - M);
+        w[s] = ws;
+        lloc += ws * part_ml[(prow0 + (long long)s * heads) * 2 + 1];
     }
-    const float inv = 1.0f / Lsum;
-    OutT* dst = out + ((((long long)b * tokens + t) * heads) + h) * LAT + tid * 4;
-    dst[0] = OutT(acc.x * inv);
-    dst[1] = OutT(acc.y * inv);
-    dst[2] = OutT(acc.z * inv);
-    dst[3] = OutT(acc.w * inv);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
+    if ((tid & 31) == 0) red[tid >> 5] = lloc;
+    __syncthreads();
+    const float inv = 1.0f / (red[0] + red[1] + red[2] + red[3]);
+    // pass 3: weighted sum of the partial outputs, one column per thread
+    const float* src = part_acc + prow0 * LAT + quarter * 128 + tid;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < n_valid; ++s) acc += w[s] * src[(long long)s * heads * LAT];
+    out[((((long long)b * tokens + t) * heads) + h) * LAT + quarter * 128 + tid] = OutT(acc * inv);
 }
 
 }  // namespace
@@ -366,6 +380,7 @@ extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, cons
     int n_splits = ctx->sm_count / ctas_per_split;
     if (n_splits < 1) n_splits = 1;
     if (n_splits > max_pages_used) n_splits = max_pages_used;
+    if (n_splits > MAX_SPLITS) n_splits = MAX_SPLITS;
     // even out: with `per` pages per split only ceil(pages/per) splits do work
     const int per = (max_pages_used + n_splits - 1) / n_splits;
     n_splits = (max_pages_used + per - 1) / per;
@@ -414,7 +429,7 @@ extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, cons
         mla_decode_partial_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tq, tkv, p);
     }
     INF_LAUNCH_CHECK(ctx, "mla_decode_partial_kernel");
-    dim3 cgrid(heads, tokens, table->batch);
+    dim3 cgrid(heads, tokens * table->batch, 4);
     if (out_dtype == INF_DTYPE_F32)
         mla_decode_combine_kernel<float><<<cgrid, 128, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
                                                                          (float*)out, tokens, heads, n_splits);

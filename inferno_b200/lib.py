@@ -58,6 +58,7 @@ _L = C.c_int64
 SIGNATURES = {
     "inf_ctx_create": (_I, [_I, _P, C.POINTER(_P)]),
     "inf_ctx_destroy": (_I, [_P]),
+    "inf_ctx_set_stream": (_I, [_P, _P]),
     "inf_last_error": (C.c_char_p, [_P]),
     "inf_device_values_supported": (_I, [_P]),
     "inf_flush": (_I, [_P]),
