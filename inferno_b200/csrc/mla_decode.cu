@@ -46,8 +46,8 @@ struct MlaParams {
     int tokens, heads, head_blocks, batch;
     int n_splits;
     float scale_log2;
-    float* part_acc;  // [batch][tokens][n_splits][heads][512]
-    float* part_ml;   // [batch][tokens][n_splits][heads][2]
+    __half* part_acc; // [batch][tokens][n_splits][heads][512], each row already divided by its own sum
+    float* part_ml;   // [batch][tokens][n_splits][heads][2]: running max (log2 domain) and sum
     int* status;
 };
 
@@ -282,7 +282,10 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             const long long prow =
                 ((((long long)b * p.tokens + t) * p.n_splits + split) * p.heads) + head;
             const bool valid = head < p.heads;
-            float* dst = p.part_acc + prow * LAT + (lane >> 4) * 256;
+            // the partial row is stored normalised by its own sum, as fp16: half the bytes of an fp32 partial,
+            // and the values are bounded by the largest cached latent
+            const float inv_l = 1.0f / __shfl_sync(0xffffffffu, l, lane & 15);
+            __half* dst = p.part_acc + prow * LAT + (lane >> 4) * 256;
 #pragma unroll
             for (int c = 0; c < 256 / 32; ++c) {
                 uint32_t o[32];
@@ -290,10 +293,14 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 tc_wait_ld();
                 if (valid) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<float4*>(dst + c * 32 + i) =
-                            make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]),
-                                        __uint_as_float(o[i + 3]));
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                        v.y = pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                        v.z = pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                        v.w = pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+                    }
                 }
             }
             if (valid && s_owner) {
@@ -314,7 +321,7 @@ constexpr int MAX_SPLITS = 1024;
 
 template <typename OutT>
 __global__ void __launch_bounds__(128)
-mla_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, OutT* __restrict__ out, int tokens, int heads, int n_splits) {
     __shared__ float w[MAX_SPLITS];
     __shared__ float red[4];
@@ -337,9 +344,10 @@ mla_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
     // pass 2: weights and the normaliser
     float lloc = 0.f;
     for (int s = tid; s < n_valid; s += 128) {
-        const float ws = ex2_approx(part_ml[(prow0 + (long long)s * heads) * 2] - M);
+        const float ws = ex2_approx(part_ml[(prow0 + (long long)s * heads) * 2] - M) *
+                         part_ml[(prow0 + (long long)s * heads) * 2 + 1];  // weight of a normalised partial
         w[s] = ws;
-        lloc += ws * part_ml[(prow0 + (long long)s * heads) * 2 + 1];
+        lloc += ws;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
@@ -347,10 +355,10 @@ mla_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
     __syncthreads();
     const float inv = 1.0f / (red[0] + red[1] + red[2] + red[3]);
     // pass 3: weighted sum of the partial outputs, one column per thread
-    const float* src = part_acc + prow0 * LAT + quarter * 128 + tid;
+    const __half* src = part_acc + prow0 * LAT + quarter * 128 + tid;
     float acc = 0.f;
 #pragma unroll 8
-    for (int s = 0; s < n_valid; ++s) acc += w[s] * src[(long long)s * heads * LAT];
+    for (int s = 0; s < n_valid; ++s) acc += w[s] * __half2float(src[(long long)s * heads * LAT]);
     out[((((long long)b * tokens + t) * heads) + h) * LAT + quarter * 128 + tid] = OutT(acc * inv);
 }
 
@@ -386,7 +394,8 @@ extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, cons
     n_splits = (max_pages_used + per - 1) / per;
 
     const size_t prows = (size_t)table->batch * tokens * n_splits * heads;
-    rc = inf_ensure_workspace(ctx, prows * (LAT + 2) * sizeof(float));
+    const size_t acc_bytes = (prows * LAT * sizeof(__half) + 255) & ~(size_t)255;
+    rc = inf_ensure_workspace(ctx, acc_bytes + prows * 2 * sizeof(float));
     if (rc != INF_OK) return rc;
 
     CUtensorMap tq, tkv;
@@ -415,8 +424,8 @@ extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, cons
     p.batch = table->batch;
     p.n_splits = n_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.part_acc = (float*)ctx->workspace;
-    p.part_ml = p.part_acc + prows * LAT;
+    p.part_acc = (__half*)ctx->workspace;
+    p.part_ml = (float*)((char*)ctx->workspace + acc_bytes);
     p.status = ctx->status;
     if (!(ctx->func_attr_done & 16u)) {
         INF_CUDA(ctx, cudaFuncSetAttribute(mla_decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
