@@ -108,6 +108,7 @@ class GqaDecodeB32:
     metric, unit, bound = "attn_decode_hbm_gbs", "GB/s", "hbm"
     kernel = "gqa_decode_partial_kernel"
     launches_per_step = 3  # rope+append, split-KV partial, combine
+    traffic = 1.0319e9 + 15.2e6  # DRAM bytes read + written per launch, ncu (profiles/gqa_decode_partial_b32.md)
     B, Hq, Hkv, D, P, CHUNK, THETA = 32, 48, 8, 128, 16, 512, 500000.0
 
     def __init__(self, be, rank):
@@ -205,6 +206,8 @@ class MlaDecode:
         import torch
         self.torch, self.be, self.ctx_len = torch, be, ctx_len
         self.name = f"mla_decode_{ctx_len // 1024}k"
+        # DRAM bytes per launch from ncu at 32k context (profiles/mla_decode_partial_32k.md); proportional to context
+        self.traffic = (37.88e6 + 0.37e6) * ctx_len / 32768
         row_bytes = (self.L + self.R) * 2
         self.n_caches = max(2, int(np.ceil(320e6 / (ctx_len * row_bytes))))  # rotate through > L2 worth of caches
         pages_per = (ctx_len + self.P - 1) // self.P
@@ -267,6 +270,7 @@ class GqaPrefill2k:
     metric, unit, bound = "gqa_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_gqa_kernel"
     launches_per_step = 2  # rope+append, flash prefill
+    traffic = 33.61e6 + 0.07e6  # DRAM bytes per launch, ncu (profiles/flash_prefill_gqa_2k.md)
     T, Hq, Hkv, D, P, THETA = 2048, 48, 8, 128, 16, 500000.0
     max_steps = 400
     N_SETS = 8
@@ -349,6 +353,9 @@ class MlaPrefill32k:
     metric, unit, bound = "mla_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_mla_kernel"
     launches_per_step = 1
+    # ncu at 8192 tokens: 2.151 GB read + 0.138 GB written (profiles/flash_prefill_mla_8k.md).  K/V re-streaming grows
+    # with tokens^2 and the output with tokens, so a full 32768-token launch is estimated at 16x / 4x of those.
+    traffic = 2.151e9 * 16 + 0.138e9 * 4
     T, H = 32768, 64
     max_steps = 3
 
