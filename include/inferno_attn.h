@@ -277,6 +277,19 @@ int32_t inf_paged_decode_attention_resident(inf_ctx* ctx, const float* q, const 
 int32_t inf_linearize_paged(inf_ctx* ctx, const void* pool_f16, const inf_kv_pool* shape,
                             const inf_page_table* table, int32_t tokens, void* out_f16);
 
+/* ---- multi-GPU: the one collective of the path ------------------------------------------------------ */
+/* Head-sharded prefill / MLA leaves every rank with [tokens, heads/N, dim]; the output is all-gathered over
+ * NCCL (NVLink / NVSwitch) on the context's stream.  (The reference is single-device; no counterpart.)
+ * NCCL is loaded at run time (libnccl.so.2, or the path in INFERNO_NCCL_LIB).  Rank 0 creates the id and the
+ * host hands its INF_COMM_ID_BYTES bytes to the other ranks by any means; every rank then calls inf_comm_init
+ * with its own context.  recv holds nranks * bytes, in rank order. */
+#define INF_COMM_ID_BYTES 128
+typedef struct inf_comm inf_comm;
+int32_t inf_comm_unique_id(inf_ctx* ctx, void* id_out);
+int32_t inf_comm_init(inf_ctx* ctx, const void* id, int32_t rank, int32_t nranks, inf_comm** out);
+int32_t inf_comm_destroy(inf_comm* comm);
+int32_t inf_allgather_heads(inf_comm* comm, const void* send, void* recv, size_t bytes);
+
 #ifdef __cplusplus
 }
 #endif

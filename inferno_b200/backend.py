@@ -92,7 +92,36 @@ class CudaBackend:
         torch.cuda.current_stream(self.device).wait_stream(side)
         return graph
 
+    # ------------------------------------------------------------------ multi-GPU
+    def comm_unique_id(self) -> bytes:
+        buf = C.create_string_buffer(128)
+        self._check(self._lib.inf_comm_unique_id(self._ctx, buf))
+        return buf.raw
+
+    def comm_init(self, unique_id: bytes, rank: int, nranks: int):
+        h = C.c_void_p()
+        self._check(self._lib.inf_comm_init(self._ctx, C.create_string_buffer(unique_id, 128), rank, nranks, C.byref(h)))
+        self._comm, self._comm_size = h, nranks
+        return h
+
+    def allgather_heads(self, local_out: torch.Tensor) -> torch.Tensor:
+        """local_out [tokens, heads/N, dim] -> [tokens, heads, dim] through inf_allgather_heads (NCCL)."""
+        n = self._comm_size
+        t, h, d = local_out.shape
+        local_out = local_out.contiguous()
+        gathered = torch.empty((n * t, h, d), dtype=local_out.dtype, device=local_out.device)
+        rc = self._lib.inf_allgather_heads(self._comm, _ptr(local_out), _ptr(gathered),
+                                           local_out.numel() * local_out.element_size())
+        self._check(rc)
+        return gathered.view(n, t, h, d).permute(1, 0, 2, 3).reshape(t, n * h, d)
+
+    def comm_destroy(self):
+        if getattr(self, "_comm", None):
+            self._lib.inf_comm_destroy(self._comm)
+            self._comm = None
+
     def close(self):
+        self.comm_destroy()
         if getattr(self, "_ctx", None):
             self._lib.inf_ctx_destroy(self._ctx)
             self._ctx = None

@@ -96,6 +96,10 @@ SIGNATURES = {
                                     _L, _I]),
     "inf_linearize_paged": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _P]),
     "inf_paged_decode_attention_resident": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "inf_comm_unique_id": (_I, [_P, _P]),
+    "inf_comm_init": (_I, [_P, _P, _I, _I, C.POINTER(_P)]),
+    "inf_comm_destroy": (_I, [_P]),
+    "inf_allgather_heads": (_I, [_P, _P, _P, C.c_size_t]),
     "inf_paged_index_create": (_I, [_I, _I, _I, _I, C.POINTER(_P)]),
     "inf_paged_index_destroy": (_I, [_P]),
     "inf_paged_index_last_error": (C.c_char_p, [_P]),
