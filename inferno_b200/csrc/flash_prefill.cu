@@ -1,10 +1,11 @@
 // Causal flash attention for prefill on tcgen05 / TMEM, fed by TMA.
 //
-// One CTA per SM runs TWO query streams of 128 rows each against one shared ring of K/V tiles, so
-// every K/V tile is fetched once for 256 query rows and the tensor pipe always has the other
-// stream's MMAs to run while one stream is in softmax.  The two streams are either two query heads
-// of the same KV group at the same rows (GQA: identical causal structure, perfectly balanced) or
-// two consecutive 128-row tiles of one head (MHA / MLA prefill).
+// One CTA per SM runs TWO query streams of 128 rows each against one shared ring of 128-key K/V tiles,
+// so every K/V tile is fetched once for 256 query rows, and the MMA issue order is staggered by half a
+// tile between the streams: while one stream is in softmax the tensor pipe runs the other stream's
+// PV and next QK^T.  The two streams are either two query heads of the same KV group at the same rows
+// (GQA: identical causal structure, perfectly balanced) or two consecutive 128-row tiles of one head
+// (MHA / MLA prefill).
 //
 // Twelve warps, specialised:
 //   warps 0-3   softmax + epilogue of stream 0; thread r owns query row r and TMEM lane r
@@ -12,14 +13,16 @@
 //   warp 8      TMA producer for Q and the K tiles
 //   warp 9      allocates TMEM and issues every tcgen05.mma
 //   warp 10     TMA producer for the V tiles            (warp 11 only pads the third warpgroup)
-// Per stream and 64-key tile:  S = Q K^T  (SS MMA, M128 N64, both operands K-major, 128-byte swizzle)
-//                              softmax in registers, P written back to TMEM as packed fp16 over its S buffer
+// Per stream and 128-key tile: S = Q K^T  (SS MMA, M128 N128, both operands K-major, 128-byte swizzle;
+//                                          N = 128 keeps the operand traffic at the 128 B/clk the shared
+//                                          memory can feed, N = 64 would need 192 B/clk)
+//                              softmax in registers (two passes over S in 32-column chunks), P written back
+//                              to TMEM as packed fp16 over the first half of its own S columns
 //                              O += P V   (TS MMA, A = P from TMEM, B = V MN-major from its [key][dim] tile)
-// TMEM: 256 columns per stream (S double-buffered in 0-63 / 64-127, O in 128-255).  O is rescaled lazily
-// (only when a row maximum grew by more than 2^8).  The K/V ring is 5 (GQA) or 3 (MLA) tiles deep,
-// enough to cover L2/HBM latency at one tile per ~1000 cycles.
+// TMEM: 256 columns per stream (S/P in 0-127, O in 128-255).  O is rescaled lazily (only when a row
+// maximum grew by more than 2^8).
 //
-// Two instantiations: paged GQA prefill (head_dim 128; a K/V tile is four 16-token page boxes addressed
+// Two instantiations: paged GQA prefill (head_dim 128; a K/V tile is eight 16-token page boxes addressed
 // through the page table; reference kernel f16_attention_kernels.metal:153-316) and dense MLA prefill
 // over expanded heads (qk 128+64 with the rope tail shared by all heads, v 128; reference kernel
 // attention_kernels.metal:723-968 with no past, K laid out as in layout_kernels.metal:148-183).
@@ -34,12 +37,12 @@ using namespace inf;
 namespace {
 
 constexpr int BM = 128;
-constexpr int BN = 64;
+constexpr int BN = 128;
 constexpr int NUM_THREADS = 384;
 constexpr float M_INIT = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t STREAM_COLS = 256, COL_S0 = 0, COL_S1 = 64, COL_O = 128;
+constexpr uint32_t STREAM_COLS = 256, COL_S = 0, COL_O = 128;
 
 struct FlashParams {
     int tokens, q_heads, kv_heads, group, batch;
@@ -54,7 +57,18 @@ struct FlashParams {
     int out_f16;
     long long o_ts, o_hs, o_bs;  // element strides of the output: token, head, batch
     int* status;
+#ifdef INF_KPROF
+    long long* kprof;  // debug builds only: cycle counters of CTA (0,0,0)
+#endif
 };
+
+#ifdef INF_KPROF
+#define KP_T0() long long kp_t = clock64()
+#define KP_ADD(slot) do { long long kp_n = clock64(); if (kp_on) kp_acc[slot] += kp_n - kp_t; kp_t = kp_n; } while (0)
+#else
+#define KP_T0() do {} while (0)
+#define KP_ADD(slot) do {} while (0)
+#endif
 
 // kernels/fp8_attention_kernels.metal:56-64
 __device__ __forceinline__ float softplus_ref(float v) {
@@ -63,13 +77,13 @@ __device__ __forceinline__ float softplus_ref(float v) {
     return logf(1.0f + expf(v));
 }
 
-template <int DQK, int DV, int KS, int VS>
+template <int DQK, int DV, int KB, int VS>
 struct SmemLayout {
     static constexpr int Q_BYTES = BM * DQK * 2;  // per stream
-    static constexpr int K_BYTES = BN * DQK * 2;
+    static constexpr int KBLK_BYTES = BN * 128;   // one [128 keys][64 dims] block of a K tile
     static constexpr int V_BYTES = BN * DV * 2;
     static constexpr int OFF_K = 2 * Q_BYTES;
-    static constexpr int OFF_V = OFF_K + KS * K_BYTES;
+    static constexpr int OFF_V = OFF_K + KB * KBLK_BYTES;
     static constexpr int OFF_BAR = OFF_V + VS * V_BYTES;
     static constexpr int TOTAL = OFF_BAR + 512;
 };
@@ -78,26 +92,34 @@ struct Stream {
     int head, q0, kt_begin, kt_end;  // key-tile range [kt_begin, kt_end); empty when the stream has no rows
 };
 
-template <int DQK, int DV, int KS, int VS, bool PAGED>
+template <int DQK, int DV, int KB, int VS, bool PAGED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_k2, const __grid_constant__ CUtensorMap tm_v,
                      FlashParams p) {
-    using L = SmemLayout<DQK, DV, KS, VS>;
+    using L = SmemLayout<DQK, DV, KB, VS>;
+    constexpr int NB = DQK / 64;  // 64-column blocks per K tile
+    constexpr int SR = (KB + NB - 1) / NB + 1;
+    static_assert(VS == 2, "the o_ready rotation assumes a two-tile V ring");
+    static_assert((1 + KB + VS + 2 * SR + 4 + 4 + 2) * 8 + 4 <= 512, "barrier area");
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = smem + L::OFF_K;
     uint8_t* sV = smem + L::OFF_V;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
     uint64_t* q_full = bars;            // [1]
-    uint64_t* k_full = bars + 1;        // [KS]
-    uint64_t* k_empty = k_full + KS;    // [KS]
-    uint64_t* v_full = k_empty + KS;    // [VS]
-    uint64_t* v_empty = v_full + VS;    // [VS]
-    uint64_t* s_full = v_empty + VS;    // [2 streams][2 buffers]
-    uint64_t* p_full = s_full + 4;      // [2][2]
-    uint64_t* o_ready = p_full + 4;     // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 2);
+    // Every tcgen05.commit costs tensor-pipe time, so a stream commits exactly twice per tile: s_full after its QK
+    // and o_ready after its PV.  The same two barriers also tell the producers when ring slots are free again,
+    // which is why they rotate over SR (resp. 2) barriers: a producer may look at a tile's barrier long after the
+    // softmax did, and the rotation keeps the phase parity it tests unambiguous (the ring holds fewer than SR - 1
+    // K tiles and VS = 2 V tiles, so the barrier cannot have been reused twice in between).
+    uint64_t* k_full = bars + 1;        // [KB]: one per 64-column block of the K ring
+    uint64_t* v_full = k_full + KB;     // [VS]
+    uint64_t* s_full = v_full + VS;     // [2 streams][SR]: S of local tile jl is in TMEM (its K blocks are consumed)
+    uint64_t* p_full = s_full + 2 * SR; // [2][2]: P of keys 0-63 / 64-127 of the current tile is in TMEM
+    uint64_t* o_ready = p_full + 4;     // [2][2]: PV of local tile jl has retired (its V tile is consumed)
+    uint64_t* sm_done = o_ready + 4;    // [2]: a stream's softmax warpgroup has finished the exponentials of a tile
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm_done + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b = blockIdx.z;
@@ -124,6 +146,11 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int kt_lo = act0 && act1 ? min(st[0].kt_begin, st[1].kt_begin) : (act0 ? st[0].kt_begin : st[1].kt_begin);
     const int kt_hi = act0 && act1 ? max(st[0].kt_end, st[1].kt_end) : (act0 ? st[0].kt_end : st[1].kt_end);
     const int n = kt_hi - kt_lo;
+    // Both streams start at the CTA's first key tile (with a sliding window the later rows' stream then sees one
+    // fully masked tile, which contributes exact zeros): an issuer that skipped leading tiles would have to test
+    // ring barriers whose phase it has not followed.
+    if (act0) st[0].kt_begin = kt_lo;
+    if (act1) st[1].kt_begin = kt_lo;
     // both streams of a CTA read the same KV head (pair_heads pairs lie inside one KV group)
     const int kvh = PAGED ? st[act0 ? 0 : 1].head / p.group : st[act0 ? 0 : 1].head;
 
@@ -133,20 +160,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int i = 0; i < KS; ++i) {
-            mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
-        }
-        for (int i = 0; i < VS; ++i) {
-            mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
-        }
-        for (int i = 0; i < 4; ++i) {
-            mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
-        }
-        mbar_init(&o_ready[0], 1);
-        mbar_init(&o_ready[1], 1);
+        for (int i = 0; i < KB; ++i) mbar_init(&k_full[i], 1);
+        for (int i = 0; i < VS; ++i) mbar_init(&v_full[i], 1);
+        for (int i = 0; i < 2 * SR; ++i) mbar_init(&s_full[i], 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&o_ready[i], 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 128);
+        mbar_init(&sm_done[0], 128);
+        mbar_init(&sm_done[1], 128);
         mbar_fence_init();
     }
     if (warp == 9) {
@@ -157,6 +177,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
+
+    // 384 threads start with 168 registers each; the data-movement / issue warpgroup keeps 40 and the two softmax
+    // warpgroups take the rest (256 * 232 + 128 * 40 = 384 * 168), so a 128-key S row fits in registers
+    if (warp >= 8) setmaxnreg_dec<40>();
 
     if (warp == 8) {
         // ------------------------------------------------ Q + K producer
@@ -173,11 +197,12 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                     b * p.tokens + st[s].q0, q_full);
         }
         const int oob_row = p.num_pages * p.kv_heads * p.page_size;
-        for (int j = 0; j < n; ++j) {
+        int g = 0;  // running block index over the whole CTA: ring slot g % KB, phase (g / KB) & 1
+        bool alive = true;
+        for (int j = 0; j < n && alive; ++j) {
             const int k0 = (kt_lo + j) * BN;
-            const int ks = j % KS;
             int y = oob_row;
-            if (PAGED && lane < 4) {
+            if (PAGED && lane < 8) {
                 const int token = k0 + lane * 16;
                 const int slot = token / p.page_size;
                 if (token < kv_total && slot < p.max_pages) {
@@ -188,30 +213,41 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         atomicOr(p.status, INF_STATUS_BAD_PAGE);
                 }
             }
-            int ok = 1;
-            if (lane == 0) ok = mbar_wait(&k_empty[ks], (((uint32_t)(j / KS)) & 1u) ^ 1u) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) {
-                if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
-                break;
-            }
-            const int y0 = __shfl_sync(0xffffffffu, y, 0), y1 = __shfl_sync(0xffffffffu, y, 1);
-            const int y2 = __shfl_sync(0xffffffffu, y, 2), y3 = __shfl_sync(0xffffffffu, y, 3);
-            if (lane == 0) {
-                uint8_t* dst = sK + ks * L::K_BYTES;
-                mbar_arrive_expect_tx(&k_full[ks], L::K_BYTES);
-                if (PAGED) {
-                    const int ys[4] = {y0, y1, y2, y3};
+            int ys[8];
 #pragma unroll
-                    for (int sub = 0; sub < 4; ++sub)
+            for (int i = 0; i < 8; ++i) ys[i] = __shfl_sync(0xffffffffu, y, i);
 #pragma unroll
-                        for (int blk = 0; blk < DQK / 64; ++blk)
-                            tma_load_2d(dst + blk * BN * 128 + sub * 2048, &tm_k, blk * 64, ys[sub], &k_full[ks]);
-                } else {
-                    // 128 no-rope dims of this head, then the 64-dim rope tail shared by every head
-                    tma_load_3d(dst, &tm_k, 0, kvh, k0, &k_full[ks]);
-                    tma_load_3d(dst + BN * 128, &tm_k, 64, kvh, k0, &k_full[ks]);
-                    if (DQK == 192) tma_load_2d(dst + 2 * BN * 128, &tm_k2, 0, k0, &k_full[ks]);
+            for (int blk = 0; blk < NB; ++blk, ++g) {
+                const int slot = g % KB;
+                int ok = 1;
+                if (lane == 0 && g >= KB) {
+                    // the slot held block g - KB of tile tp: free once every stream that uses tp has finished its QK
+                    const int tp = (g - KB) / NB;
+#pragma unroll
+                    for (int s = 0; s < 2; ++s) {
+                        const int jl = tp - (st[s].kt_begin - kt_lo);
+                        if (ok && jl >= 0 && jl < st[s].kt_end - st[s].kt_begin)
+                            ok = mbar_wait(&s_full[s * SR + jl % SR], ((uint32_t)(jl / SR)) & 1u) ? 1 : 0;
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                    alive = false;
+                    break;
+                }
+                if (lane == 0) {
+                    uint8_t* dst = sK + slot * L::KBLK_BYTES;
+                    mbar_arrive_expect_tx(&k_full[slot], L::KBLK_BYTES);
+                    if (PAGED) {
+#pragma unroll
+                        for (int sub = 0; sub < 8; ++sub)
+                            tma_load_2d(dst + sub * 2048, &tm_k, blk * 64, ys[sub], &k_full[slot]);
+                    } else if (blk < 2) {
+                        tma_load_3d(dst, &tm_k, blk * 64, kvh, k0, &k_full[slot]);  // no-rope dims of this head
+                    } else {
+                        tma_load_2d(dst, &tm_k2, 0, k0, &k_full[slot]);  // the rope tail shared by every head
+                    }
                 }
             }
         }
@@ -223,7 +259,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const int k0 = (kt_lo + j) * BN;
             const int vs = j % VS;
             int y = oob_row;
-            if (PAGED && lane < 4) {
+            if (PAGED && lane < 8) {
                 const int token = k0 + lane * 16;
                 const int slot = token / p.page_size;
                 if (token < kv_total && slot < p.max_pages) {
@@ -232,21 +268,29 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
             }
             int ok = 1;
-            if (lane == 0) ok = mbar_wait(&v_empty[vs], (((uint32_t)(j / VS)) & 1u) ^ 1u) ? 1 : 0;
+            if (lane == 0 && j >= VS) {
+                // the slot held tile j - VS: free once every stream that uses it has retired its PV
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    const int jl = j - VS - (st[s].kt_begin - kt_lo);
+                    if (ok && jl >= 0 && jl < st[s].kt_end - st[s].kt_begin)
+                        ok = mbar_wait(&o_ready[s * 2 + (jl & 1)], ((uint32_t)(jl >> 1)) & 1u) ? 1 : 0;
+                }
+            }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
                 if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
                 break;
             }
-            const int y0 = __shfl_sync(0xffffffffu, y, 0), y1 = __shfl_sync(0xffffffffu, y, 1);
-            const int y2 = __shfl_sync(0xffffffffu, y, 2), y3 = __shfl_sync(0xffffffffu, y, 3);
+            int ys[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ys[i] = __shfl_sync(0xffffffffu, y, i);
             if (lane == 0) {
                 uint8_t* dst = sV + vs * L::V_BYTES;
                 mbar_arrive_expect_tx(&v_full[vs], L::V_BYTES);
                 if (PAGED) {
-                    const int ys[4] = {y0, y1, y2, y3};
 #pragma unroll
-                    for (int sub = 0; sub < 4; ++sub)
+                    for (int sub = 0; sub < 8; ++sub)
 #pragma unroll
                         for (int blk = 0; blk < DV / 64; ++blk)
                             tma_load_2d(dst + blk * BN * 128 + sub * 2048, &tm_v, blk * 64, ys[sub], &v_full[vs]);
@@ -257,128 +301,134 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
             }
         }
-    } else if (warp == 9) {
-        // ------------------------------------------------ MMA issuer (one thread)
-        // Everything this thread does between two MMAs delays the tensor pipe, so descriptors are kept as
-        // precomputed 32-bit words that only receive compile-time offsets, and ring indices and phases are
-        // carried incrementally instead of being recomputed with divisions.
+    } else if (warp == 9 || warp == 11) {
+        // ------------------------------------------------ MMA issuers: warp 9 for stream 0, warp 11 for stream 1
+        // Each stream has its own issuing thread, so a stream that is waiting for its softmax never holds back
+        // the other stream's MMAs; the tensor pipe takes work from whichever stream is ready.  Within a stream
+        // the order is QK(j) | PV(j) | QK(j+1): S is single-buffered (P overwrites it), and MMAs issued by one
+        // thread execute in order, so QK(j+1) cannot overwrite P(j) before PV(j) has read it.  Both issuers walk
+        // every K/V tile the CTA loads; for a tile outside its own stream's range an issuer only hands the ring
+        // slots back (after seeing them filled, which keeps it at most one phase ahead of the other stream).
         if (lane == 0) {
+            const int s = warp == 11 ? 1 : 0;
             constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc_f16(BM, DV, 0, 1);
             constexpr uint32_t hi_k = umma_desc_hi(1024, UMMA_SW128);
-            const uint32_t q_lo[2] = {umma_desc_lo(smem_u32(sQ), 16), umma_desc_lo(smem_u32(sQ) + L::Q_BYTES, 16)};
+            const uint32_t q_lo = umma_desc_lo(smem_u32(sQ) + s * L::Q_BYTES, 16);
             const uint32_t k_lo0 = umma_desc_lo(smem_u32(sK), 16);
             const uint32_t v_lo0 = umma_desc_lo(smem_u32(sV), BN * 128);
-            // per stream: first CTA tile index and tile count, so that "active" and "local index" are cheap
-            const int first[2] = {st[0].kt_begin - kt_lo, st[1].kt_begin - kt_lo};
-            const int count[2] = {st[0].kt_end - st[0].kt_begin, st[1].kt_end - st[1].kt_begin};
-            auto issue_qk = [&](int j, int ks) {
-                const uint32_t k_lo = k_lo0 + (uint32_t)ks * (L::K_BYTES >> 4);
+            const uint32_t s_col = tbase + s * STREAM_COLS + COL_S;
+            const uint32_t o_col = tbase + s * STREAM_COLS + COL_O;
+            const int first = st[s].kt_begin - kt_lo;
+            const int count = st[s].kt_end - st[s].kt_begin;
+            bool ok = true;
+#ifdef INF_KPROF
+            const bool kp_on = s == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+            long long kp_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+            const long long kp_start = clock64();
+#endif
+            if (count > 0) ok = mbar_wait(q_full, 0);
+#pragma unroll 1
+            for (int jl = 0; ok && jl < count; ++jl) {
+                const int j = first + jl;
+                // ---- S = Q K(j)^T, block by block of the K ring
 #pragma unroll
-                for (int s = 0; s < 2; ++s) {
-                    const int jl = j - first[s];
-                    if (jl < 0 || jl >= count[s]) continue;
-                    const uint32_t s_col = tbase + s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
-#pragma unroll
-                    for (int kk = 0; kk < DQK / 16; ++kk) {
-                        const uint32_t a_off = ((kk / 4) * BM * 128 + (kk % 4) * 32) >> 4;
-                        const uint32_t b_off = ((kk / 4) * BN * 128 + (kk % 4) * 32) >> 4;
-                        umma_ss(s_col, umma_desc_pack(q_lo[s] + a_off, hi_k), umma_desc_pack(k_lo + b_off, hi_k),
-                                idesc_qk, kk > 0 ? 1u : 0u);
-                    }
-                    tc_commit(&s_full[s * 2 + (jl & 1)]);
-                }
-                tc_commit(&k_empty[ks]);
-            };
-            bool ok = mbar_wait(q_full, 0);
-            if (ok) ok = mbar_wait(&k_full[0], 0);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0, 0);
-            }
-            int ks_next = KS > 1 ? 1 : 0;
-            uint32_t k_phase = KS > 1 ? 0u : 1u;  // phase of the stage that tile j+1 lands in
-            int vs = 0;
-            uint32_t v_phase = 0u;
-            for (int j = 0; ok && j < n; ++j) {
-                if (j + 1 < n) {
-                    ok = mbar_wait(&k_full[ks_next], k_phase);
+                for (int blk = 0; blk < NB; ++blk) {
+                    const int g = j * NB + blk;
+                    const int slot = g % KB;
+                    KP_T0();
+                    ok = mbar_wait(&k_full[slot], ((uint32_t)(g / KB)) & 1u);
+                    KP_ADD(0);
                     if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(j + 1, ks_next);
-                    if (++ks_next == KS) {
-                        ks_next = 0;
-                        k_phase ^= 1u;
-                    }
+                    const uint32_t k_lo = k_lo0 + (uint32_t)slot * (L::KBLK_BYTES >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_ss(s_col, umma_desc_pack(q_lo + ((blk * BM * 128 + kk * 32) >> 4), hi_k),
+                                umma_desc_pack(k_lo + ((kk * 32) >> 4), hi_k), idesc_qk, (blk > 0 || kk > 0) ? 1u : 0u);
+                    KP_ADD(1);
                 }
-                ok = mbar_wait(&v_full[vs], v_phase);
                 if (!ok) break;
+                tc_commit(&s_full[s * SR + jl % SR]);
+                // ---- O += P V(j)
+                const int vs = j % VS;
+                KP_T0();
+                ok = mbar_wait(&v_full[vs], ((uint32_t)(j / VS)) & 1u);
+                KP_ADD(4);
                 const uint32_t v_lo = v_lo0 + (uint32_t)vs * (L::V_BYTES >> 4);
 #pragma unroll
-                for (int s = 0; s < 2; ++s) {
-                    const int jl = j - first[s];
-                    if (jl < 0 || jl >= count[s]) continue;
-                    ok = mbar_wait(&p_full[s * 2 + (jl & 1)], ((uint32_t)(jl >> 1)) & 1u);
+                for (int h = 0; h < 2; ++h) {  // the two 64-key halves of P arrive separately
+                    if (ok) ok = mbar_wait(&p_full[s * 2 + h], ((uint32_t)jl) & 1u);
+                    KP_ADD(2 + h);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t o_col = tbase + s * STREAM_COLS + COL_O;
-                    const uint32_t p_col = tbase + s * STREAM_COLS + ((jl & 1) ? COL_S1 : COL_S0);
-                    if (jl == 0) {
+                    if (jl == 0 && h == 0) {
 #pragma unroll
-                        for (int kk = 0; kk < BN / 16; ++kk)
-                            umma_ts(o_col, p_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv,
+                        for (int kk = 0; kk < BN / 32; ++kk)
+                            umma_ts(o_col, s_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv,
                                     kk > 0 ? 1u : 0u);
                     } else {
 #pragma unroll
-                        for (int kk = 0; kk < BN / 16; ++kk)
-                            umma_ts(o_col, p_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv, 1u);
+                        for (int kk = h * (BN / 32); kk < (h + 1) * (BN / 32); ++kk)
+                            umma_ts(o_col, s_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv, 1u);
                     }
-                    tc_commit(&o_ready[s]);
+                    KP_ADD(5);
                 }
                 if (!ok) break;
-                tc_commit(&v_empty[vs]);
-                if (++vs == VS) {
-                    vs = 0;
-                    v_phase ^= 1u;
-                }
+                tc_commit(&o_ready[s * 2 + (jl & 1)]);
+                KP_ADD(5);
             }
             if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+#ifdef INF_KPROF
+            if (kp_on && p.kprof) {
+                for (int i = 0; i < 12; ++i) p.kprof[i] = kp_acc[i];
+                p.kprof[6] = clock64() - kp_start;
+                p.kprof[7] = n;
+            }
+#endif
         }
     } else if (warp < 8) {
+        setmaxnreg_inc<232>();
         // ------------------------------------------------ softmax + epilogue: thread = query row of its stream
         const int s = warp >> 2;
         const Stream me = st[s];
         const int n_s = me.kt_end - me.kt_begin;
+        const int n_other = st[s ^ 1].kt_end - st[s ^ 1].kt_begin;
         if (n_s > 0) {
             const int r = tid & 127;
             const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
             const uint32_t col0 = tbase + lane_addr + s * STREAM_COLS;
             const int qpos = past + me.q0 + r;
+            const int first_key = p.window > 0 ? qpos + 1 - p.window : 0;
             float m_used = M_INIT, l = 0.f;
             bool ok = true;
+#ifdef INF_KPROF
+            const bool kp_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid & 127) == 0;
+            long long kp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long kp_start = clock64();
+#endif
             for (int j = 0; j < n_s; ++j) {
                 const int k0 = (me.kt_begin + j) * BN;
-                const uint32_t buf_col = (j & 1) ? COL_S1 : COL_S0;
-                if (!mbar_wait(&s_full[s * 2 + (j & 1)], ((uint32_t)(j >> 1)) & 1u)) {
+                KP_T0();
+                if (!mbar_wait(&s_full[s * SR + j % SR], ((uint32_t)(j / SR)) & 1u)) {
                     ok = false;
                     break;
                 }
+                KP_ADD(0);
                 tc_fence_after();
-                uint32_t sraw[BN];
-                tmem_ld32(col0 + buf_col, sraw);
-                tmem_ld32(col0 + buf_col + 32, sraw + 32);
-                tc_wait_ld();
                 const bool need_mask = (k0 + BN - 1 > past + me.q0) || (k0 + BN > kv_total) ||
                                        (p.window > 0 && k0 < past + me.q0 + BM - p.window);
+                // ---- the whole S row of this tile lives in registers (the softmax warpgroups run with 232 registers)
+                uint32_t sraw[BN];
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) tmem_ld32(col0 + COL_S + c * 32, sraw + c * 32);
+                tc_wait_ld();
                 if (need_mask) {
-                    const int first = p.window > 0 ? qpos + 1 - p.window : 0;
 #pragma unroll
                     for (int i = 0; i < BN; ++i) {
                         const int key = k0 + i;
-                        if (key > qpos || key < first || key >= kv_total) sraw[i] = 0xff800000u;  // -inf
+                        if (key > qpos || key < first_key || key >= kv_total) sraw[i] = 0xff800000u;  // -inf
                     }
                 }
-                // row maximum: eight independent chains, then a short tree (keeps the dependent path short)
                 float mxs[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) mxs[i] = __uint_as_float(sraw[i]);
@@ -387,6 +437,16 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
                                        fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
                 const float m_cand = fmaxf(m_used, mx * p.scale_log2);  // scale > 0, so max and scale commute
+                KP_ADD(1);
+                // The two streams take turns at the exponentials (0, 1, 0, 1, ... while both have tiles left): the
+                // special-function unit is shared, and while one stream is here the other stream's MMAs run.
+                if (s == 0 ? (j >= 1 && j - 1 < n_other) : (j < n_other)) {
+                    if (!mbar_wait(&sm_done[s ^ 1], ((uint32_t)(s == 0 ? j - 1 : j)) & 1u)) {
+                        ok = false;
+                        break;
+                    }
+                }
+                KP_ADD(5);
                 if (j == 0) {
                     m_used = m_cand;
                 } else {
@@ -395,7 +455,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         const float alpha = ex2_approx(m_used - m_cand);
                         m_used = m_cand;
                         l *= alpha;
-                        if (!mbar_wait(&o_ready[s], ((uint32_t)(j - 1)) & 1u)) {
+                        if (!mbar_wait(&o_ready[s * 2 + ((j - 1) & 1)], ((uint32_t)((j - 1) >> 1)) & 1u)) {
                             ok = false;
                             break;
                         }
@@ -412,27 +472,40 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         tc_wait_st();
                     }
                 }
-                // exponentials in two halves of 32 keys; each half of P is stored as soon as it is packed
+                KP_ADD(2);
+                // ---- exponentials; the packed pairs overwrite the front of the same register array, and each
+                //      32-key chunk of P is stored (over S columns this thread has consumed) as soon as it is ready
                 const float neg_m = -m_used;
                 float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t packed[16];
+                for (int c = 0; c < BN / 32; ++c) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[half * 32 + i]), p.scale_log2, neg_m));
-                        const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[half * 32 + i + 1]), p.scale_log2, neg_m));
+                    for (int i = c * 32; i < c * 32 + 32; i += 2) {
+                        const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[i]), p.scale_log2, neg_m));
+                        const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[i + 1]), p.scale_log2, neg_m));
                         sums[(i >> 1) & 3] += p0 + p1;
-                        packed[i / 2] = pack_half2(p0, p1);
+                        sraw[i / 2] = pack_half2(p0, p1);
                     }
-                    tmem_st16(col0 + buf_col + half * 16, packed);
+                    tmem_st16(col0 + COL_S + c * 16, sraw + c * 16);
+                    if (c & 1) {  // a 64-key half of P is complete: its PV MMAs may start while the rest is computed
+                        tc_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(&p_full[s * 2 + (c >> 1)]);
+                    }
                 }
                 l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-                tc_wait_st();
-                tc_fence_before();
-                mbar_arrive(&p_full[s * 2 + (j & 1)]);
+                KP_ADD(3);
+                mbar_arrive(&sm_done[s]);
+                KP_ADD(4);
             }
-            if (ok && !mbar_wait(&o_ready[s], ((uint32_t)(n_s - 1)) & 1u)) ok = false;
+#ifdef INF_KPROF
+            if (kp_on && p.kprof) {
+                for (int i = 0; i < 6; ++i) p.kprof[16 + s * 8 + i] = kp_acc[i];
+                p.kprof[16 + s * 8 + 6] = clock64() - kp_start;
+                p.kprof[16 + s * 8 + 7] = n_s;
+            }
+#endif
+            if (ok && !mbar_wait(&o_ready[s * 2 + ((n_s - 1) & 1)], ((uint32_t)((n_s - 1) >> 1)) & 1u)) ok = false;
             if (!ok) {
                 if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
             } else {
@@ -478,24 +551,43 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (warp == 9) tmem_dealloc(tbase, TMEM_COLS);
 }
 
-template <int DQK, int DV, int KS, int VS, bool PAGED>
+template <int DQK, int DV, int KB, int VS, bool PAGED>
 int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tk2,
                  const CUtensorMap& tv, const FlashParams& p, const char* name) {
-    using L = SmemLayout<DQK, DV, KS, VS>;
+    using L = SmemLayout<DQK, DV, KB, VS>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA per SM");
-    auto kernel = flash_prefill_kernel<DQK, DV, KS, VS, PAGED>;
+    auto kernel = flash_prefill_kernel<DQK, DV, KB, VS, PAGED>;
     if (!(ctx->func_attr_done & attr_bit)) {
         INF_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         ctx->func_attr_done |= attr_bit;
     }
     const int q_tiles = (p.tokens + BM - 1) / BM;
     dim3 grid(p.pair_heads ? p.q_heads / 2 : p.q_heads, p.pair_heads ? q_tiles : (q_tiles + 1) / 2, p.batch);
+#ifdef INF_KPROF
+    FlashParams pp = p;
+    static long long* d_kprof = nullptr;
+    if (!d_kprof) cudaMalloc(&d_kprof, 64 * sizeof(long long));
+    cudaMemsetAsync(d_kprof, 0, 64 * sizeof(long long), ctx->stream);
+    pp.kprof = d_kprof;
+    kernel<<<grid, NUM_THREADS, L::TOTAL, ctx->stream>>>(tq, tk, tk2, tv, pp);
+    long long h[64];
+    cudaMemcpy(h, d_kprof, sizeof(h), cudaMemcpyDeviceToHost);
+    fprintf(stderr, "KPROF %s mma: wait_k %lld issue_qk %lld wait_p0 %lld wait_p1 %lld wait_v %lld issue_pv %lld total %lld tiles %lld\n",
+            name, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7]);
+    for (int s2 = 0; s2 < 2; ++s2)
+        fprintf(stderr, "KPROF %s softmax%d: wait_s %lld pass1 %lld rescale %lld pass2 %lld st+arrive %lld turn %lld total %lld tiles %lld\n",
+                name, s2, h[16 + s2 * 8], h[16 + s2 * 8 + 1], h[16 + s2 * 8 + 2], h[16 + s2 * 8 + 3], h[16 + s2 * 8 + 4], h[16 + s2 * 8 + 5],
+                h[16 + s2 * 8 + 6], h[16 + s2 * 8 + 7]);
+    INF_LAUNCH_CHECK(ctx, name);
+    return INF_OK;
+#else
     {
         inf_prof_scope prof(ctx, name);
         kernel<<<grid, NUM_THREADS, L::TOTAL, ctx->stream>>>(tq, tk, tk2, tv, p);
     }
     INF_LAUNCH_CHECK(ctx, name);
     return INF_OK;
+#endif
 }
 
 }  // namespace
@@ -556,7 +648,7 @@ int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* p
     p.o_ts = (long long)q_heads * 128;
     p.o_bs = (long long)tokens * q_heads * 128;
     p.status = ctx->status;
-    return launch_flash<128, 128, 5, 5, true>(ctx, 2u, tq, tk, tk, tv, p, "flash_prefill_gqa_kernel");
+    return launch_flash<128, 128, 6, 2, true>(ctx, 2u, tq, tk, tk, tv, p, "flash_prefill_gqa_kernel");
 }
 
 extern "C" int32_t inf_gqa_prefill_paged(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
@@ -629,6 +721,6 @@ extern "C" int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q
     p.o_hs = o_hs;
     p.o_bs = 0;
     p.status = ctx->status;
-    if (rope_dim) return launch_flash<192, 128, 3, 3, false>(ctx, 4u, tq, tk, tk2, tv, p, "flash_prefill_mla_kernel");
-    return launch_flash<128, 128, 5, 5, false>(ctx, 8u, tq, tk, tk2, tv, p, "flash_prefill_mha_kernel");
+    if (rope_dim) return launch_flash<192, 128, 4, 2, false>(ctx, 4u, tq, tk, tk2, tv, p, "flash_prefill_mla_kernel");
+    return launch_flash<128, 128, 6, 2, false>(ctx, 8u, tq, tk, tk2, tv, p, "flash_prefill_mha_kernel");
 }

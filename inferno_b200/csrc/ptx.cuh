@@ -210,6 +210,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         : "memory");
 }
 
+// Register re-balancing between warpgroups (every warp of an aligned group of four must execute it; the
+// registers handed out by the increases must have been released by the decreases of the same CTA).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
