@@ -42,7 +42,9 @@ constexpr int NUM_THREADS = 384;
 constexpr float M_INIT = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t STREAM_COLS = 256, COL_S = 0, COL_O = 128;
+// TMEM columns: one S buffer shared by both streams (a stream's softmax copies its S row into registers at
+// once, which frees the buffer for the other stream's next QK), then per stream P (fp16 pairs) and O (fp32).
+constexpr uint32_t COL_S = 0, COL_STREAM0 = 128, STREAM_COLS = 192, COL_P = 0, COL_O = 64;
 
 struct FlashParams {
     int tokens, q_heads, kv_heads, group, batch;
@@ -100,8 +102,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     using L = SmemLayout<DQK, DV, KB, VS>;
     constexpr int NB = DQK / 64;  // 64-column blocks per K tile
     constexpr int SR = (KB + NB - 1) / NB + 1;
-    static_assert(VS == 2, "the o_ready rotation assumes a two-tile V ring");
-    static_assert((1 + KB + VS + 2 * SR + 4 + 4 + 2) * 8 + 4 <= 512, "barrier area");
+    static_assert(VS >= 1 && VS <= 2, "the o_ready rotation covers a V ring of at most two tiles");
+    static_assert((1 + 2 * KB + VS + 2 * SR + 4 + 4 + 2 + 1) * 8 + 4 <= 512, "barrier area");
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = smem + L::OFF_K;
@@ -119,7 +121,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint64_t* p_full = s_full + 2 * SR; // [2][2]: P of keys 0-63 / 64-127 of the current tile is in TMEM
     uint64_t* o_ready = p_full + 4;     // [2][2]: PV of local tile jl has retired (its V tile is consumed)
     uint64_t* sm_done = o_ready + 4;    // [2]: a stream's softmax warpgroup has finished the exponentials of a tile
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm_done + 2);
+    uint64_t* s_free = sm_done + 2;     // [1]: the shared S buffer has been copied into registers (128 arrivals)
+    uint64_t* k_free = s_free + 1;      // [KB]: the last QK that reads this K block has retired
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(k_free + KB);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b = blockIdx.z;
@@ -160,13 +164,17 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int i = 0; i < KB; ++i) mbar_init(&k_full[i], 1);
+        for (int i = 0; i < KB; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_free[i], 1);
+        }
         for (int i = 0; i < VS; ++i) mbar_init(&v_full[i], 1);
         for (int i = 0; i < 2 * SR; ++i) mbar_init(&s_full[i], 1);
         for (int i = 0; i < 4; ++i) mbar_init(&o_ready[i], 1);
         for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 128);
         mbar_init(&sm_done[0], 128);
         mbar_init(&sm_done[1], 128);
+        mbar_init(s_free, 128);
         mbar_fence_init();
     }
     if (warp == 9) {
@@ -220,16 +228,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int blk = 0; blk < NB; ++blk, ++g) {
                 const int slot = g % KB;
                 int ok = 1;
-                if (lane == 0 && g >= KB) {
-                    // the slot held block g - KB of tile tp: free once every stream that uses tp has finished its QK
-                    const int tp = (g - KB) / NB;
-#pragma unroll
-                    for (int s = 0; s < 2; ++s) {
-                        const int jl = tp - (st[s].kt_begin - kt_lo);
-                        if (ok && jl >= 0 && jl < st[s].kt_end - st[s].kt_begin)
-                            ok = mbar_wait(&s_full[s * SR + jl % SR], ((uint32_t)(jl / SR)) & 1u) ? 1 : 0;
-                    }
-                }
+                if (lane == 0 && g >= KB)  // the slot held block g - KB: free once the last QK that reads it has retired
+                    ok = mbar_wait(&k_free[slot], ((uint32_t)(g / KB - 1)) & 1u) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
@@ -301,88 +301,130 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
             }
         }
-    } else if (warp == 9 || warp == 11) {
-        // ------------------------------------------------ MMA issuers: warp 9 for stream 0, warp 11 for stream 1
-        // Each stream has its own issuing thread, so a stream that is waiting for its softmax never holds back
-        // the other stream's MMAs; the tensor pipe takes work from whichever stream is ready.  Within a stream
-        // the order is QK(j) | PV(j) | QK(j+1): S is single-buffered (P overwrites it), and MMAs issued by one
-        // thread execute in order, so QK(j+1) cannot overwrite P(j) before PV(j) has read it.  Both issuers walk
-        // every K/V tile the CTA loads; for a tile outside its own stream's range an issuer only hands the ring
-        // slots back (after seeing them filled, which keeps it at most one phase ahead of the other stream).
+    } else if (warp == 9) {
+        // ------------------------------------------------ QK issuer (one thread): S_s(j) = Q_s K(j)^T into the
+        // shared S buffer, in the fixed order (s, j) = (0,0) (1,0) (0,1) (1,1) ...  A QK only needs the buffer
+        // (the previous S has been copied out by its softmax warpgroup) and its K blocks: it depends neither on
+        // the same stream's softmax nor on its PV, so the next S is normally waiting when a softmax finishes.
         if (lane == 0) {
-            const int s = warp == 11 ? 1 : 0;
             constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, 0, 0);
-            constexpr uint32_t idesc_pv = umma_idesc_f16(BM, DV, 0, 1);
             constexpr uint32_t hi_k = umma_desc_hi(1024, UMMA_SW128);
-            const uint32_t q_lo = umma_desc_lo(smem_u32(sQ) + s * L::Q_BYTES, 16);
             const uint32_t k_lo0 = umma_desc_lo(smem_u32(sK), 16);
-            const uint32_t v_lo0 = umma_desc_lo(smem_u32(sV), BN * 128);
-            const uint32_t s_col = tbase + s * STREAM_COLS + COL_S;
-            const uint32_t o_col = tbase + s * STREAM_COLS + COL_O;
-            const int first = st[s].kt_begin - kt_lo;
-            const int count = st[s].kt_end - st[s].kt_begin;
+            const uint32_t s_col = tbase + COL_S;
             bool ok = true;
 #ifdef INF_KPROF
-            const bool kp_on = s == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-            long long kp_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+            const bool kp_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+            long long kp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             const long long kp_start = clock64();
 #endif
-            if (count > 0) ok = mbar_wait(q_full, 0);
+            ok = mbar_wait(q_full, 0);
+            uint32_t seq = 0;  // number of S tiles produced so far
+            const int first[2] = {st[0].kt_begin - kt_lo, st[1].kt_begin - kt_lo};
+            const int count[2] = {st[0].kt_end - st[0].kt_begin, st[1].kt_end - st[1].kt_begin};
+            const uint32_t q_los[2] = {umma_desc_lo(smem_u32(sQ), 16), umma_desc_lo(smem_u32(sQ) + L::Q_BYTES, 16)};
 #pragma unroll 1
-            for (int jl = 0; ok && jl < count; ++jl) {
-                const int j = first + jl;
-                // ---- S = Q K(j)^T, block by block of the K ring
-#pragma unroll
-                for (int blk = 0; blk < NB; ++blk) {
-                    const int g = j * NB + blk;
-                    const int slot = g % KB;
+            for (int j = 0; ok && j < n; ++j) {
+#pragma unroll 1
+                for (int s = 0; s < 2; ++s) {
+                    const int jl = j - first[s];
+                    if (jl < 0 || jl >= count[s]) continue;
                     KP_T0();
-                    ok = mbar_wait(&k_full[slot], ((uint32_t)(g / KB)) & 1u);
-                    KP_ADD(0);
-                    if (!ok) break;
-                    const uint32_t k_lo = k_lo0 + (uint32_t)slot * (L::KBLK_BYTES >> 4);
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_ss(s_col, umma_desc_pack(q_lo + ((blk * BM * 128 + kk * 32) >> 4), hi_k),
-                                umma_desc_pack(k_lo + ((kk * 32) >> 4), hi_k), idesc_qk, (blk > 0 || kk > 0) ? 1u : 0u);
-                    KP_ADD(1);
-                }
-                if (!ok) break;
-                tc_commit(&s_full[s * SR + jl % SR]);
-                // ---- O += P V(j)
-                const int vs = j % VS;
-                KP_T0();
-                ok = mbar_wait(&v_full[vs], ((uint32_t)(j / VS)) & 1u);
-                KP_ADD(4);
-                const uint32_t v_lo = v_lo0 + (uint32_t)vs * (L::V_BYTES >> 4);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {  // the two 64-key halves of P arrive separately
-                    if (ok) ok = mbar_wait(&p_full[s * 2 + h], ((uint32_t)jl) & 1u);
-                    KP_ADD(2 + h);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (jl == 0 && h == 0) {
-#pragma unroll
-                        for (int kk = 0; kk < BN / 32; ++kk)
-                            umma_ts(o_col, s_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv,
-                                    kk > 0 ? 1u : 0u);
-                    } else {
-#pragma unroll
-                        for (int kk = h * (BN / 32); kk < (h + 1) * (BN / 32); ++kk)
-                            umma_ts(o_col, s_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv, 1u);
+                    if (seq > 0) {
+                        ok = mbar_wait(s_free, (seq - 1) & 1u);
+                        if (!ok) break;
+                        tc_fence_after();
                     }
-                    KP_ADD(5);
+                    KP_ADD(0);
+                    const uint32_t q_lo = q_los[s];
+                    // K blocks go back to the producer one by one, after the last stream that reads them
+                    const int jl1 = j - first[1];
+                    const bool last_user = s == 1 || jl1 < 0 || jl1 >= count[1];
+#pragma unroll
+                    for (int blk = 0; blk < NB; ++blk) {
+                        const int g = j * NB + blk;
+                        const int slot = g % KB;
+                        ok = mbar_wait(&k_full[slot], ((uint32_t)(g / KB)) & 1u);
+                        KP_ADD(1);
+                        if (!ok) break;
+                        const uint32_t k_lo = k_lo0 + (uint32_t)slot * (L::KBLK_BYTES >> 4);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_ss(s_col, umma_desc_pack(q_lo + ((blk * BM * 128 + kk * 32) >> 4), hi_k),
+                                    umma_desc_pack(k_lo + ((kk * 32) >> 4), hi_k), idesc_qk, (blk > 0 || kk > 0) ? 1u : 0u);
+                        if (last_user) tc_commit(&k_free[slot]);
+                        KP_ADD(2);
+                    }
+                    if (!ok) break;
+                    tc_commit(&s_full[s * SR + jl % SR]);
+                    ++seq;
                 }
-                if (!ok) break;
-                tc_commit(&o_ready[s * 2 + (jl & 1)]);
-                KP_ADD(5);
             }
             if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
 #ifdef INF_KPROF
             if (kp_on && p.kprof) {
-                for (int i = 0; i < 12; ++i) p.kprof[i] = kp_acc[i];
+                for (int i = 0; i < 6; ++i) p.kprof[i] = kp_acc[i];
                 p.kprof[6] = clock64() - kp_start;
                 p.kprof[7] = n;
+            }
+#endif
+        }
+    } else if (warp == 11) {
+        // ------------------------------------------------ PV issuer (one thread): O_s += P_s V(j), in the order the
+        // softmax warpgroups produce P (stream 0 then stream 1 of every tile), each 64-key half as it arrives.
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = umma_idesc_f16(BM, DV, 0, 1);
+            constexpr uint32_t hi_k = umma_desc_hi(1024, UMMA_SW128);
+            const uint32_t v_lo0 = umma_desc_lo(smem_u32(sV), BN * 128);
+            bool ok = true;
+            const int first[2] = {st[0].kt_begin - kt_lo, st[1].kt_begin - kt_lo};
+            const int count[2] = {st[0].kt_end - st[0].kt_begin, st[1].kt_end - st[1].kt_begin};
+#ifdef INF_KPROF
+            const bool kp_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+            long long kp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long kp_start = clock64();
+#endif
+#pragma unroll 1
+            for (int j = 0; ok && j < n; ++j) {
+                const int vs = j % VS;
+                KP_T0();
+                ok = mbar_wait(&v_full[vs], ((uint32_t)(j / VS)) & 1u);
+                KP_ADD(0);
+                if (!ok) break;
+                const uint32_t v_lo = v_lo0 + (uint32_t)vs * (L::V_BYTES >> 4);
+#pragma unroll 1
+                for (int s = 0; s < 2; ++s) {
+                    const int jl = j - first[s];
+                    if (jl < 0 || jl >= count[s]) continue;
+                    const uint32_t p_col = tbase + COL_STREAM0 + s * STREAM_COLS + COL_P;
+                    const uint32_t o_col = tbase + COL_STREAM0 + s * STREAM_COLS + COL_O;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {  // the two 64-key halves of P arrive separately
+                        ok = mbar_wait(&p_full[s * 2 + h], ((uint32_t)jl) & 1u);
+                        KP_ADD(1);
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (h == 0) {
+                            const uint32_t acc0 = jl > 0 ? 1u : 0u;
+#pragma unroll
+                            for (int kk = 0; kk < BN / 32; ++kk)
+                                umma_ts(o_col, p_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv,
+                                        kk > 0 ? 1u : acc0);
+                        } else {
+#pragma unroll
+                            for (int kk = BN / 32; kk < BN / 16; ++kk)
+                                umma_ts(o_col, p_col + kk * 8, umma_desc_pack(v_lo + kk * (2048 >> 4), hi_k), idesc_pv, 1u);
+                        }
+                        KP_ADD(2);
+                    }
+                    if (!ok) break;
+                    tc_commit(&o_ready[s * 2 + (jl & 1)]);
+                }
+            }
+            if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+#ifdef INF_KPROF
+            if (kp_on && p.kprof) {
+                for (int i = 0; i < 6; ++i) p.kprof[8 + i] = kp_acc[i];
+                p.kprof[8 + 6] = clock64() - kp_start;
             }
 #endif
         }
@@ -396,7 +438,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (n_s > 0) {
             const int r = tid & 127;
             const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-            const uint32_t col0 = tbase + lane_addr + s * STREAM_COLS;
+            const uint32_t col_s = tbase + lane_addr + COL_S;
+            const uint32_t col0 = tbase + lane_addr + COL_STREAM0 + s * STREAM_COLS;
             const int qpos = past + me.q0 + r;
             const int first_key = p.window > 0 ? qpos + 1 - p.window : 0;
             float m_used = M_INIT, l = 0.f;
@@ -420,8 +463,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 // ---- the whole S row of this tile lives in registers (the softmax warpgroups run with 232 registers)
                 uint32_t sraw[BN];
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) tmem_ld32(col0 + COL_S + c * 32, sraw + c * 32);
+                for (int c = 0; c < BN / 32; ++c) tmem_ld32(col_s + c * 32, sraw + c * 32);
                 tc_wait_ld();
+                tc_fence_before();
+                mbar_arrive(s_free);  // the next QK (of either stream) may overwrite the buffer
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < BN; ++i) {
@@ -438,15 +483,14 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                        fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
                 const float m_cand = fmaxf(m_used, mx * p.scale_log2);  // scale > 0, so max and scale commute
                 KP_ADD(1);
-                // The two streams take turns at the exponentials (0, 1, 0, 1, ... while both have tiles left): the
-                // special-function unit is shared, and while one stream is here the other stream's MMAs run.
-                if (s == 0 ? (j >= 1 && j - 1 < n_other) : (j < n_other)) {
-                    if (!mbar_wait(&sm_done[s ^ 1], ((uint32_t)(s == 0 ? j - 1 : j)) & 1u)) {
+                // ---- P(j) will overwrite P(j-1) and O may be rescaled: PV(j-1) must have retired (it normally has)
+                if (j > 0) {
+                    if (!mbar_wait(&o_ready[s * 2 + ((j - 1) & 1)], ((uint32_t)((j - 1) >> 1)) & 1u)) {
                         ok = false;
                         break;
                     }
+                    tc_fence_after();
                 }
-                KP_ADD(5);
                 if (j == 0) {
                     m_used = m_cand;
                 } else {
@@ -455,11 +499,6 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         const float alpha = ex2_approx(m_used - m_cand);
                         m_used = m_cand;
                         l *= alpha;
-                        if (!mbar_wait(&o_ready[s * 2 + ((j - 1) & 1)], ((uint32_t)((j - 1) >> 1)) & 1u)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
 #pragma unroll
                         for (int c = 0; c < DV / 32; ++c) {
                             uint32_t o[32];
@@ -473,8 +512,17 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     }
                 }
                 KP_ADD(2);
+                // The two streams take turns at the exponentials (0, 1, 0, 1, ... while both have tiles left): the
+                // special-function unit is shared, and the turn order is the order in which the issuers serve them.
+                if (s == 0 ? (j >= 1 && j - 1 < n_other) : (j < n_other)) {
+                    if (!mbar_wait(&sm_done[s ^ 1], ((uint32_t)(s == 0 ? j - 1 : j)) & 1u)) {
+                        ok = false;
+                        break;
+                    }
+                }
+                KP_ADD(5);
                 // ---- exponentials; the packed pairs overwrite the front of the same register array, and each
-                //      32-key chunk of P is stored (over S columns this thread has consumed) as soon as it is ready
+                //      32-key chunk of P is stored as soon as it is ready
                 const float neg_m = -m_used;
                 float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -486,7 +534,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         sums[(i >> 1) & 3] += p0 + p1;
                         sraw[i / 2] = pack_half2(p0, p1);
                     }
-                    tmem_st16(col0 + COL_S + c * 16, sraw + c * 16);
+                    tmem_st16(col0 + COL_P + c * 16, sraw + c * 16);
                     if (c & 1) {  // a 64-key half of P is complete: its PV MMAs may start while the rest is computed
                         tc_wait_st();
                         tc_fence_before();
@@ -572,8 +620,8 @@ int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const C
     kernel<<<grid, NUM_THREADS, L::TOTAL, ctx->stream>>>(tq, tk, tk2, tv, pp);
     long long h[64];
     cudaMemcpy(h, d_kprof, sizeof(h), cudaMemcpyDeviceToHost);
-    fprintf(stderr, "KPROF %s mma: wait_k %lld issue_qk %lld wait_p0 %lld wait_p1 %lld wait_v %lld issue_pv %lld total %lld tiles %lld\n",
-            name, h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7]);
+    fprintf(stderr, "KPROF %s qk issuer: wait_free %lld wait_k %lld issue %lld total %lld tiles %lld\n", name, h[0], h[1], h[2], h[6], h[7]);
+    fprintf(stderr, "KPROF %s pv issuer: wait_v %lld wait_p %lld issue %lld total %lld\n", name, h[8], h[9], h[10], h[14]);
     for (int s2 = 0; s2 < 2; ++s2)
         fprintf(stderr, "KPROF %s softmax%d: wait_s %lld pass1 %lld rescale %lld pass2 %lld st+arrive %lld turn %lld total %lld tiles %lld\n",
                 name, s2, h[16 + s2 * 8], h[16 + s2 * 8 + 1], h[16 + s2 * 8 + 2], h[16 + s2 * 8 + 3], h[16 + s2 * 8 + 4], h[16 + s2 * 8 + 5],
