@@ -251,6 +251,28 @@ int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, const inf_mla_p
                                 const inf_page_table* table, int32_t tokens, int32_t heads, int32_t max_len,
                                 float scale, void* out, int32_t out_dtype);
 
+/* Per-head Q8_0 matvec (kernel q8_0_packed_heads_matvec_f32_kernel, crates/backend/src/metal/kernels/
+ * q2_kernels.metal:3146; host crates/backend/src/metal/q2.rs:2656): weights (device) [heads][out_features]
+ * [in_features] in Q8_0 row blocks of 34 bytes (little-endian f16 scale, 32 signed quants); input f32
+ * [rows, heads, in_features]; output f32 [rows, heads, out_features].  in_features % 32 == 0. */
+int32_t inf_q8_0_packed_heads_matvec(inf_ctx* ctx, const void* weights, const float* input, int32_t rows,
+                                     int32_t heads, int32_t in_features, int32_t out_features, float* output);
+
+/* q8_0_absorbed_mla_device (backend.rs:1982, 7695; driver crates/backend/src/metal/device.rs:3501-3585) as one
+ * call: q_latent = K_b . q_no_rope, absorbed MLA attention over the paged cache, out = V_b . context.
+ * k_b_weights / v_b_weights: device copies of the Q8_0 bytes, [heads][latent][q_no_rope_dim] and
+ * [heads][value_dim][latent].  q_no_rope f32 [batch, tokens, heads, q_no_rope_dim], q_rope f32 [batch, tokens,
+ * heads, rope].  current_latent f32 [batch, tokens, latent] and current_rope f32 [batch, tokens, rope] are the
+ * already post-processed rows of this call's tokens: when given they are stored RNE-fp16 at slots
+ * lens[b] .. lens[b]+tokens-1 first; pass both null when inf_mla_kv_postprocess_append has stored them.
+ * lens[b] = rows cached before the call; row t sees rows 0 .. lens[b]+t; score scale 1/sqrt(qk_head_dim),
+ * qk_head_dim = q_no_rope_dim + rope (checked, as backend.rs:7767).  out f32 [batch, tokens, heads, value_dim]. */
+int32_t inf_q8_0_absorbed_mla(inf_ctx* ctx, const void* k_b_weights, const void* v_b_weights, const float* q_no_rope,
+                              const float* q_rope, const float* current_latent, const float* current_rope,
+                              const inf_mla_pool* pool, const inf_page_table* table, int32_t tokens, int32_t heads,
+                              int32_t q_no_rope_dim, int32_t value_dim, int32_t qk_head_dim, int32_t max_len,
+                              float* out);
+
 /* Causal attention over expanded heads = the reference's MLA prefill
  * (causal_sequence_attention_device backend.rs:2028; kernel attention_kernels.metal:723).
  * fp16 tensors with element strides: q [tokens][heads][nope+rope], k_nope [tokens][heads][nope],

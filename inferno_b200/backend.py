@@ -311,6 +311,26 @@ class CudaBackend:
                                                            C.byref(table.desc), T, H, max_len, scale, _ptr(out), dt))
         return out if ok else None
 
+    def q8_0_packed_heads_matvec(self, weights_u8, x, out_features: int):
+        """Per-head Q8_0 matvec (q2_kernels.metal:3146): weights uint8 device tensor, x f32 [rows, heads, in]."""
+        rows, heads, in_features = x.shape
+        out = torch.empty((rows, heads, out_features), dtype=torch.float32, device=self.device)
+        self._check(self._lib.inf_q8_0_packed_heads_matvec(self._ctx, _ptr(weights_u8), _ptr(x), rows, heads,
+                                                           in_features, out_features, _ptr(out)))
+        return out
+
+    def q8_0_absorbed_mla_device(self, k_b_weights, v_b_weights, q_no_rope, q_rope, current_latent, current_rope,
+                                 pool: MlaPool, table: PageTable, qk_head_dim: int, value_dim: int, max_len: int):
+        """q8_0_absorbed_mla_device (backend.rs:1982): returns [B, T, H, value_dim] f32, or None when the pool's
+        geometry has no device path.  current_latent / current_rope may be None when the rows are already stored."""
+        B, T, H, qn = q_no_rope.shape
+        out = torch.empty((B, T, H, value_dim), dtype=torch.float32, device=self.device)
+        ok = self._check(self._lib.inf_q8_0_absorbed_mla(
+            self._ctx, _ptr(k_b_weights), _ptr(v_b_weights), _ptr(q_no_rope), _ptr(q_rope), _ptr(current_latent),
+            _ptr(current_rope), C.byref(pool.desc), C.byref(table.desc), T, H, qn, value_dim, qk_head_dim, max_len,
+            _ptr(out)))
+        return out if ok else None
+
     def causal_sequence_attention_device(self, q, k_nope, k_rope, v, scale: float, out_dtype=torch.float16):
         """causal_sequence_attention_device (backend.rs:2028) for MLA prefill: q [T,H,dn+dr], k_nope [T,H,dn],
         k_rope [T,dr] shared by the heads (or None), v [T,H,dv]; any token/head strides, unit inner stride."""

@@ -1,0 +1,193 @@
+// q8_0_absorbed_mla_device (crates/backend/src/backend.rs:1982, 7695) as one C-ABI call, in the order the
+// reference encodes it (crates/backend/src/metal/device.rs:3537-3584):
+//     q_latent[h] = K_b[h] . q_no_rope[h]                     Q8_0 per-head matvec
+//     context     = absorbed MLA attention over the paged latent / rope cache   (mla_decode.cu)
+//     out[h]      = V_b[h] . context[h]                       Q8_0 per-head matvec
+// plus the per-head matvec itself (kernel q8_0_packed_heads_matvec_f32_kernel,
+// crates/backend/src/metal/kernels/q2_kernels.metal:3146).
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+size_t inf_mla_decode_scratch_bytes(const inf_ctx* ctx, int batch, int tokens, int heads, int max_len);
+int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool, const inf_page_table* table,
+                          int tokens, int heads, int max_len, float scale, void* out, int out_dtype, size_t ws_offset);
+
+namespace {
+
+constexpr int Q8_BLOCK_VALUES = 32;  // q2_kernels.metal:13
+constexpr int Q8_BLOCK_BYTES = 34;   // q2_kernels.metal:14: little-endian f16 scale, then 32 signed quants
+constexpr int MV_WARPS = 8;
+constexpr int MV_ROWS = 4;  // input rows that share one pass over a weight row
+
+// Weight [heads][out_features][in_features] in Q8_0 row blocks, input f32 [rows][heads][in_features].
+// One warp per (head, output feature); lane = value inside a block, as in the reference kernel, so a warp
+// reads each 34-byte block with one coalesced request.  HBM-bound: every weight byte is read once per
+// MV_ROWS input rows.  out element (row, head, o) goes to out[(row * heads + head) * out_stride + o].
+template <typename OutT>
+__global__ void __launch_bounds__(MV_WARPS * 32)
+q8_0_heads_matvec_kernel(const uint8_t* __restrict__ weights, const float* __restrict__ input, OutT* __restrict__ out,
+                         int rows, int heads, int in_features, int out_features, long long out_stride) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int o = blockIdx.x * MV_WARPS + warp;
+    const int head = blockIdx.y;
+    const int row0 = blockIdx.z * MV_ROWS;
+    if (o >= out_features) return;
+    const int blocks_per_row = in_features / Q8_BLOCK_VALUES;
+    const uint8_t* wrow = weights + ((size_t)head * out_features + o) * blocks_per_row * Q8_BLOCK_BYTES;
+    float sum[MV_ROWS];
+#pragma unroll
+    for (int r = 0; r < MV_ROWS; ++r) sum[r] = 0.f;
+#pragma unroll 4
+    for (int blk = 0; blk < blocks_per_row; ++blk) {
+        const uint8_t* bp = wrow + (size_t)blk * Q8_BLOCK_BYTES;
+        const float d = __half2float(__ushort_as_half((unsigned short)(bp[0] | (bp[1] << 8))));
+        const float w = d * (float)(signed char)bp[2 + lane];
+#pragma unroll
+        for (int r = 0; r < MV_ROWS; ++r)
+            if (row0 + r < rows)
+                sum[r] += input[((size_t)(row0 + r) * heads + head) * in_features + blk * Q8_BLOCK_VALUES + lane] * w;
+    }
+#pragma unroll
+    for (int r = 0; r < MV_ROWS; ++r) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], off);
+        if (lane == 0 && row0 + r < rows) out[((size_t)(row0 + r) * heads + head) * out_stride + o] = OutT(sum[r]);
+    }
+}
+
+// q_rope f32 [rows*heads][rope] -> fp16 columns [latent, latent+rope) of the absorbed query rows.
+__global__ void pack_q_rope_kernel(const float* __restrict__ q_rope, __half* __restrict__ q_abs, long long n, int rope,
+                                   int row_width, int col0) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long r = i / rope;
+    const int d = (int)(i % rope);
+    q_abs[r * row_width + col0 + d] = __float2half_rn(q_rope[i]);
+}
+
+// Already post-processed latent / rope rows (the two outputs of mla_kv_postprocess_device) stored RNE-fp16 at
+// logical slot lens[b] + t: the device-side form of the reference's row blits into the paged window
+// (crates/runtime/src/lib.rs:4963-5045).
+__global__ void append_latent_rows_kernel(const float* __restrict__ latent, const float* __restrict__ rope,
+                                          __half* __restrict__ pool, int num_pages, int page_size,
+                                          const int* __restrict__ pages, const int* __restrict__ lens, int max_pages,
+                                          int tokens, int L, int R, int* __restrict__ status) {
+    const long long row = blockIdx.x;
+    const int b = (int)(row / tokens), t = (int)(row % tokens);
+    const int position = lens[b] + t;
+    const int slot = position / page_size;
+    if (position < 0 || slot >= max_pages) {
+        if (threadIdx.x == 0) atomicOr(status, INF_STATUS_BAD_LEN);
+        return;
+    }
+    const int page = pages[(long long)b * max_pages + slot];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(status, INF_STATUS_BAD_PAGE);
+        return;
+    }
+    __half* dst = pool + ((long long)page * page_size + position % page_size) * (L + R);
+    for (int d = threadIdx.x; d < L; d += blockDim.x) dst[d] = __float2half_rn(latent[row * L + d]);
+    for (int d = threadIdx.x; d < R; d += blockDim.x) dst[L + d] = __float2half_rn(rope[row * R + d]);
+}
+
+template <typename OutT>
+int launch_matvec(inf_ctx* ctx, const void* weights, const float* input, OutT* out, int rows, int heads, int in_features,
+                  int out_features, long long out_stride, const char* name) {
+    dim3 grid((out_features + MV_WARPS - 1) / MV_WARPS, heads, (rows + MV_ROWS - 1) / MV_ROWS);
+    {
+        inf_prof_scope prof(ctx, name);
+        q8_0_heads_matvec_kernel<OutT><<<grid, MV_WARPS * 32, 0, ctx->stream>>>(
+            (const uint8_t*)weights, input, out, rows, heads, in_features, out_features, out_stride);
+    }
+    INF_LAUNCH_CHECK(ctx, name);
+    return INF_OK;
+}
+
+int check_matvec_dims(inf_ctx* ctx, long long rows, int heads, int in_features, int out_features, const char* what) {
+    // crates/backend/src/metal/q2.rs:2668-2677
+    if (rows <= 0 || heads <= 0 || in_features <= 0 || out_features <= 0)
+        return inf_fail(ctx, INF_E_BACKEND, "%s: packed-head Q8_0 matvec dimensions must be positive", what);
+    if (in_features % Q8_BLOCK_VALUES != 0)
+        return inf_fail(ctx, INF_E_BACKEND, "%s: packed-head Q8_0 input width %d must be divisible by %d", what,
+                        in_features, Q8_BLOCK_VALUES);
+    if (heads > 65535 || (rows + MV_ROWS - 1) / MV_ROWS > 65535)
+        return inf_fail(ctx, INF_E_SHAPE, "%s: %d heads x %lld rows exceed the launch grid", what, heads, rows);
+    return INF_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t inf_q8_0_packed_heads_matvec(inf_ctx* ctx, const void* weights, const float* input, int32_t rows,
+                                                int32_t heads, int32_t in_features, int32_t out_features,
+                                                float* output) {
+    INF_CHECK_CTX(ctx);
+    if (!weights || !input || !output) return inf_fail(ctx, INF_E_ARG, "q8_0_packed_heads_matvec: null pointer");
+    int rc = check_matvec_dims(ctx, rows, heads, in_features, out_features, "q8_0_packed_heads_matvec");
+    if (rc != INF_OK) return rc;
+    return launch_matvec<float>(ctx, weights, input, output, rows, heads, in_features, out_features, out_features,
+                                "q8_0_heads_matvec_kernel");
+}
+
+extern "C" int32_t inf_q8_0_absorbed_mla(inf_ctx* ctx, const void* k_b_weights, const void* v_b_weights,
+                                         const float* q_no_rope, const float* q_rope, const float* current_latent,
+                                         const float* current_rope, const inf_mla_pool* pool,
+                                         const inf_page_table* table, int32_t tokens, int32_t heads,
+                                         int32_t q_no_rope_dim, int32_t value_dim, int32_t qk_head_dim,
+                                         int32_t max_len, float* out) {
+    INF_CHECK_CTX(ctx);
+    if (!k_b_weights || !v_b_weights || !q_no_rope || !q_rope || !pool || !table || !out)
+        return inf_fail(ctx, INF_E_ARG, "q8_0_absorbed_mla: null pointer");
+    if ((current_latent == nullptr) != (current_rope == nullptr))
+        return inf_fail(ctx, INF_E_ARG, "q8_0_absorbed_mla: current latent and rope rows come together or not at all");
+    if (!pool->rows) return inf_fail(ctx, INF_E_ARG, "q8_0_absorbed_mla: pool has no storage");
+    if (pool->latent_dim != 512 || pool->rope_dim != 64 || pool->page_size != 64) return INF_UNSUPPORTED;
+    const int L = pool->latent_dim, R = pool->rope_dim;
+    if (tokens <= 0 || heads <= 0 || max_len <= 0)
+        return inf_fail(ctx, INF_E_SHAPE, "q8_0_absorbed_mla: sizes must be positive");
+    if (qk_head_dim != q_no_rope_dim + R)  // backend.rs:7767-7771
+        return inf_fail(ctx, INF_E_BACKEND, "absorbed MLA qk_head_dim %d must equal no-RoPE %d + RoPE %d", qk_head_dim,
+                        q_no_rope_dim, R);
+    const long long rows = (long long)table->batch * tokens;
+    int rc = check_matvec_dims(ctx, rows, heads, q_no_rope_dim, L, "absorbed MLA K_b");
+    if (rc != INF_OK) return rc;
+    rc = check_matvec_dims(ctx, rows, heads, L, value_dim, "absorbed MLA V_b");
+    if (rc != INF_OK) return rc;
+    rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "q8_0_absorbed_mla");
+    if (rc != INF_OK) return rc;
+    if (table->host_lens)
+        for (int b = 0; b < table->batch; ++b)
+            if (table->host_lens[b] + tokens > max_len)
+                return inf_fail(ctx, INF_E_SHAPE, "q8_0_absorbed_mla: sequence %d reaches %d rows, beyond max_len %d", b,
+                                table->host_lens[b] + tokens, max_len);
+
+    // scratch: absorbed query rows (fp16), attended latent (f32), then the decode kernel's split partials
+    const size_t q_bytes = ((size_t)rows * heads * (L + R) * sizeof(__half) + 255) & ~(size_t)255;
+    const size_t ctx_bytes = ((size_t)rows * heads * L * sizeof(float) + 255) & ~(size_t)255;
+    const size_t total = q_bytes + ctx_bytes + inf_mla_decode_scratch_bytes(ctx, table->batch, tokens, heads, max_len);
+    rc = inf_ensure_workspace(ctx, total);
+    if (rc != INF_OK) return rc;
+    __half* q_abs = (__half*)ctx->workspace;
+    float* context = (float*)((char*)ctx->workspace + q_bytes);
+
+    if (current_latent) {
+        append_latent_rows_kernel<<<(unsigned)rows, 128, 0, ctx->stream>>>(
+            current_latent, current_rope, (__half*)pool->rows, pool->num_pages, pool->page_size, table->pages,
+            table->lens, table->max_pages, tokens, L, R, ctx->status);
+        INF_LAUNCH_CHECK(ctx, "append_latent_rows_kernel");
+    }
+    rc = launch_matvec<__half>(ctx, k_b_weights, q_no_rope, q_abs, (int)rows, heads, q_no_rope_dim, L, L + R,
+                               "q8_0_heads_matvec_kernel(K_b)");
+    if (rc != INF_OK) return rc;
+    {
+        const long long n = rows * heads * R;
+        pack_q_rope_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(q_rope, q_abs, n, R, L + R, L);
+        INF_LAUNCH_CHECK(ctx, "pack_q_rope_kernel");
+    }
+    const float scale = 1.0f / sqrtf((float)qk_head_dim);  // attention_kernels.metal:501: scale_dim = qk_head_dim
+    rc = inf_mla_decode_launch(ctx, q_abs, pool, table, tokens, heads, max_len, scale, context, INF_DTYPE_F32,
+                               q_bytes + ctx_bytes);
+    if (rc != INF_OK) return rc;
+    return launch_matvec<float>(ctx, v_b_weights, context, out, (int)rows, heads, L, value_dim, value_dim,
+                                "q8_0_heads_matvec_kernel(V_b)");
+}

@@ -364,38 +364,35 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
 
 }  // namespace
 
-extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool,
-                                           const inf_page_table* table, int32_t tokens, int32_t heads,
-                                           int32_t max_len, float scale, void* out, int32_t out_dtype) {
-    INF_CHECK_CTX(ctx);
-    if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "mla_decode: null pointer");
-    if (!pool->rows) return inf_fail(ctx, INF_E_ARG, "mla_decode: pool has no storage");
-    if (pool->latent_dim != LAT || pool->rope_dim != ROPE || pool->page_size != PAGE) return INF_UNSUPPORTED;
-    if (tokens <= 0 || heads <= 0 || max_len <= 0) return inf_fail(ctx, INF_E_SHAPE, "mla_decode: sizes must be positive");
-    if (!(scale > 0.f)) return inf_fail(ctx, INF_E_CONFIG, "mla_decode: scale must be positive");
-    if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
-        return inf_fail(ctx, INF_E_DTYPE, "mla_decode: output dtype must be f32 or f16");
-    int rc = inf_validate_table(ctx, table, pool->num_pages, PAGE, tokens, "mla_decode");
-    if (rc != INF_OK) return rc;
-    if (table->host_lens)
-        for (int b = 0; b < table->batch; ++b)
-            if (table->host_lens[b] + tokens > max_len)
-                return inf_fail(ctx, INF_E_SHAPE, "mla_decode: sequence %d reaches %d rows, beyond max_len %d", b,
-                                table->host_lens[b] + tokens, max_len);
+namespace {
+// Split count: enough CTAs to fill the GPU, never more splits than pages, evened out so every split does work.
+int mla_decode_splits(const inf_ctx* ctx, int batch, int tokens, int heads, int max_len) {
     const int head_blocks = (heads + HB - 1) / HB;
     const int max_pages_used = (max_len + PAGE - 1) / PAGE;
-    const int ctas_per_split = table->batch * tokens * head_blocks;
+    const int ctas_per_split = batch * tokens * head_blocks;
     int n_splits = ctx->sm_count / ctas_per_split;
     if (n_splits < 1) n_splits = 1;
     if (n_splits > max_pages_used) n_splits = max_pages_used;
     if (n_splits > MAX_SPLITS) n_splits = MAX_SPLITS;
-    // even out: with `per` pages per split only ceil(pages/per) splits do work
     const int per = (max_pages_used + n_splits - 1) / n_splits;
-    n_splits = (max_pages_used + per - 1) / per;
+    return (max_pages_used + per - 1) / per;
+}
+}  // namespace
 
+size_t inf_mla_decode_scratch_bytes(const inf_ctx* ctx, int batch, int tokens, int heads, int max_len) {
+    const size_t prows = (size_t)batch * tokens * mla_decode_splits(ctx, batch, tokens, heads, max_len) * heads;
+    const size_t acc_bytes = (prows * LAT * sizeof(__half) + 255) & ~(size_t)255;
+    return acc_bytes + prows * 2 * sizeof(float);
+}
+
+int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool, const inf_page_table* table,
+                          int tokens, int heads, int max_len, float scale, void* out, int out_dtype, size_t ws_offset) {
+    int rc;
+    const int head_blocks = (heads + HB - 1) / HB;
+    const int n_splits = mla_decode_splits(ctx, table->batch, tokens, heads, max_len);
     const size_t prows = (size_t)table->batch * tokens * n_splits * heads;
     const size_t acc_bytes = (prows * LAT * sizeof(__half) + 255) & ~(size_t)255;
-    rc = inf_ensure_workspace(ctx, acc_bytes + prows * 2 * sizeof(float));
+    rc = inf_ensure_workspace(ctx, ws_offset + acc_bytes + prows * 2 * sizeof(float));
     if (rc != INF_OK) return rc;
 
     CUtensorMap tq, tkv;
@@ -424,8 +421,8 @@ extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, cons
     p.batch = table->batch;
     p.n_splits = n_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.part_acc = (__half*)ctx->workspace;
-    p.part_ml = (float*)((char*)ctx->workspace + acc_bytes);
+    p.part_acc = (__half*)((char*)ctx->workspace + ws_offset);
+    p.part_ml = (float*)((char*)ctx->workspace + ws_offset + acc_bytes);
     p.status = ctx->status;
     if (!(ctx->func_attr_done & 16u)) {
         INF_CUDA(ctx, cudaFuncSetAttribute(mla_decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -448,3 +445,25 @@ extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, cons
     INF_LAUNCH_CHECK(ctx, "mla_decode_combine_kernel");
     return INF_OK;
 }
+
+extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool,
+                                           const inf_page_table* table, int32_t tokens, int32_t heads,
+                                           int32_t max_len, float scale, void* out, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "mla_decode: null pointer");
+    if (!pool->rows) return inf_fail(ctx, INF_E_ARG, "mla_decode: pool has no storage");
+    if (pool->latent_dim != LAT || pool->rope_dim != ROPE || pool->page_size != PAGE) return INF_UNSUPPORTED;
+    if (tokens <= 0 || heads <= 0 || max_len <= 0) return inf_fail(ctx, INF_E_SHAPE, "mla_decode: sizes must be positive");
+    if (!(scale > 0.f)) return inf_fail(ctx, INF_E_CONFIG, "mla_decode: scale must be positive");
+    if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
+        return inf_fail(ctx, INF_E_DTYPE, "mla_decode: output dtype must be f32 or f16");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, PAGE, tokens, "mla_decode");
+    if (rc != INF_OK) return rc;
+    if (table->host_lens)
+        for (int b = 0; b < table->batch; ++b)
+            if (table->host_lens[b] + tokens > max_len)
+                return inf_fail(ctx, INF_E_SHAPE, "mla_decode: sequence %d reaches %d rows, beyond max_len %d", b,
+                                table->host_lens[b] + tokens, max_len);
+    return inf_mla_decode_launch(ctx, q_f16, pool, table, tokens, heads, max_len, scale, out, out_dtype, 0);
+}
+

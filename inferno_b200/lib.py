@@ -92,6 +92,9 @@ SIGNATURES = {
     "inf_laguna_gated_gqa_f16_attention": (_I, [_P, _P, _P, _P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I,
                                                 _I, _I, _P]),
     "inf_mla_decode_absorbed": (_I, [_P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _I, _I, _F, _P, _I]),
+    "inf_q8_0_packed_heads_matvec": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
+    "inf_q8_0_absorbed_mla": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _I, _I,
+                                   _I, _I, _I, _P]),
     "inf_mla_prefill_causal": (_I, [_P, _P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P, _L,
                                     _L, _I]),
     "inf_linearize_paged": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _P]),
