@@ -207,7 +207,7 @@ class MlaDecode:
         self.torch, self.be, self.ctx_len = torch, be, ctx_len
         self.name = f"mla_decode_{ctx_len // 1024}k"
         # DRAM bytes per launch from ncu at 32k context (profiles/mla_decode_partial_32k.md); proportional to context
-        self.traffic = (37.88e6 + 0.37e6) * ctx_len / 32768
+        self.traffic = (37.89e6 + 0.12e6) * ctx_len / 32768
         row_bytes = (self.L + self.R) * 2
         self.n_caches = max(2, int(np.ceil(320e6 / (ctx_len * row_bytes))))  # rotate through > L2 worth of caches
         pages_per = (ctx_len + self.P - 1) // self.P
@@ -270,7 +270,7 @@ class GqaPrefill2k:
     metric, unit, bound = "gqa_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_gqa_kernel"
     launches_per_step = 2  # rope+append, flash prefill
-    traffic = 33.61e6 + 0.07e6  # DRAM bytes per launch, ncu (profiles/flash_prefill_gqa_2k.md)
+    traffic = 33.66e6 + 0.23e6  # DRAM bytes per launch, ncu (profiles/flash_prefill_gqa_2k.md)
     T, Hq, Hkv, D, P, THETA = 2048, 48, 8, 128, 16, 500000.0
     max_steps = 400
     N_SETS = 8
@@ -355,7 +355,7 @@ class MlaPrefill32k:
     launches_per_step = 1
     # ncu at 8192 tokens: 2.151 GB read + 0.138 GB written (profiles/flash_prefill_mla_8k.md).  K/V re-streaming grows
     # with tokens^2 and the output with tokens, so a full 32768-token launch is estimated at 16x / 4x of those.
-    traffic = 2.151e9 * 16 + 0.138e9 * 4
+    traffic = 2.152e9 * 16 + 0.138e9 * 4
     T, H = 32768, 64
     max_steps = 3
 

@@ -319,13 +319,17 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 // coalesced loads instead of a chain of dependent ones.
 constexpr int MAX_SPLITS = 1024;
 
+// One CTA per (head, query row): 256 threads.  The split weights are computed once; for the weighted sum the
+// threads form four groups that walk the splits with stride four, each thread owning eight adjacent columns
+// (one 16-byte load per split), and the four partial sums meet in shared memory.
 template <typename OutT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, OutT* __restrict__ out, int tokens, int heads, int n_splits) {
     __shared__ float w[MAX_SPLITS];
-    __shared__ float red[4];
-    const int h = blockIdx.x, t = blockIdx.y % tokens, b = blockIdx.y / tokens, quarter = blockIdx.z;
+    __shared__ float red[8];
+    __shared__ float group_acc[3][LAT];
+    const int h = blockIdx.x, t = blockIdx.y % tokens, b = blockIdx.y / tokens;
     const int tid = threadIdx.x;
     const int kv_len = lens[b] + t + 1;
     const int n_pages = (kv_len + PAGE - 1) / PAGE;
@@ -334,16 +338,18 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     const long long prow0 = (((long long)b * tokens + t) * n_splits) * heads + h;
     // pass 1: global maximum
     float mloc = M_INIT;
-    for (int s = tid; s < n_valid; s += 128) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)s * heads) * 2]);
+    for (int s = tid; s < n_valid; s += 256) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)s * heads) * 2]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
     if ((tid & 31) == 0) red[tid >> 5] = mloc;
     __syncthreads();
-    const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float M = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) M = fmaxf(M, red[i]);
     __syncthreads();
     // pass 2: weights and the normaliser
     float lloc = 0.f;
-    for (int s = tid; s < n_valid; s += 128) {
+    for (int s = tid; s < n_valid; s += 256) {
         const float ws = ex2_approx(part_ml[(prow0 + (long long)s * heads) * 2] - M) *
                          part_ml[(prow0 + (long long)s * heads) * 2 + 1];  // weight of a normalised partial
         w[s] = ws;
@@ -353,13 +359,39 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
     if ((tid & 31) == 0) red[tid >> 5] = lloc;
     __syncthreads();
-    const float inv = 1.0f / (red[0] + red[1] + red[2] + red[3]);
-    // pass 3: weighted sum of the partial outputs, one column per thread
-    const __half* src = part_acc + prow0 * LAT + quarter * 128 + tid;
-    float acc = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < n_valid; ++s) acc += w[s] * __half2float(src[(long long)s * heads * LAT]);
-    out[((((long long)b * tokens + t) * heads) + h) * LAT + quarter * 128 + tid] = OutT(acc * inv);
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += red[i];
+    const float inv = 1.0f / total;
+    // pass 3: weighted sum of the partial outputs
+    const int g = tid >> 6, c = (tid & 63) * 8;
+    const __half* src = part_acc + prow0 * LAT + c;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
+    for (int s = g; s < n_valid; s += 4) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + (long long)s * heads * LAT);
+        const float ws = w[s];
+        const __half2* hv = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(hv[i]);
+            acc[2 * i] = fmaf(ws, f.x, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(ws, f.y, acc[2 * i + 1]);
+        }
+    }
+    if (g > 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) group_acc[g - 1][c + i] = acc[i];
+    }
+    __syncthreads();
+    if (g == 0) {
+        OutT* dst = out + ((((long long)b * tokens + t) * heads) + h) * LAT + c;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            dst[i] = OutT((acc[i] + group_acc[0][c + i] + group_acc[1][c + i] + group_acc[2][c + i]) * inv);
+    }
 }
 
 }  // namespace
@@ -435,12 +467,12 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
         mla_decode_partial_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tq, tkv, p);
     }
     INF_LAUNCH_CHECK(ctx, "mla_decode_partial_kernel");
-    dim3 cgrid(heads, tokens * table->batch, 4);
+    dim3 cgrid(heads, tokens * table->batch);
     if (out_dtype == INF_DTYPE_F32)
-        mla_decode_combine_kernel<float><<<cgrid, 128, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
+        mla_decode_combine_kernel<float><<<cgrid, 256, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
                                                                          (float*)out, tokens, heads, n_splits);
     else
-        mla_decode_combine_kernel<__half><<<cgrid, 128, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
+        mla_decode_combine_kernel<__half><<<cgrid, 256, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
                                                                           (__half*)out, tokens, heads, n_splits);
     INF_LAUNCH_CHECK(ctx, "mla_decode_combine_kernel");
     return INF_OK;
