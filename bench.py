@@ -262,6 +262,82 @@ class MlaDecode:
         return run, self.units_per_step, "whole workload (1 sequence, 64 heads, full context)"
 
 
+class MlaAbsorbedDecode(MlaDecode):
+    """q8_0_absorbed_mla_device as one call at the GLM decode shape (64 heads, q_no_rope 192, latent 512, value
+    256): K_b Q8_0 matvec, append of the current row, absorbed MLA over the pages, V_b Q8_0 matvec.  The bytes
+    that must move are the cached rows plus both weight matrices."""
+    metric = "mla_absorbed_decode_hbm_gbs"
+    launches_per_step = 6  # append, K_b matvec, rope pack, split partial, combine, V_b matvec
+    QN, DV = 192, 256
+
+    def __init__(self, be, rank, ctx_len):
+        super().__init__(be, rank, ctx_len)
+        torch = self.torch
+        self.name = f"mla_absorbed_decode_{ctx_len // 1024}k"
+        self.traffic = None
+        gd = torch.Generator(device=be.device).manual_seed(SEED + 27 + rank)
+
+        def q8(heads, fout, fin, scale):
+            nblk = heads * fout * fin // 32
+            blocks = torch.empty((nblk, 34), dtype=torch.uint8, device=be.device)
+            sc = torch.full((nblk,), scale, dtype=torch.float16, device=be.device)
+            blocks[:, :2] = sc.view(torch.uint8).view(nblk, 2)
+            blocks[:, 2:] = torch.randint(0, 256, (nblk, 32), generator=gd, device=be.device, dtype=torch.uint8)
+            return blocks.view(-1)
+        self.k_b = q8(self.H, self.L, self.QN, 1.0e-3)
+        self.v_b = q8(self.H, self.DV, self.L, 1.0e-3)
+        self.q_no = torch.randn((1, 1, self.H, self.QN), generator=gd, device=be.device, dtype=torch.float32)
+        self.q_rope = torch.randn((1, 1, self.H, self.R), generator=gd, device=be.device, dtype=torch.float32)
+        self.cur_lat = torch.randn((1, 1, self.L), generator=gd, device=be.device, dtype=torch.float32) * 0.5
+        self.cur_rope = torch.randn((1, 1, self.R), generator=gd, device=be.device, dtype=torch.float32) * 0.5
+        self.hqn, self.hqr = self.q_no.cpu().pin_memory(), self.q_rope.cpu().pin_memory()
+        self.hcl, self.hcr = self.cur_lat.cpu().pin_memory(), self.cur_rope.cpu().pin_memory()
+        self.hout = torch.empty((1, 1, self.H, self.DV), dtype=torch.float32).pin_memory()
+        self.weight_bytes = self.k_b.numel() + self.v_b.numel()
+        self.kernel_units_per_launch = self.units_per_step  # the attention kernel itself moves only the cached rows
+        self.units_per_step += self.weight_bytes
+        self.flops_per_step += 2.0 * self.H * self.L * (self.QN + self.DV)
+        self.h2d = 4 * (self.hqn.numel() + self.hqr.numel() + self.hcl.numel() + self.hcr.numel())
+        self.d2h = self.hout.numel() * 4
+        self.config.update({"workload": self.name, "q_no_rope_dim": self.QN, "value_dim": self.DV,
+                            "weights": "Q8_0 K_b [64][512][192] + V_b [64][256][512]",
+                            "weight_bytes_per_step": int(self.weight_bytes), "flops_per_step": self.flops_per_step,
+                            "bytes_per_step": int(self.units_per_step)})
+        self.out = torch.empty((1, 1, self.H, self.DV), dtype=torch.float32, device=be.device)
+
+    def step(self):
+        t = self.tables[self.i % self.n_caches]
+        self.i += 1
+        self.be.q8_0_absorbed_mla_device(self.k_b, self.v_b, self.q_no, self.q_rope, self.cur_lat, self.cur_rope,
+                                         self.pool, t, self.QN + self.R, self.DV, max_len=self.ctx_len, out=self.out)
+
+    def step_e2e(self):
+        self.q_no.copy_(self.hqn, non_blocking=True)
+        self.q_rope.copy_(self.hqr, non_blocking=True)
+        self.cur_lat.copy_(self.hcl, non_blocking=True)
+        self.cur_rope.copy_(self.hcr, non_blocking=True)
+        self.step()
+        self.hout.copy_(self.out, non_blocking=True)
+
+    def cpu_sample(self):
+        from oracle import pyoracle as orc
+        n, W = self.ctx_len, self.L + self.R
+        table = np.random.RandomState(SEED + 23).permutation((n + self.P - 1) // self.P).astype(np.int32)[None]
+        pool = np.resize(np.random.RandomState(SEED + 24).standard_normal(1 << 20).astype(np.float16).view(np.uint16),
+                         table.size * self.P * W).reshape(-1, self.P, W)
+        k_b, v_b = self.k_b.cpu().numpy(), self.v_b.cpu().numpy()
+        q_no = orc.fill_normal((1, self.H, self.QN), SEED + 28, 1.0, False)
+        q_rope = orc.fill_normal((1, 1, self.H, self.R), SEED + 29, 1.0, False)
+        cur = orc.fill_normal((1, 1, W), SEED + 26, 0.5)
+
+        def run():
+            q_lat = orc.q8_0_heads_matvec(k_b, q_no, self.H, self.QN, self.L).reshape(1, 1, self.H, self.L)
+            q = np.concatenate([q_lat, q_rope], axis=-1)
+            ctx = orc.mla_absorbed_paged(q, cur, pool, table, [n - 1], self.P, self.L, self.R, self.scale)
+            return orc.q8_0_heads_matvec(v_b, ctx.reshape(1, self.H, self.L), self.H, self.L, self.DV)
+        return run, self.units_per_step, "whole workload (1 sequence, 64 heads, full context, both projections)"
+
+
 class GqaPrefill2k:
     """Causal GQA prefill, one 2048-token prompt, 48 q / 8 kv heads, fused RoPE + KV-append (fourth configuration).
     With N > 1 ranks the heads are sharded (48/N query heads with their 8/N KV heads per rank) and the output is
@@ -416,6 +492,8 @@ def make_workload(name, be, rank, world=1, dist=None, tokens=0):
         return MlaDecode(be, rank, 4096)
     if name == "mla_decode_32k":
         return MlaDecode(be, rank, 32768)
+    if name == "mla_absorbed_decode_32k":
+        return MlaAbsorbedDecode(be, rank, 32768)
     if name == "gqa_prefill_2k":
         return GqaPrefill2k(be, rank, world, dist)
     if name == "mla_prefill_32k":
@@ -430,7 +508,8 @@ def make_workload(name, be, rank, world=1, dist=None, tokens=0):
     raise KeyError(name)
 
 
-WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "gqa_prefill_2k", "mla_prefill_32k"]
+WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "gqa_prefill_2k",
+                  "mla_prefill_32k"]
 STRONG = {"gqa_prefill_2k", "mla_prefill_32k"}  # head-sharded with an all-gather; the others replicate/shard by sequence
 
 
@@ -533,7 +612,8 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
     e2e = total_units * steps / (ms_e2e * 1e-3) * scale
     k_ms, k_n = kernel_time(be, torch, wl, profile_steps)
     peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops"]
-    achieved = units / (k_ms * 1e-3) * scale if k_ms else None
+    k_units = getattr(wl, "kernel_units_per_launch", units)  # algorithmic units of the dominant kernel's launch
+    achieved = k_units / (k_ms * 1e-3) * scale if k_ms else None
     roof = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": "GB/s" if wl.bound == "hbm" else "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "traffic": getattr(wl, "traffic", None),
             "kernel": wl.kernel, "kernel_ms": k_ms, "kernel_launches_timed": k_n,

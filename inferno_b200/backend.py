@@ -320,11 +320,12 @@ class CudaBackend:
         return out
 
     def q8_0_absorbed_mla_device(self, k_b_weights, v_b_weights, q_no_rope, q_rope, current_latent, current_rope,
-                                 pool: MlaPool, table: PageTable, qk_head_dim: int, value_dim: int, max_len: int):
+                                 pool: MlaPool, table: PageTable, qk_head_dim: int, value_dim: int, max_len: int, out=None):
         """q8_0_absorbed_mla_device (backend.rs:1982): returns [B, T, H, value_dim] f32, or None when the pool's
         geometry has no device path.  current_latent / current_rope may be None when the rows are already stored."""
         B, T, H, qn = q_no_rope.shape
-        out = torch.empty((B, T, H, value_dim), dtype=torch.float32, device=self.device)
+        if out is None:
+            out = torch.empty((B, T, H, value_dim), dtype=torch.float32, device=self.device)
         ok = self._check(self._lib.inf_q8_0_absorbed_mla(
             self._ctx, _ptr(k_b_weights), _ptr(v_b_weights), _ptr(q_no_rope), _ptr(q_rope), _ptr(current_latent),
             _ptr(current_rope), C.byref(pool.desc), C.byref(table.desc), T, H, qn, value_dim, qk_head_dim, max_len,

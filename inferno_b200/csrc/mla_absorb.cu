@@ -56,6 +56,63 @@ q8_0_heads_matvec_kernel(const uint8_t* __restrict__ weights, const float* __res
     }
 }
 
+// The same product for out_features % 32 == 0 (every shape of the absorbed-MLA path): a CTA owns 32 consecutive
+// output features of one head, whose weight rows are one contiguous, 16-byte aligned run of 32 * 34 * blocks
+// bytes.  The run is staged in shared memory with 16-byte loads (every byte of the matrix crosses HBM once, with
+// many independent requests in flight), then each warp reduces four of the rows against the input rows, lane =
+// value inside a block as in the reference kernel.  Optionally the CTAs with blockIdx.x == 0 also convert the
+// head's `tail` f32 values per input row into fp16 columns [tail_col0, tail_col0 + tail_n) of the output row
+// (the RoPE part of the absorbed query).
+constexpr int TILE_ROWS = 32;
+template <typename OutT>
+__global__ void __launch_bounds__(MV_WARPS * 32)
+q8_0_heads_matvec_tile_kernel(const uint8_t* __restrict__ weights, const float* __restrict__ input,
+                              OutT* __restrict__ out, int rows, int heads, int in_features, int out_features,
+                              long long out_stride, const float* __restrict__ tail, int tail_n, int tail_col0) {
+    extern __shared__ __align__(16) uint8_t tile[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int o0 = blockIdx.x * TILE_ROWS;
+    const int head = blockIdx.y;
+    const int row0 = blockIdx.z * MV_ROWS;
+    const int blocks_per_row = in_features / Q8_BLOCK_VALUES;
+    const int row_bytes = blocks_per_row * Q8_BLOCK_BYTES;
+    const uint4* src = reinterpret_cast<const uint4*>(weights + ((size_t)head * out_features + o0) * row_bytes);
+    const int n16 = TILE_ROWS * row_bytes / 16;
+    for (int i = threadIdx.x; i < n16; i += MV_WARPS * 32) reinterpret_cast<uint4*>(tile)[i] = src[i];
+    if (tail && blockIdx.x == 0) {
+        for (int r = 0; r < MV_ROWS && row0 + r < rows; ++r)
+            for (int d = threadIdx.x; d < tail_n; d += MV_WARPS * 32)
+                out[((size_t)(row0 + r) * heads + head) * out_stride + tail_col0 + d] =
+                    OutT(tail[((size_t)(row0 + r) * heads + head) * tail_n + d]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < TILE_ROWS / MV_WARPS; ++i) {
+        const int lr = warp * (TILE_ROWS / MV_WARPS) + i;
+        const uint8_t* wrow = tile + lr * row_bytes;
+        float sum[MV_ROWS];
+#pragma unroll
+        for (int r = 0; r < MV_ROWS; ++r) sum[r] = 0.f;
+        for (int blk = 0; blk < blocks_per_row; ++blk) {
+            const uint8_t* bp = wrow + blk * Q8_BLOCK_BYTES;
+            const float d = __half2float(*reinterpret_cast<const __half*>(bp));  // block starts are 2-byte aligned
+            const float w = d * (float)(signed char)bp[2 + lane];
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; ++r)
+                if (row0 + r < rows)
+                    sum[r] = fmaf(input[((size_t)(row0 + r) * heads + head) * in_features + blk * Q8_BLOCK_VALUES + lane],
+                                  w, sum[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < MV_ROWS; ++r) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], off);
+            if (lane == 0 && row0 + r < rows)
+                out[((size_t)(row0 + r) * heads + head) * out_stride + o0 + lr] = OutT(sum[r]);
+        }
+    }
+}
+
 // q_rope f32 [rows*heads][rope] -> fp16 columns [latent, latent+rope) of the absorbed query rows.
 __global__ void pack_q_rope_kernel(const float* __restrict__ q_rope, __half* __restrict__ q_abs, long long n, int rope,
                                    int row_width, int col0) {
@@ -93,12 +150,25 @@ __global__ void append_latent_rows_kernel(const float* __restrict__ latent, cons
 
 template <typename OutT>
 int launch_matvec(inf_ctx* ctx, const void* weights, const float* input, OutT* out, int rows, int heads, int in_features,
-                  int out_features, long long out_stride, const char* name) {
-    dim3 grid((out_features + MV_WARPS - 1) / MV_WARPS, heads, (rows + MV_ROWS - 1) / MV_ROWS);
-    {
-        inf_prof_scope prof(ctx, name);
+                  int out_features, long long out_stride, const char* name, const float* tail = nullptr, int tail_n = 0,
+                  int tail_col0 = 0) {
+    const size_t tile_bytes = (size_t)TILE_ROWS * (in_features / Q8_BLOCK_VALUES) * Q8_BLOCK_BYTES;
+    const bool tiled = out_features % TILE_ROWS == 0 && tile_bytes <= 48 * 1024 && ((uintptr_t)weights & 15) == 0;
+    inf_prof_scope prof(ctx, name);
+    if (tiled) {
+        dim3 grid(out_features / TILE_ROWS, heads, (rows + MV_ROWS - 1) / MV_ROWS);
+        q8_0_heads_matvec_tile_kernel<OutT><<<grid, MV_WARPS * 32, tile_bytes, ctx->stream>>>(
+            (const uint8_t*)weights, input, out, rows, heads, in_features, out_features, out_stride, tail, tail_n,
+            tail_col0);
+    } else {
+        dim3 grid((out_features + MV_WARPS - 1) / MV_WARPS, heads, (rows + MV_ROWS - 1) / MV_ROWS);
         q8_0_heads_matvec_kernel<OutT><<<grid, MV_WARPS * 32, 0, ctx->stream>>>(
             (const uint8_t*)weights, input, out, rows, heads, in_features, out_features, out_stride);
+        if (tail) {
+            const long long n = (long long)rows * heads * tail_n;
+            pack_q_rope_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(tail, (__half*)out, n, tail_n,
+                                                                                    (int)out_stride, tail_col0);
+        }
     }
     INF_LAUNCH_CHECK(ctx, name);
     return INF_OK;
@@ -177,13 +247,8 @@ extern "C" int32_t inf_q8_0_absorbed_mla(inf_ctx* ctx, const void* k_b_weights, 
         INF_LAUNCH_CHECK(ctx, "append_latent_rows_kernel");
     }
     rc = launch_matvec<__half>(ctx, k_b_weights, q_no_rope, q_abs, (int)rows, heads, q_no_rope_dim, L, L + R,
-                               "q8_0_heads_matvec_kernel(K_b)");
+                               "q8_0_heads_matvec_kernel(K_b)", q_rope, R, L);
     if (rc != INF_OK) return rc;
-    {
-        const long long n = rows * heads * R;
-        pack_q_rope_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(q_rope, q_abs, n, R, L + R, L);
-        INF_LAUNCH_CHECK(ctx, "pack_q_rope_kernel");
-    }
     const float scale = 1.0f / sqrtf((float)qk_head_dim);  // attention_kernels.metal:501: scale_dim = qk_head_dim
     rc = inf_mla_decode_launch(ctx, q_abs, pool, table, tokens, heads, max_len, scale, context, INF_DTYPE_F32,
                                q_bytes + ctx_bytes);
