@@ -29,6 +29,9 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <algorithm>
+#include <vector>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -60,7 +63,8 @@ struct FlashParams {
     long long o_ts, o_hs, o_bs;  // element strides of the output: token, head, batch
     int* status;
 #ifdef INF_KPROF
-    long long* kprof;  // debug builds only: cycle counters of CTA (0,0,0)
+    long long* kprof;      // debug builds only: cycle counters of CTA (0,0,0)
+    long long* kprof_cta;  // debug builds only: per CTA {sm id, ns at entry, after set-up, before the last sync, at exit}
 #endif
 };
 
@@ -121,11 +125,20 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint64_t* p_full = s_full + 2 * SR; // [2][2]: P of keys 0-63 / 64-127 of the current tile is in TMEM
     uint64_t* o_ready = p_full + 4;     // [2][2]: PV of local tile jl has retired (its V tile is consumed)
     uint64_t* sm_done = o_ready + 4;    // [2]: a stream's softmax warpgroup has finished the exponentials of a tile
-    uint64_t* s_free = sm_done + 2;     // [1]: the shared S buffer has been copied into registers (128 arrivals)
+    uint64_t* s_free = sm_done + 2;     // [1]: the shared S buffer has been copied into registers (one arrival per softmax warp)
     uint64_t* k_free = s_free + 1;      // [KB]: the last QK that reads this K block has retired
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(k_free + KB);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef INF_KPROF
+    const long long kp_cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (tid == 0 && p.kprof_cta && kp_cta < 8192) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        p.kprof_cta[kp_cta * 5 + 0] = smid;
+        p.kprof_cta[kp_cta * 5 + 1] = (long long)global_timer_ns();
+    }
+#endif
     const int b = blockIdx.z;
     const int past = PAGED ? p.lens[b] : 0;
     const int kv_total = past + p.tokens;
@@ -171,10 +184,11 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int i = 0; i < VS; ++i) mbar_init(&v_full[i], 1);
         for (int i = 0; i < 2 * SR; ++i) mbar_init(&s_full[i], 1);
         for (int i = 0; i < 4; ++i) mbar_init(&o_ready[i], 1);
-        for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 128);
-        mbar_init(&sm_done[0], 128);
-        mbar_init(&sm_done[1], 128);
-        mbar_init(s_free, 128);
+        // the softmax barriers take one arrival per warp: tcgen05.wait is warp-wide, so lane 0 can speak for its warp
+        for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], 4);
+        mbar_init(&sm_done[0], 4);
+        mbar_init(&sm_done[1], 4);
+        mbar_init(s_free, 4);
         mbar_fence_init();
     }
     if (warp == 9) {
@@ -185,6 +199,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
+#ifdef INF_KPROF
+    if (tid == 0 && p.kprof_cta && kp_cta < 8192) p.kprof_cta[kp_cta * 5 + 2] = (long long)global_timer_ns();
+#endif
 
     // 384 threads start with 168 registers each; the data-movement / issue warpgroup keeps 40 and the two softmax
     // warpgroups take the rest (256 * 232 + 128 * 40 = 384 * 168), so a 128-key S row fits in registers
@@ -448,6 +465,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const bool kp_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid & 127) == 0;
             long long kp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             const long long kp_start = clock64();
+            const bool kp_tl = tid == 0 && p.kprof_cta && kp_cta < 8192 && p.kprof;  // timeline of every CTA's thread 0
+            long long kp_ns[5] = {(long long)global_timer_ns(), 0, 0, 0, 0};
 #endif
             for (int j = 0; j < n_s; ++j) {
                 const int k0 = (me.kt_begin + j) * BN;
@@ -457,6 +476,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     break;
                 }
                 KP_ADD(0);
+#ifdef INF_KPROF
+                if (j == 0) kp_ns[1] = (long long)global_timer_ns();
+#endif
                 tc_fence_after();
                 const bool need_mask = (k0 + BN - 1 > past + me.q0) || (k0 + BN > kv_total) ||
                                        (p.window > 0 && k0 < past + me.q0 + BM - p.window);
@@ -466,7 +488,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 for (int c = 0; c < BN / 32; ++c) tmem_ld32(col_s + c * 32, sraw + c * 32);
                 tc_wait_ld();
                 tc_fence_before();
-                mbar_arrive(s_free);  // the next QK (of either stream) may overwrite the buffer
+                if (lane == 0) mbar_arrive(s_free);  // the next QK (of either stream) may overwrite the buffer
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < BN; ++i) {
@@ -538,12 +560,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (c & 1) {  // a 64-key half of P is complete: its PV MMAs may start while the rest is computed
                         tc_wait_st();
                         tc_fence_before();
-                        mbar_arrive(&p_full[s * 2 + (c >> 1)]);
+                        if (lane == 0) mbar_arrive(&p_full[s * 2 + (c >> 1)]);
                     }
                 }
                 l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
                 KP_ADD(3);
-                mbar_arrive(&sm_done[s]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm_done[s]);
                 KP_ADD(4);
             }
 #ifdef INF_KPROF
@@ -553,7 +576,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 p.kprof[16 + s * 8 + 7] = n_s;
             }
 #endif
+#ifdef INF_KPROF
+            kp_ns[2] = (long long)global_timer_ns();
+#endif
             if (ok && !mbar_wait(&o_ready[s * 2 + ((n_s - 1) & 1)], ((uint32_t)((n_s - 1) >> 1)) & 1u)) ok = false;
+#ifdef INF_KPROF
+            kp_ns[3] = (long long)global_timer_ns();
+#endif
             if (!ok) {
                 if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
             } else {
@@ -592,11 +621,28 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     }
                 }
             }
+#ifdef INF_KPROF
+            if (kp_tl) {
+                kp_ns[4] = (long long)global_timer_ns();
+                const long long e = p.kprof_cta[kp_cta * 5 + 1];
+                // accumulate over CTAs (atomics): softmax loop start, first S, loop end, last PV retired, stores done
+                for (int i = 0; i < 5; ++i) atomicAdd((unsigned long long*)&p.kprof[40 + i], (unsigned long long)(kp_ns[i] - e));
+                atomicAdd((unsigned long long*)&p.kprof[45], 1ull);
+                atomicAdd((unsigned long long*)&p.kprof[46], (unsigned long long)(clock64() - kp_start));
+                atomicAdd((unsigned long long*)&p.kprof[47], (unsigned long long)(kp_ns[4] - kp_ns[0]));
+            }
+#endif
         }
     }
+#ifdef INF_KPROF
+    if (tid == 0 && p.kprof_cta && kp_cta < 8192) p.kprof_cta[kp_cta * 5 + 3] = (long long)global_timer_ns();
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 9) tmem_dealloc(tbase, TMEM_COLS);
+#ifdef INF_KPROF
+    if (tid == 32 * 9 && p.kprof_cta && kp_cta < 8192) p.kprof_cta[kp_cta * 5 + 4] = (long long)global_timer_ns();
+#endif
 }
 
 template <int DQK, int DV, int KB, int VS, bool PAGED>
@@ -617,6 +663,10 @@ int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const C
     if (!d_kprof) cudaMalloc(&d_kprof, 64 * sizeof(long long));
     cudaMemsetAsync(d_kprof, 0, 64 * sizeof(long long), ctx->stream);
     pp.kprof = d_kprof;
+    static long long* d_cta = nullptr;
+    if (!d_cta) cudaMalloc(&d_cta, 8192 * 5 * sizeof(long long));
+    cudaMemsetAsync(d_cta, 0, 8192 * 5 * sizeof(long long), ctx->stream);
+    pp.kprof_cta = d_cta;
     kernel<<<grid, NUM_THREADS, L::TOTAL, ctx->stream>>>(tq, tk, tk2, tv, pp);
     long long h[64];
     cudaMemcpy(h, d_kprof, sizeof(h), cudaMemcpyDeviceToHost);
@@ -626,6 +676,45 @@ int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const C
         fprintf(stderr, "KPROF %s softmax%d: wait_s %lld pass1 %lld rescale %lld pass2 %lld st+arrive %lld turn %lld total %lld tiles %lld\n",
                 name, s2, h[16 + s2 * 8], h[16 + s2 * 8 + 1], h[16 + s2 * 8 + 2], h[16 + s2 * 8 + 3], h[16 + s2 * 8 + 4], h[16 + s2 * 8 + 5],
                 h[16 + s2 * 8 + 6], h[16 + s2 * 8 + 7]);
+    {   // per-SM schedule: where the time between and inside CTAs goes
+        const int ncta = (int)std::min<long long>(8192, (long long)grid.x * grid.y * grid.z);
+        std::vector<long long> c(ncta * 5);
+        cudaMemcpy(c.data(), d_cta, c.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+        long long t0 = c[1], t1 = 0;
+        for (int i = 0; i < ncta; ++i) { t0 = std::min(t0, c[i * 5 + 1]); t1 = std::max(t1, c[i * 5 + 4]); }
+        std::vector<std::vector<int>> per_sm(256);
+        for (int i = 0; i < ncta; ++i) per_sm[c[i * 5] & 255].push_back(i);
+        double setup = 0, body = 0, tail = 0, gap = 0, idle_end = 0; int ngap = 0, nsm = 0;
+        for (auto& v : per_sm) {
+            if (v.empty()) continue;
+            ++nsm;
+            std::sort(v.begin(), v.end(), [&](int a, int b) { return c[a * 5 + 1] < c[b * 5 + 1]; });
+            for (size_t k = 0; k < v.size(); ++k) {
+                const long long* e = &c[v[k] * 5];
+                setup += e[2] - e[1]; body += e[3] - e[2]; tail += e[4] - e[3];
+                if (k > 0) { gap += e[1] - c[v[k - 1] * 5 + 4]; ++ngap; }
+            }
+            idle_end += t1 - c[v.back() * 5 + 4];
+        }
+        if (grid.y <= 64) {
+            fprintf(stderr, "KPROF %s body us by blockIdx.y:", name);
+            for (unsigned y = 0; y < grid.y; ++y) {
+                double sum = 0; int cnt = 0;
+                for (int i = 0; i < ncta; ++i)
+                    if ((unsigned)((i / grid.x) % grid.y) == y) { sum += c[i * 5 + 3] - c[i * 5 + 2]; ++cnt; }
+                fprintf(stderr, " %.1f", cnt ? sum / cnt * 1e-3 : 0.0);
+            }
+            fprintf(stderr, "\n");
+        }
+        fprintf(stderr, "KPROF %s thread-0 timeline, mean over %lld CTAs, us after CTA entry: softmax loop entered %.2f, first S %.2f, loop left %.2f, last PV retired %.2f, output stored %.2f\n",
+                name, h[45], h[40] * 1e-3 / std::max(1ll, h[45]), h[41] * 1e-3 / std::max(1ll, h[45]), h[42] * 1e-3 / std::max(1ll, h[45]),
+                h[43] * 1e-3 / std::max(1ll, h[45]), h[44] * 1e-3 / std::max(1ll, h[45]));
+        fprintf(stderr, "KPROF %s SM clock inside the kernel: %.0f MHz (cycles / globaltimer over the softmax thread's life)\n", name,
+                h[47] ? (double)h[46] / (double)h[47] * 1e3 : 0.0);
+        fprintf(stderr, "KPROF %s schedule: span %.1f us, %d CTAs on %d SMs; per CTA: set-up %.2f us, body %.2f us, exit %.2f us; gap between CTAs on an SM %.2f us; idle at the end per SM %.2f us; first start spread n/a\n",
+                name, (t1 - t0) * 1e-3, ncta, nsm, setup / ncta * 1e-3, body / ncta * 1e-3, tail / ncta * 1e-3,
+                ngap ? gap / ngap * 1e-3 : 0.0, idle_end / nsm * 1e-3);
+    }
     INF_LAUNCH_CHECK(ctx, name);
     return INF_OK;
 #else

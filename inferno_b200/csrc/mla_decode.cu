@@ -7,13 +7,19 @@
 // range).  A page (64 rows x 576) arrives as nine [64 x 64] TMA boxes with the 128-byte swizzle; the
 // same shared-memory bytes serve as the K-major B operand of QK^T and, columns 0-511, as the MN-major B
 // operand of PV.  M = 64 accumulators use 16 lanes of each TMEM quadrant, so the 512 output columns are
-// held as two interleaved halves (lane offset 0 and 16) over TMEM columns 0-255; S is double-buffered in
-// columns 256-383.  Softmax runs on lanes 0-15 of the four softmax warps, P goes to shared memory as the
-// K-major A operand, O is rescaled lazily.  Split partials (max, sum, O) are merged by a second kernel.
+// held as two interleaved halves (lane offset 0 and 16) over TMEM columns 0-255.  Q is the TMEM A operand of
+// QK^T, stored as two halves of 288 columns (144 TMEM columns, lane offsets 0 and 16); each half multiplies
+// the matching 288 columns of the page into its own partial S on the same lanes (an M = 64 MMA keeps A and D
+// on the same 16 lanes of a quadrant), and the softmax threads add the two partial S rows with a shuffle.
+// Keeping Q out of shared memory leaves room for a ring of three whole pages (216 KB), which is what hides
+// the HBM latency at batch 1.  There is one S buffer: the softmax copies it into registers at once and hands
+// it back, so QK^T of the next page overlaps the exponentials.  P goes to shared memory as the K-major A
+// operand of PV, O is rescaled lazily.  Split partials (max, sum, O) are merged by a second kernel.
 //
-// Warps: 0-3 softmax/epilogue, 4 TMA producer, 5 TMEM allocation + MMA issue.
+// Warps: 0-3 Q load, softmax, epilogue; 4 TMA producer; 5 TMEM allocation + MMA issue.
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdio.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -32,10 +38,12 @@ constexpr int NUM_THREADS = 192;
 constexpr float M_INIT = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t COL_O = 0, COL_S0 = 256, COL_S1 = 320;
+constexpr uint32_t COL_O = 0, COL_S = 256, COL_Q = 320;  // O 256 columns, S 64, Q 144 (each on both lane halves)
+constexpr int STAGES = 3;
+constexpr int QHALF = ROW / 2;  // 288 query columns per lane half
 
-constexpr int OFF_KV = TILE_BYTES;
-constexpr int OFF_P = OFF_KV + 2 * TILE_BYTES;
+constexpr int OFF_KV = 0;
+constexpr int OFF_P = OFF_KV + STAGES * TILE_BYTES;
 constexpr int OFF_BAR = OFF_P + BLK_BYTES;
 constexpr int SMEM_TOTAL = OFF_BAR + 128;
 
@@ -49,7 +57,16 @@ struct MlaParams {
     __half* part_acc; // [batch][tokens][n_splits][heads][512], each row already divided by its own sum
     float* part_ml;   // [batch][tokens][n_splits][heads][2]: running max (log2 domain) and sum
     int* status;
+#ifdef INF_KPROF
+    long long* kprof;  // debug builds only: timeline of CTA 0's first softmax thread, ns after entry
+#endif
 };
+
+#ifdef INF_KPROF
+#define KP_MARK(i) do { if (kp_on) p.kprof[i] = (long long)global_timer_ns() - kp_t0; } while (0)
+#else
+#define KP_MARK(i) do {} while (0)
+#endif
 
 __device__ __forceinline__ void split_range(int n_pages, int n_splits, int s, int& begin, int& end) {
     const int per = (n_pages + n_splits - 1) / n_splits;
@@ -61,19 +78,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                           MlaParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;
     uint8_t* sKV = smem + OFF_KV;
     uint8_t* sP = smem + OFF_P;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* q_full = bars;
-    uint64_t* kv_full = bars + 1;   // [2]
-    uint64_t* kv_empty = bars + 3;  // [2]
-    uint64_t* s_full = bars + 5;    // [2]
-    uint64_t* p_full = bars + 7;
-    uint64_t* pv_done = bars + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t* kv_full = bars + 1;            // [STAGES]
+    uint64_t* kv_empty = kv_full + STAGES;   // [STAGES]
+    uint64_t* s_full = kv_empty + STAGES;    // [1]
+    uint64_t* s_free = s_full + 1;           // [1]: the S buffer has been copied into registers
+    uint64_t* p_full = s_full + 2;
+    uint64_t* pv_done = p_full + 1;
+    uint64_t* q_landed = pv_done + 1;  // Q is in the last ring stage (TMA), before it moves to TMEM
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_landed + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef INF_KPROF
+    const bool kp_on = tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.kprof;
+    const long long kp_t0 = (long long)global_timer_ns();
+    const int kp_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (tid == 0 && p.kprof && kp_cta < 256) p.kprof[64 + kp_cta * 2] = kp_t0;
+#endif
     const int split = blockIdx.x;
     const int t = blockIdx.y % p.tokens, hb = blockIdx.y / p.tokens;
     const int b = blockIdx.z;
@@ -88,12 +112,14 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         return;
     }
     if (tid == 0) {
-        mbar_init(q_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        mbar_init(q_full, 128);
+        mbar_init(q_landed, 1);
+        for (int i = 0; i < STAGES; ++i) {
             mbar_init(&kv_full[i], 1);
             mbar_init(&kv_empty[i], 1);
-            mbar_init(&s_full[i], 1);
         }
+        mbar_init(s_full, 1);
+        mbar_init(s_free, 4);  // lane 0 of each softmax warp
         mbar_init(p_full, 128);
         mbar_init(pv_done, 1);
         mbar_fence_init();
@@ -106,16 +132,19 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
+    KP_MARK(0);
 
     if (warp == 4) {
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_kv);
-            mbar_arrive_expect_tx(q_full, TILE_BYTES);
+            // Q first, into the last ring stage: it is needed before any page and must not queue behind them
+            mbar_arrive_expect_tx(q_landed, TILE_BYTES);
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
-                tma_load_3d(sQ + blk * BLK_BYTES, &tm_q, blk * 64, hb * HB, b * p.tokens + t, q_full);
+                tma_load_3d(sKV + (STAGES - 1) * TILE_BYTES + blk * BLK_BYTES, &tm_q, blk * 64, hb * HB,
+                            b * p.tokens + t, q_landed);
             const int oob_row = p.num_pages * PAGE;
             for (int j = 0; j < n; ++j) {
                 const int slot = pg_begin + j;
@@ -129,8 +158,12 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 } else {
                     atomicOr(p.status, INF_STATUS_BAD_LEN);
                 }
-                const int st = j & 1;
-                if (!mbar_wait(&kv_empty[st], (((uint32_t)(j >> 1)) & 1u) ^ 1u)) {
+                const int st = j % STAGES;
+                if (j == STAGES - 1 && !mbar_wait(q_full, 0)) {  // the stage still holds Q until it is in TMEM
+                    atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                    break;
+                }
+                if (!mbar_wait(&kv_empty[st], (((uint32_t)(j / STAGES)) & 1u) ^ 1u)) {
                     atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
                     break;
                 }
@@ -145,17 +178,22 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc_f16(HB, PAGE, 0, 0);
             const uint32_t idesc_pv = umma_idesc_f16(HB, 256, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), kv_addr = smem_u32(sKV), p_addr = smem_u32(sP);
-            auto issue_qk = [&](int j) {
-                const uint32_t s_col = (j & 1) ? COL_S1 : COL_S0;
-                const uint32_t tile = kv_addr + (j & 1) * TILE_BYTES;
+            const uint32_t kv_addr = smem_u32(sKV), p_addr = smem_u32(sP);
+            auto issue_qk = [&](int j) {  // two partial S = Q[:, half] C_j[:, half]^T, A from TMEM, B K-major
+                const uint32_t tile = kv_addr + (j % STAGES) * TILE_BYTES;
+                // the two halves are independent accumulation chains: alternate them so that one MMA does not
+                // have to wait for the previous one's accumulator
 #pragma unroll
-                for (int kk = 0; kk < ROW / 16; ++kk) {
-                    const uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
-                    umma_ss(tbase + s_col, umma_smem_desc(q_addr + off, 16, 1024, UMMA_SW128),
-                            umma_smem_desc(tile + off, 16, 1024, UMMA_SW128), idesc_qk, kk > 0);
-                }
-                tc_commit(&s_full[j & 1]);
+                for (int i = 0; i < ROW / 32; ++i)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int kk = h * (ROW / 32) + i;
+                        const uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
+                        const uint32_t lane_half = (uint32_t)(h * 16) << 16;
+                        umma_ts(tbase + lane_half + COL_S, tbase + lane_half + COL_Q + i * 8,
+                                umma_smem_desc(tile + off, 16, 1024, UMMA_SW128), idesc_qk, i > 0);
+                    }
+                tc_commit(s_full);
             };
             bool ok = mbar_wait(q_full, 0);
             if (ok) ok = mbar_wait(&kv_full[0], 0);
@@ -165,7 +203,8 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             }
             for (int j = 0; ok && j < n; ++j) {
                 if (j + 1 < n) {
-                    ok = mbar_wait(&kv_full[(j + 1) & 1], ((uint32_t)((j + 1) >> 1)) & 1u);
+                    ok = mbar_wait(&kv_full[(j + 1) % STAGES], ((uint32_t)((j + 1) / STAGES)) & 1u);
+                    if (ok) ok = mbar_wait(s_free, ((uint32_t)j) & 1u);  // S of page j is in registers
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk(j + 1);
@@ -173,7 +212,7 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 ok = mbar_wait(p_full, ((uint32_t)j) & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t tile = kv_addr + (j & 1) * TILE_BYTES;
+                const uint32_t tile = kv_addr + (j % STAGES) * TILE_BYTES;
 #pragma unroll
                 for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -182,7 +221,7 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                                 umma_smem_desc(p_addr + kk * 32, 16, 1024, UMMA_SW128),
                                 umma_smem_desc(tile + half * 4 * BLK_BYTES + kk * 2048, BLK_BYTES, 1024, UMMA_SW128),
                                 idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(&kv_empty[j & 1]);
+                tc_commit(&kv_empty[j % STAGES]);
                 tc_commit(pv_done);
             }
             if (!ok) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
@@ -192,52 +231,84 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         // lanes 0-15 of warp w own rows 16w..16w+15 of S and of O[:, 0:256]; lanes 16-31 own the same rows of
         // O[:, 256:512] (the accumulator half that sits at TMEM lane offset 16).
         const int row = warp * 16 + (lane & 15);
-        const bool s_owner = lane < 16;
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        float m_used = M_INIT, l = 0.f;
+        {   // Q row of this head, columns [288 * (lane / 16), +288), from the staged tile into TMEM (packed fp16 pairs)
+            bool q_ok = mbar_wait(q_landed, 0);
+            const uint8_t* sq = sKV + (STAGES - 1) * TILE_BYTES;
+            const int col0 = (lane >> 4) * QHALF;
+#pragma unroll
+            for (int c = 0; c < QHALF / 32; ++c) {  // 9 groups of 16 TMEM columns = 32 query columns
+                uint32_t v[16];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int col = col0 + c * 32 + i * 8;
+                    const uint4 u = *reinterpret_cast<const uint4*>(sq + (col >> 6) * BLK_BYTES + sw128_offset(row, col & 63));
+                    v[4 * i] = u.x;
+                    v[4 * i + 1] = u.y;
+                    v[4 * i + 2] = u.z;
+                    v[4 * i + 3] = u.w;
+                }
+                tmem_st16(tbase + lane_addr + COL_Q + c * 16, v);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(q_full);
+            if (!q_ok && lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+            KP_MARK(1);
+        }
+        float m_used = M_INIT, l = 0.f;  // kept identically in both lane halves of a row
         bool ok = true;
+        const int half = lane >> 4;  // this thread exponentiates keys [32 * half, +32) of its row
         for (int j = 0; j < n; ++j) {
-            const uint32_t s_col = (j & 1) ? COL_S1 : COL_S0;
-            if (!mbar_wait(&s_full[j & 1], ((uint32_t)(j >> 1)) & 1u)) {
+            if (!mbar_wait(s_full, ((uint32_t)j) & 1u)) {
                 ok = false;
                 break;
             }
+            if (j < 6) KP_MARK(4 + j * 4);
             tc_fence_after();
             uint32_t sraw[PAGE];
-            tmem_ld32(tbase + lane_addr + s_col, sraw);
-            tmem_ld32(tbase + lane_addr + s_col + 32, sraw + 32);
+            tmem_ld32(tbase + lane_addr + COL_S, sraw);
+            tmem_ld32(tbase + lane_addr + COL_S + 32, sraw + 32);
             tc_wait_ld();
-            float x[PAGE];
-            const int k0 = (pg_begin + j) * PAGE;
+            tc_fence_before();
+            if (lane == 0) mbar_arrive(s_free);
+            // full scores of the row = the two partial products held by lanes i and i + 16
+            float x[PAGE / 2];
+            const int k0 = (pg_begin + j) * PAGE + half * (PAGE / 2);
 #pragma unroll
             for (int i = 0; i < PAGE; ++i) {
-                x[i] = __uint_as_float(sraw[i]) * p.scale_log2;
-                if (k0 + i >= kv_len) x[i] = -INFINITY;
+                const float other = __shfl_xor_sync(0xffffffffu, __uint_as_float(sraw[i]), 16);
+                if ((i >> 5) == half) {
+                    const int ii = i & 31;
+                    x[ii] = (__uint_as_float(sraw[i]) + other) * p.scale_log2;
+                    if (k0 + ii >= kv_len) x[ii] = -INFINITY;
+                }
             }
             float mx = x[0];
 #pragma unroll
-            for (int i = 1; i < PAGE; ++i) mx = fmaxf(mx, x[i]);
-            if (!s_owner) mx = -INFINITY;
+            for (int i = 1; i < PAGE / 2; ++i) mx = fmaxf(mx, x[i]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
             const float m_cand = fmaxf(m_used, mx);
             float alpha = 1.0f;
             bool rescale = false;
             if (j == 0) {
                 m_used = m_cand;
             } else {
-                rescale = __any_sync(0xffffffffu, s_owner && (m_cand - m_used) > RESCALE_THRESHOLD);
+                rescale = __any_sync(0xffffffffu, (m_cand - m_used) > RESCALE_THRESHOLD);
                 if (rescale) {
                     alpha = ex2_approx(m_used - m_cand);
                     m_used = m_cand;
                     l *= alpha;
                 }
             }
+            if (j < 6) KP_MARK(5 + j * 4);
             // P (and O) may only be touched once the previous tile's PV has drained
             if (j > 0 && !mbar_wait(pv_done, ((uint32_t)(j - 1)) & 1u)) {
                 ok = false;
                 break;
             }
+            if (j < 6) KP_MARK(6 + j * 4);
             if (rescale) {
-                alpha = __shfl_sync(0xffffffffu, alpha, lane & 15);
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < 256 / 32; ++c) {
@@ -250,30 +321,30 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 }
                 tc_wait_st();
             }
-            if (s_owner) {
-                float sum = 0.f;
+            float sum = 0.f;
 #pragma unroll
-                for (int c = 0; c < PAGE / 8; ++c) {
-                    float pv[8];
+            for (int c = 0; c < PAGE / 2 / 8; ++c) {
+                float pv[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        pv[i] = ex2_approx(x[c * 8 + i] - m_used);
-                        sum += pv[i];
-                    }
-                    uint4 v;
-                    v.x = pack_half2(pv[0], pv[1]);
-                    v.y = pack_half2(pv[2], pv[3]);
-                    v.z = pack_half2(pv[4], pv[5]);
-                    v.w = pack_half2(pv[6], pv[7]);
-                    *reinterpret_cast<uint4*>(sP + sw128_offset(row, c * 8)) = v;
+                for (int i = 0; i < 8; ++i) {
+                    pv[i] = ex2_approx(x[c * 8 + i] - m_used);
+                    sum += pv[i];
                 }
-                l += sum;
+                uint4 v;
+                v.x = pack_half2(pv[0], pv[1]);
+                v.y = pack_half2(pv[2], pv[3]);
+                v.z = pack_half2(pv[4], pv[5]);
+                v.w = pack_half2(pv[6], pv[7]);
+                *reinterpret_cast<uint4*>(sP + sw128_offset(row, half * (PAGE / 2) + c * 8)) = v;
             }
+            l += sum + __shfl_xor_sync(0xffffffffu, sum, 16);
             fence_proxy_async_smem();  // P was written through the generic proxy, the MMA reads it through the async one
             tc_fence_before();
             mbar_arrive(p_full);
+            if (j < 6) KP_MARK(7 + j * 4);
         }
         if (ok && !mbar_wait(pv_done, ((uint32_t)(n - 1)) & 1u)) ok = false;
+        KP_MARK(2);
         if (!ok) {
             if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
         } else {
@@ -284,7 +355,7 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             const bool valid = head < p.heads;
             // the partial row is stored normalised by its own sum, as fp16: half the bytes of an fp32 partial,
             // and the values are bounded by the largest cached latent
-            const float inv_l = 1.0f / __shfl_sync(0xffffffffu, l, lane & 15);
+            const float inv_l = 1.0f / l;
             __half* dst = p.part_acc + prow * LAT + (lane >> 4) * 256;
 #pragma unroll
             for (int c = 0; c < 256 / 32; ++c) {
@@ -303,15 +374,19 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                     }
                 }
             }
-            if (valid && s_owner) {
+            if (valid && lane < 16) {
                 p.part_ml[prow * 2] = m_used;
                 p.part_ml[prow * 2 + 1] = l;
             }
+            KP_MARK(3);
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 5) tmem_dealloc(tbase, TMEM_COLS);
+#ifdef INF_KPROF
+    if (tid == 0 && p.kprof && kp_cta < 256) p.kprof[64 + kp_cta * 2 + 1] = (long long)global_timer_ns();
+#endif
 }
 
 // Merge of the split partials.  One CTA per (head, token, quarter of the 512 output columns); the split
@@ -462,10 +537,35 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
         ctx->func_attr_done |= 16u;
     }
     dim3 grid(n_splits, tokens * head_blocks, table->batch);
+#ifdef INF_KPROF
+    static long long* d_kprof = nullptr;
+    if (!d_kprof) cudaMalloc(&d_kprof, 576 * sizeof(long long));
+    cudaMemsetAsync(d_kprof, 0, 576 * sizeof(long long), ctx->stream);
+    p.kprof = d_kprof;
+#endif
     {
         inf_prof_scope prof(ctx, "mla_decode_partial_kernel");
         mla_decode_partial_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tq, tkv, p);
     }
+#ifdef INF_KPROF
+    {
+        long long h[576];
+        cudaMemcpy(h, d_kprof, sizeof(h), cudaMemcpyDeviceToHost);
+        {
+            long long e0 = 0, e1 = 0, x0 = 0, x1 = 0; int nc = 0;
+            for (int i = 0; i < 256; ++i) {
+                if (!h[64 + 2 * i]) continue;
+                const long long e = h[64 + 2 * i], x = h[65 + 2 * i];
+                if (!nc) { e0 = e1 = e; x0 = x1 = x; }
+                e0 = e < e0 ? e : e0; e1 = e > e1 ? e : e1; x0 = x < x0 ? x : x0; x1 = x > x1 ? x : x1; ++nc;
+            }
+            fprintf(stderr, "KPROF mla_decode %d CTAs: entries spread over %lld ns, first exit %lld ns, last exit %lld ns after the first entry\n", nc, e1 - e0, x0 - e0, x1 - e0);
+        }
+        fprintf(stderr, "KPROF mla_decode CTA 0 thread 0, ns after entry: set-up %lld, Q in TMEM %lld, last PV retired %lld, partial stored %lld; per page (S ready, max known, PV(j-1) retired, P handed over):", h[0], h[1], h[2], h[3]);
+        for (int j = 0; j < 6 && h[4 + j * 4]; ++j) fprintf(stderr, " [%lld %lld %lld %lld]", h[4 + j * 4], h[5 + j * 4], h[6 + j * 4], h[7 + j * 4]);
+        fprintf(stderr, "\n");
+    }
+#endif
     INF_LAUNCH_CHECK(ctx, "mla_decode_partial_kernel");
     dim3 cgrid(heads, tokens * table->batch);
     if (out_dtype == INF_DTYPE_F32)
