@@ -103,6 +103,32 @@ int inf_make_tmap(inf_ctx* ctx, const void* base, uint32_t rank, const uint64_t*
             return inf_fail(ctx, INF_E_BACKEND, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
     } while (0)
 
+// Programmatic dependent launch for the kernels of one decode step.  A kernel launched through inf_launch_pdl may
+// be scheduled while the kernel before it in the stream is still running; it must execute inf_pdl_wait() before
+// its first access to global memory (which waits for that kernel to finish and its writes to be visible), so all
+// that overlaps is the launch itself and the block set-up.  inf_pdl_release() lets the next kernel of the stream
+// be scheduled early in the same way.  Outside such a launch both calls return at once.
+#ifdef __CUDACC__
+__device__ __forceinline__ void inf_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void inf_pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t inf_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // Host-side range check of the page-table entries a launch may touch (needs the host mirrors).
 int inf_validate_table(inf_ctx* ctx, const inf_page_table* t, int num_pages, int page_size, int extra_tokens,
                        const char* what);

@@ -79,6 +79,8 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     __shared__ float warp_m[CONSUMER_WARPS][16], warp_l[CONSUMER_WARPS][16];
     float* merge = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);  // [warp][group rows][128], not in the ring
 
+    inf_pdl_wait();  // the appended K/V rows and the roped query come from the kernel before this one
+    inf_pdl_release();
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv_len = p.lens[b] + p.len_add;
@@ -366,6 +368,8 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
                           int q_heads, int max_chunks, int chunk, int window, int len_add) {
     __shared__ float w[MAX_CHUNK / TILE_KEYS * 16];  // up to 512 chunks
     __shared__ float red[4];
+    inf_pdl_wait();
+    inf_pdl_release();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int kv_len = lens[b] + len_add;
     const long long orow = ((long long)b * q_heads + h) * D + d;
@@ -493,18 +497,18 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     dim3 grid((max_chunks + p.chunks_per_cta - 1) / p.chunks_per_cta, pool->kv_heads, table->batch);
     {
         inf_prof_scope prof(ctx, "gqa_decode_partial_kernel");
-        gqa_decode_partial_kernel<<<grid, THREADS, smem, ctx->stream>>>(tm_k, tm_v, p);
+        INF_CUDA(ctx, inf_launch_pdl(gqa_decode_partial_kernel, grid, dim3(THREADS), smem, ctx->stream, tm_k, tm_v, p));
     }
     INF_LAUNCH_CHECK(ctx, "gqa_decode_partial_kernel");
     dim3 cgrid(q_heads, table->batch);
     if (out_dtype == INF_DTYPE_F32)
-        gqa_decode_combine_kernel<float><<<cgrid, D, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens, gate,
-                                                                        (float*)out, q_heads, max_chunks, split_chunk,
-                                                                        sliding_window, len_add);
+        INF_CUDA(ctx, inf_launch_pdl(gqa_decode_combine_kernel<float>, cgrid, dim3(D), 0, ctx->stream, p.part_acc, p.part_ml,
+                                     table->lens, gate, (float*)out, q_heads, max_chunks, split_chunk, sliding_window,
+                                     len_add));
     else
-        gqa_decode_combine_kernel<__half><<<cgrid, D, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens, gate,
-                                                                         (__half*)out, q_heads, max_chunks,
-                                                                         split_chunk, sliding_window, len_add);
+        INF_CUDA(ctx, inf_launch_pdl(gqa_decode_combine_kernel<__half>, cgrid, dim3(D), 0, ctx->stream, p.part_acc,
+                                     p.part_ml, table->lens, gate, (__half*)out, q_heads, max_chunks, split_chunk,
+                                     sliding_window, len_add));
     INF_LAUNCH_CHECK(ctx, "gqa_decode_combine_kernel");
     return INF_OK;
 }

@@ -28,6 +28,8 @@ template <typename OutT>
 __global__ void __launch_bounds__(MV_WARPS * 32)
 q8_0_heads_matvec_kernel(const uint8_t* __restrict__ weights, const float* __restrict__ input, OutT* __restrict__ out,
                          int rows, int heads, int in_features, int out_features, long long out_stride) {
+    inf_pdl_wait();
+    inf_pdl_release();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int o = blockIdx.x * MV_WARPS + warp;
     const int head = blockIdx.y;
@@ -72,6 +74,7 @@ q8_0_heads_matvec_tile_kernel(const uint8_t* __restrict__ weights, const float* 
     extern __shared__ __align__(16) uint8_t tile[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int o0 = blockIdx.x * TILE_ROWS;
+    // the weights never change: stage them before waiting for the kernel that produces the input rows
     const int head = blockIdx.y;
     const int row0 = blockIdx.z * MV_ROWS;
     const int blocks_per_row = in_features / Q8_BLOCK_VALUES;
@@ -79,6 +82,8 @@ q8_0_heads_matvec_tile_kernel(const uint8_t* __restrict__ weights, const float* 
     const uint4* src = reinterpret_cast<const uint4*>(weights + ((size_t)head * out_features + o0) * row_bytes);
     const int n16 = TILE_ROWS * row_bytes / 16;
     for (int i = threadIdx.x; i < n16; i += MV_WARPS * 32) reinterpret_cast<uint4*>(tile)[i] = src[i];
+    inf_pdl_wait();
+    inf_pdl_release();
     if (tail && blockIdx.x == 0) {
         for (int r = 0; r < MV_ROWS && row0 + r < rows; ++r)
             for (int d = threadIdx.x; d < tail_n; d += MV_WARPS * 32)
@@ -116,6 +121,8 @@ q8_0_heads_matvec_tile_kernel(const uint8_t* __restrict__ weights, const float* 
 // q_rope f32 [rows*heads][rope] -> fp16 columns [latent, latent+rope) of the absorbed query rows.
 __global__ void pack_q_rope_kernel(const float* __restrict__ q_rope, __half* __restrict__ q_abs, long long n, int rope,
                                    int row_width, int col0) {
+    inf_pdl_wait();
+    inf_pdl_release();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const long long r = i / rope;
@@ -130,6 +137,8 @@ __global__ void append_latent_rows_kernel(const float* __restrict__ latent, cons
                                           __half* __restrict__ pool, int num_pages, int page_size,
                                           const int* __restrict__ pages, const int* __restrict__ lens, int max_pages,
                                           int tokens, int L, int R, int* __restrict__ status) {
+    inf_pdl_wait();  // the pages may still be read by the attention kernels of the previous step
+    inf_pdl_release();
     const long long row = blockIdx.x;
     const int b = (int)(row / tokens), t = (int)(row % tokens);
     const int position = lens[b] + t;
@@ -157,17 +166,18 @@ int launch_matvec(inf_ctx* ctx, const void* weights, const float* input, OutT* o
     inf_prof_scope prof(ctx, name);
     if (tiled) {
         dim3 grid(out_features / TILE_ROWS, heads, (rows + MV_ROWS - 1) / MV_ROWS);
-        q8_0_heads_matvec_tile_kernel<OutT><<<grid, MV_WARPS * 32, tile_bytes, ctx->stream>>>(
-            (const uint8_t*)weights, input, out, rows, heads, in_features, out_features, out_stride, tail, tail_n,
-            tail_col0);
+        INF_CUDA(ctx, inf_launch_pdl(q8_0_heads_matvec_tile_kernel<OutT>, grid, dim3(MV_WARPS * 32), tile_bytes, ctx->stream,
+                                     (const uint8_t*)weights, input, out, rows, heads, in_features, out_features,
+                                     out_stride, tail, tail_n, tail_col0));
     } else {
         dim3 grid((out_features + MV_WARPS - 1) / MV_WARPS, heads, (rows + MV_ROWS - 1) / MV_ROWS);
-        q8_0_heads_matvec_kernel<OutT><<<grid, MV_WARPS * 32, 0, ctx->stream>>>(
-            (const uint8_t*)weights, input, out, rows, heads, in_features, out_features, out_stride);
+        INF_CUDA(ctx, inf_launch_pdl(q8_0_heads_matvec_kernel<OutT>, grid, dim3(MV_WARPS * 32), 0, ctx->stream,
+                                     (const uint8_t*)weights, input, out, rows, heads, in_features, out_features,
+                                     out_stride));
         if (tail) {
             const long long n = (long long)rows * heads * tail_n;
-            pack_q_rope_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(tail, (__half*)out, n, tail_n,
-                                                                                    (int)out_stride, tail_col0);
+            INF_CUDA(ctx, inf_launch_pdl(pack_q_rope_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, ctx->stream,
+                                         tail, (__half*)out, n, tail_n, (int)out_stride, tail_col0));
         }
     }
     INF_LAUNCH_CHECK(ctx, name);
@@ -241,10 +251,9 @@ extern "C" int32_t inf_q8_0_absorbed_mla(inf_ctx* ctx, const void* k_b_weights, 
     float* context = (float*)((char*)ctx->workspace + q_bytes);
 
     if (current_latent) {
-        append_latent_rows_kernel<<<(unsigned)rows, 128, 0, ctx->stream>>>(
-            current_latent, current_rope, (__half*)pool->rows, pool->num_pages, pool->page_size, table->pages,
-            table->lens, table->max_pages, tokens, L, R, ctx->status);
-        INF_LAUNCH_CHECK(ctx, "append_latent_rows_kernel");
+        INF_CUDA(ctx, inf_launch_pdl(append_latent_rows_kernel, dim3((unsigned)rows), dim3(128), 0, ctx->stream,
+                                     current_latent, current_rope, (__half*)pool->rows, pool->num_pages, pool->page_size,
+                                     table->pages, table->lens, table->max_pages, tokens, L, R, ctx->status));
     }
     rc = launch_matvec<__half>(ctx, k_b_weights, q_no_rope, q_abs, (int)rows, heads, q_no_rope_dim, L, L + R,
                                "q8_0_heads_matvec_kernel(K_b)", q_rope, R, L);

@@ -98,6 +98,8 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int kp_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
     if (tid == 0 && p.kprof && kp_cta < 256) p.kprof[64 + kp_cta * 2] = kp_t0;
 #endif
+    inf_pdl_wait();  // the appended row and the query come from kernels earlier in the stream
+    inf_pdl_release();
     const int split = blockIdx.x;
     const int t = blockIdx.y % p.tokens, hb = blockIdx.y / p.tokens;
     const int b = blockIdx.z;
@@ -404,6 +406,8 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     __shared__ float w[MAX_SPLITS];
     __shared__ float red[8];
     __shared__ float group_acc[3][LAT];
+    inf_pdl_wait();
+    inf_pdl_release();
     const int h = blockIdx.x, t = blockIdx.y % tokens, b = blockIdx.y / tokens;
     const int tid = threadIdx.x;
     const int kv_len = lens[b] + t + 1;
@@ -545,7 +549,7 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
 #endif
     {
         inf_prof_scope prof(ctx, "mla_decode_partial_kernel");
-        mla_decode_partial_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tq, tkv, p);
+        INF_CUDA(ctx, inf_launch_pdl(mla_decode_partial_kernel, grid, dim3(NUM_THREADS), SMEM_TOTAL, ctx->stream, tq, tkv, p));
     }
 #ifdef INF_KPROF
     {
@@ -569,11 +573,11 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
     INF_LAUNCH_CHECK(ctx, "mla_decode_partial_kernel");
     dim3 cgrid(heads, tokens * table->batch);
     if (out_dtype == INF_DTYPE_F32)
-        mla_decode_combine_kernel<float><<<cgrid, 256, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
-                                                                         (float*)out, tokens, heads, n_splits);
+        INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<float>, cgrid, dim3(256), 0, ctx->stream, p.part_acc,
+                                     p.part_ml, table->lens, (float*)out, tokens, heads, n_splits));
     else
-        mla_decode_combine_kernel<__half><<<cgrid, 256, 0, ctx->stream>>>(p.part_acc, p.part_ml, table->lens,
-                                                                          (__half*)out, tokens, heads, n_splits);
+        INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<__half>, cgrid, dim3(256), 0, ctx->stream, p.part_acc,
+                                     p.part_ml, table->lens, (__half*)out, tokens, heads, n_splits));
     INF_LAUNCH_CHECK(ctx, "mla_decode_combine_kernel");
     return INF_OK;
 }

@@ -89,6 +89,8 @@ __global__ void rope_append_gqa_kernel(const T* __restrict__ q, const T* __restr
                                        int max_pages, int tokens, int q_heads, int kv_heads,
                                        __half* __restrict__ q_out, float* __restrict__ k_f32_out, long long q_rows,
                                        long long kv_rows, int* __restrict__ status) {
+    inf_pdl_wait();  // the pages may still be read by the attention kernels of the previous step
+    inf_pdl_release();
     long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= q_rows + 2 * kv_rows) return;
@@ -154,6 +156,8 @@ mla_postprocess_append_kernel(const float* __restrict__ in, const float* __restr
                               __half* __restrict__ pool, int num_pages, int page_size, const int* __restrict__ pages,
                               const int* __restrict__ lens, int max_pages, int tokens, int L, int R,
                               float* __restrict__ latent_out, float* __restrict__ rope_out, int* __restrict__ status) {
+    inf_pdl_wait();  // the pages may still be read by the attention kernels of the previous step
+    inf_pdl_release();
     long long row = blockIdx.x;
     int tid = threadIdx.x;
     int b = (int)(row / tokens), token = (int)(row % tokens);
@@ -280,16 +284,17 @@ int32_t inf_rope_append_gqa(inf_ctx* ctx, const void* q, const void* k, const vo
     int rd = rope ? rope->rotary_dim : 64;
     float factor = rope ? rope->attention_factor : 1.0f;
     if (in_dtype == INF_DTYPE_F32)
-        rope_append_gqa_kernel<float><<<blocks, 256, 0, ctx->stream>>>(
-            (const float*)q, (const float*)k, (const float*)v, qw, kw, inv, rd, factor, eps, (__half*)pool->k,
-            (__half*)pool->v, pool->num_pages, pool->page_size, table->pages, table->lens, table->max_pages, tokens,
-            q_heads, pool->kv_heads, (__half*)q_out_f16, k_f32_out, q_rows, kv_rows, ctx->status);
+        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<float>, dim3(blocks), dim3(256), 0, ctx->stream,
+                                     (const float*)q, (const float*)k, (const float*)v, qw, kw, inv, rd, factor, eps,
+                                     (__half*)pool->k, (__half*)pool->v, pool->num_pages, pool->page_size, table->pages,
+                                     table->lens, table->max_pages, tokens, q_heads, pool->kv_heads, (__half*)q_out_f16,
+                                     k_f32_out, q_rows, kv_rows, ctx->status));
     else
-        rope_append_gqa_kernel<__half><<<blocks, 256, 0, ctx->stream>>>(
-            (const __half*)q, (const __half*)k, (const __half*)v, qw, kw, inv, rd, factor, eps, (__half*)pool->k,
-            (__half*)pool->v, pool->num_pages, pool->page_size, table->pages, table->lens, table->max_pages, tokens,
-            q_heads, pool->kv_heads, (__half*)q_out_f16, k_f32_out, q_rows, kv_rows, ctx->status);
-    INF_LAUNCH_CHECK(ctx, "rope_append_gqa_kernel");
+        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<__half>, dim3(blocks), dim3(256), 0, ctx->stream,
+                                     (const __half*)q, (const __half*)k, (const __half*)v, qw, kw, inv, rd, factor, eps,
+                                     (__half*)pool->k, (__half*)pool->v, pool->num_pages, pool->page_size, table->pages,
+                                     table->lens, table->max_pages, tokens, q_heads, pool->kv_heads, (__half*)q_out_f16,
+                                     k_f32_out, q_rows, kv_rows, ctx->status));
     return INF_OK;
 }
 
@@ -324,10 +329,10 @@ int32_t inf_mla_kv_postprocess_append(inf_ctx* ctx, const float* input, const fl
     InvFreq64 f;
     host_inv_freq_glm(theta, pool->rope_dim, &f);
     long long rows = (long long)table->batch * tokens;
-    mla_postprocess_append_kernel<<<(unsigned)rows, 128, 0, ctx->stream>>>(
-        input, norm_weight, eps, f, (__half*)pool->rows, pool->num_pages, pool->page_size, table->pages, table->lens,
-        table->max_pages, tokens, pool->latent_dim, pool->rope_dim, latent_out, rope_out, ctx->status);
-    INF_LAUNCH_CHECK(ctx, "mla_postprocess_append_kernel");
+    INF_CUDA(ctx, inf_launch_pdl(mla_postprocess_append_kernel, dim3((unsigned)rows), dim3(128), 0, ctx->stream, input,
+                                 norm_weight, eps, f, (__half*)pool->rows, pool->num_pages, pool->page_size, table->pages,
+                                 table->lens, table->max_pages, tokens, pool->latent_dim, pool->rope_dim, latent_out,
+                                 rope_out, ctx->status));
     return INF_OK;
 }
 
