@@ -338,6 +338,45 @@ class MlaAbsorbedDecode(MlaDecode):
         return run, self.units_per_step, "whole workload (1 sequence, 64 heads, full context, both projections)"
 
 
+class MlaSelectedDecode(MlaDecode):
+    """DSA sparse decode, attention step: absorbed MLA over 2048 selected rows (seeded choice, newest row always
+    kept) of a 32 768-row paged latent cache, the gather fused into the kernel.  Only the selected rows move."""
+    metric = "mla_selected_decode_hbm_gbs"
+    N_SEL = 2048
+
+    def __init__(self, be, rank, ctx_len):
+        super().__init__(be, rank, ctx_len)
+        torch = self.torch
+        self.name = f"mla_selected_decode_{self.N_SEL}_of_{ctx_len // 1024}k"
+        self.traffic = None
+        g = torch.Generator(device="cpu").manual_seed(SEED + 31 + rank)
+        ids = torch.randperm(ctx_len - 1, generator=g)[: self.N_SEL - 1].sort().values.to(torch.int32)
+        self.sel = torch.cat([ids, torch.tensor([ctx_len - 1], dtype=torch.int32)]).view(1, -1).to(be.device)
+        self.counts = torch.tensor([self.N_SEL], dtype=torch.int32, device=be.device)
+        row_bytes = (self.L + self.R) * 2
+        self.units_per_step = float(self.N_SEL) * row_bytes
+        self.flops_per_step = 2.0 * self.H * (self.L + self.R + self.L) * self.N_SEL
+        self.config.update({"workload": self.name, "selected_rows": self.N_SEL, "kv_bytes_per_step": int(self.units_per_step),
+                            "flops_per_step": self.flops_per_step})
+
+    def step(self):
+        t = self.tables[self.i % self.n_caches]
+        self.i += 1
+        self.be.mla_kv_postprocess_device(self.x, self.w, 1e-6, 1.0e7, self.pool, t, want_outputs=False)
+        self.be.mla_decode_absorbed_selected(self.q, self.pool, t, self.sel, self.counts, self.scale, out=self.out)
+
+    def cpu_sample(self):
+        from oracle import pyoracle as orc
+        n, W = self.N_SEL, self.L + self.R  # the oracle runs on the gathered rows, as the reference does
+        table = np.arange((n + self.P - 1) // self.P, dtype=np.int32)[None]
+        pool = np.resize(np.random.RandomState(SEED + 24).standard_normal(1 << 20).astype(np.float16).view(np.uint16),
+                         table.size * self.P * W).reshape(-1, self.P, W)
+        q = orc.fill_normal((1, 1, self.H, W), SEED + 25)
+        cur = orc.fill_normal((1, 1, W), SEED + 26, 0.5)
+        run = lambda: orc.mla_absorbed_paged(q, cur, pool, table, [n - 1], self.P, self.L, self.R, self.scale)
+        return run, self.units_per_step, "whole workload (2048 gathered rows, 64 heads)"
+
+
 class GqaPrefill2k:
     """Causal GQA prefill, one 2048-token prompt, 48 q / 8 kv heads, fused RoPE + KV-append (fourth configuration).
     With N > 1 ranks the heads are sharded (48/N query heads with their 8/N KV heads per rank) and the output is
@@ -492,6 +531,8 @@ def make_workload(name, be, rank, world=1, dist=None, tokens=0):
         return MlaDecode(be, rank, 4096)
     if name == "mla_decode_32k":
         return MlaDecode(be, rank, 32768)
+    if name == "mla_selected_decode_32k":
+        return MlaSelectedDecode(be, rank, 32768)
     if name == "mla_absorbed_decode_32k":
         return MlaAbsorbedDecode(be, rank, 32768)
     if name == "gqa_prefill_2k":
@@ -508,7 +549,8 @@ def make_workload(name, be, rank, world=1, dist=None, tokens=0):
     raise KeyError(name)
 
 
-WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "gqa_prefill_2k",
+WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "mla_selected_decode_32k",
+                  "gqa_prefill_2k",
                   "mla_prefill_32k"]
 STRONG = {"gqa_prefill_2k", "mla_prefill_32k"}  # head-sharded with an all-gather; the others replicate/shard by sequence
 

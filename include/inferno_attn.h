@@ -251,6 +251,19 @@ int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, const inf_mla_p
                                 const inf_page_table* table, int32_t tokens, int32_t heads, int32_t max_len,
                                 float scale, void* out, int32_t out_dtype);
 
+/* Absorbed-MLA decode over SELECTED cached rows: the attention step of the reference's DSA sparse decode
+ * (crates/model/src/attention.rs:2843-2960: the rows chosen by the indexer are copied into a compact cache by
+ * selected_kv_for_tokens and attended to with the current token; the expanded-head form of the same step is
+ * selected_decode_attention_device, backend.rs:1999, kernel attention_kernels.metal:605).  Here the gather is
+ * part of the kernel: selected[b][i], i < selected_counts[b] <= selected_stride, are logical row ids of sequence
+ * b (each < lens[b] + 1, the current token's row included by listing it; order free, no duplicates expected);
+ * the softmax runs over exactly those rows.  One query token per sequence: q fp16 [batch, 1, heads, 576],
+ * out [batch, 1, heads, 512].  Ids outside the visible rows set the context's error status (inf_flush). */
+int32_t inf_mla_decode_absorbed_selected(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool,
+                                         const inf_page_table* table, const int32_t* selected,
+                                         const int32_t* selected_counts, int32_t selected_stride, int32_t heads,
+                                         float scale, void* out, int32_t out_dtype);
+
 /* Per-head Q8_0 matvec (kernel q8_0_packed_heads_matvec_f32_kernel, crates/backend/src/metal/kernels/
  * q2_kernels.metal:3146; host crates/backend/src/metal/q2.rs:2656): weights (device) [heads][out_features]
  * [in_features] in Q8_0 row blocks of 34 bytes (little-endian f16 scale, 32 signed quants); input f32

@@ -311,6 +311,20 @@ class CudaBackend:
                                                            C.byref(table.desc), T, H, max_len, scale, _ptr(out), dt))
         return out if ok else None
 
+    def mla_decode_absorbed_selected(self, q_f16, pool: MlaPool, table: PageTable, selected, selected_counts,
+                                     scale: float, out_dtype=torch.float32, out=None):
+        """Absorbed-MLA decode over the rows listed in `selected` (int32 [B, stride] logical row ids, the first
+        selected_counts[b] of each row are used): the attention step of DSA sparse decode with the gather fused in."""
+        B, T, H, W = q_f16.shape
+        assert T == 1 and selected.dtype == torch.int32 and selected_counts.dtype == torch.int32
+        if out is None:
+            out = torch.empty((B, 1, H, pool.desc.latent_dim), dtype=out_dtype, device=self.device)
+        dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
+        ok = self._check(self._lib.inf_mla_decode_absorbed_selected(
+            self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc), _ptr(selected), _ptr(selected_counts),
+            selected.shape[1], H, scale, _ptr(out), dt))
+        return out if ok else None
+
     def q8_0_packed_heads_matvec(self, weights_u8, x, out_features: int):
         """Per-head Q8_0 matvec (q2_kernels.metal:3146): weights uint8 device tensor, x f32 [rows, heads, in]."""
         rows, heads, in_features = x.shape

@@ -11,7 +11,8 @@
 
 size_t inf_mla_decode_scratch_bytes(const inf_ctx* ctx, int batch, int tokens, int heads, int max_len);
 int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool, const inf_page_table* table,
-                          int tokens, int heads, int max_len, float scale, void* out, int out_dtype, size_t ws_offset);
+                          int tokens, int heads, int max_len, float scale, void* out, int out_dtype, size_t ws_offset,
+                          const int* sel, const int* sel_counts, int sel_stride);
 
 namespace {
 
@@ -260,7 +261,7 @@ extern "C" int32_t inf_q8_0_absorbed_mla(inf_ctx* ctx, const void* k_b_weights, 
     if (rc != INF_OK) return rc;
     const float scale = 1.0f / sqrtf((float)qk_head_dim);  // attention_kernels.metal:501: scale_dim = qk_head_dim
     rc = inf_mla_decode_launch(ctx, q_abs, pool, table, tokens, heads, max_len, scale, context, INF_DTYPE_F32,
-                               q_bytes + ctx_bytes);
+                               q_bytes + ctx_bytes, nullptr, nullptr, 0);
     if (rc != INF_OK) return rc;
     return launch_matvec<float>(ctx, v_b_weights, context, out, (int)rows, heads, L, value_dim, value_dim,
                                 "q8_0_heads_matvec_kernel(V_b)");

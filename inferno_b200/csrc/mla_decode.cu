@@ -40,6 +40,7 @@ constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0, COL_S = 256, COL_Q = 320;  // O 256 columns, S 64, Q 144 (each on both lane halves)
 constexpr int STAGES = 3;
+constexpr int GATHER_UNIT = 16;  // the gather form splits the row list in units of 16 rows, so a short list still fills the GPU
 constexpr int QHALF = ROW / 2;  // 288 query columns per lane half
 
 constexpr int OFF_KV = 0;
@@ -50,6 +51,9 @@ constexpr int SMEM_TOTAL = OFF_BAR + 128;
 struct MlaParams {
     const int* pages;
     const int* lens;
+    const int* sel;         // gather form: [batch][sel_stride] logical row ids; null for the contiguous form
+    const int* sel_counts;  // gather form: rows selected per sequence
+    int sel_stride;
     int max_pages, num_pages;
     int tokens, heads, head_blocks, batch;
     int n_splits;
@@ -74,6 +78,10 @@ __device__ __forceinline__ void split_range(int n_pages, int n_splits, int s, in
     end = min(n_pages, begin + per);
 }
 
+// GATHER: the keys are not the first kv_len rows of the sequence but the rows listed in p.sel (the DSA indexer's
+// choice); a "page" is then any 64 listed rows, fetched row by row with one-row TMA boxes (tm_kv has a box of
+// one row in that form), and everything after the load is unchanged.
+template <bool GATHER>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                           MlaParams p) {
@@ -103,11 +111,15 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int split = blockIdx.x;
     const int t = blockIdx.y % p.tokens, hb = blockIdx.y / p.tokens;
     const int b = blockIdx.z;
-    const int kv_len = p.lens[b] + t + 1;  // rows visible to this query token
-    const int n_pages = (kv_len + PAGE - 1) / PAGE;
-    int pg_begin, pg_end;
-    split_range(n_pages, p.n_splits, split, pg_begin, pg_end);
-    const int n = pg_end - pg_begin;
+    const int seq_rows = p.lens[b] + t + 1;                     // rows visible to this query token
+    const int kv_len = GATHER ? p.sel_counts[b] : seq_rows;  // keys this call attends to
+    // this CTA's keys: rows [row_begin, row_end) of the sequence (contiguous form: whole pages) or of the list
+    const int unit = GATHER ? GATHER_UNIT : PAGE;
+    int u_begin, u_end;
+    split_range((kv_len + unit - 1) / unit, p.n_splits, split, u_begin, u_end);
+    const int row_begin = u_begin * unit, row_end = min(kv_len, u_end * unit);
+    const int pg_begin = row_begin / PAGE;           // contiguous form only
+    const int n = (row_end - row_begin + PAGE - 1) / PAGE;  // 64-row tiles
     if (n <= 0) return;
     if ((smem_u32(smem) & 1023u) != 0) {
         if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
@@ -147,32 +159,91 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             for (int blk = 0; blk < NBLK; ++blk)
                 tma_load_3d(sKV + (STAGES - 1) * TILE_BYTES + blk * BLK_BYTES, &tm_q, blk * 64, hb * HB,
                             b * p.tokens + t, q_landed);
+            if (!GATHER) {
+                const int oob_row = p.num_pages * PAGE;
+                for (int j = 0; j < n; ++j) {
+                    const int slot = pg_begin + j;
+                    int y = oob_row;
+                    if (slot < p.max_pages) {
+                        const int page = p.pages[(long long)b * p.max_pages + slot];
+                        if (page >= 0 && page < p.num_pages)
+                            y = page * PAGE;
+                        else
+                            atomicOr(p.status, INF_STATUS_BAD_PAGE);
+                    } else {
+                        atomicOr(p.status, INF_STATUS_BAD_LEN);
+                    }
+                    const int st = j % STAGES;
+                    if (j == STAGES - 1 && !mbar_wait(q_full, 0)) {  // the stage still holds Q until it is in TMEM
+                        atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                        break;
+                    }
+                    if (!mbar_wait(&kv_empty[st], (((uint32_t)(j / STAGES)) & 1u) ^ 1u)) {
+                        atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&kv_full[st], TILE_BYTES);
+#pragma unroll
+                    for (int blk = 0; blk < NBLK; ++blk)
+                        tma_load_2d(sKV + st * TILE_BYTES + blk * BLK_BYTES, &tm_kv, blk * 64, y, &kv_full[st]);
+                }
+            }
+        }
+        if (GATHER) {  // the whole warp: lane l fetches rows l and l + 32 of every group of 64 listed rows
             const int oob_row = p.num_pages * PAGE;
             for (int j = 0; j < n; ++j) {
-                const int slot = pg_begin + j;
-                int y = oob_row;
-                if (slot < p.max_pages) {
-                    const int page = p.pages[(long long)b * p.max_pages + slot];
-                    if (page >= 0 && page < p.num_pages)
-                        y = page * PAGE;
-                    else
-                        atomicOr(p.status, INF_STATUS_BAD_PAGE);
-                } else {
-                    atomicOr(p.status, INF_STATUS_BAD_LEN);
+                const int rows_here = min(PAGE, row_end - (row_begin + j * PAGE));  // listed rows in this 64-row tile
+                int ys[2];
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int i = row_begin + j * PAGE + lane + 32 * rr;
+                    ys[rr] = oob_row;  // an id the query may not see is fetched as a row of zeros
+                    if (i < row_end) {
+                        const int id = p.sel[(long long)b * p.sel_stride + i];
+                        if (id >= 0 && id < seq_rows && id / PAGE < p.max_pages) {
+                            const int page = p.pages[(long long)b * p.max_pages + id / PAGE];
+                            if (page >= 0 && page < p.num_pages)
+                                ys[rr] = page * PAGE + id % PAGE;
+                            else
+                                atomicOr(p.status, INF_STATUS_BAD_PAGE);
+                        } else {
+                            atomicOr(p.status, INF_STATUS_BAD_LEN);  // a listed row the query may not see
+                        }
+                    }
                 }
                 const int st = j % STAGES;
-                if (j == STAGES - 1 && !mbar_wait(q_full, 0)) {  // the stage still holds Q until it is in TMEM
-                    atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+                int ok = 1;
+                if (lane == 0) {
+                    if (j == STAGES - 1 && !mbar_wait(q_full, 0)) ok = 0;  // the stage still holds Q until it is in TMEM
+                    if (ok && !mbar_wait(&kv_empty[st], (((uint32_t)(j / STAGES)) & 1u) ^ 1u)) ok = 0;
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
                     break;
                 }
-                if (!mbar_wait(&kv_empty[st], (((uint32_t)(j / STAGES)) & 1u) ^ 1u)) {
-                    atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
-                    break;
-                }
-                mbar_arrive_expect_tx(&kv_full[st], TILE_BYTES);
+                // Rows of the tile beyond the list are not fetched (a one-row TMA request costs as much as any other):
+                // they are cleared here, because a masked key still enters PV as 0 x (whatever the stage held).
 #pragma unroll
-                for (int blk = 0; blk < NBLK; ++blk)
-                    tma_load_2d(sKV + st * TILE_BYTES + blk * BLK_BYTES, &tm_kv, blk * 64, y, &kv_full[st]);
+                for (int rr = 0; rr < 2; ++rr)
+                    if (lane + 32 * rr >= rows_here)
+#pragma unroll
+                        for (int blk = 0; blk < NBLK; ++blk) {
+                            uint4* dst = reinterpret_cast<uint4*>(sKV + st * TILE_BYTES + blk * BLK_BYTES + (lane + 32 * rr) * 128);
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_expect_tx(&kv_full[st], (uint32_t)rows_here * ROW * 2);
+                __syncwarp();
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr)
+                    if (lane + 32 * rr < rows_here)
+#pragma unroll
+                        for (int blk = 0; blk < NBLK; ++blk)
+                            tma_load_2d(sKV + st * TILE_BYTES + blk * BLK_BYTES + (lane + 32 * rr) * 128, &tm_kv, blk * 64,
+                                        ys[rr], &kv_full[st]);
             }
         }
     } else if (warp == 5) {
@@ -276,14 +347,14 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             if (lane == 0) mbar_arrive(s_free);
             // full scores of the row = the two partial products held by lanes i and i + 16
             float x[PAGE / 2];
-            const int k0 = (pg_begin + j) * PAGE + half * (PAGE / 2);
+            const int k0 = row_begin + j * PAGE + half * (PAGE / 2);
 #pragma unroll
             for (int i = 0; i < PAGE; ++i) {
                 const float other = __shfl_xor_sync(0xffffffffu, __uint_as_float(sraw[i]), 16);
                 if ((i >> 5) == half) {
                     const int ii = i & 31;
                     x[ii] = (__uint_as_float(sraw[i]) + other) * p.scale_log2;
-                    if (k0 + ii >= kv_len) x[ii] = -INFINITY;
+                    if (k0 + ii >= row_end) x[ii] = -INFINITY;
                 }
             }
             float mx = x[0];
@@ -402,7 +473,8 @@ constexpr int MAX_SPLITS = 1024;
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __restrict__ part_ml,
-                          const int* __restrict__ lens, OutT* __restrict__ out, int tokens, int heads, int n_splits) {
+                          const int* __restrict__ lens, const int* __restrict__ counts, OutT* __restrict__ out, int tokens,
+                          int heads, int n_splits) {
     __shared__ float w[MAX_SPLITS];
     __shared__ float red[8];
     __shared__ float group_acc[3][LAT];
@@ -410,8 +482,8 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     inf_pdl_release();
     const int h = blockIdx.x, t = blockIdx.y % tokens, b = blockIdx.y / tokens;
     const int tid = threadIdx.x;
-    const int kv_len = lens[b] + t + 1;
-    const int n_pages = (kv_len + PAGE - 1) / PAGE;
+    const int kv_len = counts ? counts[b] : lens[b] + t + 1;  // keys the partial kernel saw
+    const int n_pages = (kv_len + (counts ? GATHER_UNIT : PAGE) - 1) / (counts ? GATHER_UNIT : PAGE);  // split units
     const int per = (n_pages + n_splits - 1) / n_splits;
     const int n_valid = (n_pages + per - 1) / per;  // splits [0, n_valid) did work
     const long long prow0 = (((long long)b * tokens + t) * n_splits) * heads + h;
@@ -496,11 +568,15 @@ size_t inf_mla_decode_scratch_bytes(const inf_ctx* ctx, int batch, int tokens, i
     return acc_bytes + prows * 2 * sizeof(float);
 }
 
+// sel == nullptr: keys are rows 0 .. lens[b]+t of each sequence (max_len bounds them).  Otherwise keys are the
+// sel_counts[b] rows listed in sel[b][...] (max_len bounds the counts) and tokens must be 1.
 int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool, const inf_page_table* table,
-                          int tokens, int heads, int max_len, float scale, void* out, int out_dtype, size_t ws_offset) {
+                          int tokens, int heads, int max_len, float scale, void* out, int out_dtype, size_t ws_offset,
+                          const int* sel, const int* sel_counts, int sel_stride) {
     int rc;
     const int head_blocks = (heads + HB - 1) / HB;
-    const int n_splits = mla_decode_splits(ctx, table->batch, tokens, heads, max_len);
+    // the gather form splits in units of GATHER_UNIT rows: scaling max_len makes the same split arithmetic count units
+    const int n_splits = mla_decode_splits(ctx, table->batch, tokens, heads, sel ? max_len * (PAGE / GATHER_UNIT) : max_len);
     const size_t prows = (size_t)table->batch * tokens * n_splits * heads;
     const size_t acc_bytes = (prows * LAT * sizeof(__half) + 255) & ~(size_t)255;
     rc = inf_ensure_workspace(ctx, ws_offset + acc_bytes + prows * 2 * sizeof(float));
@@ -517,13 +593,16 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
     {
         uint64_t dims[2] = {(uint64_t)ROW, (uint64_t)pool->num_pages * PAGE};
         uint64_t strides[1] = {(uint64_t)ROW * 2};
-        uint32_t box[2] = {64, (uint32_t)PAGE};
+        uint32_t box[2] = {64, sel ? 1u : (uint32_t)PAGE};  // the gather form fetches single rows
         rc = inf_make_tmap(ctx, pool->rows, 2, dims, strides, box, &tkv);
         if (rc != INF_OK) return rc;
     }
     MlaParams p{};
     p.pages = table->pages;
     p.lens = table->lens;
+    p.sel = sel;
+    p.sel_counts = sel_counts;
+    p.sel_stride = sel_stride;
     p.max_pages = table->max_pages;
     p.num_pages = pool->num_pages;
     p.tokens = tokens;
@@ -536,7 +615,9 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
     p.part_ml = (float*)((char*)ctx->workspace + ws_offset + acc_bytes);
     p.status = ctx->status;
     if (!(ctx->func_attr_done & 16u)) {
-        INF_CUDA(ctx, cudaFuncSetAttribute(mla_decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        INF_CUDA(ctx, cudaFuncSetAttribute(mla_decode_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SMEM_TOTAL));
+        INF_CUDA(ctx, cudaFuncSetAttribute(mla_decode_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            SMEM_TOTAL));
         ctx->func_attr_done |= 16u;
     }
@@ -549,7 +630,10 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
 #endif
     {
         inf_prof_scope prof(ctx, "mla_decode_partial_kernel");
-        INF_CUDA(ctx, inf_launch_pdl(mla_decode_partial_kernel, grid, dim3(NUM_THREADS), SMEM_TOTAL, ctx->stream, tq, tkv, p));
+        if (sel)
+            INF_CUDA(ctx, inf_launch_pdl(mla_decode_partial_kernel<true>, grid, dim3(NUM_THREADS), SMEM_TOTAL, ctx->stream, tq, tkv, p));
+        else
+            INF_CUDA(ctx, inf_launch_pdl(mla_decode_partial_kernel<false>, grid, dim3(NUM_THREADS), SMEM_TOTAL, ctx->stream, tq, tkv, p));
     }
 #ifdef INF_KPROF
     {
@@ -574,10 +658,10 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
     dim3 cgrid(heads, tokens * table->batch);
     if (out_dtype == INF_DTYPE_F32)
         INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<float>, cgrid, dim3(256), 0, ctx->stream, p.part_acc,
-                                     p.part_ml, table->lens, (float*)out, tokens, heads, n_splits));
+                                     p.part_ml, table->lens, sel_counts, (float*)out, tokens, heads, n_splits));
     else
         INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<__half>, cgrid, dim3(256), 0, ctx->stream, p.part_acc,
-                                     p.part_ml, table->lens, (__half*)out, tokens, heads, n_splits));
+                                     p.part_ml, table->lens, sel_counts, (__half*)out, tokens, heads, n_splits));
     INF_LAUNCH_CHECK(ctx, "mla_decode_combine_kernel");
     return INF_OK;
 }
@@ -600,6 +684,26 @@ extern "C" int32_t inf_mla_decode_absorbed(inf_ctx* ctx, const void* q_f16, cons
             if (table->host_lens[b] + tokens > max_len)
                 return inf_fail(ctx, INF_E_SHAPE, "mla_decode: sequence %d reaches %d rows, beyond max_len %d", b,
                                 table->host_lens[b] + tokens, max_len);
-    return inf_mla_decode_launch(ctx, q_f16, pool, table, tokens, heads, max_len, scale, out, out_dtype, 0);
+    return inf_mla_decode_launch(ctx, q_f16, pool, table, tokens, heads, max_len, scale, out, out_dtype, 0, nullptr,
+                                 nullptr, 0);
 }
 
+extern "C" int32_t inf_mla_decode_absorbed_selected(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* pool,
+                                                    const inf_page_table* table, const int32_t* selected,
+                                                    const int32_t* selected_counts, int32_t selected_stride,
+                                                    int32_t heads, float scale, void* out, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    if (!q_f16 || !pool || !table || !selected || !selected_counts || !out)
+        return inf_fail(ctx, INF_E_ARG, "mla_decode_selected: null pointer");
+    if (!pool->rows) return inf_fail(ctx, INF_E_ARG, "mla_decode_selected: pool has no storage");
+    if (pool->latent_dim != LAT || pool->rope_dim != ROPE || pool->page_size != PAGE) return INF_UNSUPPORTED;
+    if (heads <= 0 || selected_stride <= 0)
+        return inf_fail(ctx, INF_E_SHAPE, "mla_decode_selected: sizes must be positive");
+    if (!(scale > 0.f)) return inf_fail(ctx, INF_E_CONFIG, "mla_decode_selected: scale must be positive");
+    if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
+        return inf_fail(ctx, INF_E_DTYPE, "mla_decode_selected: output dtype must be f32 or f16");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, PAGE, 1, "mla_decode_selected");
+    if (rc != INF_OK) return rc;
+    return inf_mla_decode_launch(ctx, q_f16, pool, table, 1, heads, selected_stride, scale, out, out_dtype, 0, selected,
+                                 selected_counts, selected_stride);
+}
