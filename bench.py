@@ -377,6 +377,61 @@ class MlaSelectedDecode(MlaDecode):
         return run, self.units_per_step, "whole workload (2048 gathered rows, 64 heads)"
 
 
+class DsaSparseDecode(MlaSelectedDecode):
+    """One DSA sparse decode step: index scores over all 32 768 cached tokens (32 index heads x 128), top-2048,
+    absorbed MLA over the selected rows.  Bytes that must move: the f32 index keys plus the selected latent rows."""
+    metric = "dsa_sparse_decode_hbm_gbs"
+    kernel = "dsa_scores_kernel"
+    launches_per_step = 5  # append, scores, top-k, split partial, combine
+    HI, DI = 32, 128
+
+    def __init__(self, be, rank, ctx_len):
+        super().__init__(be, rank, ctx_len)
+        torch = self.torch
+        self.name = f"dsa_sparse_decode_{ctx_len // 1024}k"
+        gd = torch.Generator(device=be.device).manual_seed(SEED + 33 + rank)
+        self.n_key_sets = 8  # 8 x 16.8 MB of index keys > L2
+        self.idx_keys = [torch.randn((1, ctx_len - 1, self.DI), generator=gd, device=be.device, dtype=torch.float32)
+                         for _ in range(self.n_key_sets)]
+        self.idx_cur = torch.randn((1, self.DI), generator=gd, device=be.device, dtype=torch.float32)
+        self.idx_q = torch.randn((1, self.HI, self.DI), generator=gd, device=be.device, dtype=torch.float32)
+        self.idx_w = torch.rand((1, self.HI), generator=gd, device=be.device, dtype=torch.float32)
+        self.scores = torch.empty((1, ctx_len), dtype=torch.float32, device=be.device)
+        self.ids = torch.empty((1, self.N_SEL), dtype=torch.int32, device=be.device)
+        self.n_variants = max(self.n_caches, self.n_key_sets)
+        self.key_bytes = float(ctx_len) * self.DI * 4
+        self.kernel_units_per_launch = self.key_bytes
+        self.units_per_step = self.key_bytes + float(self.N_SEL) * (self.L + self.R) * 2
+        self.flops_per_step += 2.0 * self.HI * self.DI * ctx_len
+        self.config.update({"workload": self.name, "index_heads": self.HI, "index_dim": self.DI,
+                            "index_key_bytes_per_step": int(self.key_bytes), "bytes_per_step": int(self.units_per_step),
+                            "flops_per_step": self.flops_per_step,
+                            "l2": f"rotates through {self.n_key_sets} index-key sets ({self.n_key_sets * self.key_bytes / 1e6:.0f} MB > L2)"})
+
+    def step(self):
+        t = self.tables[self.i % self.n_caches]
+        keys = self.idx_keys[self.i % self.n_key_sets]
+        self.i += 1
+        self.be.mla_kv_postprocess_device(self.x, self.w, 1e-6, 1.0e7, self.pool, t, want_outputs=False)
+        self.be.dsa_scores(self.idx_q, self.idx_w, keys, self.idx_cur, out=self.scores)
+        self.be.dsa_topk(self.scores, self.N_SEL, out=self.ids)
+        self.be.mla_decode_absorbed_selected(self.q, self.pool, t, self.ids, self.counts, self.scale, out=self.out)
+
+    def cpu_sample(self):
+        from oracle import pyoracle as orc
+        run_attn, _, _ = super().cpu_sample()
+        q = orc.fill_normal((1, self.HI, self.DI), SEED + 34, 1.0, False)
+        w = np.abs(orc.fill_normal((1, self.HI), SEED + 35, 1.0, False))
+        pk = orc.fill_normal((1, self.ctx_len - 1, self.DI), SEED + 36, 1.0, False)
+        ck = orc.fill_normal((1, self.DI), SEED + 37, 1.0, False)
+
+        def run():
+            sc = orc.dsa_scores(q, w, pk, ck)
+            orc.dsa_topk(sc, self.N_SEL)
+            return run_attn()
+        return run, self.units_per_step, "whole step (numpy index scores and top-k, oracle attention over 2048 rows)"
+
+
 class GqaPrefill2k:
     """Causal GQA prefill, one 2048-token prompt, 48 q / 8 kv heads, fused RoPE + KV-append (fourth configuration).
     With N > 1 ranks the heads are sharded (48/N query heads with their 8/N KV heads per rank) and the output is
@@ -531,6 +586,8 @@ def make_workload(name, be, rank, world=1, dist=None, tokens=0):
         return MlaDecode(be, rank, 4096)
     if name == "mla_decode_32k":
         return MlaDecode(be, rank, 32768)
+    if name == "dsa_sparse_decode_32k":
+        return DsaSparseDecode(be, rank, 32768)
     if name == "mla_selected_decode_32k":
         return MlaSelectedDecode(be, rank, 32768)
     if name == "mla_absorbed_decode_32k":
@@ -550,7 +607,7 @@ def make_workload(name, be, rank, world=1, dist=None, tokens=0):
 
 
 WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "mla_selected_decode_32k",
-                  "gqa_prefill_2k",
+                  "dsa_sparse_decode_32k", "gqa_prefill_2k",
                   "mla_prefill_32k"]
 STRONG = {"gqa_prefill_2k", "mla_prefill_32k"}  # head-sharded with an all-gather; the others replicate/shard by sequence
 

@@ -264,6 +264,21 @@ int32_t inf_mla_decode_absorbed_selected(inf_ctx* ctx, const void* q_f16, const 
                                          const int32_t* selected_counts, int32_t selected_stride, int32_t heads,
                                          float scale, void* out, int32_t out_dtype);
 
+/* DSA indexer, the step before inf_mla_decode_absorbed_selected.
+ * inf_dsa_scores (kernel dsa_scores_f32_kernel, crates/backend/src/metal/kernels/dsa_kernels.metal:137-176):
+ * q f32 [batch, heads, head_dim] (already roped), weights f32 [batch, heads], past_keys f32 [batch, past_tokens,
+ * head_dim], current_key f32 [batch, head_dim]; scores f32 [batch, past_tokens + 1],
+ * score[t] = sum_h weights[h] * max(0, q[h] . key[t] / sqrt(head_dim)).  head_dim % 4 == 0.
+ * inf_dsa_topk (kernels dsa_topk_block_sort_u32 / dsa_topk_merge_u32, dsa_kernels.metal:211-393): the top_k
+ * (<= 2048) token ids of every row of scores [batch, key_tokens], best first, where a precedes b iff
+ * score_a > score_b or (score_a == score_b and id_a < id_b); selected uint32 [batch, selected_stride], entries
+ * beyond min(top_k, key_tokens) are 0xffffffff.  Scores are expected to be free of NaN. */
+int32_t inf_dsa_scores(inf_ctx* ctx, const float* q, const float* weights, const float* past_keys,
+                       const float* current_key, int32_t batch, int32_t past_tokens, int32_t heads, int32_t head_dim,
+                       float* scores);
+int32_t inf_dsa_topk(inf_ctx* ctx, const float* scores, int32_t batch, int32_t key_tokens, int32_t top_k,
+                     uint32_t* selected, int32_t selected_stride);
+
 /* Per-head Q8_0 matvec (kernel q8_0_packed_heads_matvec_f32_kernel, crates/backend/src/metal/kernels/
  * q2_kernels.metal:3146; host crates/backend/src/metal/q2.rs:2656): weights (device) [heads][out_features]
  * [in_features] in Q8_0 row blocks of 34 bytes (little-endian f16 scale, 32 signed quants); input f32

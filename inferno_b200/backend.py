@@ -325,6 +325,26 @@ class CudaBackend:
             selected.shape[1], H, scale, _ptr(out), dt))
         return out if ok else None
 
+    def dsa_scores(self, q, weights, past_keys, current_key, out=None):
+        """DSA index scores (dsa_kernels.metal:137): q f32 [B,H,D], weights f32 [B,H], past_keys f32 [B,past,D],
+        current_key f32 [B,D] -> f32 [B, past + 1]."""
+        B, H, D = q.shape
+        past = past_keys.shape[1]
+        if out is None:
+            out = torch.empty((B, past + 1), dtype=torch.float32, device=self.device)
+        self._check(self._lib.inf_dsa_scores(self._ctx, _ptr(q), _ptr(weights), _ptr(past_keys) if past else None,
+                                             _ptr(current_key), B, past, H, D, _ptr(out)))
+        return out
+
+    def dsa_topk(self, scores, top_k: int, out=None):
+        """Ids of the top_k scores of every row, best first, ties by lower id (dsa_kernels.metal:182-393);
+        int32 [B, top_k] whose entries beyond the row length are -1 (0xffffffff)."""
+        B, n = scores.shape
+        if out is None:
+            out = torch.empty((B, top_k), dtype=torch.int32, device=self.device)
+        ok = self._check(self._lib.inf_dsa_topk(self._ctx, _ptr(scores), B, n, top_k, _ptr(out), out.shape[1]))
+        return out if ok else None
+
     def q8_0_packed_heads_matvec(self, weights_u8, x, out_features: int):
         """Per-head Q8_0 matvec (q2_kernels.metal:3146): weights uint8 device tensor, x f32 [rows, heads, in]."""
         rows, heads, in_features = x.shape

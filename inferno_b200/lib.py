@@ -94,6 +94,8 @@ SIGNATURES = {
     "inf_mla_decode_absorbed": (_I, [_P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _I, _I, _F, _P, _I]),
     "inf_mla_decode_absorbed_selected": (_I, [_P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _P, _P, _I, _I, _F, _P,
                                               _I]),
+    "inf_dsa_scores": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "inf_dsa_topk": (_I, [_P, _P, _I, _I, _I, _P, _I]),
     "inf_q8_0_packed_heads_matvec": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "inf_q8_0_absorbed_mla": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _I, _I,
                                    _I, _I, _I, _P]),

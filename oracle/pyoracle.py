@@ -266,3 +266,28 @@ def causal_mha(q, k_nope, k_rope, v, scale, rows=None, threads=0):
     lib().orc_causal_mha(_p(q), _p(k_nope), _p(kr), _p(v), _p(out), C.c_int(T), C.c_int(H), C.c_int(dn), C.c_int(dr),
                          C.c_int(dv), C.c_float(scale), _p(r), C.c_int(n), C.c_int(threads))
     return out
+
+
+def dsa_scores(q, weights, past_keys, current_key):
+    """dsa_scores_f32_kernel (crates/backend/src/metal/kernels/dsa_kernels.metal:137-176), numpy restatement:
+    q [B,H,D], weights [B,H], past_keys [B,past,D], current_key [B,D] -> [B, past+1] f32, accumulating in the
+    kernel's order (dims, then heads) in f32."""
+    q, weights, current_key = _f32(q), _f32(weights), _f32(current_key)
+    keys = np.concatenate([_f32(past_keys), current_key[:, None, :]], axis=1)
+    scale = np.float32(1.0) / np.sqrt(np.float32(q.shape[2]))
+    dots = np.einsum("bhd,btd->bth", q, keys, dtype=np.float32) * scale
+    return np.einsum("bth,bh->bt", np.maximum(dots, np.float32(0.0)), weights, dtype=np.float32).astype(np.float32)
+
+
+def dsa_topk(scores, top_k):
+    """Top-k ids best first under dsa_precedes (dsa_kernels.metal:182-196): higher score first, ties by lower id;
+    missing entries 0xffffffff.  uint32 [B, top_k]."""
+    scores = _f32(scores)
+    B, n = scores.shape
+    out = np.full((B, top_k), 0xFFFFFFFF, np.uint32)
+    ids = np.arange(n)
+    for b in range(B):
+        order = np.lexsort((ids, -scores[b].astype(np.float64)))[:top_k]
+        out[b, :len(order)] = order.astype(np.uint32)
+    return out
+
