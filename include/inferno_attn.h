@@ -279,6 +279,20 @@ int32_t inf_dsa_scores(inf_ctx* ctx, const float* q, const float* weights, const
 int32_t inf_dsa_topk(inf_ctx* ctx, const float* scores, int32_t batch, int32_t key_tokens, int32_t top_k,
                      uint32_t* selected, int32_t selected_stride);
 
+/* Q8Row cold-store codec (crates/cache/src/cold_kv.rs:1624-1703; device decode kernel q8_rows_to_f32_kernel,
+ * crates/backend/src/metal/kernels/cast_kernels.metal:31-56).  A row of `dim` values is 4 + dim bytes: the
+ * little-endian f32 scale max|x| / 127 (1.0 for an all-zero row), then round(x / scale) as signed bytes clamped to
+ * +-127 (ties away from zero).  payload and input / output are device pointers; rows = batch * heads * tokens. */
+int32_t inf_q8_rows_encode(inf_ctx* ctx, const float* input, int64_t rows, int32_t dim, void* payload);
+int32_t inf_q8_rows_decode(inf_ctx* ctx, const void* payload, int64_t rows, int32_t dim, float* output);
+/* Thaw of cold MLA rows into the paged pool (dequantise on load): latent_payload holds batch * tokens Q8Row rows
+ * of width pool->latent_dim, rope_payload as many of width pool->rope_dim (the reference keeps the latent and the
+ * rope tail as the K and V records of a page); row (b, t) is stored RNE-fp16 at logical slot first_token + t of
+ * sequence b.  table->lens is not read; the caller sets the lengths when the range is resident again. */
+int32_t inf_mla_pool_thaw_q8_rows(inf_ctx* ctx, const void* latent_payload, const void* rope_payload,
+                                  const inf_mla_pool* pool, const inf_page_table* table, int32_t first_token,
+                                  int32_t tokens);
+
 /* Per-head Q8_0 matvec (kernel q8_0_packed_heads_matvec_f32_kernel, crates/backend/src/metal/kernels/
  * q2_kernels.metal:3146; host crates/backend/src/metal/q2.rs:2656): weights (device) [heads][out_features]
  * [in_features] in Q8_0 row blocks of 34 bytes (little-endian f16 scale, 32 signed quants); input f32

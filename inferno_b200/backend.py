@@ -345,6 +345,27 @@ class CudaBackend:
         ok = self._check(self._lib.inf_dsa_topk(self._ctx, _ptr(scores), B, n, top_k, _ptr(out), out.shape[1]))
         return out if ok else None
 
+    def q8_rows_encode(self, x):
+        """Q8Row encode (crates/cache/src/cold_kv.rs:1624): f32 [..., dim] -> uint8 [rows, 4 + dim]."""
+        dim = x.shape[-1]
+        rows = x.numel() // dim
+        out = torch.empty((rows, dim + 4), dtype=torch.uint8, device=self.device)
+        self._check(self._lib.inf_q8_rows_encode(self._ctx, _ptr(x), rows, dim, _ptr(out)))
+        return out
+
+    def q8_rows_decode(self, payload, dim: int):
+        """Q8Row decode (cast_kernels.metal:31): uint8 [rows, 4 + dim] -> f32 [rows, dim]."""
+        rows = payload.numel() // (dim + 4)
+        out = torch.empty((rows, dim), dtype=torch.float32, device=self.device)
+        self._check(self._lib.inf_q8_rows_decode(self._ctx, _ptr(payload), rows, dim, _ptr(out)))
+        return out
+
+    def mla_pool_thaw_q8_rows(self, latent_payload, rope_payload, pool: MlaPool, table: PageTable, first_token: int,
+                              tokens: int):
+        """Cold Q8Row latent / rope rows dequantised straight into the pages of the MLA pool."""
+        self._check(self._lib.inf_mla_pool_thaw_q8_rows(self._ctx, _ptr(latent_payload), _ptr(rope_payload),
+                                                        C.byref(pool.desc), C.byref(table.desc), first_token, tokens))
+
     def q8_0_packed_heads_matvec(self, weights_u8, x, out_features: int):
         """Per-head Q8_0 matvec (q2_kernels.metal:3146): weights uint8 device tensor, x f32 [rows, heads, in]."""
         rows, heads, in_features = x.shape

@@ -291,3 +291,25 @@ def dsa_topk(scores, top_k):
         out[b, :len(order)] = order.astype(np.uint32)
     return out
 
+
+def q8_rows_encode(x):
+    """encode_q8_rows (crates/cache/src/cold_kv.rs:1624-1655): f32 [rows, dim] -> uint8 [rows, 4 + dim];
+    scale = max|x| / 127 (1.0 for a zero row), value = round-half-away(x / scale) clamped to +-127, all in f32."""
+    x = _f32(x)
+    rows, dim = x.shape
+    m = np.abs(x).max(axis=1).astype(np.float32)
+    scale = np.where(m == 0, np.float32(1.0), (m / np.float32(127.0)).astype(np.float32)).astype(np.float32)
+    r = (x / scale[:, None]).astype(np.float32)
+    qv = np.clip(np.sign(r) * np.floor(np.abs(r) + np.float32(0.5)), -127, 127).astype(np.int8)
+    out = np.empty((rows, dim + 4), np.uint8)
+    out[:, :4] = scale.astype("<f4").view(np.uint8).reshape(rows, 4)
+    out[:, 4:] = qv.view(np.uint8)
+    return out
+
+
+def q8_rows_decode(payload, dim):
+    """decode_q8_rows (cold_kv.rs:1657-1703) / q8_rows_to_f32_kernel (cast_kernels.metal:31-56)."""
+    p = np.ascontiguousarray(payload, dtype=np.uint8).reshape(-1, dim + 4)
+    scale = p[:, :4].copy().view("<f4").reshape(-1).astype(np.float32)
+    return (p[:, 4:].view(np.int8).astype(np.float32) * scale[:, None]).astype(np.float32)
+

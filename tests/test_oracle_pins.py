@@ -363,3 +363,42 @@ def test_paged_gqa_equals_ring_under_any_page_table():
             lib().orc_gqa_ring_attention(_p(qb), _p(kb), _p(vb), None, _p(ck), _p(cv), _p(o), B, Hq, Hkv, D, 1, T0, T0, cap, 0, 1)
         outs.append(o)
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_q8_row_codec_round_trips_with_bounded_error():
+    """crates/cache/src/cold_kv.rs:1903-1911: tensor(2, -1.0) = [1,2,2,32] with values -1 + i/10 round-trips within
+    0.08 and the payload is smaller than the f32 tensor; plus the layout facts of encode_q8_rows (:1624-1655)."""
+    src = (-1.0 + np.arange(1 * 2 * 2 * 32, dtype=np.float32) / np.float32(10.0)).reshape(-1, 32)
+    payload = orc.q8_rows_encode(src)
+    back = orc.q8_rows_decode(payload, 32)
+    assert np.max(np.abs(back - src)) <= 0.08
+    assert payload.size < src.size * 4 and payload.shape == (4, 36)
+    # scale = max|x| / 127 as little-endian f32, the extreme value maps to +-127
+    scale = payload[:, :4].copy().view("<f4").reshape(-1)
+    assert np.array_equal(scale, (np.abs(src).max(axis=1) / np.float32(127.0)).astype(np.float32))
+    assert np.all(np.abs(payload[:, 4:].view(np.int8)).max(axis=1) == 127)
+    # an all-zero row has scale 1.0 and zero quants; halves round away from zero
+    z = orc.q8_rows_encode(np.array([[0, 0, 0, 0], [127, 0.5, -0.5, 2.5]], np.float32))
+    assert z[0].tolist() == [0, 0, 128, 63, 0, 0, 0, 0]
+    assert z[1, 4:].view(np.int8).tolist() == [127, 1, -1, 3]
+
+
+def test_dsa_topk_ordering_rule():
+    """dsa_precedes (crates/backend/src/metal/kernels/dsa_kernels.metal:182-196): higher score first, equal scores by
+    lower id, invalid ids last."""
+    scores = np.array([[0.5, 2.0, 2.0, -1.0, 0.5, 0.0, -0.0]], np.float32)
+    assert orc.dsa_topk(scores, 5)[0].tolist() == [1, 2, 0, 4, 5]
+    assert orc.dsa_topk(scores, 9)[0].tolist() == [1, 2, 0, 4, 5, 6, 3, 0xFFFFFFFF, 0xFFFFFFFF]
+
+
+def test_dsa_scores_formula():
+    """dsa_scores_f32_kernel (dsa_kernels.metal:137-176) on a closed-form case: one-hot queries pick key columns."""
+    q = np.zeros((1, 2, 4), np.float32)
+    q[0, 0, 0] = 1.0
+    q[0, 1, 1] = 2.0
+    w = np.array([[0.5, 0.25]], np.float32)
+    past = np.array([[[4.0, -1.0, 9, 9], [-2.0, 3.0, 9, 9]]], np.float32)
+    cur = np.array([[1.0, 1.0, 9, 9]], np.float32)
+    # scale 1/sqrt(4) = 0.5: token0: 0.5*relu(2) + 0.25*relu(-1) = 1.0; token1: 0.5*relu(-1) + 0.25*relu(3) = 0.75;
+    # current: 0.5*relu(0.5) + 0.25*relu(1) = 0.5
+    assert np.allclose(orc.dsa_scores(q, w, past, cur), [[1.0, 0.75, 0.5]])
