@@ -662,6 +662,9 @@ def kernel_time(be, torch, wl, steps):
     """Average device time of the dominant kernel, from CUDA event pairs recorded around each launch."""
     be.device_profile_boundary(True)
     for _ in range(steps):
+        # keep the stream busy while the host enqueues the step, so that the event pair around a kernel brackets its
+        # device time and not the host's launch latency
+        torch.cuda._sleep(400000)
         wl.step()
     be.device_profile_boundary(False)
     ms, n = be.profile_read(wl.kernel)

@@ -10,12 +10,15 @@ namespace {
 
 // ---------------------------------------------------------------------------------------------- scores
 // score[b][t] = sum_h w[b][h] * max(0, q[b][h] . key[b][t] / sqrt(D)), key = past_keys[b][t] for t < past, the
-// current key for t == past (dsa_kernels.metal:137-176).  HBM-bound on the f32 index keys: a CTA stages 64 key rows
-// with coalesced 16-byte loads (row pitch D + 4 floats, so the per-thread row reads below do not collide on
-// banks), then thread (token, head quarter) accumulates its heads against q held in shared memory, eight heads at
-// a time so that a key value read from shared memory is used eight times.
-constexpr int SC_TOKENS = 64;
+// current key for t == past (dsa_kernels.metal:137-176).  HBM-bound on the f32 index keys.  A CTA stages 128 key
+// rows with coalesced 16-byte loads (row pitch D + 4 floats, so the row reads below do not collide on banks) and
+// q in shared memory; thread (lane = token within a group of 32, warp = head residue mod 8) keeps a 4 token x 4
+// head block of dot products in registers, so every value read from shared memory feeds four multiply-adds.
+constexpr int SC_TOKENS = 128;
 constexpr int SC_THREADS = 256;
+constexpr int SC_TB = SC_TOKENS / 32;  // tokens per thread
+constexpr int SC_HB = 4;               // heads per thread and pass
+constexpr int SC_HG = SC_THREADS / 32; // head residues
 
 __global__ void __launch_bounds__(SC_THREADS)
 dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights, const float* __restrict__ past_keys,
@@ -27,11 +30,11 @@ dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights
     float* s_keys = sm;                          // [SC_TOKENS][pitch]
     float* s_q = sm + SC_TOKENS * pitch;         // [heads][dim]
     float* s_w = s_q + heads * dim;              // [heads]
-    float* s_part = s_w + heads;                 // [4][SC_TOKENS]
+    float* s_part = s_w + heads;                 // [SC_HG][SC_TOKENS]
     const int b = blockIdx.y;
     const int t0 = blockIdx.x * SC_TOKENS;
     const int n = past + 1;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, hg = tid >> 5;
     for (int i = tid; i < heads * dim / 4; i += SC_THREADS)
         reinterpret_cast<float4*>(s_q)[i] = reinterpret_cast<const float4*>(q + (size_t)b * heads * dim)[i];
     for (int i = tid; i < heads; i += SC_THREADS) s_w[i] = weights[(size_t)b * heads + i];
@@ -47,40 +50,56 @@ dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights
         *reinterpret_cast<float4*>(s_keys + r * pitch + c * 4) = v;
     }
     __syncthreads();
-    const int r = tid & (SC_TOKENS - 1), quarter = tid / SC_TOKENS;  // 4 head quarters
     const float scale = rsqrtf((float)dim);
-    const float* key = s_keys + r * pitch;
-    float acc = 0.f;
-    constexpr int HG = 8;  // heads per pass: this thread's heads are quarter, quarter + 4, quarter + 8, ...
-    for (int h0 = quarter; h0 < heads; h0 += HG * (SC_THREADS / SC_TOKENS)) {
-        float dot[HG];
+    float acc[SC_TB];
 #pragma unroll
-        for (int g = 0; g < HG; ++g) dot[g] = 0.f;
-#pragma unroll 4
+    for (int tb = 0; tb < SC_TB; ++tb) acc[tb] = 0.f;
+    for (int h0 = hg; h0 < heads; h0 += SC_HB * SC_HG) {  // this thread's heads: h0, h0 + 8, h0 + 16, h0 + 24
+        float dot[SC_TB][SC_HB];
+#pragma unroll
+        for (int tb = 0; tb < SC_TB; ++tb)
+#pragma unroll
+            for (int g = 0; g < SC_HB; ++g) dot[tb][g] = 0.f;
+#pragma unroll 2
         for (int d = 0; d < dim; d += 4) {
-            const float4 kv = *reinterpret_cast<const float4*>(key + d);
+            float4 kv[SC_TB], qv[SC_HB];
 #pragma unroll
-            for (int g = 0; g < HG; ++g) {
-                const int h = h0 + g * (SC_THREADS / SC_TOKENS);
-                if (h < heads) {
-                    const float4 qv = *reinterpret_cast<const float4*>(s_q + h * dim + d);  // same address in the warp
-                    dot[g] = fmaf(kv.x, qv.x, dot[g]);
-                    dot[g] = fmaf(kv.y, qv.y, dot[g]);
-                    dot[g] = fmaf(kv.z, qv.z, dot[g]);
-                    dot[g] = fmaf(kv.w, qv.w, dot[g]);
+            for (int tb = 0; tb < SC_TB; ++tb)
+                kv[tb] = *reinterpret_cast<const float4*>(s_keys + (lane + 32 * tb) * pitch + d);
+#pragma unroll
+            for (int g = 0; g < SC_HB; ++g) {
+                const int h = min(h0 + g * SC_HG, heads - 1);  // a head past the end repeats the last one and is dropped below
+                qv[g] = *reinterpret_cast<const float4*>(s_q + h * dim + d);  // same address in the warp
+            }
+#pragma unroll
+            for (int tb = 0; tb < SC_TB; ++tb)
+#pragma unroll
+                for (int g = 0; g < SC_HB; ++g) {
+                    dot[tb][g] = fmaf(kv[tb].x, qv[g].x, dot[tb][g]);
+                    dot[tb][g] = fmaf(kv[tb].y, qv[g].y, dot[tb][g]);
+                    dot[tb][g] = fmaf(kv[tb].z, qv[g].z, dot[tb][g]);
+                    dot[tb][g] = fmaf(kv[tb].w, qv[g].w, dot[tb][g]);
                 }
+        }
+#pragma unroll
+        for (int g = 0; g < SC_HB; ++g) {
+            const int h = h0 + g * SC_HG;
+            if (h < heads) {
+                const float w = s_w[h];
+#pragma unroll
+                for (int tb = 0; tb < SC_TB; ++tb) acc[tb] = fmaf(w, fmaxf(dot[tb][g] * scale, 0.f), acc[tb]);
             }
         }
-#pragma unroll
-        for (int g = 0; g < HG; ++g) {
-            const int h = h0 + g * (SC_THREADS / SC_TOKENS);
-            if (h < heads) acc = fmaf(s_w[h], fmaxf(dot[g] * scale, 0.f), acc);
-        }
     }
-    s_part[quarter * SC_TOKENS + r] = acc;
+#pragma unroll
+    for (int tb = 0; tb < SC_TB; ++tb) s_part[hg * SC_TOKENS + lane + 32 * tb] = acc[tb];
     __syncthreads();
-    if (tid < SC_TOKENS && t0 + tid < n)
-        scores[(size_t)b * n + t0 + tid] = (s_part[tid] + s_part[SC_TOKENS + tid]) + (s_part[2 * SC_TOKENS + tid] + s_part[3 * SC_TOKENS + tid]);
+    if (tid < SC_TOKENS && t0 + tid < n) {
+        float sum = 0.f;
+#pragma unroll
+        for (int g = 0; g < SC_HG; ++g) sum += s_part[g * SC_TOKENS + tid];
+        scores[(size_t)b * n + t0 + tid] = sum;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------- top-k
@@ -151,16 +170,33 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
             }
         }
         __syncthreads();
-        if (tid == 0) {
-            int remaining = sh_remaining;
-            int bin = 255;
-            for (; bin > 0; --bin) {
-                if ((int)hist[bin] >= remaining) break;
-                remaining -= (int)hist[bin];
+        if (warp == 0) {
+            // the bin that holds the remaining-th largest candidate: lane l owns bins 8l .. 8l+7; counts of the bins
+            // above a lane come from a suffix sum across the warp, the owner then walks its eight bins
+            const int remaining = sh_remaining;
+            int mine[8], sum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                mine[i] = (int)hist[lane * 8 + i];
+                sum += mine[i];
             }
-            sh_prefix = prefix | ((unsigned)bin << shift);
-            sh_mask = mask | (255u << shift);
-            sh_remaining = remaining;  // how many entries equal to the final value are taken
+            int above = sum;  // inclusive suffix sum over lanes >= this one
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_down_sync(0xffffffffu, above, o);
+                if (lane + o < 32) above += y;
+            }
+            above -= sum;  // candidates in bins owned by higher lanes
+            if (above < remaining && remaining <= above + sum) {
+                int left = remaining - above, bin = 7;
+                for (; bin > 0; --bin) {
+                    if (mine[bin] >= left) break;
+                    left -= mine[bin];
+                }
+                sh_prefix = prefix | ((unsigned)(lane * 8 + bin) << shift);
+                sh_mask = mask | (255u << shift);
+                sh_remaining = left;  // how many entries equal to the final value are taken
+            }
         }
         __syncthreads();
     }
@@ -187,15 +223,24 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
         w_tie[warp] = c_tie;
     }
     __syncthreads();
-    if (tid == 0) {
-        int base = 0, ties_before = 0;
-        for (int w = 0; w < 32; ++w) {
-            const int quota = max(0, min(w_tie[w], ties_wanted - ties_before));
-            w_base[w] = base;
-            w_quota[w] = quota;
-            base += w_above[w] + quota;
-            ties_before += w_tie[w];
+    if (warp == 0) {  // exclusive prefixes over the 32 warps' counts
+        const int t_w = w_tie[lane];
+        int ties_incl = t_w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, ties_incl, o);
+            if (lane >= o) ties_incl += y;
         }
+        const int quota = max(0, min(t_w, ties_wanted - (ties_incl - t_w)));
+        const int out_w = w_above[lane] + quota;
+        int out_incl = out_w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, out_incl, o);
+            if (lane >= o) out_incl += y;
+        }
+        w_base[lane] = out_incl - out_w;
+        w_quota[lane] = quota;
     }
     __syncthreads();
     {
@@ -254,7 +299,7 @@ extern "C" int32_t inf_dsa_scores(inf_ctx* ctx, const float* q, const float* wei
         return inf_fail(ctx, INF_E_SHAPE, "dsa_scores: sizes must be positive");
     if (head_dim % 4 != 0) return inf_fail(ctx, INF_E_SHAPE, "dsa_scores: head_dim %d must be a multiple of 4", head_dim);
     if (batch > 65535) return inf_fail(ctx, INF_E_SHAPE, "dsa_scores: batch %d exceeds the launch grid", batch);
-    const size_t smem = ((size_t)SC_TOKENS * (head_dim + 4) + (size_t)heads * head_dim + heads + 4 * SC_TOKENS) * sizeof(float);
+    const size_t smem = ((size_t)SC_TOKENS * (head_dim + 4) + (size_t)heads * head_dim + heads + SC_HG * SC_TOKENS) * sizeof(float);
     if (smem > 200 * 1024) return INF_UNSUPPORTED;
     if (smem > 48 * 1024 && !(ctx->func_attr_done & 4096u)) {
         INF_CUDA(ctx, cudaFuncSetAttribute(dsa_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
