@@ -467,17 +467,18 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 // coalesced loads instead of a chain of dependent ones.
 constexpr int MAX_SPLITS = 1024;
 
-// One CTA per (head, query row): 256 threads.  The split weights are computed once; for the weighted sum the
-// threads form four groups that walk the splits with stride four, each thread owning eight adjacent columns
-// (one 16-byte load per split), and the four partial sums meet in shared memory.
+// One CTA per (head, query row): 512 threads.  The split weights are computed once; for the weighted sum the
+// threads form eight groups that walk the splits with stride eight, each thread owning eight adjacent columns
+// (one 16-byte load per split, all of a thread's loads in flight together), and the partial sums meet in shared
+// memory.
 template <typename OutT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, const int* __restrict__ counts, OutT* __restrict__ out, int tokens,
                           int heads, int n_splits) {
     __shared__ float w[MAX_SPLITS];
-    __shared__ float red[8];
-    __shared__ float group_acc[3][LAT];
+    __shared__ float red[16];
+    __shared__ float group_acc[7][LAT];
     inf_pdl_wait();
     inf_pdl_release();
     const int h = blockIdx.x, t = blockIdx.y % tokens, b = blockIdx.y / tokens;
@@ -489,18 +490,18 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     const long long prow0 = (((long long)b * tokens + t) * n_splits) * heads + h;
     // pass 1: global maximum
     float mloc = M_INIT;
-    for (int s = tid; s < n_valid; s += 256) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)s * heads) * 2]);
+    for (int s = tid; s < n_valid; s += 512) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)s * heads) * 2]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
     if ((tid & 31) == 0) red[tid >> 5] = mloc;
     __syncthreads();
     float M = red[0];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) M = fmaxf(M, red[i]);
+    for (int i = 1; i < 16; ++i) M = fmaxf(M, red[i]);
     __syncthreads();
     // pass 2: weights and the normaliser
     float lloc = 0.f;
-    for (int s = tid; s < n_valid; s += 256) {
+    for (int s = tid; s < n_valid; s += 512) {
         const float ws = ex2_approx(part_ml[(prow0 + (long long)s * heads) * 2] - M) *
                          part_ml[(prow0 + (long long)s * heads) * 2 + 1];  // weight of a normalised partial
         w[s] = ws;
@@ -512,7 +513,7 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     __syncthreads();
     float total = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) total += red[i];
+    for (int i = 0; i < 16; ++i) total += red[i];
     const float inv = 1.0f / total;
     // pass 3: weighted sum of the partial outputs
     const int g = tid >> 6, c = (tid & 63) * 8;
@@ -520,8 +521,8 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll 4
-    for (int s = g; s < n_valid; s += 4) {
+#pragma unroll 8
+    for (int s = g; s < n_valid; s += 8) {
         const uint4 v = *reinterpret_cast<const uint4*>(src + (long long)s * heads * LAT);
         const float ws = w[s];
         const __half2* hv = reinterpret_cast<const __half2*>(&v);
@@ -541,7 +542,8 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
         OutT* dst = out + ((((long long)b * tokens + t) * heads) + h) * LAT + c;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-            dst[i] = OutT((acc[i] + group_acc[0][c + i] + group_acc[1][c + i] + group_acc[2][c + i]) * inv);
+            dst[i] = OutT((((acc[i] + group_acc[0][c + i]) + (group_acc[1][c + i] + group_acc[2][c + i])) +
+                           ((group_acc[3][c + i] + group_acc[4][c + i]) + (group_acc[5][c + i] + group_acc[6][c + i]))) * inv);
     }
 }
 
@@ -657,10 +659,10 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
     INF_LAUNCH_CHECK(ctx, "mla_decode_partial_kernel");
     dim3 cgrid(heads, tokens * table->batch);
     if (out_dtype == INF_DTYPE_F32)
-        INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<float>, cgrid, dim3(256), 0, ctx->stream, p.part_acc,
+        INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<float>, cgrid, dim3(512), 0, ctx->stream, p.part_acc,
                                      p.part_ml, table->lens, sel_counts, (float*)out, tokens, heads, n_splits));
     else
-        INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<__half>, cgrid, dim3(256), 0, ctx->stream, p.part_acc,
+        INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<__half>, cgrid, dim3(512), 0, ctx->stream, p.part_acc,
                                      p.part_ml, table->lens, sel_counts, (__half*)out, tokens, heads, n_splits));
     INF_LAUNCH_CHECK(ctx, "mla_decode_combine_kernel");
     return INF_OK;
