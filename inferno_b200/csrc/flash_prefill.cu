@@ -593,30 +593,64 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     gain *= softplus_ref(p.gate[((long long)b * p.tokens + me.q0 + r) * p.q_heads + me.head]);
                 const long long obase =
                     (long long)b * p.o_bs + (long long)(me.q0 + r) * p.o_ts + (long long)me.head * p.o_hs;
+                if (p.out_f16 && DV == 128) {
+                    // fp16 rows go through this stream's Q tile (dead since its last QK^T): each thread parks its row
+                    // there, then the warp writes its 32 rows back out as whole 256-byte lines.  16-byte chunks are
+                    // XORed with the row so that neither pass collides on banks.
+                    uint8_t* stage = sQ + s * L::Q_BYTES + (warp & 3) * (32 * 256);
 #pragma unroll
-                for (int c = 0; c < DV / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld32(col0 + COL_O + c * 32, o);
-                    tc_wait_ld();
-                    if (valid) {
-                        if (p.out_f16) {
-                            __half* dst = reinterpret_cast<__half*>(p.out) + obase + c * 32;
+                    for (int c = 0; c < DV / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(col0 + COL_O + c * 32, o);
+                        tc_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 v;
-                                v.x = pack_half2(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain);
-                                v.y = pack_half2(__uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
-                                v.z = pack_half2(__uint_as_float(o[i + 4]) * gain, __uint_as_float(o[i + 5]) * gain);
-                                v.w = pack_half2(__uint_as_float(o[i + 6]) * gain, __uint_as_float(o[i + 7]) * gain);
-                                *reinterpret_cast<uint4*>(dst + i) = v;
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 v;
+                            v.x = pack_half2(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain);
+                            v.y = pack_half2(__uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                            v.z = pack_half2(__uint_as_float(o[i + 4]) * gain, __uint_as_float(o[i + 5]) * gain);
+                            v.w = pack_half2(__uint_as_float(o[i + 6]) * gain, __uint_as_float(o[i + 7]) * gain);
+                            const int chunk = c * 4 + (i >> 3);
+                            *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = v;
+                        }
+                    }
+                    __syncwarp();
+                    const int chunk = lane & 15;
+#pragma unroll 4
+                    for (int rr = 0; rr < 16; ++rr) {
+                        const int row_l = rr * 2 + (lane >> 4);
+                        const int row_g = me.q0 + (warp & 3) * 32 + row_l;
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage + row_l * 256 + ((chunk ^ (row_l & 15)) << 4));
+                        if (row_g < p.tokens)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + (long long)b * p.o_bs +
+                                                      (long long)row_g * p.o_ts + (long long)me.head * p.o_hs + chunk * 8) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < DV / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(col0 + COL_O + c * 32, o);
+                        tc_wait_ld();
+                        if (valid) {
+                            if (p.out_f16) {
+                                __half* dst = reinterpret_cast<__half*>(p.out) + obase + c * 32;
+#pragma unroll
+                                for (int i = 0; i < 32; i += 8) {
+                                    uint4 v;
+                                    v.x = pack_half2(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain);
+                                    v.y = pack_half2(__uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                                    v.z = pack_half2(__uint_as_float(o[i + 4]) * gain, __uint_as_float(o[i + 5]) * gain);
+                                    v.w = pack_half2(__uint_as_float(o[i + 6]) * gain, __uint_as_float(o[i + 7]) * gain);
+                                    *reinterpret_cast<uint4*>(dst + i) = v;
+                                }
+                            } else {
+                                float* dst = reinterpret_cast<float*>(p.out) + obase + c * 32;
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4)
+                                    *reinterpret_cast<float4*>(dst + i) =
+                                        make_float4(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain,
+                                                    __uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
                             }
-                        } else {
-                            float* dst = reinterpret_cast<float*>(p.out) + obase + c * 32;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4)
-                                *reinterpret_cast<float4*>(dst + i) =
-                                    make_float4(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain,
-                                                __uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
                         }
                     }
                 }
