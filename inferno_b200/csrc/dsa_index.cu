@@ -20,6 +20,13 @@ constexpr int SC_TB = SC_TOKENS / 32;  // tokens per thread
 constexpr int SC_HB = 4;               // heads per thread and pass
 constexpr int SC_HG = SC_THREADS / 32; // head residues
 
+// two fp32 multiply-adds in one instruction (packed pairs in 64-bit registers)
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 __global__ void __launch_bounds__(SC_THREADS)
 dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights, const float* __restrict__ past_keys,
                   const float* __restrict__ current_key, float* __restrict__ scores, int past, int heads, int dim) {
@@ -39,48 +46,62 @@ dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights
         reinterpret_cast<float4*>(s_q)[i] = reinterpret_cast<const float4*>(q + (size_t)b * heads * dim)[i];
     for (int i = tid; i < heads; i += SC_THREADS) s_w[i] = weights[(size_t)b * heads + i];
     const int vec_per_row = dim / 4;
+    // the key rows go straight from global to shared memory (cp.async): all of a thread's 16-byte pieces are in
+    // flight at once instead of one load-store round trip after another
     for (int i = tid; i < SC_TOKENS * vec_per_row; i += SC_THREADS) {
         const int r = i / vec_per_row, c = i % vec_per_row;
         const int t = t0 + r;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t < past)
-            v = reinterpret_cast<const float4*>(past_keys + ((size_t)b * past + t) * dim)[c];
-        else if (t == past)
-            v = reinterpret_cast<const float4*>(current_key + (size_t)b * dim)[c];
-        *reinterpret_cast<float4*>(s_keys + r * pitch + c * 4) = v;
+        float* dst = s_keys + r * pitch + c * 4;
+        if (t < past) {
+            const float* src = past_keys + ((size_t)b * past + t) * dim + c * 4;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src)
+                         : "memory");
+        } else {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t == past) v = reinterpret_cast<const float4*>(current_key + (size_t)b * dim)[c];
+            *reinterpret_cast<float4*>(dst) = v;
+        }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     const float scale = rsqrtf((float)dim);
     float acc[SC_TB];
 #pragma unroll
     for (int tb = 0; tb < SC_TB; ++tb) acc[tb] = 0.f;
     for (int h0 = hg; h0 < heads; h0 += SC_HB * SC_HG) {  // this thread's heads: h0, h0 + 8, h0 + 16, h0 + 24
-        float dot[SC_TB][SC_HB];
+        // each accumulator holds the (even dims, odd dims) halves of one dot product: a 16-byte shared-memory read
+        // is two such pairs, so the inner step is two packed multiply-adds per (token, head) and no data movement
+        unsigned long long dot2[SC_TB][SC_HB];
 #pragma unroll
         for (int tb = 0; tb < SC_TB; ++tb)
 #pragma unroll
-            for (int g = 0; g < SC_HB; ++g) dot[tb][g] = 0.f;
+            for (int g = 0; g < SC_HB; ++g) dot2[tb][g] = 0ull;
 #pragma unroll 2
         for (int d = 0; d < dim; d += 4) {
-            float4 kv[SC_TB], qv[SC_HB];
+            ulonglong2 kv[SC_TB], qv[SC_HB];
 #pragma unroll
             for (int tb = 0; tb < SC_TB; ++tb)
-                kv[tb] = *reinterpret_cast<const float4*>(s_keys + (lane + 32 * tb) * pitch + d);
+                kv[tb] = *reinterpret_cast<const ulonglong2*>(s_keys + (lane + 32 * tb) * pitch + d);
 #pragma unroll
             for (int g = 0; g < SC_HB; ++g) {
                 const int h = min(h0 + g * SC_HG, heads - 1);  // a head past the end repeats the last one and is dropped below
-                qv[g] = *reinterpret_cast<const float4*>(s_q + h * dim + d);  // same address in the warp
+                qv[g] = *reinterpret_cast<const ulonglong2*>(s_q + h * dim + d);  // same address in the warp
             }
 #pragma unroll
             for (int tb = 0; tb < SC_TB; ++tb)
 #pragma unroll
                 for (int g = 0; g < SC_HB; ++g) {
-                    dot[tb][g] = fmaf(kv[tb].x, qv[g].x, dot[tb][g]);
-                    dot[tb][g] = fmaf(kv[tb].y, qv[g].y, dot[tb][g]);
-                    dot[tb][g] = fmaf(kv[tb].z, qv[g].z, dot[tb][g]);
-                    dot[tb][g] = fmaf(kv[tb].w, qv[g].w, dot[tb][g]);
+                    dot2[tb][g] = ffma2(kv[tb].x, qv[g].x, dot2[tb][g]);
+                    dot2[tb][g] = ffma2(kv[tb].y, qv[g].y, dot2[tb][g]);
                 }
         }
+        float dot[SC_TB][SC_HB];
+#pragma unroll
+        for (int tb = 0; tb < SC_TB; ++tb)
+#pragma unroll
+            for (int g = 0; g < SC_HB; ++g)
+                dot[tb][g] = __uint_as_float((unsigned)(dot2[tb][g] & 0xffffffffull)) + __uint_as_float((unsigned)(dot2[tb][g] >> 32));
 #pragma unroll
         for (int g = 0; g < SC_HB; ++g) {
             const int h = h0 + g * SC_HG;
