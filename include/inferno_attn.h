@@ -279,6 +279,18 @@ int32_t inf_dsa_scores(inf_ctx* ctx, const float* q, const float* weights, const
 int32_t inf_dsa_topk(inf_ctx* ctx, const float* scores, int32_t batch, int32_t key_tokens, int32_t top_k,
                      uint32_t* selected, int32_t selected_stride);
 
+/* FP8 E4M3FN KV storage of the Laguna safetensors cache (crates/backend/src/metal/kernels/
+ * fp8_attention_kernels.metal:11-54 codec, :227-263 append): stored byte = encode(x / scale), read value =
+ * decode(byte) * scale, one scale per tensor.  Encode saturates at +-448, maps NaN and 0 to 0x00, rounds ties to
+ * even, and below 2^-6 stores multiples of 2^-9; decode maps the two NaN codes to 0.  count values, device
+ * pointers.  inf_kv_pool_from_fp8 dequantises whole FP8 K and V page arrays (same geometry as the pool,
+ * [num_pages][kv_heads][page_size][head_dim] bytes) into the fp16 pool the attention kernels read; attention
+ * directly over FP8 pages is not part of this library yet. */
+int32_t inf_fp8_e4m3fn_encode(inf_ctx* ctx, const float* input, int64_t count, float scale, void* output);
+int32_t inf_fp8_e4m3fn_decode(inf_ctx* ctx, const void* input, int64_t count, float scale, float* output);
+int32_t inf_kv_pool_from_fp8(inf_ctx* ctx, const void* k_fp8, const void* v_fp8, float key_scale, float value_scale,
+                             const inf_kv_pool* pool);
+
 /* Q8Row cold-store codec (crates/cache/src/cold_kv.rs:1624-1703; device decode kernel q8_rows_to_f32_kernel,
  * crates/backend/src/metal/kernels/cast_kernels.metal:31-56).  A row of `dim` values is 4 + dim bytes: the
  * little-endian f32 scale max|x| / 127 (1.0 for an all-zero row), then round(x / scale) as signed bytes clamped to

@@ -345,6 +345,23 @@ class CudaBackend:
         ok = self._check(self._lib.inf_dsa_topk(self._ctx, _ptr(scores), B, n, top_k, _ptr(out), out.shape[1]))
         return out if ok else None
 
+    def fp8_e4m3fn_encode(self, x, scale: float):
+        """FP8 E4M3FN encode of x / scale (fp8_attention_kernels.metal:29-54): f32 -> uint8, same shape."""
+        out = torch.empty(x.shape, dtype=torch.uint8, device=self.device)
+        self._check(self._lib.inf_fp8_e4m3fn_encode(self._ctx, _ptr(x), x.numel(), scale, _ptr(out)))
+        return out
+
+    def fp8_e4m3fn_decode(self, b, scale: float):
+        """FP8 E4M3FN decode times scale (fp8_attention_kernels.metal:11-27): uint8 -> f32, same shape."""
+        out = torch.empty(b.shape, dtype=torch.float32, device=self.device)
+        self._check(self._lib.inf_fp8_e4m3fn_decode(self._ctx, _ptr(b), b.numel(), scale, _ptr(out)))
+        return out
+
+    def kv_pool_from_fp8(self, k_fp8, v_fp8, key_scale: float, value_scale: float, pool: KvPool):
+        """FP8 K / V page arrays dequantised into the fp16 pool of the same geometry."""
+        self._check(self._lib.inf_kv_pool_from_fp8(self._ctx, _ptr(k_fp8), _ptr(v_fp8), key_scale, value_scale,
+                                                   C.byref(pool.desc)))
+
     def q8_rows_encode(self, x):
         """Q8Row encode (crates/cache/src/cold_kv.rs:1624): f32 [..., dim] -> uint8 [rows, 4 + dim]."""
         dim = x.shape[-1]

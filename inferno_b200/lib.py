@@ -96,6 +96,9 @@ SIGNATURES = {
                                               _I]),
     "inf_dsa_scores": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "inf_dsa_topk": (_I, [_P, _P, _I, _I, _I, _P, _I]),
+    "inf_fp8_e4m3fn_encode": (_I, [_P, _P, _L, _F, _P]),
+    "inf_fp8_e4m3fn_decode": (_I, [_P, _P, _L, _F, _P]),
+    "inf_kv_pool_from_fp8": (_I, [_P, _P, _P, _F, _F, C.POINTER(KvPool)]),
     "inf_q8_rows_encode": (_I, [_P, _P, _L, _I, _P]),
     "inf_q8_rows_decode": (_I, [_P, _P, _L, _I, _P]),
     "inf_mla_pool_thaw_q8_rows": (_I, [_P, _P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _I]),

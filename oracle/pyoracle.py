@@ -313,3 +313,40 @@ def q8_rows_decode(payload, dim):
     scale = p[:, :4].copy().view("<f4").reshape(-1).astype(np.float32)
     return (p[:, 4:].view(np.int8).astype(np.float32) * scale[:, None]).astype(np.float32)
 
+
+def fp8_e4m3fn_decode(bits):
+    """laguna_fp8_e4m3fn_decode (crates/backend/src/metal/kernels/fp8_attention_kernels.metal:11-27): uint8 -> f32."""
+    b = np.asarray(bits, dtype=np.uint8).astype(np.int32)
+    sign, exponent, mant = b >> 7, (b >> 3) & 15, b & 7
+    mag = np.where(exponent == 0, mant * np.float32(2.0 ** -9),
+                   (1.0 + mant * 0.125) * np.exp2((exponent - 7).astype(np.float64))).astype(np.float32)
+    mag = np.where((exponent == 15) & (mant == 7), np.float32(0.0), mag)
+    return np.where(sign == 1, -mag, mag).astype(np.float32)
+
+
+def fp8_e4m3fn_encode(x):
+    """laguna_fp8_e4m3fn_encode (fp8_attention_kernels.metal:29-54): f32 -> uint8 (the caller divides by the scale)."""
+    x = _f32(x)
+    out = np.zeros(x.shape, np.uint8)
+    ok = ~(np.isnan(x) | (x == 0))
+    sign = np.where(x < 0, 0x80, 0).astype(np.uint32)
+    mag = np.minimum(np.abs(x), np.float32(448.0)).astype(np.float32)
+    small = mag < np.float32(0.015625)
+    m_small = np.minimum(np.rint(mag.astype(np.float64) * 512.0), 8).astype(np.uint32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        _, e2 = np.frexp(np.where(ok, mag, np.float32(1.0)).astype(np.float64))  # mag = m * 2^e2, m in [0.5, 1)
+    e = e2 - 1
+    norm = np.where(ok, mag, np.float32(1.0)).astype(np.float64) * np.exp2(-e.astype(np.float64))
+    mant = np.rint((norm - 1.0) * 8.0).astype(np.int64)
+    exponent = (e + 7).astype(np.int64)
+    bump = mant == 8
+    mant = np.where(bump, 0, mant)
+    exponent = np.where(bump, exponent + 1, exponent)
+    sat = (exponent > 15) | ((exponent == 15) & (mant > 6))
+    exponent = np.where(sat, 15, exponent)
+    mant = np.where(sat, 6, mant)
+    normal = (sign | (exponent.astype(np.uint32) << 3) | mant.astype(np.uint32)).astype(np.uint32)
+    res = np.where(small, sign | m_small, normal)
+    out[ok] = res[ok].astype(np.uint8)
+    return out
+

@@ -402,3 +402,23 @@ def test_dsa_scores_formula():
     # scale 1/sqrt(4) = 0.5: token0: 0.5*relu(2) + 0.25*relu(-1) = 1.0; token1: 0.5*relu(-1) + 0.25*relu(3) = 0.75;
     # current: 0.5*relu(0.5) + 0.25*relu(1) = 0.5
     assert np.allclose(orc.dsa_scores(q, w, past, cur), [[1.0, 0.75, 0.5]])
+
+
+def test_fp8_e4m3fn_codec_matches_the_published_format():
+    """The FP8 codec restatement (fp8_attention_kernels.metal:11-54) against the E4M3FN format itself: known codes,
+    a round trip of every code, saturation and NaN handling, and torch's own float8_e4m3fn cast for in-range values."""
+    torch = pytest.importorskip("torch")
+    dec = orc.fp8_e4m3fn_decode(np.arange(256, dtype=np.uint8))
+    assert dec[0x38] == 1.0 and dec[0x7E] == 448.0 and dec[0x08] == 2.0 ** -6 and dec[0x01] == 2.0 ** -9
+    assert dec[0x7F] == 0.0 and dec[0xFF] == 0.0 and dec[0xB8] == -1.0
+    codes = np.array([c for c in range(256) if c not in (0x7F, 0xFF, 0x80)], np.uint8)
+    assert np.array_equal(orc.fp8_e4m3fn_encode(dec[codes]), codes)
+    special = np.array([np.nan, 0.0, -0.0, 1e9, -1e9, 464.0, 2.0 ** -10, 3 * 2.0 ** -10], np.float32)
+    assert orc.fp8_e4m3fn_encode(special).tolist() == [0, 0, 0, 0x7E, 0xFE, 0x7E, 0, 2]
+    x = np.concatenate([orc.fill_normal((50000,), 0xF8000 + 1500, 4.0, False),
+                        orc.fill_normal((50000,), 0xF8000 + 1501, 0.02, False)]).astype(np.float32)
+    x = x[(np.abs(x) <= 448) & (x != 0)]
+    want = torch.from_numpy(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    got = orc.fp8_e4m3fn_encode(x)
+    # torch keeps the sign of values that round to zero; the reference encoder does too (sign | 0)
+    assert np.array_equal(got, want)
