@@ -22,7 +22,7 @@ __device__ __forceinline__ uint8_t fp8_e4m3fn_encode(float value) {
     }
     int e = (int)((__float_as_uint(mag) >> 23) & 0xffu) - 127;  // floor(log2(mag)) for a normal float
     uint32_t exponent = (uint32_t)(e + 7);
-    const float normalized = mag * exp2f((float)-e);              // in [1, 2), exact
+    const float normalized = mag * __uint_as_float((uint32_t)(127 - e) << 23);  // mag * 2^-e, in [1, 2), exact
     uint32_t mant = (uint32_t)rintf((normalized - 1.0f) * 8.0f);  // ties to even
     if (mant == 8u) {
         mant = 0u;
@@ -40,7 +40,7 @@ __device__ __forceinline__ float fp8_e4m3fn_decode(uint8_t bits) {
     const uint32_t sign = bits >> 7, exponent = (bits >> 3) & 0x0fu, mant = bits & 0x07u;
     if (exponent == 15u && mant == 7u) return 0.0f;
     const float mag = exponent == 0u ? (float)mant * 0.001953125f
-                                     : (1.0f + (float)mant * 0.125f) * exp2f((float)((int)exponent - 7));
+                                     : (1.0f + (float)mant * 0.125f) * __uint_as_float((exponent + 120u) << 23);  // 2^(exponent-7)
     return sign ? -mag : mag;
 }
 

@@ -320,8 +320,8 @@ def fp8_e4m3fn_decode(bits):
     sign, exponent, mant = b >> 7, (b >> 3) & 15, b & 7
     mag = np.where(exponent == 0, mant * np.float32(2.0 ** -9),
                    (1.0 + mant * 0.125) * np.exp2((exponent - 7).astype(np.float64))).astype(np.float32)
-    mag = np.where((exponent == 15) & (mant == 7), np.float32(0.0), mag)
-    return np.where(sign == 1, -mag, mag).astype(np.float32)
+    out = np.where(sign == 1, -mag, mag).astype(np.float32)
+    return np.where((exponent == 15) & (mant == 7), np.float32(0.0), out).astype(np.float32)  # both NaN codes read +0
 
 
 def fp8_e4m3fn_encode(x):
