@@ -126,9 +126,9 @@ dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights
 // ---------------------------------------------------------------------------------------------- top-k
 // ids of the k best tokens, best first, where a precedes b iff score_a > score_b or (score_a == score_b and
 // id_a < id_b) (dsa_precedes, dsa_kernels.metal:182-196); missing entries are 0xffffffff.  The reference sorts
-// 256-token blocks and merges runs; here one CTA per sequence finds the k-th largest score with a four-pass radix
-// select over the order-preserving integer image of the scores, collects everything above it plus the lowest-id
-// ties, and sorts those k entries in shared memory.
+// 256-token blocks and merges runs; here one CTA per sequence finds the k-th largest score with a three-pass radix
+// select (12 + 10 + 10 bits) over the order-preserving integer image of the scores, collects everything above it
+// plus the lowest-id ties in id order, and sorts those k entries by score with a stable counting sort in shared memory.
 constexpr int TK_THREADS = 1024;
 constexpr int TK_MAX_K = 2048;
 constexpr unsigned TK_INVALID = 0xffffffffu;
@@ -141,16 +141,36 @@ __device__ __forceinline__ unsigned ordered_bits(float f) {  // larger float <->
 
 // One CTA per sequence.  The row is turned into ordered integers once and kept in shared memory when it fits
 // (up to TK_SMEM_ROWS tokens); the radix passes, the collection sweep and the final sort then never leave the SM.
-constexpr int TK_SMEM_ROWS = 49152;  // 192 KB of ordered scores
+// The k-th largest value is found 12 + 10 + 10 bits at a time: twelve leading bits spread real scores (a few
+// exponents, sixteen mantissa steps each) over enough bins that the shared-memory adds of a warp rarely meet.
+constexpr int TK_SMEM_ROWS = 47104;  // 184 KB of ordered scores
+constexpr int TK_WARPS = TK_THREADS / 32;
+constexpr int TK_BINS = 4096;
+constexpr int TK_SORT_TABLE_BYTES = TK_WARPS * 256 * (int)sizeof(unsigned);
+static_assert(TK_BINS * sizeof(unsigned) == TK_MAX_K * sizeof(unsigned long long), "the histogram doubles as the sort's second buffer");
+constexpr int TK_LOAD_DEPTH = 8;  // 16-byte global loads in flight per thread while the row comes in
+
+// the lanes of the warp that hold the same eight-bit digit, one vote per bit
+__device__ __forceinline__ unsigned tk_same_digit_lanes(unsigned digit) {
+    unsigned lanes = 0xffffffffu;
+#pragma unroll
+    for (int bit = 0; bit < 8; ++bit) {
+        const bool set = (digit >> bit) & 1u;
+        const unsigned vote = __ballot_sync(0xffffffffu, set);
+        lanes &= set ? vote : ~vote;
+    }
+    return lanes;
+}
 
 __global__ void __launch_bounds__(TK_THREADS)
 dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids, int n, int k, int out_stride,
                 int row_in_smem) {
     extern __shared__ __align__(16) unsigned srow[];
-    __shared__ unsigned hist[256];
+    __shared__ __align__(16) unsigned hist[TK_BINS];
+    __shared__ unsigned sort_part[4][256];
     __shared__ unsigned long long keys[TK_MAX_K];
-    __shared__ int w_above[32], w_tie[32], w_base[32], w_quota[32];
-    __shared__ unsigned sh_prefix, sh_mask;
+    __shared__ int w_above[TK_WARPS], w_tie[TK_WARPS];
+    __shared__ unsigned sh_prefix, sh_mask, sh_any, sh_all;
     __shared__ int sh_remaining;
     inf_pdl_wait();
     inf_pdl_release();
@@ -159,63 +179,115 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
     unsigned* out = out_ids + (size_t)b * out_stride;
     const int want = min(k, n);
     auto value = [&](int i) -> unsigned { return row_in_smem ? srow[i] : ordered_bits(row[i]); };
-    if (row_in_smem)
-        for (int i = tid; i < n; i += TK_THREADS) srow[i] = ordered_bits(row[i]);
-    // ---- the want-th largest value, eight bits at a time
+    for (int i = tid; i < TK_MAX_K; i += TK_THREADS) keys[i] = ~0ull;
     if (tid == 0) {
         sh_prefix = 0u;
         sh_mask = 0u;
+        sh_any = 0u;
+        sh_all = ~0u;
         sh_remaining = want;
     }
-    for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        for (int i = tid; i < 256; i += TK_THREADS) hist[i] = 0u;
+    const int n4 = n >> 2;  // whole groups of four scores
+    for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 20 : (pass == 1 ? 10 : 0);
+        const int bins = pass == 0 ? TK_BINS : 1024;
+        for (int i = tid; i < bins; i += TK_THREADS) hist[i] = 0u;
         __syncthreads();
-        const unsigned prefix = sh_prefix, mask = sh_mask;
-        // whole warps walk the row together so that lanes with the same digit can add once (the leading digits
-        // of real scores are nearly all equal, and same-address shared atomics would serialise)
-        for (int base = 0; base < n; base += TK_THREADS) {
-            const int i = base + tid;
-            unsigned digit = 0x100u;  // no candidate
-            if (i < n) {
-                const unsigned u = value(i);
-                if ((u & mask) == prefix) digit = (u >> shift) & 255u;
+        const unsigned prefix = sh_prefix, mask = sh_mask, digit_mask = (unsigned)bins - 1u;
+        if (pass == 0 && row_in_smem && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+            // The first pass also brings the row into shared memory, TK_LOAD_DEPTH groups of four per thread at a
+            // time.  A warp whose 128 scores all share one digit (constant rows, padding) adds once.
+            for (int base = warp * 32; base < n4; base += TK_THREADS * TK_LOAD_DEPTH) {
+                float4 f[TK_LOAD_DEPTH];
+#pragma unroll
+                for (int d = 0; d < TK_LOAD_DEPTH; ++d) {
+                    const int v = base + d * TK_THREADS + lane;
+                    if (v < n4) f[d] = reinterpret_cast<const float4*>(row)[v];
+                }
+#pragma unroll
+                for (int d = 0; d < TK_LOAD_DEPTH; ++d) {
+                    const int v = base + d * TK_THREADS + lane;
+                    if (base + d * TK_THREADS >= n4) break;  // the whole warp is past the end
+                    const bool valid = v < n4;
+                    uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                    if (valid) {
+                        q = make_uint4(ordered_bits(f[d].x), ordered_bits(f[d].y), ordered_bits(f[d].z), ordered_bits(f[d].w));
+                        reinterpret_cast<uint4*>(srow)[v] = q;
+                    }
+                    const unsigned d0 = q.x >> 20, d1 = q.y >> 20, d2 = q.z >> 20, d3 = q.w >> 20;
+                    const unsigned first = __shfl_sync(0xffffffffu, d0, 0);  // lane 0 is valid whenever the warp is here
+                    const bool same = !valid || (d0 == first && d1 == first && d2 == first && d3 == first);
+                    if (__all_sync(0xffffffffu, same)) {
+                        const unsigned live = __ballot_sync(0xffffffffu, valid);
+                        if (lane == 0) atomicAdd(&hist[first], 4u * (unsigned)__popc(live));
+                    } else if (valid) {
+                        atomicAdd(&hist[d0], 1u);
+                        atomicAdd(&hist[d1], 1u);
+                        atomicAdd(&hist[d2], 1u);
+                        atomicAdd(&hist[d3], 1u);
+                    }
+                }
             }
-            // lanes that share lane 0's digit add once through lane 0; the others add on their own
-            const unsigned first = __shfl_sync(0xffffffffu, digit, 0);
-            const unsigned same = __ballot_sync(0xffffffffu, digit == first);
-            if (digit == first) {
-                if (lane == 0 && digit < 256u) atomicAdd(&hist[digit], (unsigned)__popc(same));
-            } else if (digit < 256u) {
-                atomicAdd(&hist[digit], 1u);
+            if (n4 * 4 + tid < n) {
+                const unsigned u = ordered_bits(row[n4 * 4 + tid]);
+                srow[n4 * 4 + tid] = u;
+                atomicAdd(&hist[u >> 20], 1u);
+            }
+        } else if (pass == 0 || !row_in_smem) {
+            for (int i = tid; i < n; i += TK_THREADS) {
+                const unsigned u = ordered_bits(row[i]);
+                if (pass == 0 && row_in_smem) srow[i] = u;
+                if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & digit_mask], 1u);
+            }
+        } else {
+            for (int v = tid; v < n4; v += TK_THREADS) {
+                const uint4 q = reinterpret_cast<const uint4*>(srow)[v];
+                if ((q.x & mask) == prefix) atomicAdd(&hist[(q.x >> shift) & digit_mask], 1u);
+                if ((q.y & mask) == prefix) atomicAdd(&hist[(q.y >> shift) & digit_mask], 1u);
+                if ((q.z & mask) == prefix) atomicAdd(&hist[(q.z >> shift) & digit_mask], 1u);
+                if ((q.w & mask) == prefix) atomicAdd(&hist[(q.w >> shift) & digit_mask], 1u);
+            }
+            if (n4 * 4 + tid < n) {
+                const unsigned u = srow[n4 * 4 + tid];
+                if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & digit_mask], 1u);
             }
         }
         __syncthreads();
-        if (warp == 0) {
-            // the bin that holds the remaining-th largest candidate: lane l owns bins 8l .. 8l+7; counts of the bins
-            // above a lane come from a suffix sum across the warp, the owner then walks its eight bins
+        {
+            // The bin that holds the remaining-th largest candidate.  Thread t owns `per` consecutive bins; the
+            // candidates in bins above a thread come from a suffix sum over the CTA, the owner then walks its bins.
+            const int per = bins / TK_THREADS;  // 4 or 1
             const int remaining = sh_remaining;
-            int mine[8], sum = 0;
+            int mine[TK_BINS / TK_THREADS], sum = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                mine[i] = (int)hist[lane * 8 + i];
+            for (int i = 0; i < TK_BINS / TK_THREADS; ++i) {
+                mine[i] = i < per ? (int)hist[tid * per + i] : 0;
                 sum += mine[i];
             }
-            int above = sum;  // inclusive suffix sum over lanes >= this one
+            int suffix = sum;  // inclusive suffix sum over the lanes of this warp
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
-                const int y = __shfl_down_sync(0xffffffffu, above, o);
-                if (lane + o < 32) above += y;
+                const int y = __shfl_down_sync(0xffffffffu, suffix, o);
+                if (lane + o < 32) suffix += y;
             }
-            above -= sum;  // candidates in bins owned by higher lanes
+            if (lane == 0) w_above[warp] = suffix;
+            __syncthreads();
+            int warps = w_above[lane];  // inclusive suffix sum over the warps
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_down_sync(0xffffffffu, warps, o);
+                if (lane + o < 32) warps += y;
+            }
+            const int next_warp = __shfl_sync(0xffffffffu, warps, (warp + 1) & 31);
+            const int above = (warp < 31 ? next_warp : 0) + suffix - sum;  // candidates in bins of later threads
             if (above < remaining && remaining <= above + sum) {
-                int left = remaining - above, bin = 7;
+                int left = remaining - above, bin = per - 1;
                 for (; bin > 0; --bin) {
                     if (mine[bin] >= left) break;
                     left -= mine[bin];
                 }
-                sh_prefix = prefix | ((unsigned)(lane * 8 + bin) << shift);
-                sh_mask = mask | (255u << shift);
+                sh_prefix = prefix | ((unsigned)(tid * per + bin) << shift);
+                sh_mask = mask | (digit_mask << shift);
                 sh_remaining = left;  // how many entries equal to the final value are taken
             }
         }
@@ -223,89 +295,177 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
     }
     const unsigned threshold = sh_prefix;
     const int ties_wanted = sh_remaining;
-    // ---- collect everything above the threshold and the ties with the lowest ids.  Warp w owns the contiguous
-    //      token range [w * seg, (w + 1) * seg): a counting sweep, a prefix over the 32 warps, a writing sweep.
-    for (int i = tid; i < TK_MAX_K; i += TK_THREADS) keys[i] = ~0ull;
-    const int seg = ((n + 32 * 32 - 1) / (32 * 32)) * 32;  // multiple of 32, so a warp's chunks stay in id order
-    const int s0 = min(n, warp * seg), s1 = min(n, s0 + seg);
-    int c_above = 0, c_tie = 0;
-    for (int i = s0 + lane; i < s1; i += 32) {
-        const unsigned u = value(i);
-        c_above += u > threshold;
-        c_tie += u == threshold;
-    }
+    // ---- collect everything above the threshold and the ties with the lowest ids.  In each round thread t owns
+    //      the 32 consecutive tokens [round + 32t, round + 32t + 32): it records which are above and which tie as
+    //      two bit masks, a scan over the CTA gives its place in the output, and it writes its own entries.  Lane l
+    //      starts its walk at element l of its chunk, so the 32 lanes of a warp hit 32 different banks.
+    int out_base = 0, ties_before = 0;  // the same in every thread
+    for (int round = 0; round < n; round += 32 * TK_THREADS) {
+        const int c = round + tid * 32;
+        unsigned above_mask = 0u, tie_mask = 0u;
+        if (row_in_smem && c + 32 <= n) {
+            // eight 16-byte reads; bit p of the masks built here belongs to element (p + 4 * lane) mod 32
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        c_above += __shfl_xor_sync(0xffffffffu, c_above, o);
-        c_tie += __shfl_xor_sync(0xffffffffu, c_tie, o);
-    }
-    if (lane == 0) {
-        w_above[warp] = c_above;
-        w_tie[warp] = c_tie;
-    }
-    __syncthreads();
-    if (warp == 0) {  // exclusive prefixes over the 32 warps' counts
-        const int t_w = w_tie[lane];
-        int ties_incl = t_w;
+            for (int q = 0; q < 8; ++q) {
+                const uint4 v = reinterpret_cast<const uint4*>(srow + c)[(q + lane) & 7];
+                above_mask |= ((unsigned)(v.x > threshold) << (4 * q)) | ((unsigned)(v.y > threshold) << (4 * q + 1)) |
+                              ((unsigned)(v.z > threshold) << (4 * q + 2)) | ((unsigned)(v.w > threshold) << (4 * q + 3));
+                tie_mask |= ((unsigned)(v.x == threshold) << (4 * q)) | ((unsigned)(v.y == threshold) << (4 * q + 1)) |
+                            ((unsigned)(v.z == threshold) << (4 * q + 2)) | ((unsigned)(v.w == threshold) << (4 * q + 3));
+            }
+            above_mask = __funnelshift_l(above_mask, above_mask, 4 * lane);
+            tie_mask = __funnelshift_l(tie_mask, tie_mask, 4 * lane);
+        } else if (c < n) {
+            for (int j = 0; j < 32; ++j) {
+                const int jj = (j + lane) & 31;
+                if (c + jj < n) {
+                    const unsigned u = value(c + jj);
+                    above_mask |= (unsigned)(u > threshold) << jj;
+                    tie_mask |= (unsigned)(u == threshold) << jj;
+                }
+            }
+        }
+        const int ca = __popc(above_mask), ct = __popc(tie_mask);
+        int ia = ca, it = ct;  // inclusive scans inside the warp
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const int y = __shfl_up_sync(0xffffffffu, ties_incl, o);
-            if (lane >= o) ties_incl += y;
+            const int ya = __shfl_up_sync(0xffffffffu, ia, o), yt = __shfl_up_sync(0xffffffffu, it, o);
+            if (lane >= o) {
+                ia += ya;
+                it += yt;
+            }
         }
-        const int quota = max(0, min(t_w, ties_wanted - (ties_incl - t_w)));
-        const int out_w = w_above[lane] + quota;
-        int out_incl = out_w;
+        if (lane == 31) {
+            w_above[warp] = ia;
+            w_tie[warp] = it;
+        }
+        __syncthreads();
+        int wa = w_above[lane], wt = w_tie[lane];  // every warp scans the 32 warp totals for itself
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const int y = __shfl_up_sync(0xffffffffu, out_incl, o);
-            if (lane >= o) out_incl += y;
+            const int ya = __shfl_up_sync(0xffffffffu, wa, o), yt = __shfl_up_sync(0xffffffffu, wt, o);
+            if (lane >= o) {
+                wa += ya;
+                wt += yt;
+            }
         }
-        w_base[lane] = out_incl - out_w;
-        w_quota[lane] = quota;
+        const int round_above = __shfl_sync(0xffffffffu, wa, 31), round_ties = __shfl_sync(0xffffffffu, wt, 31);
+        const int warp_a = warp ? __shfl_sync(0xffffffffu, wa, (warp + 31) & 31) : 0;  // totals of the warps before
+        const int warp_t = warp ? __shfl_sync(0xffffffffu, wt, (warp + 31) & 31) : 0;
+        const int ex_a = warp_a + ia - ca, ex_t = warp_t + it - ct;  // entries of earlier threads in this round
+        const int ties_open = max(ties_wanted - ties_before, 0);     // ties this round may still take
+        const int quota = max(0, min(ct, ties_open - ex_t));
+        unsigned take = tie_mask;
+        if (quota < ct) {  // the lowest `quota` ids of this thread's ties
+            take = 0u;
+            unsigned m = tie_mask;
+            for (int x = 0; x < quota; ++x) {
+                const unsigned low = m & (0u - m);
+                take |= low;
+                m ^= low;
+            }
+        }
+        int pos = out_base + ex_a + min(ties_open, ex_t);
+        unsigned sel = above_mask | take;
+        while (sel) {
+            const int jj = __ffs(sel) - 1;
+            sel &= sel - 1u;
+            const int i = c + jj;
+            keys[pos++] = ((unsigned long long)(~value(i)) << 32) | (unsigned)i;
+        }
+        out_base += round_above + min(ties_open, round_ties);
+        ties_before += round_ties;
+        __syncthreads();
     }
-    __syncthreads();
+    // ---- sort of the 2048 entries, best first.  The sweep above wrote them in id order, so a stable sort on the score
+    //      word alone gives the reference's order (ties by lower id; the all-ones padding stays last).  Four stable
+    //      counting passes of eight bits: warp w owns entries 64w .. 64w+63, counts their digits in its own row of a
+    //      32 x 256 table (the dead row buffer), a scan over bins and warps turns counts into places, each entry moves.
+    const unsigned long long* sorted;
     {
-        int pos = w_base[warp], ties_taken = 0;
-        const int quota = w_quota[warp];
-        for (int c0 = s0; c0 < s1; c0 += 32) {
-            const int i = c0 + lane;
-            unsigned u = 0u;
-            bool above = false, tie = false;
-            if (i < s1) {
-                u = value(i);
-                above = u > threshold;
-                tie = u == threshold;
+        unsigned long long* from = keys;
+        unsigned long long* to = reinterpret_cast<unsigned long long*>(hist);  // TK_BINS words = TK_MAX_K entries
+        unsigned* table = srow;
+        unsigned* my_row = table + warp * 256;
+        const unsigned lanes_below = (1u << lane) - 1u;
+        const int group = tid >> 8, bin = tid & 255;  // scan roles: 4 groups of 8 warps x 256 bins
+        // score bits that are the same in every real entry need no pass (the leading byte of the best scores of a
+        // long row usually is): a skipped pass would have moved nothing, the padding already sits last
+        {
+            const int e = warp * 64 + lane;
+            const unsigned h0 = (unsigned)(keys[e] >> 32), h1 = (unsigned)(keys[e + 32] >> 32);
+            unsigned any = (e < want ? h0 : 0u) | (e + 32 < want ? h1 : 0u);
+            unsigned all = (e < want ? h0 : ~0u) & (e + 32 < want ? h1 : ~0u);
+            any = __reduce_or_sync(0xffffffffu, any);
+            all = __reduce_and_sync(0xffffffffu, all);
+            if (lane == 0) {
+                atomicOr(&sh_any, any);
+                atomicAnd(&sh_all, all);
             }
-            const unsigned tie_mask = __ballot_sync(0xffffffffu, tie);
-            const bool take = above || (tie && ties_taken + __popc(tie_mask & ((1u << lane) - 1u)) < quota);
-            const unsigned take_mask = __ballot_sync(0xffffffffu, take);
-            if (take) keys[pos + __popc(take_mask & ((1u << lane) - 1u))] = ((unsigned long long)(~u) << 32) | (unsigned)i;
-            pos += __popc(take_mask);
-            ties_taken += __popc(tie_mask);
+            __syncthreads();
         }
+        const unsigned varying = sh_any ^ sh_all;
+        for (int pass = 0; pass < 4; ++pass) {
+            if (((varying >> (8 * pass)) & 255u) == 0u) continue;
+            const int shift = 32 + 8 * pass;
+            for (int i = tid; i < TK_WARPS * 256; i += TK_THREADS) table[i] = 0u;
+            __syncthreads();
+            const unsigned long long x0 = from[warp * 64 + lane], x1 = from[warp * 64 + 32 + lane];
+            const unsigned d0 = (unsigned)(x0 >> shift) & 255u, d1 = (unsigned)(x1 >> shift) & 255u;
+            const unsigned m0 = tk_same_digit_lanes(d0);
+            const unsigned r0 = (unsigned)__popc(m0 & lanes_below);
+            if ((m0 & lanes_below) == 0u) my_row[d0] = (unsigned)__popc(m0);
+            __syncwarp();
+            const unsigned m1 = tk_same_digit_lanes(d1);
+            const unsigned before = my_row[d1];  // entries with this digit among the warp's first 32
+            const unsigned r1 = before + (unsigned)__popc(m1 & lanes_below);
+            __syncwarp();
+            if ((m1 & lanes_below) == 0u) my_row[d1] = before + (unsigned)__popc(m1);
+            __syncthreads();
+            {  // counts of one bin over the 8 warps of a group -> places inside the group, group total aside
+                unsigned run = 0u;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    unsigned* cell = table + (group * 8 + w) * 256 + bin;
+                    const unsigned c = *cell;
+                    *cell = run;
+                    run += c;
+                }
+                sort_part[group][bin] = run;
+            }
+            __syncthreads();
+            unsigned p0 = 0u, p1 = 0u, p2 = 0u, total = 0u, incl = 0u;
+            if (tid < 256) {
+                p0 = sort_part[0][tid], p1 = sort_part[1][tid], p2 = sort_part[2][tid];
+                total = p0 + p1 + p2 + sort_part[3][tid];
+                incl = total;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned y = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += y;
+                }
+                if (lane == 31) w_above[warp] = (int)incl;
+            }
+            __syncthreads();
+            if (tid < 256) {
+                unsigned start = incl - total;  // entries in lower bins
+                for (int w = 0; w < warp; ++w) start += (unsigned)w_above[w];
+                sort_part[0][tid] = start;
+                sort_part[1][tid] = start + p0;
+                sort_part[2][tid] = start + p0 + p1;
+                sort_part[3][tid] = start + p0 + p1 + p2;
+            }
+            __syncthreads();
+            to[sort_part[warp >> 3][d0] + my_row[d0] + r0] = x0;
+            to[sort_part[warp >> 3][d1] + my_row[d1] + r1] = x1;
+            __syncthreads();
+            unsigned long long* t = from;
+            from = to;
+            to = t;
+        }
+        sorted = from;
     }
-    __syncthreads();
-    // ---- bitonic sort of the (at most 2048) entries, ascending = best first.  Exchanges at a distance below 32
-    //      stay inside the 64 entries one warp owns and need only a warp barrier.
-    for (int size = 2; size <= TK_MAX_K; size <<= 1)
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            const int i = tid;  // TK_MAX_K / 2 == TK_THREADS comparators per step
-            const int lo = 2 * i - (i & (stride - 1));
-            const int hi = lo + stride;
-            const bool up = (lo & size) == 0;
-            const unsigned long long a = keys[lo], c = keys[hi];
-            if ((a > c) == up) {
-                keys[lo] = c;
-                keys[hi] = a;
-            }
-            if (stride > 32)
-                __syncthreads();
-            else
-                __syncwarp();
-            if (stride == 1 && size >= 64) __syncthreads();  // the next size starts with a long distance again
-        }
-    __syncthreads();
-    for (int i = tid; i < k; i += TK_THREADS) out[i] = i < want ? (unsigned)(keys[i] & 0xffffffffull) : TK_INVALID;
+    for (int i = tid; i < k; i += TK_THREADS) out[i] = i < want ? (unsigned)(sorted[i] & 0xffffffffull) : TK_INVALID;
 }
 
 }  // namespace
@@ -345,7 +505,8 @@ extern "C" int32_t inf_dsa_topk(inf_ctx* ctx, const float* scores, int32_t batch
     {
         inf_prof_scope prof(ctx, "dsa_topk_kernel");
         const int in_smem = key_tokens <= TK_SMEM_ROWS ? 1 : 0;
-        const size_t smem = in_smem ? (size_t)key_tokens * sizeof(unsigned) : 0;
+        // the row when it fits; never less than the sort's 32 x 256 table, which reuses the space
+        const size_t smem = max(in_smem ? (size_t)((key_tokens + 3) & ~3) * sizeof(unsigned) : (size_t)0, (size_t)TK_SORT_TABLE_BYTES);
         if (smem > 48 * 1024 && !(ctx->func_attr_done & 8192u)) {
             INF_CUDA(ctx, cudaFuncSetAttribute(dsa_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                TK_SMEM_ROWS * (int)sizeof(unsigned)));

@@ -38,7 +38,8 @@ def test_dsa_scores_match_oracle(be, B, past, H, D):
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("B,n,k", [(1, 32768, 2048), (2, 5000, 2048), (1, 100, 2048), (3, 2048, 2048), (1, 4097, 7), (1, 1, 1)])
+@pytest.mark.parametrize("B,n,k", [(1, 32768, 2048), (2, 5000, 2048), (1, 100, 2048), (3, 2048, 2048), (1, 4097, 7), (1, 1, 1),
+                                   (1, 32769, 2048), (2, 40960, 2048), (1, 45000, 512), (1, 70001, 2048)])
 def test_dsa_topk_is_exact(be, B, n, k):
     rs = np.random.RandomState(SEED0 % 65536 + n + k)
     scores = rs.standard_normal((B, n)).astype(np.float32)
@@ -51,6 +52,23 @@ def test_dsa_topk_is_exact(be, B, n, k):
     be.device_flush()
     want = orc.dsa_topk(scores, k)
     assert np.array_equal(got.cpu().numpy().view(np.uint32), want)
+
+
+def test_topk_ties_taken_across_rounds_of_the_collection_sweep(be):
+    # 100 zeros among the first 32768 tokens (all else -1), zeros after: the 2048 best are the zeros with the lowest ids,
+    # 100 from the first round of the sweep and 1948 from the second, the last thread's ties taken in part
+    n = 36000
+    scores = np.full((1, n), -1.0, np.float32)
+    scores[0, 5:32768:331][:100] = 0.0
+    scores[0, 32768:] = 0.0
+    got = be.dsa_topk(dev(be, scores), 2048)
+    be.device_flush()
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), orc.dsa_topk(scores, 2048))
+    # fewer zeros than k: the threshold falls on -1 and the lowest-id -1 entries fill up
+    scores[0, 33000:] = -1.0
+    got = be.dsa_topk(dev(be, scores), 2048)
+    be.device_flush()
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), orc.dsa_topk(scores, 2048))
 
 
 def test_topk_with_all_equal_scores_takes_the_first_ids(be):
