@@ -40,7 +40,7 @@ constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0, COL_S = 256, COL_Q = 320;  // O 256 columns, S 64, Q 144 (each on both lane halves)
 constexpr int STAGES = 3;
-constexpr int GATHER_UNIT = 16;  // the gather form splits the row list in units of 16 rows, so a short list still fills the GPU
+constexpr int GATHER_UNIT = 64;  // the gather form splits the row list in units of 64 rows: one full tile per unit
 constexpr int QHALF = ROW / 2;  // 288 query columns per lane half
 
 constexpr int OFF_KV = 0;
@@ -49,6 +49,7 @@ constexpr int OFF_BAR = OFF_P + BLK_BYTES;
 constexpr int SMEM_TOTAL = OFF_BAR + 128;
 
 struct MlaParams {
+    const __half* rows;     // the pool's rows; the gather form copies from them directly
     const int* pages;
     const int* lens;
     const int* sel;         // gather form: [batch][sel_stride] logical row ids; null for the contiguous form
@@ -79,8 +80,8 @@ __device__ __forceinline__ void split_range(int n_pages, int n_splits, int s, in
 }
 
 // GATHER: the keys are not the first kv_len rows of the sequence but the rows listed in p.sel (the DSA indexer's
-// choice); a "page" is then any 64 listed rows, fetched row by row with one-row TMA boxes (tm_kv has a box of
-// one row in that form), and everything after the load is unchanged.
+// choice); a "page" is then any 64 listed rows, copied row by row into the swizzled tile with 16-byte asynchronous
+// copies, and everything after the load is unchanged.
 template <bool GATHER>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
@@ -189,15 +190,21 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 }
             }
         }
-        if (GATHER) {  // the whole warp: lane l fetches rows l and l + 32 of every group of 64 listed rows
-            const int oob_row = p.num_pages * PAGE;
+        if (GATHER) {
+            // The whole warp.  Lane l resolves rows l and l + 32 of every group of 64 listed rows; the rows are then
+            // copied one after another with 16-byte asynchronous copies, the 32 lanes side by side along a row (whole
+            // 512-byte runs per instruction), each chunk placed where the 128-byte swizzle of the tile expects it.
+            // One-row TMA boxes did the same job at a few hundred requests per tile, and the request rate, not the
+            // bytes, set the time to the first score.  A tile is handed over once its copies have landed, one tile late,
+            // so that the next tile's copies are already in flight.
+            int pending_stage = -1;
             for (int j = 0; j < n; ++j) {
                 const int rows_here = min(PAGE, row_end - (row_begin + j * PAGE));  // listed rows in this 64-row tile
                 int ys[2];
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                     const int i = row_begin + j * PAGE + lane + 32 * rr;
-                    ys[rr] = oob_row;  // an id the query may not see is fetched as a row of zeros
+                    ys[rr] = -1;  // an id the query may not see is read as a row of zeros
                     if (i < row_end) {
                         const int id = p.sel[(long long)b * p.sel_stride + i];
                         if (id >= 0 && id < seq_rows && id / PAGE < p.max_pages) {
@@ -222,8 +229,8 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                     if (lane == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
                     break;
                 }
-                // Rows of the tile beyond the list are not fetched (a one-row TMA request costs as much as any other):
-                // they are cleared here, because a masked key still enters PV as 0 x (whatever the stage held).
+                // Rows of the tile beyond the list are cleared: a masked key still enters PV as 0 x (whatever the
+                // stage held).
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr)
                     if (lane + 32 * rr >= rows_here)
@@ -233,17 +240,35 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #pragma unroll
                             for (int c = 0; c < 8; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
                         }
+                const uint32_t tile = smem_u32(sKV + st * TILE_BYTES);
+                for (int r = 0; r < rows_here; ++r) {
+                    const int y = __shfl_sync(0xffffffffu, r < 32 ? ys[0] : ys[1], r & 31);
+                    const __half* src = p.rows + (size_t)(y < 0 ? 0 : y) * ROW;
+                    const uint32_t bytes = y < 0 ? 0u : 16u;  // zero bytes read: the chunk is filled with zeros
+#pragma unroll
+                    for (int c0 = 0; c0 < ROW / 8; c0 += 32) {
+                        const int c = c0 + lane;  // 16-byte chunk of the row
+                        if (c < ROW / 8) {
+                            const uint32_t dst = tile + (c >> 3) * BLK_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src + c * 8), "r"(bytes)
+                                         : "memory");
+                        }
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                if (pending_stage >= 0) {
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&kv_full[pending_stage]);
+                }
+                pending_stage = st;
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            if (pending_stage >= 0) {
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_expect_tx(&kv_full[st], (uint32_t)rows_here * ROW * 2);
-                __syncwarp();
-#pragma unroll
-                for (int rr = 0; rr < 2; ++rr)
-                    if (lane + 32 * rr < rows_here)
-#pragma unroll
-                        for (int blk = 0; blk < NBLK; ++blk)
-                            tma_load_2d(sKV + st * TILE_BYTES + blk * BLK_BYTES + (lane + 32 * rr) * 128, &tm_kv, blk * 64,
-                                        ys[rr], &kv_full[st]);
+                if (lane == 0) mbar_arrive(&kv_full[pending_stage]);
             }
         }
     } else if (warp == 5) {
@@ -595,11 +620,12 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
     {
         uint64_t dims[2] = {(uint64_t)ROW, (uint64_t)pool->num_pages * PAGE};
         uint64_t strides[1] = {(uint64_t)ROW * 2};
-        uint32_t box[2] = {64, sel ? 1u : (uint32_t)PAGE};  // the gather form fetches single rows
+        uint32_t box[2] = {64, (uint32_t)PAGE};  // unused by the gather form, which copies rows itself
         rc = inf_make_tmap(ctx, pool->rows, 2, dims, strides, box, &tkv);
         if (rc != INF_OK) return rc;
     }
     MlaParams p{};
+    p.rows = (const __half*)pool->rows;
     p.pages = table->pages;
     p.lens = table->lens;
     p.sel = sel;
