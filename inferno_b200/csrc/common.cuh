@@ -43,6 +43,7 @@ struct inf_ctx {
     std::string err;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
+    size_t dsa_scores_smem = 0;  // dynamic shared memory the tensor-core index-score kernel has been allowed so far
     int* status = nullptr;       // device int32[4]
     int* host_status = nullptr;  // pinned int32[4]
     inf_tmap_encode_fn encode = nullptr;

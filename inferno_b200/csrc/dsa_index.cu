@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace {
 
@@ -121,6 +122,194 @@ dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights
         for (int g = 0; g < SC_HG; ++g) sum += s_part[g * SC_TOKENS + tid];
         scores[(size_t)b * n + t0 + tid] = sum;
     }
+}
+
+// The same scores on the tensor cores (tcgen05, kind::tf32), for 128-dim keys and head counts that are multiples of
+// 16.  The register-blocked kernel above spends ~8 us of fp32 multiply-adds per launch at 32 768 tokens; a 128-token
+// tile is 32 MMAs here.  fp32 inputs are split into two tf32 terms (hi = x with the 13 low mantissa bits cleared,
+// lo = x - hi, exact) and each product is taken as hi*hi + hi*lo + lo*hi with fp32 accumulation, which keeps the error
+// of a dot product near 2^-20 of its magnitude: as good as the fp32 reference sum, whose own rounding depends on the
+// order of addition.
+//
+// A CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Key tiles arrive by TMA (the f32 rows described to the
+// copy engine as twice as many 16-bit values; K-major, 128-byte swizzle: four blocks of 32 dims).  Warps 0-3 split a
+// landed tile block by block, in place into the hi tile and into a lo tile, and hand each block to warp 4 as soon as
+// it is done; warp 4 issues, per 8 dims, hi x [q_hi; q_lo] (N = 2 x heads) and lo x q_hi (N = heads) into a
+// [128 tokens x 2 heads] fp32 accumulator in tensor memory.  The same four warps then read their token's row back, add
+// the two halves, apply scale, relu and the head weights, and store the score.  With two key buffers the next tile's
+// copy is in flight during all of that.
+constexpr int TU_TOKENS = 128;
+constexpr int TU_DIM = 128;
+constexpr int TU_WORKERS = 128;
+constexpr int TU_THREADS = TU_WORKERS + 32;
+constexpr int TU_KEY_TILE = TU_TOKENS * TU_DIM * 4;  // 64 KB: four 128-byte-wide blocks of 128 rows
+constexpr int TU_BLOCK = TU_TOKENS * 128;             // one block of a key tile
+
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(uint32_t M, uint32_t N) {  // tf32 A/B, K-major both, fp32 accumulation
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_ss_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// x = hi + lo exactly; hi has at most 11 significant bits
+__device__ __forceinline__ void tf32_split(const float4& v, uint4& hi, float4& lo) {
+    hi.x = __float_as_uint(v.x) & 0xffffe000u, hi.y = __float_as_uint(v.y) & 0xffffe000u;
+    hi.z = __float_as_uint(v.z) & 0xffffe000u, hi.w = __float_as_uint(v.w) & 0xffffe000u;
+    lo.x = v.x - __uint_as_float(hi.x), lo.y = v.y - __uint_as_float(hi.y);
+    lo.z = v.z - __uint_as_float(hi.z), lo.w = v.w - __uint_as_float(hi.w);
+}
+
+__global__ void __launch_bounds__(TU_THREADS, 1)
+dsa_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_keys, const float* __restrict__ q,
+                       const float* __restrict__ weights, const float* __restrict__ current_key,
+                       float* __restrict__ scores, int past, int heads, int nbuf, int tmem_cols, int* status) {
+    extern __shared__ __align__(1024) uint8_t usm[];
+    __shared__ uint64_t k_full[2], a_ready[4], mma_done;
+    __shared__ uint32_t tmem_slot;
+    using namespace inf;
+    uint8_t* s_lo = usm;                                 // lo terms of the tile being multiplied
+    uint8_t* s_key = usm + TU_KEY_TILE;                  // nbuf key tiles (raw, then hi in place)
+    uint8_t* s_q = s_key + (size_t)nbuf * TU_KEY_TILE;    // four blocks of [q_hi: heads rows; q_lo: heads rows][128 bytes]
+    float* s_w = reinterpret_cast<float*>(s_q + (size_t)2 * heads * TU_DIM * 4);  // [heads]
+    const int b = blockIdx.y, n = past + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tiles = (n + TU_TOKENS - 1) / TU_TOKENS;
+    if (tid == 0) {
+        mbar_init(&k_full[0], 1);
+        mbar_init(&k_full[1], 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&a_ready[i], TU_WORKERS);
+        mbar_init(&mma_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(&tmem_slot, (uint32_t)tmem_cols);
+        tmem_relinquish();
+    }
+    inf_pdl_wait();
+    inf_pdl_release();
+    __syncthreads();
+    auto load_tile = [&](int tile, int buf) {  // one thread; rows past the end of the tensor arrive as zeros
+        mbar_arrive_expect_tx(&k_full[buf], TU_KEY_TILE);
+        const int row = b * past + tile * TU_TOKENS;
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk)
+            tma_load_2d(s_key + buf * TU_KEY_TILE + blk * TU_BLOCK, &tm_keys, blk * 64, row, &k_full[buf]);
+    };
+    if (tid == 0)
+        for (int i = 0; i < nbuf; ++i)
+            if ((int)(blockIdx.x + i * gridDim.x) < tiles) load_tile(blockIdx.x + i * gridDim.x, i);
+    if (warp < 4) {
+        // q: hi and lo terms in the same swizzled K-major layout, 2 x heads rows per 128-byte block
+        for (int i = tid; i < heads * (TU_DIM / 4); i += TU_WORKERS) {
+            const int h = i >> 5, qc = i & 31;
+            const float4 v = reinterpret_cast<const float4*>(q + ((size_t)b * heads + h) * TU_DIM)[qc];
+            uint4 hi;
+            float4 lo;
+            tf32_split(v, hi, lo);
+            uint8_t* blk = s_q + (size_t)(qc >> 3) * 2 * heads * 128;
+            *reinterpret_cast<uint4*>(blk + h * 128 + (((qc & 7) ^ (h & 7)) << 4)) = hi;
+            *reinterpret_cast<float4*>(blk + (heads + h) * 128 + (((qc & 7) ^ ((heads + h) & 7)) << 4)) = lo;
+        }
+        for (int i = tid; i < heads; i += TU_WORKERS) s_w[i] = weights[(size_t)b * heads + i];
+        fence_proxy_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = tmem_slot;
+    const float scale = rsqrtf((float)TU_DIM);
+    if (warp < 4) {
+        // this thread's share of every block: 16-byte chunk c8 of rows rbase, rbase + 16, ...
+        const int c8 = tid & 7, rbase = tid >> 3;
+        int i = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++i) {
+            const int buf = nbuf == 2 ? (i & 1) : 0;
+            uint8_t* cur = s_key + buf * TU_KEY_TILE;
+            int ok = mbar_wait(&k_full[buf], (uint32_t)((nbuf == 2 ? (i >> 1) : i) & 1));
+            const int cur_row = past - tile * TU_TOKENS;  // where the current key goes, if it is in this tile
+#pragma unroll 1
+            for (int blk = 0; ok && blk < 4; ++blk) {
+                float4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = rbase + 16 * j;
+                    v[j] = *reinterpret_cast<const float4*>(cur + blk * TU_BLOCK + r * 128 + ((c8 ^ (r & 7)) << 4));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = rbase + 16 * j;
+                    if (r == cur_row) v[j] = reinterpret_cast<const float4*>(current_key + (size_t)b * TU_DIM)[blk * 8 + c8];
+                    uint4 hi;
+                    float4 lo;
+                    tf32_split(v[j], hi, lo);
+                    const uint32_t off = (uint32_t)(blk * TU_BLOCK + r * 128 + ((c8 ^ (r & 7)) << 4));
+                    *reinterpret_cast<uint4*>(cur + off) = hi;
+                    *reinterpret_cast<float4*>(s_lo + off) = lo;
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&a_ready[blk]);
+            }
+            if (ok) ok = mbar_wait(&mma_done, (uint32_t)(i & 1));
+            if (!ok) {
+                atomicOr(status, INF_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+            tc_fence_after();
+            if (tid == 0 && tile + nbuf * (int)gridDim.x < tiles) load_tile(tile + nbuf * gridDim.x, buf);  // the buffer is free
+            __syncwarp();
+            float sum = 0.f;
+            const uint32_t trow = tbase + ((uint32_t)(warp * 32) << 16);
+            for (int h0 = 0; h0 < heads; h0 += 16) {
+                uint32_t d[16], e[16];
+                tmem_ld16(trow + (uint32_t)h0, d);            // hi x q_hi + lo x q_hi
+                tmem_ld16(trow + (uint32_t)(heads + h0), e);  // hi x q_lo
+                tc_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 16; ++x)
+                    sum = fmaf(s_w[h0 + x], fmaxf((__uint_as_float(d[x]) + __uint_as_float(e[x])) * scale, 0.f), sum);
+            }
+            tc_fence_before();  // the row is in registers before the next hand-over lets the accumulator be overwritten
+            const int tok = tile * TU_TOKENS + tid;
+            if (tok < n) scores[(size_t)b * n + tok] = sum;
+        }
+    } else if (lane == 0) {
+        const uint32_t idesc_wide = umma_idesc_tf32(TU_TOKENS, (uint32_t)(2 * heads));
+        const uint32_t idesc_narrow = umma_idesc_tf32(TU_TOKENS, (uint32_t)heads);
+        const uint32_t lo_addr = smem_u32(s_lo), q_addr = smem_u32(s_q);
+        int i = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++i) {
+            const uint32_t hi_addr = smem_u32(s_key + (nbuf == 2 ? (i & 1) : 0) * TU_KEY_TILE);
+            int ok = 1;
+            for (int blk = 0; ok && blk < 4; ++blk) {
+                ok = mbar_wait(&a_ready[blk], (uint32_t)(i & 1));
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {  // eight tf32 values = 32 bytes per step, four steps per block
+                    const uint32_t a_off = (uint32_t)(blk * TU_BLOCK + ks * 32);
+                    const uint64_t a_hi = umma_smem_desc(hi_addr + a_off, 16, 1024, UMMA_SW128);
+                    const uint64_t a_lo = umma_smem_desc(lo_addr + a_off, 16, 1024, UMMA_SW128);
+                    const uint64_t b_q = umma_smem_desc(q_addr + (uint32_t)(blk * 2 * heads * 128 + ks * 32), 16, 1024, UMMA_SW128);
+                    umma_ss_tf32(tbase, a_hi, b_q, idesc_wide, (blk | ks) != 0);  // [hi.q_hi | hi.q_lo]
+                    umma_ss_tf32(tbase, a_lo, b_q, idesc_narrow, 1u);             // + lo.q_hi on the first half
+                }
+            }
+            if (!ok) {
+                atomicOr(status, INF_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+            tc_commit(&mma_done);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tbase, (uint32_t)tmem_cols);
 }
 
 // ---------------------------------------------------------------------------------------------- top-k
@@ -480,6 +669,36 @@ extern "C" int32_t inf_dsa_scores(inf_ctx* ctx, const float* q, const float* wei
         return inf_fail(ctx, INF_E_SHAPE, "dsa_scores: sizes must be positive");
     if (head_dim % 4 != 0) return inf_fail(ctx, INF_E_SHAPE, "dsa_scores: head_dim %d must be a multiple of 4", head_dim);
     if (batch > 65535) return inf_fail(ctx, INF_E_SHAPE, "dsa_scores: batch %d exceeds the launch grid", batch);
+    if (head_dim == TU_DIM && heads % 16 == 0 && heads <= 128 && past_tokens > 0 &&
+        (reinterpret_cast<uintptr_t>(past_keys) & 15u) == 0) {
+        const size_t q_bytes = (2 * (size_t)heads * TU_DIM + heads) * sizeof(float);  // hi and lo tiles, the weights
+        const size_t smem_limit = 227 * 1024 - 2048;  // static shared memory and the 1 KB alignment of the tiles
+        const int nbuf = (3 * (size_t)TU_KEY_TILE + q_bytes <= smem_limit) ? 2 : 1;
+        const size_t smem_umma = (size_t)(1 + nbuf) * TU_KEY_TILE + q_bytes;
+        if (smem_umma <= smem_limit) {
+            if (ctx->dsa_scores_smem < smem_umma) {
+                INF_CUDA(ctx, cudaFuncSetAttribute(dsa_scores_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_umma));
+                ctx->dsa_scores_smem = smem_umma;
+            }
+            // the f32 key rows as 16-bit pairs: 256 per row, boxes of 64 (one 128-byte swizzle line) x 128 rows
+            CUtensorMap tm_keys;
+            uint64_t dims[2] = {2 * (uint64_t)TU_DIM, (uint64_t)batch * past_tokens};
+            uint64_t strides[1] = {(uint64_t)TU_DIM * sizeof(float)};
+            uint32_t box[2] = {64, (uint32_t)TU_TOKENS};
+            int rc = inf_make_tmap(ctx, past_keys, 2, dims, strides, box, &tm_keys);
+            if (rc != INF_OK) return rc;
+            int tmem_cols = 32;
+            while (tmem_cols < 2 * heads) tmem_cols *= 2;
+            const int tiles = (past_tokens + 1 + TU_TOKENS - 1) / TU_TOKENS;
+            // one CTA per SM; every CTA takes the same number of tiles where that is possible
+            const int per_cta = (tiles * batch + ctx->sm_count - 1) / ctx->sm_count;
+            dim3 grid((tiles + per_cta - 1) / per_cta, batch);
+            inf_prof_scope prof(ctx, "dsa_scores_kernel");
+            INF_CUDA(ctx, inf_launch_pdl(dsa_scores_umma_kernel, grid, dim3(TU_THREADS), smem_umma, ctx->stream, tm_keys, q,
+                                         weights, current_key, scores, past_tokens, heads, nbuf, tmem_cols, ctx->status));
+            return INF_OK;
+        }
+    }
     const size_t smem = ((size_t)SC_TOKENS * (head_dim + 4) + (size_t)heads * head_dim + heads + SC_HG * SC_TOKENS) * sizeof(float);
     if (smem > 200 * 1024) return INF_UNSUPPORTED;
     if (smem > 48 * 1024 && !(ctx->func_attr_done & 4096u)) {

@@ -36,6 +36,12 @@ def test_dsa_scores_match_oracle(be, B, past, H, D):
     be.device_flush()
     want = orc.dsa_scores(q, w, pk, ck)
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
+    # against exact arithmetic the kernel must be as good as an fp32 sum (the tensor-core form splits every input
+    # into two tf32 terms; a plain tf32 product would miss this bound by two orders of magnitude)
+    keys = np.concatenate([pk, ck[:, None, :]], axis=1).astype(np.float64)
+    dots = np.einsum("bhd,btd->bth", q.astype(np.float64), keys) / math.sqrt(D)
+    exact = np.einsum("bth,bh->bt", np.maximum(dots, 0.0), w.astype(np.float64))
+    np.testing.assert_allclose(got.cpu().numpy(), exact, rtol=2e-5, atol=2e-5)
 
 
 @pytest.mark.parametrize("B,n,k", [(1, 32768, 2048), (2, 5000, 2048), (1, 100, 2048), (3, 2048, 2048), (1, 4097, 7), (1, 1, 1),
