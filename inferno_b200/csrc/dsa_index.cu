@@ -129,11 +129,13 @@ dsa_scores_kernel(const float* __restrict__ q, const float* __restrict__ weights
 // tile is 32 MMAs here.  fp32 inputs are split into two tf32 terms (hi = x with the 13 low mantissa bits cleared,
 // lo = x - hi, exact) and each product is taken as hi*hi + hi*lo + lo*hi with fp32 accumulation, which keeps the error
 // of a dot product near 2^-20 of its magnitude: as good as the fp32 reference sum, whose own rounding depends on the
-// order of addition.
+// order of addition.  The tensor core reads only the 19 leading bits of a tf32 operand, so the key tile as it landed
+// is its own hi term and only the lo tile is written (q's hi term is stored masked); the accuracy test against exact
+// arithmetic would fail by two orders of magnitude if an operand were rounded instead.
 //
 // A CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Key tiles arrive by TMA (the f32 rows described to the
 // copy engine as twice as many 16-bit values; K-major, 128-byte swizzle: four blocks of 32 dims).  Warps 0-3 split a
-// landed tile block by block, in place into the hi tile and into a lo tile, and hand each block to warp 4 as soon as
+// landed tile block by block (the lo terms into a tile of their own), and hand each block to warp 4 as soon as
 // it is done; warp 4 issues, per 8 dims, hi x [q_hi; q_lo] (N = 2 x heads) and lo x q_hi (N = heads) into a
 // [128 tokens x 2 heads] fp32 accumulator in tensor memory.  The same four warps then read their token's row back, add
 // the two halves, apply scale, relu and the head weights, and store the score.  With two key buffers the next tile's
@@ -174,7 +176,7 @@ dsa_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_keys, const float*
     __shared__ uint32_t tmem_slot;
     using namespace inf;
     uint8_t* s_lo = usm;                                 // lo terms of the tile being multiplied
-    uint8_t* s_key = usm + TU_KEY_TILE;                  // nbuf key tiles (raw, then hi in place)
+    uint8_t* s_key = usm + TU_KEY_TILE;                  // nbuf key tiles as they landed
     uint8_t* s_q = s_key + (size_t)nbuf * TU_KEY_TILE;    // four blocks of [q_hi: heads rows; q_lo: heads rows][128 bytes]
     float* s_w = reinterpret_cast<float*>(s_q + (size_t)2 * heads * TU_DIM * 4);  // [heads]
     const int b = blockIdx.y, n = past + 1;
@@ -244,13 +246,15 @@ dsa_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_keys, const float*
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int r = rbase + 16 * j;
-                    if (r == cur_row) v[j] = reinterpret_cast<const float4*>(current_key + (size_t)b * TU_DIM)[blk * 8 + c8];
+                    const uint32_t off = (uint32_t)(blk * TU_BLOCK + r * 128 + ((c8 ^ (r & 7)) << 4));
+                    if (r == cur_row) {
+                        v[j] = reinterpret_cast<const float4*>(current_key + (size_t)b * TU_DIM)[blk * 8 + c8];
+                        *reinterpret_cast<float4*>(cur + off) = v[j];
+                    }
                     uint4 hi;
                     float4 lo;
                     tf32_split(v[j], hi, lo);
-                    const uint32_t off = (uint32_t)(blk * TU_BLOCK + r * 128 + ((c8 ^ (r & 7)) << 4));
-                    *reinterpret_cast<uint4*>(cur + off) = hi;
-                    *reinterpret_cast<float4*>(s_lo + off) = lo;
+                    *reinterpret_cast<float4*>(s_lo + off) = lo;  // the raw tile serves as hi: see the kernel's header
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&a_ready[blk]);
