@@ -163,15 +163,25 @@ mla_postprocess_append_kernel(const float* __restrict__ in, const float* __restr
     int b = (int)(row / tokens), token = (int)(row % tokens);
     const float* x = in + row * (L + R);
     __shared__ float warp_sums[4];
-    float ss = 0.0f;
-    for (int d = tid; d < L; d += 128) ss += x[d] * x[d];
+    // Everything that does not depend on another load is requested first (the sequence length, up to four latent
+    // values and weights per thread, the rope pair), and the page lookup, which does, runs under the reduction: the
+    // kernel is one token's worth of work and its time is the length of its chain of loads.
+    constexpr int KEEP = 4;
+    const bool in_regs = L <= KEEP * 128;
+    const int len_b = lens[b];
+    float xv[KEEP], wv[KEEP];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((tid & 31) == 0) warp_sums[tid >> 5] = ss;
-    __syncthreads();
-    float total = warp_sums[0] + warp_sums[1] + warp_sums[2] + warp_sums[3];
-    float norm_scale = rsqrtf(total / (float)L + eps);
-    int position = lens[b] + token;
+    for (int k = 0; k < KEEP; ++k) {
+        const int d = tid + 128 * k;
+        xv[k] = (in_regs && d < L) ? x[d] : 0.0f;
+        wv[k] = (in_regs && d < L) ? w[d] : 0.0f;
+    }
+    float rope_value = 0.0f, rope_partner = 0.0f;
+    if (tid < R) {
+        rope_value = x[L + tid];
+        rope_partner = x[L + ((tid & 1) == 0 ? tid + 1 : tid - 1)];
+    }
+    int position = len_b + token;
     int slot = position / page_size;
     __half* dst = nullptr;
     if (position < 0 || slot >= max_pages) {
@@ -184,15 +194,40 @@ mla_postprocess_append_kernel(const float* __restrict__ in, const float* __restr
             dst = pool + ((long long)page * page_size + position % page_size) * (L + R);
         }
     }
-    for (int d = tid; d < L; d += 128) {
-        float y = x[d] * norm_scale * w[d];
-        if (latent_out) latent_out[row * L + d] = y;
-        if (dst) dst[d] = __float2half_rn(y);
+    float ss = 0.0f;
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) ss += xv[k] * xv[k];  // same order as the loop below: d = tid, tid + 128, ...
+    } else {
+        for (int d = tid; d < L; d += 128) ss += x[d] * x[d];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) warp_sums[tid >> 5] = ss;
+    __syncthreads();
+    float total = warp_sums[0] + warp_sums[1] + warp_sums[2] + warp_sums[3];
+    float norm_scale = rsqrtf(total / (float)L + eps);
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int d = tid + 128 * k;
+            if (d < L) {
+                float y = xv[k] * norm_scale * wv[k];
+                if (latent_out) latent_out[row * L + d] = y;
+                if (dst) dst[d] = __float2half_rn(y);
+            }
+        }
+    } else {
+        for (int d = tid; d < L; d += 128) {
+            float y = x[d] * norm_scale * w[d];
+            if (latent_out) latent_out[row * L + d] = y;
+            if (dst) dst[d] = __float2half_rn(y);
+        }
     }
     for (int d = tid; d < R; d += 128) {
         bool even = (d & 1) == 0;
         float angle = (float)position * f.v[d >> 1];
-        float value = x[L + d], partner = x[L + (even ? d + 1 : d - 1)];
+        float value = d == tid ? rope_value : x[L + d], partner = d == tid ? rope_partner : x[L + (even ? d + 1 : d - 1)];
         float rotated = even ? -partner : partner;
         float y = value * cosf(angle) + rotated * sinf(angle);
         if (rope_out) rope_out[row * R + d] = y;
