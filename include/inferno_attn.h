@@ -279,6 +279,23 @@ int32_t inf_dsa_scores(inf_ctx* ctx, const float* q, const float* weights, const
 int32_t inf_dsa_topk(inf_ctx* ctx, const float* scores, int32_t batch, int32_t key_tokens, int32_t top_k,
                      uint32_t* selected, int32_t selected_stride);
 
+/* DSA indexer preparation (trait methods dsa_index_key_device, backend.rs:2061, and the first half of
+ * dsa_decode_topk_device, backend.rs:2074; CPU semantics crates/model/src/indexer.rs:174-203, :397-428, :483-543;
+ * Metal kernels dsa_kernels.metal:23-135).  Device pointers, f32.
+ *   inf_dsa_index_key: raw_key [batch][tokens][head_dim] -> LayerNorm (weight, bias [head_dim], eps; the reference
+ *     uses 1e-6) -> rotary encoding of the first rope_dim values at position position_offset + token with
+ *     freq(pair) = 1 / theta^(2 pair / rope_dim): interleaved pairs (2p, 2p+1) in, halves out (p and rope_dim/2 + p).
+ *   inf_dsa_query_weights: weights_out [batch][heads] = hidden_states [batch][hidden_size] . weights_proj
+ *     [hidden_size][heads] / sqrt(heads); q_out [batch][heads][head_dim] = q_raw under the same rotation at
+ *     position_offset.  Their outputs feed inf_dsa_scores.
+ * An odd rope_dim or one larger than head_dim is INF_E_CONFIG with the reference's message. */
+int32_t inf_dsa_index_key(inf_ctx* ctx, const float* raw_key, const float* weight, const float* bias, int32_t batch,
+                          int32_t tokens, int32_t head_dim, int32_t rope_dim, int32_t position_offset, float theta,
+                          float eps, float* out);
+int32_t inf_dsa_query_weights(inf_ctx* ctx, const float* hidden_states, const float* q_raw, const float* weights_proj,
+                              int32_t batch, int32_t hidden_size, int32_t heads, int32_t head_dim, int32_t rope_dim,
+                              int32_t position_offset, float theta, float* q_out, float* weights_out);
+
 /* FP8 E4M3FN KV storage of the Laguna safetensors cache (crates/backend/src/metal/kernels/
  * fp8_attention_kernels.metal:11-54 codec, :227-263 append): stored byte = encode(x / scale), read value =
  * decode(byte) * scale, one scale per tensor.  Encode saturates at +-448, maps NaN and 0 to 0x00, rounds ties to

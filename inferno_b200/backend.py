@@ -345,6 +345,39 @@ class CudaBackend:
         ok = self._check(self._lib.inf_dsa_topk(self._ctx, _ptr(scores), B, n, top_k, _ptr(out), out.shape[1]))
         return out if ok else None
 
+    def dsa_index_key_device(self, raw_key, weight, bias, rope_dim: int, position_offset: int, theta: float,
+                             eps: float = 1e-6):
+        """trait Backend::dsa_index_key_device (backend.rs:2061): raw_key f32 [B,T,D] -> LayerNorm(weight, bias) ->
+        interleaved-pair rotary encoding of the first rope_dim values (indexer.rs:174-203); f32 [B,T,D]."""
+        B, T, D = raw_key.shape
+        out = torch.empty_like(raw_key)
+        self._check(self._lib.inf_dsa_index_key(self._ctx, _ptr(raw_key), _ptr(weight), _ptr(bias), B, T, D, rope_dim,
+                                                position_offset, theta, eps, _ptr(out)))
+        return out
+
+    def dsa_query_weights(self, hidden_states, q_raw, weights_proj, heads: int, head_dim: int, rope_dim: int,
+                          position_offset: int, theta: float):
+        """First half of dsa_decode_topk_device (dsa_kernels.metal:83-135): hidden_states f32 [B,hidden], q_raw f32
+        [B,heads*head_dim], weights_proj f32 [hidden,heads] -> (q f32 [B,heads,head_dim] rotated, weights f32 [B,heads])."""
+        B, hidden = hidden_states.shape
+        q = torch.empty((B, heads, head_dim), dtype=torch.float32, device=self.device)
+        w = torch.empty((B, heads), dtype=torch.float32, device=self.device)
+        self._check(self._lib.inf_dsa_query_weights(self._ctx, _ptr(hidden_states), _ptr(q_raw), _ptr(weights_proj), B,
+                                                    hidden, heads, head_dim, rope_dim, position_offset, theta, _ptr(q),
+                                                    _ptr(w)))
+        return q, w
+
+    def dsa_decode_topk_device(self, hidden_states, q_raw, past_index_keys, current_index_key, weights_proj, heads: int,
+                               head_dim: int, rope_dim: int, position_offset: int, theta: float, top_k: int):
+        """trait Backend::dsa_decode_topk_device (backend.rs:2074): query rotation and head weights, index scores over
+        the past keys and the current one, top-k.  hidden_states [B,1,hidden], q_raw [B,1,heads*head_dim],
+        past_index_keys [B,past,head_dim], current_index_key [B,1,head_dim]; int32 ids [B, top_k] on the device."""
+        B = hidden_states.shape[0]
+        q, w = self.dsa_query_weights(hidden_states.reshape(B, -1), q_raw.reshape(B, -1), weights_proj, heads, head_dim,
+                                      rope_dim, position_offset, theta)
+        scores = self.dsa_scores(q, w, past_index_keys, current_index_key.reshape(B, head_dim))
+        return self.dsa_topk(scores, top_k)
+
     def fp8_e4m3fn_encode(self, x, scale: float):
         """FP8 E4M3FN encode of x / scale (fp8_attention_kernels.metal:29-54): f32 -> uint8, same shape."""
         out = torch.empty(x.shape, dtype=torch.uint8, device=self.device)

@@ -2,6 +2,7 @@
 // inf_mla_decode_absorbed_selected.  Reference: dsa_scores_f32_kernel and dsa_topk_block_sort / dsa_topk_merge
 // (crates/backend/src/metal/kernels/dsa_kernels.metal:137-176, 178-393).
 #include <cuda_fp16.h>
+#include <math.h>
 #include <stdint.h>
 
 #include "common.cuh"
@@ -314,6 +315,111 @@ dsa_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_keys, const float*
     tc_fence_before();
     __syncthreads();
     if (warp == 4) tmem_dealloc(tbase, (uint32_t)tmem_cols);
+}
+
+// ---------------------------------------------------------------------------------------------- preparation
+// The two small operators in front of the scores: the index key of new tokens (LayerNorm over the key, then rotary
+// position encoding of the first rope_dim values, interleaved pairs in, halves out) and, per decode step, the query
+// heads under the same rotation plus the per-head weights hidden . weights_proj / sqrt(heads).  Semantics follow the
+// reference's CPU indexer (crates/model/src/indexer.rs:174-203 key, :397-428 LayerNorm, :483-514 rotation, :516-543
+// weights), which rotates out of a temporary; its Metal kernel for the key (dsa_kernels.metal:23-81) rotates in
+// place and reads values it has already replaced once rope_dim >= 4, so it is not the model followed here.
+struct DsaFreq {
+    float v[64];  // 1 / theta^(pair / pair_count), computed on the host
+};
+
+__device__ __forceinline__ void dsa_rotate(float x0, float x1, float angle, float& out0, float& out1) {
+    const float c = cosf(angle), s = sinf(angle);
+    out0 = x0 * c - x1 * s;
+    out1 = x1 * c + x0 * s;
+}
+
+// one warp per key row; head_dim <= 1024
+__global__ void __launch_bounds__(128)
+dsa_index_key_kernel(const float* __restrict__ raw, const float* __restrict__ weight, const float* __restrict__ bias,
+                     float* __restrict__ out, long long rows, int tokens, int head_dim, int rope_dim, int position_offset,
+                     float eps, DsaFreq f) {
+    extern __shared__ float s_rows[];  // [4 warps][head_dim] normalised rows
+    inf_pdl_wait();
+    inf_pdl_release();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    const float* x = raw + row * head_dim;
+    float* y = s_rows + warp * head_dim;
+    float sum = 0.f;
+    for (int d = lane; d < head_dim; d += 32) sum += x[d];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / (float)head_dim;
+    float var = 0.f;
+    for (int d = lane; d < head_dim; d += 32) {
+        const float c = x[d] - mean;
+        var += c * c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+    const float inv_std = 1.0f / sqrtf(var / (float)head_dim + eps);
+    for (int d = lane; d < head_dim; d += 32) y[d] = (x[d] - mean) * inv_std * weight[d] + bias[d];
+    __syncwarp();
+    const int pairs = rope_dim / 2;
+    const int position = position_offset + (int)(row % tokens);
+    float* o = out + row * head_dim;
+    for (int p = lane; p < pairs; p += 32) {
+        float a, b;
+        dsa_rotate(y[2 * p], y[2 * p + 1], (float)position * f.v[p], a, b);
+        o[p] = a;
+        o[pairs + p] = b;
+    }
+    for (int d = rope_dim + lane; d < head_dim; d += 32) o[d] = y[d];
+}
+
+// one CTA of 256 threads per sequence: the weights (eight warps share the hidden dimension, lane = head within a
+// group of 32), then the rotated query heads
+__global__ void __launch_bounds__(256)
+dsa_query_weights_kernel(const float* __restrict__ hidden, const float* __restrict__ q_raw, const float* __restrict__ proj,
+                         float* __restrict__ q_out, float* __restrict__ w_out, int hidden_size, int heads, int head_dim,
+                         int rope_dim, int position, DsaFreq f) {
+    __shared__ float part[8][32];
+    inf_pdl_wait();
+    inf_pdl_release();
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* h = hidden + (size_t)b * hidden_size;
+    const int per = (hidden_size + 7) / 8, d0 = warp * per, d1 = min(hidden_size, d0 + per);
+    for (int h0 = 0; h0 < heads; h0 += 32) {
+        const int head = h0 + lane;
+        float acc = 0.f;
+        if (head < heads)
+            for (int d = d0; d < d1; ++d) acc = fmaf(h[d], proj[(size_t)d * heads + head], acc);
+        part[warp][lane] = acc;
+        __syncthreads();
+        if (warp == 0 && head < heads) {
+            float total = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) total += part[w][lane];
+            w_out[(size_t)b * heads + head] = total * (1.0f / sqrtf((float)heads));
+        }
+        __syncthreads();
+    }
+    const int pairs = rope_dim / 2;
+    const float* q = q_raw + (size_t)b * heads * head_dim;
+    float* o = q_out + (size_t)b * heads * head_dim;
+    for (int i = tid; i < heads * head_dim; i += 256) {
+        const int head = i / head_dim, d = i % head_dim;
+        if (d >= rope_dim) {
+            o[i] = q[i];
+        } else if (d < pairs) {  // this thread produces both outputs of pair d
+            float a, c;
+            dsa_rotate(q[head * head_dim + 2 * d], q[head * head_dim + 2 * d + 1], (float)position * f.v[d], a, c);
+            o[head * head_dim + d] = a;
+            o[head * head_dim + pairs + d] = c;
+        }
+    }
+}
+
+void dsa_host_freq(float theta, int rope_dim, DsaFreq* f) {
+    const int pairs = rope_dim / 2;
+    for (int p = 0; p < 64; ++p) f->v[p] = p < pairs ? 1.0f / powf(theta, (float)(2 * p) / (float)rope_dim) : 0.0f;
 }
 
 // ---------------------------------------------------------------------------------------------- top-k
@@ -738,5 +844,47 @@ extern "C" int32_t inf_dsa_topk(inf_ctx* ctx, const float* scores, int32_t batch
         INF_CUDA(ctx, inf_launch_pdl(dsa_topk_kernel, dim3(batch), dim3(TK_THREADS), smem, ctx->stream, scores, selected,
                                      key_tokens, top_k, selected_stride, in_smem));
     }
+    return INF_OK;
+}
+
+extern "C" int32_t inf_dsa_index_key(inf_ctx* ctx, const float* raw_key, const float* weight, const float* bias,
+                                     int32_t batch, int32_t tokens, int32_t head_dim, int32_t rope_dim,
+                                     int32_t position_offset, float theta, float eps, float* out) {
+    INF_CHECK_CTX(ctx);
+    if (!raw_key || !weight || !bias || !out) return inf_fail(ctx, INF_E_ARG, "dsa_index_key: null pointer");
+    if (batch <= 0 || tokens <= 0 || head_dim <= 0 || head_dim > 1024)
+        return inf_fail(ctx, INF_E_SHAPE, "dsa_index_key: sizes must be positive and head_dim at most 1024");
+    if (rope_dim % 2 != 0) return inf_fail(ctx, INF_E_CONFIG, "DSA indexer RoPE dim must be even");
+    if (rope_dim < 0 || rope_dim > head_dim)
+        return inf_fail(ctx, INF_E_CONFIG, "DSA indexer RoPE dim %d exceeds head dim %d", rope_dim, head_dim);
+    if (rope_dim > 128) return INF_UNSUPPORTED;
+    if (position_offset < 0 || !(theta > 0.f)) return inf_fail(ctx, INF_E_CONFIG, "dsa_index_key: bad position or theta");
+    DsaFreq f;
+    dsa_host_freq(theta, rope_dim, &f);
+    const long long rows = (long long)batch * tokens;
+    INF_CUDA(ctx, inf_launch_pdl(dsa_index_key_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128),
+                                 (size_t)4 * head_dim * sizeof(float), ctx->stream, raw_key, weight, bias, out, rows, tokens,
+                                 head_dim, rope_dim, position_offset, eps, f));
+    return INF_OK;
+}
+
+extern "C" int32_t inf_dsa_query_weights(inf_ctx* ctx, const float* hidden_states, const float* q_raw,
+                                         const float* weights_proj, int32_t batch, int32_t hidden_size, int32_t heads,
+                                         int32_t head_dim, int32_t rope_dim, int32_t position_offset, float theta,
+                                         float* q_out, float* weights_out) {
+    INF_CHECK_CTX(ctx);
+    if (!hidden_states || !q_raw || !weights_proj || !q_out || !weights_out)
+        return inf_fail(ctx, INF_E_ARG, "dsa_query_weights: null pointer");
+    if (batch <= 0 || hidden_size <= 0 || heads <= 0 || head_dim <= 0)
+        return inf_fail(ctx, INF_E_SHAPE, "dsa_query_weights: sizes must be positive");
+    if (rope_dim % 2 != 0) return inf_fail(ctx, INF_E_CONFIG, "DSA indexer RoPE dim must be even");
+    if (rope_dim < 0 || rope_dim > head_dim)
+        return inf_fail(ctx, INF_E_CONFIG, "DSA indexer RoPE dim %d exceeds head dim %d", rope_dim, head_dim);
+    if (rope_dim > 128) return INF_UNSUPPORTED;
+    if (position_offset < 0 || !(theta > 0.f)) return inf_fail(ctx, INF_E_CONFIG, "dsa_query_weights: bad position or theta");
+    DsaFreq f;
+    dsa_host_freq(theta, rope_dim, &f);
+    INF_CUDA(ctx, inf_launch_pdl(dsa_query_weights_kernel, dim3(batch), dim3(256), 0, ctx->stream, hidden_states, q_raw,
+                                 weights_proj, q_out, weights_out, hidden_size, heads, head_dim, rope_dim, position_offset, f));
     return INF_OK;
 }

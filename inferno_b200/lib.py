@@ -96,6 +96,8 @@ SIGNATURES = {
                                               _I]),
     "inf_dsa_scores": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "inf_dsa_topk": (_I, [_P, _P, _I, _I, _I, _P, _I]),
+    "inf_dsa_index_key": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P]),
+    "inf_dsa_query_weights": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P]),
     "inf_fp8_e4m3fn_encode": (_I, [_P, _P, _L, _F, _P]),
     "inf_fp8_e4m3fn_decode": (_I, [_P, _P, _L, _F, _P]),
     "inf_kv_pool_from_fp8": (_I, [_P, _P, _P, _F, _F, C.POINTER(KvPool)]),

@@ -350,3 +350,51 @@ def fp8_e4m3fn_encode(x):
     out[ok] = res[ok].astype(np.uint8)
     return out
 
+
+def dsa_rotate_interleaved(values, rope_dim, position, theta):
+    """rotate_interleaved_pair_range (crates/model/src/indexer.rs:483-514): pairs (2p, 2p+1) of the first rope_dim
+    values rotated by position * theta^(-2p/rope_dim), written as halves (p, rope_dim/2 + p); f32 arithmetic."""
+    out = _f32(values).copy()
+    pairs = rope_dim // 2
+    p = np.arange(pairs)
+    freq = (np.float32(1.0) / np.power(np.float32(theta), (2 * p).astype(np.float32) / np.float32(rope_dim))).astype(np.float32)
+    angle = (np.float32(position) * freq).astype(np.float32)
+    c, s = np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+    x0, x1 = out[..., 0:rope_dim:2].copy(), out[..., 1:rope_dim:2].copy()
+    out[..., :pairs] = x0 * c - x1 * s
+    out[..., pairs:rope_dim] = x1 * c + x0 * s
+    return out
+
+
+def dsa_index_key(raw_key, weight, bias, rope_dim, position_offset, theta, eps=1e-6):
+    """DsaIndexer::key_f32 after the projection (indexer.rs:190-203): layer_norm_last_dim (:397-428) then
+    apply_interleaved_rope_to_key (:458-481).  raw_key [B,T,D] -> f32 [B,T,D]."""
+    x = _f32(raw_key)
+    mean = (x.sum(axis=-1, dtype=np.float32) / np.float32(x.shape[-1]))[..., None]
+    var = (np.square(x - mean).sum(axis=-1, dtype=np.float32) / np.float32(x.shape[-1]))[..., None]
+    inv_std = np.float32(1.0) / np.sqrt(var + np.float32(eps))
+    y = ((x - mean) * inv_std * _f32(weight) + _f32(bias)).astype(np.float32)
+    out = np.empty_like(y)
+    for t in range(y.shape[1]):
+        out[:, t] = dsa_rotate_interleaved(y[:, t], rope_dim, position_offset + t, theta)
+    return out
+
+
+def dsa_query_weights(hidden_states, q_raw, weights_proj, heads, head_dim, rope_dim, position_offset, theta):
+    """indexer_weights (indexer.rs:516-543) and apply_interleaved_rope_to_query (:430-456): hidden_states [B,hidden],
+    q_raw [B,heads*head_dim], weights_proj [hidden,heads] -> (q [B,heads,head_dim], weights [B,heads])."""
+    h, proj = _f32(hidden_states), _f32(weights_proj)
+    scale = np.float32(1.0) / np.sqrt(np.float32(heads))
+    w = ((h.astype(np.float64) @ proj.astype(np.float64)).astype(np.float32) * scale).astype(np.float32)
+    q = _f32(q_raw).reshape(h.shape[0], heads, head_dim)
+    return dsa_rotate_interleaved(q, rope_dim, position_offset, theta), w
+
+
+def dsa_decode_topk(hidden_states, q_raw, past_keys, current_key, weights_proj, heads, head_dim, rope_dim,
+                    position_offset, theta, top_k):
+    """Backend::dsa_decode_topk_device (crates/backend/src/backend.rs:2074) as one chain on the CPU."""
+    B = np.asarray(hidden_states).shape[0]
+    q, w = dsa_query_weights(np.reshape(hidden_states, (B, -1)), np.reshape(q_raw, (B, -1)), weights_proj, heads,
+                             head_dim, rope_dim, position_offset, theta)
+    return dsa_topk(dsa_scores(q, w, past_keys, np.reshape(current_key, (B, head_dim))), top_k)
+

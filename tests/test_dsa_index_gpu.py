@@ -112,3 +112,53 @@ def test_sparse_decode_step_end_to_end(be):
     from tests.test_mla_selected_gpu import oracle_selected
     want = oracle_selected(q, pool_np, pt, [ids.cpu().numpy()[0]], scale)
     assert_close(got.cpu().numpy(), want, "sparse decode step")
+
+
+def test_index_key_layer_norm_and_rope(be):
+    B, T, D, rope, pos, theta = 2, 5, 128, 64, 1000, 1.0e4
+    seed = SEED0 + 1300
+    raw = orc.fill_normal((B, T, D), seed, 2.0, False) + np.float32(0.3)
+    wt = orc.fill_normal((D,), seed + 1, 1.0, False)
+    bs = orc.fill_normal((D,), seed + 2, 0.1, False)
+    got = be.dsa_index_key_device(dev(be, raw), dev(be, wt), dev(be, bs), rope, pos, theta)
+    be.device_flush()
+    np.testing.assert_allclose(got.cpu().numpy(), orc.dsa_index_key(raw, wt, bs, rope, pos, theta), rtol=2e-5, atol=2e-5)
+    # no rotation at all, and a rotation of the whole (short) row
+    got = be.dsa_index_key_device(dev(be, raw), dev(be, wt), dev(be, bs), 0, pos, theta)
+    be.device_flush()
+    np.testing.assert_allclose(got.cpu().numpy(), orc.dsa_index_key(raw, wt, bs, 0, pos, theta), rtol=2e-5, atol=2e-5)
+    raw8 = orc.fill_normal((1, 3, 8), seed + 3, 1.0, False)
+    got = be.dsa_index_key_device(dev(be, raw8), dev(be, wt[:8].copy()), dev(be, bs[:8].copy()), 8, 7, theta)
+    be.device_flush()
+    np.testing.assert_allclose(got.cpu().numpy(), orc.dsa_index_key(raw8, wt[:8], bs[:8], 8, 7, theta), rtol=2e-5, atol=2e-5)
+    from inferno_b200.lib import InfernoError
+    with pytest.raises(InfernoError, match="must be even"):
+        be.dsa_index_key_device(dev(be, raw), dev(be, wt), dev(be, bs), 3, pos, theta)
+
+
+def test_query_rotation_and_head_weights(be):
+    B, hidden, H, D, rope, pos, theta = 2, 6144, 32, 128, 64, 4321, 1.0e4
+    seed = SEED0 + 1310
+    hs = orc.fill_normal((B, hidden), seed, 1.0, False)
+    q_raw = orc.fill_normal((B, H * D), seed + 1, 1.0, False)
+    proj = orc.fill_normal((hidden, H), seed + 2, 0.02, False)
+    q, w = be.dsa_query_weights(dev(be, hs), dev(be, q_raw), dev(be, proj), H, D, rope, pos, theta)
+    be.device_flush()
+    want_q, want_w = orc.dsa_query_weights(hs, q_raw, proj, H, D, rope, pos, theta)
+    np.testing.assert_allclose(q.cpu().numpy(), want_q, rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(w.cpu().numpy(), want_w, rtol=2e-5, atol=2e-5)
+
+
+def test_decode_topk_chain_reproduces_the_reference_known_answer(be):
+    # the reference's own case (two heads of two dims) with every head padded to four dims by zeros, which the score
+    # kernels need; the padding adds nothing to a dot product and the ranking does not depend on the 1/sqrt(dim) scale
+    hidden = np.array([[[math.sqrt(2.0), 0.0, 0.0, 0.0]]], np.float32)
+    q_raw = np.array([[[1.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 0.0]]], np.float32)
+    past = np.array([[[1.0, 0.0, 0.0, 0.0], [0.0, 1.0, 0.0, 0.0], [2.0, 0.0, 0.0, 0.0]]], np.float32)
+    cur = np.array([[[0.0, 2.0, 0.0, 0.0]]], np.float32)
+    proj = np.array([[1.0, 1.0], [0.0, 0.0], [0.0, 0.0], [0.0, 0.0]], np.float32)
+    ids = be.dsa_decode_topk_device(dev(be, hidden), dev(be, q_raw), dev(be, past), dev(be, cur), dev(be, proj), 2, 4, 2, 0,
+                                    10000.0, 2)
+    be.device_flush()
+    assert ids.cpu().numpy().tolist() == [[2, 3]]
+    assert orc.dsa_decode_topk(hidden, q_raw, past, cur, proj, 2, 4, 2, 0, 10000.0, 2).tolist() == [[2, 3]]

@@ -422,3 +422,24 @@ def test_fp8_e4m3fn_codec_matches_the_published_format():
     got = orc.fp8_e4m3fn_encode(x)
     # torch keeps the sign of values that round to zero; the reference encoder does too (sign | 0)
     assert np.array_equal(got, want)
+
+
+def test_dsa_decode_topk_matches_the_reference_known_answers():
+    """dsa_decode_topk_device_matches_expected_ranking_when_metal_available (crates/backend/src/backend.rs:10835):
+    hidden (sqrt 2, 0, 0, 0), two heads of two dims, three past keys and the current one -> ids [2, 3]; and
+    layer_norm_last_dim_applies_weight_and_bias (crates/model/src/indexer.rs:633)."""
+    hidden = np.array([[[math.sqrt(2.0), 0.0, 0.0, 0.0]]], np.float32)
+    q_raw = np.array([[[1.0, 0.0, 0.0, 1.0]]], np.float32)
+    past = np.array([[[1.0, 0.0], [0.0, 1.0], [2.0, 0.0]]], np.float32)
+    cur = np.array([[[0.0, 2.0]]], np.float32)
+    proj = np.array([[1.0, 1.0], [0.0, 0.0], [0.0, 0.0], [0.0, 0.0]], np.float32)
+    ids = orc.dsa_decode_topk(hidden, q_raw, past, cur, proj, 2, 2, 2, 0, 10000.0, 2)
+    assert ids.tolist() == [[2, 3]]
+    key = orc.dsa_index_key(np.array([[[1.0, 3.0]]], np.float32), np.array([2.0, 2.0], np.float32),
+                            np.array([0.5, -0.5], np.float32), 0, 0, 10000.0, 1e-6)
+    assert abs(key[0, 0, 0] - -1.499999) < 1e-4 and abs(key[0, 0, 1] - 1.499999) < 1e-4
+    # the rotation writes halves: pair (x0, x1) at position 1 with freq 1 -> (x0 cos1 - x1 sin1, x1 cos1 + x0 sin1)
+    r = orc.dsa_rotate_interleaved(np.array([1.0, 2.0, 3.0, 4.0, 9.0], np.float32), 4, 1, 10000.0)
+    c0, s0, f1 = math.cos(1.0), math.sin(1.0), 1.0 / math.sqrt(10000.0)
+    want = [1 * c0 - 2 * s0, 3 * math.cos(f1) - 4 * math.sin(f1), 2 * c0 + 1 * s0, 4 * math.cos(f1) + 3 * math.sin(f1), 9.0]
+    assert np.allclose(r, want, atol=1e-6)
