@@ -268,7 +268,9 @@ int32_t inf_mla_decode_absorbed_selected(inf_ctx* ctx, const void* q_f16, const 
  * inf_dsa_scores (kernel dsa_scores_f32_kernel, crates/backend/src/metal/kernels/dsa_kernels.metal:137-176):
  * q f32 [batch, heads, head_dim] (already roped), weights f32 [batch, heads], past_keys f32 [batch, past_tokens,
  * head_dim], current_key f32 [batch, head_dim]; scores f32 [batch, past_tokens + 1],
- * score[t] = sum_h weights[h] * max(0, q[h] . key[t] / sqrt(head_dim)).  head_dim % 4 == 0.
+ * score[t] = sum_h weights[h] * max(0, q[h] . key[t] / sqrt(head_dim)).  head_dim % 4 == 0.  fp32 accumulation;
+ * for head_dim 128 and heads a multiple of 16 the dot products run on the tensor cores with every input split into
+ * two tf32 terms, which keeps a score within 2e-5 of exact arithmetic (the fp32 sum's own rounding).
  * inf_dsa_topk (kernels dsa_topk_block_sort_u32 / dsa_topk_merge_u32, dsa_kernels.metal:211-393): the top_k
  * (<= 2048) token ids of every row of scores [batch, key_tokens], best first, where a precedes b iff
  * score_a > score_b or (score_a == score_b and id_a < id_b); selected uint32 [batch, selected_stride], entries
