@@ -351,13 +351,25 @@ def fp8_e4m3fn_encode(x):
     return out
 
 
+def _libm_powf(x, y):
+    import ctypes
+    import ctypes.util
+    libm = ctypes.CDLL(ctypes.util.find_library("m") or "libm.so.6")
+    libm.powf.restype = ctypes.c_float
+    libm.powf.argtypes = [ctypes.c_float, ctypes.c_float]
+    return libm.powf(x, y)
+
+
 def dsa_rotate_interleaved(values, rope_dim, position, theta):
     """rotate_interleaved_pair_range (crates/model/src/indexer.rs:483-514): pairs (2p, 2p+1) of the first rope_dim
     values rotated by position * theta^(-2p/rope_dim), written as halves (p, rope_dim/2 + p); f32 arithmetic."""
     out = _f32(values).copy()
     pairs = rope_dim // 2
     p = np.arange(pairs)
-    freq = (np.float32(1.0) / np.power(np.float32(theta), (2 * p).astype(np.float32) / np.float32(rope_dim))).astype(np.float32)
+    # f32::powf in the reference is libm's powf; numpy's float32 power may differ from it in the last bit, which at
+    # position 1000 is already 6e-5 rad of angle, so the frequencies come from libm itself
+    freq = np.array([np.float32(1.0) / np.float32(_libm_powf(float(np.float32(theta)), float(np.float32(2 * k) / np.float32(rope_dim))))
+                     for k in p], dtype=np.float32)
     angle = (np.float32(position) * freq).astype(np.float32)
     c, s = np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
     x0, x1 = out[..., 0:rope_dim:2].copy(), out[..., 1:rope_dim:2].copy()
