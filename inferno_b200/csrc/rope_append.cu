@@ -79,57 +79,124 @@ __global__ void qk_norm_rope_pair_kernel(const float* __restrict__ q, const floa
     for (int j = 0; j < 4; ++j) out[lane + 32 * j] = x[j];
 }
 
-// Fused RoPE + append.  Row space: [Q rows | K rows | V rows].
+// Fused RoPE + append.  One CTA per (sequence, token) and slice of its rows (q heads, then k heads, then v heads):
+// the token's position, its page and the cos / sin of its angles are found once and shared by all its rows, and a
+// row of 128 values is held by 16 threads, eight consecutive values each, so that every load and store is 16 bytes
+// per thread and 256 contiguous bytes per row.  The half-split rotation partner (d +- rotary/2) sits rotary/16 lanes
+// away in the same 16-lane group.
 template <typename T>
-__global__ void rope_append_gqa_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                                       const float* __restrict__ qw, const float* __restrict__ kw,
-                                       const float* __restrict__ inv_freq, int rotary_dim, float factor, float eps,
-                                       __half* __restrict__ k_pool, __half* __restrict__ v_pool, int num_pages,
-                                       int page_size, const int* __restrict__ pages, const int* __restrict__ lens,
-                                       int max_pages, int tokens, int q_heads, int kv_heads,
-                                       __half* __restrict__ q_out, float* __restrict__ k_f32_out, long long q_rows,
-                                       long long kv_rows, int* __restrict__ status) {
+__device__ __forceinline__ void ld8_as_f32(const T* p, float (&x)[8]);
+template <>
+__device__ __forceinline__ void ld8_as_f32<float>(const float* p, float (&x)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void ld8_as_f32<__half>(const __half* p, float (&x)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        x[2 * j] = f.x, x[2 * j + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void st8_as_f16(__half* p, const float (&x)[8]) {
+    uint4 raw;
+    __half2* h = reinterpret_cast<__half2*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(x[2 * j], x[2 * j + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_append_gqa_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                       const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ inv_freq,
+                       int rotary_dim, float factor, float eps, __half* __restrict__ k_pool, __half* __restrict__ v_pool,
+                       int num_pages, int page_size, const int* __restrict__ pages, const int* __restrict__ lens,
+                       int max_pages, int tokens, int q_heads, int kv_heads, __half* __restrict__ q_out,
+                       float* __restrict__ k_f32_out, int* __restrict__ status) {
+    __shared__ float2 s_cs[64];  // (cos, sin) * factor of the token's angles
     inf_pdl_wait();  // the pages may still be read by the attention kernels of the previous step
     inf_pdl_release();
-    long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    int lane = threadIdx.x & 31;
-    if (row >= q_rows + 2 * kv_rows) return;
-    int kind = row < q_rows ? 0 : (row < q_rows + kv_rows ? 1 : 2);
-    long long r = kind == 0 ? row : (kind == 1 ? row - q_rows : row - q_rows - kv_rows);
-    int heads = kind == 0 ? q_heads : kv_heads;
-    int head = (int)(r % heads);
-    int token = (int)((r / heads) % tokens);
-    int b = (int)(r / ((long long)heads * tokens));
-    int position = lens[b] + token;
-    const T* in = (kind == 0 ? q : (kind == 1 ? k : v)) + r * D;
-    float x[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) x[j] = ld_as_f32<T>(in + lane + 32 * j);
-    if (kind != 2 && inv_freq)
-        norm_rope_row(x, lane, kind == 0 ? qw : kw, inv_freq, rotary_dim, (float)position, eps, factor);
-    if (kind == 0) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) q_out[r * D + lane + 32 * j] = __float2half_rn(x[j]);
-        return;
+    const int bt = blockIdx.x, b = bt / tokens, token = bt - b * tokens;
+    const int tid = threadIdx.x, sub = tid & 15, slot_id = tid >> 4;
+    const int position = lens[b] + token;
+    const int half = rotary_dim >> 1;
+    if (inv_freq && tid < half) {
+        const float angle = (float)position * inv_freq[tid];
+        s_cs[tid] = make_float2(cosf(angle) * factor, sinf(angle) * factor);
     }
-    if (kind == 1 && k_f32_out) {
+    long long page_row = -1;  // first row of the token's page slot in the pools, in units of rows of 128
+    {
+        const int slot = position / page_size;
+        if (position < 0 || slot >= max_pages) {
+            if (tid == 0 && blockIdx.y == 0) atomicOr(status, INF_STATUS_BAD_LEN);
+        } else {
+            const int page = pages[(long long)b * max_pages + slot];
+            if (page < 0 || page >= num_pages) {
+                if (tid == 0 && blockIdx.y == 0) atomicOr(status, INF_STATUS_BAD_PAGE);
+            } else {
+                page_row = (long long)page * kv_heads * page_size + position % page_size;
+            }
+        }
+    }
+    __syncthreads();
+    const int rows_per_token = q_heads + 2 * kv_heads;
+    const int partner = half >> 3;  // lanes between a value and its rotation partner: 4 or 8
+    const int d0 = sub * 8;
+    for (int base = blockIdx.y * 16; base < rows_per_token; base += 16 * gridDim.y) {  // the same trips for every thread
+        const int rr = base + slot_id;
+        const bool active = rr < rows_per_token;
+        const int kind = rr < q_heads ? 0 : (rr < q_heads + kv_heads ? 1 : 2);
+        const int head = kind == 0 ? rr : (kind == 1 ? rr - q_heads : rr - q_heads - kv_heads);
+        const long long in_row = (long long)bt * (kind == 0 ? q_heads : kv_heads) + head;
+        float x[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) k_f32_out[r * D + lane + 32 * j] = x[j];
-    }
-    int slot = position / page_size;
-    if (position < 0 || slot >= max_pages) {
-        if (lane == 0) atomicOr(status, INF_STATUS_BAD_LEN);
-        return;
-    }
-    int page = pages[(long long)b * max_pages + slot];
-    if (page < 0 || page >= num_pages) {
-        if (lane == 0) atomicOr(status, INF_STATUS_BAD_PAGE);
-        return;
-    }
-    __half* dst = (kind == 1 ? k_pool : v_pool) +
-                  ((((long long)page * kv_heads + head) * page_size) + position % page_size) * D;
+        for (int j = 0; j < 8; ++j) x[j] = 0.f;
+        if (active) ld8_as_f32<T>((kind == 0 ? q : (kind == 1 ? k : v)) + in_row * D + d0, x);
+        if (inv_freq) {  // uniform; the shuffles below are executed by whole warps, rows that are not rotated drop the result
+            const float* w = kind == 0 ? qw : kw;
+            const bool rotate = active && kind != 2;
+            if (qw || kw) {
+                float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2half_rn(x[j]);
+                for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (rotate && w) {
+                    const float inv_rms = rsqrtf(ss / (float)D + eps);
+                    const float4 w0 = reinterpret_cast<const float4*>(w + d0)[0], w1 = reinterpret_cast<const float4*>(w + d0)[1];
+                    const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) x[j] = x[j] * wv[j] * inv_rms;
+                }
+            }
+            const bool first = d0 < half, second = !first && d0 < rotary_dim;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[j], partner);
+                if (rotate && (first || second)) {
+                    const float2 cs = s_cs[first ? d0 + j : d0 + j - half];
+                    const float a = first ? x[j] : other, bb = first ? other : x[j];
+                    x[j] = first ? a * cs.x + (-bb) * cs.y : bb * cs.x + a * cs.y;
+                }
+            }
+        }
+        if (!active) continue;
+        if (kind == 0) {
+            st8_as_f16(q_out + in_row * D + d0, x);
+            continue;
+        }
+        if (kind == 1 && k_f32_out) {
+            float4* o = reinterpret_cast<float4*>(k_f32_out + in_row * D + d0);
+            o[0] = make_float4(x[0], x[1], x[2], x[3]);
+            o[1] = make_float4(x[4], x[5], x[6], x[7]);
+        }
+        if (page_row >= 0)
+            st8_as_f16((kind == 1 ? k_pool : v_pool) + (page_row + (long long)head * page_size) * D + d0, x);
+    }
 }
 
 struct InvFreq64 {
@@ -311,25 +378,26 @@ int32_t inf_rope_append_gqa(inf_ctx* ctx, const void* q, const void* k, const vo
     }
     int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "rope_append_gqa");
     if (rc != INF_OK) return rc;
-    long long q_rows = (long long)table->batch * tokens * q_heads;
-    long long kv_rows = (long long)table->batch * tokens * pool->kv_heads;
-    long long rows = q_rows + 2 * kv_rows;
-    int blocks = (int)((rows + 7) / 8);
+    const long long bt = (long long)table->batch * tokens;
+    if (bt > 0x7fffffffLL) return inf_fail(ctx, INF_E_SHAPE, "rope_append_gqa: batch x tokens exceeds the launch grid");
+    const int rows_per_token = q_heads + 2 * pool->kv_heads;
+    // long prompts: one CTA per token walks its rows; short batches (decode): one CTA per 16 rows
+    dim3 grid((unsigned)bt, bt >= 2 * ctx->sm_count ? 1u : (unsigned)((rows_per_token + 15) / 16));
     const float* inv = rope ? rope->inv_freq : nullptr;
     int rd = rope ? rope->rotary_dim : 64;
     float factor = rope ? rope->attention_factor : 1.0f;
     if (in_dtype == INF_DTYPE_F32)
-        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<float>, dim3(blocks), dim3(256), 0, ctx->stream,
+        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<float>, grid, dim3(256), 0, ctx->stream,
                                      (const float*)q, (const float*)k, (const float*)v, qw, kw, inv, rd, factor, eps,
                                      (__half*)pool->k, (__half*)pool->v, pool->num_pages, pool->page_size, table->pages,
                                      table->lens, table->max_pages, tokens, q_heads, pool->kv_heads, (__half*)q_out_f16,
-                                     k_f32_out, q_rows, kv_rows, ctx->status));
+                                     k_f32_out, ctx->status));
     else
-        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<__half>, dim3(blocks), dim3(256), 0, ctx->stream,
+        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<__half>, grid, dim3(256), 0, ctx->stream,
                                      (const __half*)q, (const __half*)k, (const __half*)v, qw, kw, inv, rd, factor, eps,
                                      (__half*)pool->k, (__half*)pool->v, pool->num_pages, pool->page_size, table->pages,
                                      table->lens, table->max_pages, tokens, q_heads, pool->kv_heads, (__half*)q_out_f16,
-                                     k_f32_out, q_rows, kv_rows, ctx->status));
+                                     k_f32_out, ctx->status));
     return INF_OK;
 }
 
