@@ -84,23 +84,33 @@ __global__ void qk_norm_rope_pair_kernel(const float* __restrict__ q, const floa
 // row of 128 values is held by 16 threads, eight consecutive values each, so that every load and store is 16 bytes
 // per thread and 256 contiguous bytes per row.  The half-split rotation partner (d +- rotary/2) sits rotary/16 lanes
 // away in the same 16-lane group.
+// eight consecutive input values as they lie in memory (one 16-byte piece for fp16, two for f32) ...
 template <typename T>
-__device__ __forceinline__ void ld8_as_f32(const T* p, float (&x)[8]);
+struct Raw8;
 template <>
-__device__ __forceinline__ void ld8_as_f32<float>(const float* p, float (&x)[8]) {
-    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
-    x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
-}
-template <>
-__device__ __forceinline__ void ld8_as_f32<__half>(const __half* p, float (&x)[8]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(p);
-    const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(h[j]);
-        x[2 * j] = f.x, x[2 * j + 1] = f.y;
+struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = reinterpret_cast<const float4*>(p)[0];
+        b = reinterpret_cast<const float4*>(p)[1];
     }
-}
+    __device__ __forceinline__ void to_f32(float (&x)[8]) const {
+        x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
+    }
+};
+template <>
+struct Raw8<__half> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const __half* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void to_f32(float (&x)[8]) const {
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            x[2 * j] = f.x, x[2 * j + 1] = f.y;
+        }
+    }
+};
 __device__ __forceinline__ void st8_as_f16(__half* p, const float (&x)[8]) {
     uint4 raw;
     __half2* h = reinterpret_cast<__half2*>(&raw);
@@ -146,7 +156,16 @@ rope_append_gqa_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
     const int rows_per_token = q_heads + 2 * kv_heads;
     const int partner = half >> 3;  // lanes between a value and its rotation partner: 4 or 8
     const int d0 = sub * 8;
-    for (int base = blockIdx.y * 16; base < rows_per_token; base += 16 * gridDim.y) {  // the same trips for every thread
+    // where row rr of the token lies in its input tensor
+    auto row_source = [&](int rr) -> const T* {
+        const int kind = rr < q_heads ? 0 : (rr < q_heads + kv_heads ? 1 : 2);
+        const int head = kind == 0 ? rr : (kind == 1 ? rr - q_heads : rr - q_heads - kv_heads);
+        return (kind == 0 ? q : (kind == 1 ? k : v)) + ((long long)bt * (kind == 0 ? q_heads : kv_heads) + head) * D + d0;
+    };
+    const int stride = 16 * gridDim.y;
+    Raw8<T> ahead{};  // the next trip's values are requested before this trip's are worked on
+    if ((int)(blockIdx.y * 16) + slot_id < rows_per_token) ahead.load(row_source(blockIdx.y * 16 + slot_id));
+    for (int base = blockIdx.y * 16; base < rows_per_token; base += stride) {  // the same trips for every thread
         const int rr = base + slot_id;
         const bool active = rr < rows_per_token;
         const int kind = rr < q_heads ? 0 : (rr < q_heads + kv_heads ? 1 : 2);
@@ -155,7 +174,8 @@ rope_append_gqa_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         float x[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] = 0.f;
-        if (active) ld8_as_f32<T>((kind == 0 ? q : (kind == 1 ? k : v)) + in_row * D + d0, x);
+        if (active) ahead.to_f32(x);
+        if (rr + stride < rows_per_token) ahead.load(row_source(rr + stride));
         if (inv_freq) {  // uniform; the shuffles below are executed by whole warps, rows that are not rotated drop the result
             const float* w = kind == 0 ? qw : kw;
             const bool rotate = active && kind != 2;
