@@ -348,7 +348,7 @@ class MlaSelectedDecode(MlaDecode):
         super().__init__(be, rank, ctx_len)
         torch = self.torch
         self.name = f"mla_selected_decode_{self.N_SEL}_of_{ctx_len // 1024}k"
-        self.traffic = None
+        self.traffic = 2.51e6 if (self.N_SEL, ctx_len) == (2048, 32768) else None  # ncu, profiles/dsa_scores_topk_32k.md
         g = torch.Generator(device="cpu").manual_seed(SEED + 31 + rank)
         ids = torch.randperm(ctx_len - 1, generator=g)[: self.N_SEL - 1].sort().values.to(torch.int32)
         self.sel = torch.cat([ids, torch.tensor([ctx_len - 1], dtype=torch.int32)]).view(1, -1).to(be.device)
@@ -401,6 +401,7 @@ class DsaSparseDecode(MlaSelectedDecode):
         self.n_variants = max(self.n_caches, self.n_key_sets)
         self.key_bytes = float(ctx_len) * self.DI * 4
         self.kernel_units_per_launch = self.key_bytes
+        self.traffic = 16.83e6 * ctx_len / 32768  # DRAM bytes read by the scores kernel, ncu (profiles/dsa_scores_topk_32k.md)
         self.units_per_step = self.key_bytes + float(self.N_SEL) * (self.L + self.R) * 2
         self.flops_per_step += 2.0 * self.HI * self.DI * ctx_len
         self.config.update({"workload": self.name, "index_heads": self.HI, "index_dim": self.DI,
@@ -440,7 +441,7 @@ class GqaPrefill2k:
     metric, unit, bound = "gqa_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_gqa_kernel"
     launches_per_step = 2  # rope+append, flash prefill
-    traffic = 33.66e6 + 0.23e6  # DRAM bytes per launch, ncu (profiles/flash_prefill_gqa_2k.md)
+    traffic = 33.64e6 + 0.35e6  # DRAM bytes per launch, ncu (profiles/flash_prefill_gqa_2k.md)
     T, Hq, Hkv, D, P, THETA = 2048, 48, 8, 128, 16, 500000.0
     max_steps = 400
     N_SETS = 8
