@@ -132,11 +132,16 @@ class GqaDecodeB32:
         self.full = be.page_table(table, self.lens, validate_on_host=False)
         inv = 1.0 / np.power(np.float32(self.THETA), (2 * np.arange(32)).astype(np.float32) / np.float32(64))
         self.rope = be.prepare_rope_table(inv.astype(np.float32), 64, 1.0)
-        self.q = torch.randn((self.B, 1, self.Hq, self.D), generator=gd, device=be.device, dtype=torch.float16)
-        self.k = torch.randn((self.B, 1, self.Hkv, self.D), generator=gd, device=be.device, dtype=torch.float16)
-        self.v = torch.randn((self.B, 1, self.Hkv, self.D), generator=gd, device=be.device, dtype=torch.float16)
+        # q, k and v of a step are three views of one device buffer (and of one pinned host buffer), so that the
+        # end-to-end step moves its inputs with a single host-to-device copy
+        nq, nk = self.B * self.Hq * self.D, self.B * self.Hkv * self.D
+        self.qkv = torch.randn((nq + 2 * nk,), generator=gd, device=be.device, dtype=torch.float16)
+        self.q = self.qkv[:nq].view(self.B, 1, self.Hq, self.D)
+        self.k = self.qkv[nq:nq + nk].view(self.B, 1, self.Hkv, self.D)
+        self.v = self.qkv[nq + nk:].view(self.B, 1, self.Hkv, self.D)
         self.out = torch.empty((self.B, self.Hq, self.D), dtype=torch.float32, device=be.device)
-        self.hq, self.hk, self.hv = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
+        self.hqkv = self.qkv.cpu().pin_memory()
+        self.hq, self.hk, self.hv = self.hqkv[:nq], self.hqkv[nq:nq + nk], self.hqkv[nq + nk:]
         self.hout = torch.empty((self.B, self.Hq, self.D), dtype=torch.float32).pin_memory()
         self.max_len = int(self.lens.max())
         self.i = 0
@@ -155,9 +160,7 @@ class GqaDecodeB32:
                                  out=self.out)
 
     def step_e2e(self):
-        self.q.copy_(self.hq, non_blocking=True)
-        self.k.copy_(self.hk, non_blocking=True)
-        self.v.copy_(self.hv, non_blocking=True)
+        self.qkv.copy_(self.hqkv, non_blocking=True)
         self.step()
         self.hout.copy_(self.out, non_blocking=True)
 
