@@ -222,11 +222,19 @@ class MlaDecode:
         self.pool.rows.normal_(0, 0.5, generator=gd)
         self.tables = [be.page_table(perm[i * pages_per:(i + 1) * pages_per].view(1, -1), [ctx_len - 1],
                                      validate_on_host=False) for i in range(self.n_caches)]
-        self.q = torch.randn((1, 1, self.H, self.L + self.R), generator=gd, device=be.device, dtype=torch.float16)
-        self.x = torch.randn((1, 1, self.L + self.R), generator=gd, device=be.device, dtype=torch.float32)
+        # the step's inputs (q fp16, the new token's f32 row) are views of one byte buffer on the device and of one
+        # pinned buffer on the host: the end-to-end step moves them with a single copy
+        q_bytes, x_bytes = self.H * (self.L + self.R) * 2, (self.L + self.R) * 4
+        self.inputs = torch.empty((q_bytes + x_bytes,), dtype=torch.uint8, device=be.device)
+        self.q = self.inputs[:q_bytes].view(torch.float16).view(1, 1, self.H, self.L + self.R)
+        self.x = self.inputs[q_bytes:].view(torch.float32).view(1, 1, self.L + self.R)
+        self.q.normal_(0, 1, generator=gd)
+        self.x.normal_(0, 1, generator=gd)
         self.w = torch.ones((self.L,), device=be.device, dtype=torch.float32)
         self.out = torch.empty((1, 1, self.H, self.L), dtype=torch.float32, device=be.device)
-        self.hq, self.hx = self.q.cpu().pin_memory(), self.x.cpu().pin_memory()
+        self.hinputs = self.inputs.cpu().pin_memory()
+        self.hq = self.hinputs[:q_bytes].view(torch.float16).view(1, 1, self.H, self.L + self.R)
+        self.hx = self.hinputs[q_bytes:].view(torch.float32).view(1, 1, self.L + self.R)
         self.hout = torch.empty(self.out.shape, dtype=torch.float32).pin_memory()
         self.scale = 1.0 / float(np.sqrt(192.0))
         self.i = 0
@@ -248,8 +256,7 @@ class MlaDecode:
         self.be.mla_decode_absorbed(self.q, self.pool, t, self.ctx_len, self.scale, out=self.out)
 
     def step_e2e(self):
-        self.q.copy_(self.hq, non_blocking=True)
-        self.x.copy_(self.hx, non_blocking=True)
+        self.inputs.copy_(self.hinputs, non_blocking=True)
         self.step()
         self.hout.copy_(self.out, non_blocking=True)
 
@@ -289,12 +296,17 @@ class MlaAbsorbedDecode(MlaDecode):
             return blocks.view(-1)
         self.k_b = q8(self.H, self.L, self.QN, 1.0e-3)
         self.v_b = q8(self.H, self.DV, self.L, 1.0e-3)
-        self.q_no = torch.randn((1, 1, self.H, self.QN), generator=gd, device=be.device, dtype=torch.float32)
-        self.q_rope = torch.randn((1, 1, self.H, self.R), generator=gd, device=be.device, dtype=torch.float32)
-        self.cur_lat = torch.randn((1, 1, self.L), generator=gd, device=be.device, dtype=torch.float32) * 0.5
-        self.cur_rope = torch.randn((1, 1, self.R), generator=gd, device=be.device, dtype=torch.float32) * 0.5
-        self.hqn, self.hqr = self.q_no.cpu().pin_memory(), self.q_rope.cpu().pin_memory()
-        self.hcl, self.hcr = self.cur_lat.cpu().pin_memory(), self.cur_rope.cpu().pin_memory()
+        # the four f32 inputs of the operator are views of one buffer (device and pinned host): one copy per step
+        sizes = [self.H * self.QN, self.H * self.R, self.L, self.R]
+        offs = np.concatenate([[0], np.cumsum(sizes)]).tolist()
+        self.inputs_f32 = torch.randn((offs[-1],), generator=gd, device=be.device, dtype=torch.float32)
+        self.inputs_f32[offs[2]:] *= 0.5
+        self.hinputs_f32 = self.inputs_f32.cpu().pin_memory()
+        shapes = [(1, 1, self.H, self.QN), (1, 1, self.H, self.R), (1, 1, self.L), (1, 1, self.R)]
+        self.q_no, self.q_rope, self.cur_lat, self.cur_rope = (
+            self.inputs_f32[offs[i]:offs[i + 1]].view(shapes[i]) for i in range(4))
+        self.hqn, self.hqr, self.hcl, self.hcr = (
+            self.hinputs_f32[offs[i]:offs[i + 1]].view(shapes[i]) for i in range(4))
         self.hout = torch.empty((1, 1, self.H, self.DV), dtype=torch.float32).pin_memory()
         self.weight_bytes = self.k_b.numel() + self.v_b.numel()
         self.kernel_units_per_launch = self.units_per_step  # the attention kernel itself moves only the cached rows
@@ -315,10 +327,7 @@ class MlaAbsorbedDecode(MlaDecode):
                                          self.pool, t, self.QN + self.R, self.DV, max_len=self.ctx_len, out=self.out)
 
     def step_e2e(self):
-        self.q_no.copy_(self.hqn, non_blocking=True)
-        self.q_rope.copy_(self.hqr, non_blocking=True)
-        self.cur_lat.copy_(self.hcl, non_blocking=True)
-        self.cur_rope.copy_(self.hcr, non_blocking=True)
+        self.inputs_f32.copy_(self.hinputs_f32, non_blocking=True)
         self.step()
         self.hout.copy_(self.out, non_blocking=True)
 
