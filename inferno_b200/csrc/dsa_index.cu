@@ -442,7 +442,8 @@ __device__ __forceinline__ unsigned ordered_bits(float f) {  // larger float <->
 // (up to TK_SMEM_ROWS tokens); the radix passes, the collection sweep and the final sort then never leave the SM.
 // The k-th largest value is found 12 + 10 + 10 bits at a time: twelve leading bits spread real scores (a few
 // exponents, sixteen mantissa steps each) over enough bins that the shared-memory adds of a warp rarely meet.
-constexpr int TK_SMEM_ROWS = 47104;  // 184 KB of ordered scores
+constexpr int TK_SMEM_ROWS = 45056;  // 176 KB of ordered scores
+constexpr int TK_CAND_CAP = 2 * TK_THREADS;  // candidates of the threshold bin that are kept as a list
 constexpr int TK_WARPS = TK_THREADS / 32;
 constexpr int TK_BINS = 4096;
 constexpr int TK_SORT_TABLE_BYTES = TK_WARPS * 256 * (int)sizeof(unsigned);
@@ -470,7 +471,8 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
     __shared__ unsigned long long keys[TK_MAX_K];
     __shared__ int w_above[TK_WARPS], w_tie[TK_WARPS];
     __shared__ unsigned sh_prefix, sh_mask, sh_any, sh_all;
-    __shared__ int sh_remaining;
+    __shared__ int sh_remaining, sh_cand;
+    __shared__ unsigned cand_ids[TK_CAND_CAP];
     inf_pdl_wait();
     inf_pdl_release();
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -486,6 +488,110 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
         sh_all = ~0u;
         sh_remaining = want;
     }
+    // ---- collect everything above the threshold and the ties with the lowest ids.  In each round thread t owns
+    //      the 32 consecutive tokens [round + 32t, round + 32t + 32): it records which are above and which tie as
+    //      two bit masks, a scan over the CTA gives its place in the output, and it writes its own entries.  Lane l
+    //      starts its walk at element l of its chunk, so the 32 lanes of a warp hit 32 different banks.
+    int out_base = 0, ties_before = 0;  // the same in every thread
+    // exclusive places of this thread's (above, tie) counts among all threads, and the totals; one barrier inside
+    auto scan_counts = [&](int ca, int ct, int& ex_a, int& ex_t, int& total_a, int& total_t) {
+        int ia = ca, it = ct;  // inclusive scans inside the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int ya = __shfl_up_sync(0xffffffffu, ia, o), yt = __shfl_up_sync(0xffffffffu, it, o);
+            if (lane >= o) {
+                ia += ya;
+                it += yt;
+            }
+        }
+        if (lane == 31) {
+            w_above[warp] = ia;
+            w_tie[warp] = it;
+        }
+        __syncthreads();
+        int wa = w_above[lane], wt = w_tie[lane];  // every warp scans the 32 warp totals for itself
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int ya = __shfl_up_sync(0xffffffffu, wa, o), yt = __shfl_up_sync(0xffffffffu, wt, o);
+            if (lane >= o) {
+                wa += ya;
+                wt += yt;
+            }
+        }
+        total_a = __shfl_sync(0xffffffffu, wa, 31);
+        total_t = __shfl_sync(0xffffffffu, wt, 31);
+        const int warp_a = warp ? __shfl_sync(0xffffffffu, wa, (warp + 31) & 31) : 0;  // totals of the warps before
+        const int warp_t = warp ? __shfl_sync(0xffffffffu, wt, (warp + 31) & 31) : 0;
+        ex_a = warp_a + ia - ca;  // entries of earlier threads
+        ex_t = warp_t + it - ct;
+    };
+    // threshold and ties compare on (value >> shift).  to_list: the ties are not entries yet but candidates, all of
+    // them kept (ids only, in id order) in cand_ids, ties_before counting them.
+    auto sweep = [&](unsigned threshold, int shift, int ties_wanted, bool to_list) {
+    for (int round = 0; round < n; round += 32 * TK_THREADS) {
+        const int c = round + tid * 32;
+        unsigned above_mask = 0u, tie_mask = 0u;
+        if (row_in_smem && c + 32 <= n) {
+            // eight 16-byte reads; bit p of the masks built here belongs to element (p + 4 * lane) mod 32
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint4 v = reinterpret_cast<const uint4*>(srow + c)[(q + lane) & 7];
+                above_mask |= ((unsigned)((v.x >> shift) > threshold) << (4 * q)) | ((unsigned)((v.y >> shift) > threshold) << (4 * q + 1)) |
+                              ((unsigned)((v.z >> shift) > threshold) << (4 * q + 2)) | ((unsigned)((v.w >> shift) > threshold) << (4 * q + 3));
+                tie_mask |= ((unsigned)((v.x >> shift) == threshold) << (4 * q)) | ((unsigned)((v.y >> shift) == threshold) << (4 * q + 1)) |
+                            ((unsigned)((v.z >> shift) == threshold) << (4 * q + 2)) | ((unsigned)((v.w >> shift) == threshold) << (4 * q + 3));
+            }
+            above_mask = __funnelshift_l(above_mask, above_mask, 4 * lane);
+            tie_mask = __funnelshift_l(tie_mask, tie_mask, 4 * lane);
+        } else if (c < n) {
+            for (int j = 0; j < 32; ++j) {
+                const int jj = (j + lane) & 31;
+                if (c + jj < n) {
+                    const unsigned u = value(c + jj) >> shift;
+                    above_mask |= (unsigned)(u > threshold) << jj;
+                    tie_mask |= (unsigned)(u == threshold) << jj;
+                }
+            }
+        }
+        const int ca = __popc(above_mask), ct = __popc(tie_mask);
+        int ex_a, ex_t, round_above, round_ties;
+        scan_counts(ca, ct, ex_a, ex_t, round_above, round_ties);
+        const int ties_open = max(ties_wanted - ties_before, 0);     // ties this round may still take
+        const int quota = max(0, min(ct, ties_open - ex_t));
+        unsigned take = tie_mask;
+        if (quota < ct) {  // the lowest `quota` ids of this thread's ties
+            take = 0u;
+            unsigned m = tie_mask;
+            for (int x = 0; x < quota; ++x) {
+                const unsigned low = m & (0u - m);
+                take |= low;
+                m ^= low;
+            }
+        }
+        int pos = out_base + ex_a + (to_list ? 0 : min(ties_open, ex_t));
+        unsigned sel = to_list ? above_mask : (above_mask | take);
+        while (sel) {
+            const int jj = __ffs(sel) - 1;
+            sel &= sel - 1u;
+            const int i = c + jj;
+            keys[pos++] = ((unsigned long long)(~value(i)) << 32) | (unsigned)i;
+        }
+        if (to_list) {
+            int at = ties_before + ex_t;
+            unsigned m = tie_mask;
+            while (m) {
+                const int jj = __ffs(m) - 1;
+                m &= m - 1u;
+                cand_ids[at++] = (unsigned)(c + jj);
+            }
+        }
+        out_base += round_above + (to_list ? 0 : min(ties_open, round_ties));
+        ties_before += round_ties;
+        __syncthreads();
+    }
+    };
+    bool compact = false;  // the threshold bin's members have been few enough to be kept as a list
+    int cand_n = 0;
     const int n4 = n >> 2;  // whole groups of four scores
     for (int pass = 0; pass < 3; ++pass) {
         const int shift = pass == 0 ? 20 : (pass == 1 ? 10 : 0);
@@ -493,7 +599,12 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
         for (int i = tid; i < bins; i += TK_THREADS) hist[i] = 0u;
         __syncthreads();
         const unsigned prefix = sh_prefix, mask = sh_mask, digit_mask = (unsigned)bins - 1u;
-        if (pass == 0 && row_in_smem && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+        if (pass > 0 && compact) {
+            for (int i = tid; i < cand_n; i += TK_THREADS) {
+                const unsigned u = value((int)cand_ids[i]);
+                if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & digit_mask], 1u);
+            }
+        } else if (pass == 0 && row_in_smem && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
             // The first pass also brings the row into shared memory, TK_LOAD_DEPTH groups of four per thread at a
             // time.  A warp whose 128 scores all share one digit (constant rows, padding) adds once.
             for (int base = warp * 32; base < n4; base += TK_THREADS * TK_LOAD_DEPTH) {
@@ -588,9 +699,18 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
                 sh_prefix = prefix | ((unsigned)(tid * per + bin) << shift);
                 sh_mask = mask | (digit_mask << shift);
                 sh_remaining = left;  // how many entries equal to the final value are taken
+                sh_cand = mine[bin];   // members of the chosen bin
             }
         }
         __syncthreads();
+        if (!compact && pass < 2 && sh_cand <= TK_CAND_CAP) {
+            // Few members in the threshold bin (after the first pass for widely spread scores, after the second for
+            // scores that share their leading bits): one sweep writes everything in higher bins as entries and lists
+            // the bin's members; the remaining passes and the final choice then touch only that list.
+            compact = true;
+            sweep(sh_prefix >> shift, shift, 0x7fffffff, true);
+            cand_n = ties_before;
+        }
     }
     const unsigned threshold = sh_prefix;
     const int ties_wanted = sh_remaining;
@@ -598,82 +718,29 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
     //      the 32 consecutive tokens [round + 32t, round + 32t + 32): it records which are above and which tie as
     //      two bit masks, a scan over the CTA gives its place in the output, and it writes its own entries.  Lane l
     //      starts its walk at element l of its chunk, so the 32 lanes of a warp hit 32 different banks.
-    int out_base = 0, ties_before = 0;  // the same in every thread
-    for (int round = 0; round < n; round += 32 * TK_THREADS) {
-        const int c = round + tid * 32;
-        unsigned above_mask = 0u, tie_mask = 0u;
-        if (row_in_smem && c + 32 <= n) {
-            // eight 16-byte reads; bit p of the masks built here belongs to element (p + 4 * lane) mod 32
+    if (!compact) {
+        sweep(threshold, 0, ties_wanted, false);
+    } else {  // the same choice among the listed candidates, two consecutive ones per thread
+        unsigned u[2] = {0u, 0u}, id[2] = {0u, 0u};
+        bool above[2] = {false, false}, tie[2] = {false, false};
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const uint4 v = reinterpret_cast<const uint4*>(srow + c)[(q + lane) & 7];
-                above_mask |= ((unsigned)(v.x > threshold) << (4 * q)) | ((unsigned)(v.y > threshold) << (4 * q + 1)) |
-                              ((unsigned)(v.z > threshold) << (4 * q + 2)) | ((unsigned)(v.w > threshold) << (4 * q + 3));
-                tie_mask |= ((unsigned)(v.x == threshold) << (4 * q)) | ((unsigned)(v.y == threshold) << (4 * q + 1)) |
-                            ((unsigned)(v.z == threshold) << (4 * q + 2)) | ((unsigned)(v.w == threshold) << (4 * q + 3));
-            }
-            above_mask = __funnelshift_l(above_mask, above_mask, 4 * lane);
-            tie_mask = __funnelshift_l(tie_mask, tie_mask, 4 * lane);
-        } else if (c < n) {
-            for (int j = 0; j < 32; ++j) {
-                const int jj = (j + lane) & 31;
-                if (c + jj < n) {
-                    const unsigned u = value(c + jj);
-                    above_mask |= (unsigned)(u > threshold) << jj;
-                    tie_mask |= (unsigned)(u == threshold) << jj;
-                }
+        for (int e = 0; e < 2; ++e) {
+            const int i = 2 * tid + e;
+            if (i < cand_n) {
+                id[e] = cand_ids[i];
+                u[e] = value((int)id[e]);
+                above[e] = u[e] > threshold;
+                tie[e] = u[e] == threshold;
             }
         }
-        const int ca = __popc(above_mask), ct = __popc(tie_mask);
-        int ia = ca, it = ct;  // inclusive scans inside the warp
+        int ex_a, ex_t, total_a, total_t;
+        scan_counts((int)above[0] + (int)above[1], (int)tie[0] + (int)tie[1], ex_a, ex_t, total_a, total_t);
+        int pos = out_base + ex_a + min(ties_wanted, ex_t), ties_seen = ex_t;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int ya = __shfl_up_sync(0xffffffffu, ia, o), yt = __shfl_up_sync(0xffffffffu, it, o);
-            if (lane >= o) {
-                ia += ya;
-                it += yt;
-            }
+        for (int e = 0; e < 2; ++e) {
+            if (above[e] || (tie[e] && ties_seen < ties_wanted)) keys[pos++] = ((unsigned long long)(~u[e]) << 32) | id[e];
+            ties_seen += (int)tie[e];
         }
-        if (lane == 31) {
-            w_above[warp] = ia;
-            w_tie[warp] = it;
-        }
-        __syncthreads();
-        int wa = w_above[lane], wt = w_tie[lane];  // every warp scans the 32 warp totals for itself
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int ya = __shfl_up_sync(0xffffffffu, wa, o), yt = __shfl_up_sync(0xffffffffu, wt, o);
-            if (lane >= o) {
-                wa += ya;
-                wt += yt;
-            }
-        }
-        const int round_above = __shfl_sync(0xffffffffu, wa, 31), round_ties = __shfl_sync(0xffffffffu, wt, 31);
-        const int warp_a = warp ? __shfl_sync(0xffffffffu, wa, (warp + 31) & 31) : 0;  // totals of the warps before
-        const int warp_t = warp ? __shfl_sync(0xffffffffu, wt, (warp + 31) & 31) : 0;
-        const int ex_a = warp_a + ia - ca, ex_t = warp_t + it - ct;  // entries of earlier threads in this round
-        const int ties_open = max(ties_wanted - ties_before, 0);     // ties this round may still take
-        const int quota = max(0, min(ct, ties_open - ex_t));
-        unsigned take = tie_mask;
-        if (quota < ct) {  // the lowest `quota` ids of this thread's ties
-            take = 0u;
-            unsigned m = tie_mask;
-            for (int x = 0; x < quota; ++x) {
-                const unsigned low = m & (0u - m);
-                take |= low;
-                m ^= low;
-            }
-        }
-        int pos = out_base + ex_a + min(ties_open, ex_t);
-        unsigned sel = above_mask | take;
-        while (sel) {
-            const int jj = __ffs(sel) - 1;
-            sel &= sel - 1u;
-            const int i = c + jj;
-            keys[pos++] = ((unsigned long long)(~value(i)) << 32) | (unsigned)i;
-        }
-        out_base += round_above + min(ties_open, round_ties);
-        ties_before += round_ties;
         __syncthreads();
     }
     // ---- sort of the 2048 entries, best first.  The sweep above wrote them in id order, so a stable sort on the score
