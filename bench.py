@@ -108,7 +108,7 @@ class GqaDecodeB32:
     metric, unit, bound = "attn_decode_hbm_gbs", "GB/s", "hbm"
     kernel = "gqa_decode_partial_kernel"
     launches_per_step = 3  # rope+append, split-KV partial, combine
-    traffic = 1.0319e9 + 15.2e6  # DRAM bytes read + written per launch, ncu (profiles/gqa_decode_partial_b32.md)
+    traffic = 1.0319e9 + 15.2e6  # DRAM bytes read + written per launch, from an ncu capture
     B, Hq, Hkv, D, P, CHUNK, THETA = 32, 48, 8, 128, 16, 512, 500000.0
 
     def __init__(self, be, rank):
@@ -209,7 +209,7 @@ class MlaDecode:
         import torch
         self.torch, self.be, self.ctx_len = torch, be, ctx_len
         self.name = f"mla_decode_{ctx_len // 1024}k"
-        # DRAM bytes per launch from ncu at 32k context (profiles/mla_decode_partial_32k.md); proportional to context
+        # DRAM bytes per launch from ncu at 32k context; proportional to context
         self.traffic = (37.89e6 + 0.12e6) * ctx_len / 32768
         row_bytes = (self.L + self.R) * 2
         self.n_caches = max(2, int(np.ceil(320e6 / (ctx_len * row_bytes))))  # rotate through > L2 worth of caches
@@ -360,7 +360,7 @@ class MlaSelectedDecode(MlaDecode):
         super().__init__(be, rank, ctx_len)
         torch = self.torch
         self.name = f"mla_selected_decode_{self.N_SEL}_of_{ctx_len // 1024}k"
-        self.traffic = 2.51e6 if (self.N_SEL, ctx_len) == (2048, 32768) else None  # ncu, profiles/dsa_scores_topk_32k.md
+        self.traffic = 2.51e6 if (self.N_SEL, ctx_len) == (2048, 32768) else None  # ncu
         g = torch.Generator(device="cpu").manual_seed(SEED + 31 + rank)
         ids = torch.randperm(ctx_len - 1, generator=g)[: self.N_SEL - 1].sort().values.to(torch.int32)
         self.sel = torch.cat([ids, torch.tensor([ctx_len - 1], dtype=torch.int32)]).view(1, -1).to(be.device)
@@ -413,7 +413,7 @@ class DsaSparseDecode(MlaSelectedDecode):
         self.n_variants = max(self.n_caches, self.n_key_sets)
         self.key_bytes = float(ctx_len) * self.DI * 4
         self.kernel_units_per_launch = self.key_bytes
-        self.traffic = 16.83e6 * ctx_len / 32768  # DRAM bytes read by the scores kernel, ncu (profiles/dsa_scores_topk_32k.md)
+        self.traffic = 16.83e6 * ctx_len / 32768  # DRAM bytes read by the scores kernel, from an ncu capture
         self.units_per_step = self.key_bytes + float(self.N_SEL) * (self.L + self.R) * 2
         self.flops_per_step += 2.0 * self.HI * self.DI * ctx_len
         self.config.update({"workload": self.name, "index_heads": self.HI, "index_dim": self.DI,
@@ -453,7 +453,7 @@ class GqaPrefill2k:
     metric, unit, bound = "gqa_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_gqa_kernel"
     launches_per_step = 2  # rope+append, flash prefill
-    traffic = 33.64e6 + 0.35e6  # DRAM bytes per launch, ncu (profiles/flash_prefill_gqa_2k.md)
+    traffic = 33.64e6 + 0.35e6  # DRAM bytes per launch, from an ncu capture
     T, Hq, Hkv, D, P, THETA = 2048, 48, 8, 128, 16, 500000.0
     max_steps = 400
     N_SETS = 8
@@ -536,7 +536,7 @@ class MlaPrefill32k:
     metric, unit, bound = "mla_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_mla_kernel"
     launches_per_step = 1
-    # ncu at 8192 tokens: 2.151 GB read + 0.138 GB written (profiles/flash_prefill_mla_8k.md).  K/V re-streaming grows
+    # ncu at 8192 tokens: 2.151 GB read + 0.138 GB written.  K/V re-streaming grows
     # with tokens^2 and the output with tokens, so a full 32768-token launch is estimated at 16x / 4x of those.
     traffic = 2.152e9 * 16 + 0.138e9 * 4
     T, H = 32768, 64
@@ -687,6 +687,7 @@ def kernel_time(be, torch, wl, steps):
 def cpu_baseline(wl, budget_s=12.0):
     """The oracle (a scalar port of the reference kernels) on all host threads, on a bounded sample."""
     from oracle import pyoracle as orc
+    orc.use_all_host_threads()
     run, units, sample = wl.cpu_sample()
     t0 = time.perf_counter()
     run()
@@ -805,6 +806,7 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import pyoracle as orc
+    orc.use_all_host_threads()  # the same thread count at every N: a launcher's OMP_NUM_THREADS=1 does not apply
     protos = {"gqa_decode_b32": GqaDecodeB32, "mla_decode_4k": MlaDecode, "mla_decode_32k": MlaDecode,
               "gqa_prefill_2k": GqaPrefill2k, "mla_prefill_32k": MlaPrefill32k}
     cls = protos[args.workload]

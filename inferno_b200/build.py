@@ -1,8 +1,13 @@
 """Builds libinferno_attn.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python -m inferno_b200.build [--force]
+    python -m inferno_b200.build [--force] [--kprof]
 
 nvcc cross-compiles without a GPU, so this runs anywhere the CUDA toolkit is installed.
+
+--kprof builds a second, instrumented copy of the library into inferno_b200/kprof/ (compiled with
+-DINF_KPROF: the tcgen05 kernels record a timeline of one CTA with %globaltimer and the host prints it to
+stderr after each launch, synchronising to do so).  It is a diagnostic build, never the default; select it
+with INFERNO_ATTN_LIB=inferno_b200/kprof/libinferno_attn.so.
 """
 from __future__ import annotations
 
@@ -31,12 +36,12 @@ def _newest_header() -> float:
     return t
 
 
-def _compile(src: str, force: bool) -> str:
-    obj = os.path.join(CSRC, src[:-3] + ".o")
+def _compile(src: str, force: bool, out_dir: str = CSRC, extra=()) -> str:
+    obj = os.path.join(out_dir, src[:-3] + ".o")
     spath = os.path.join(CSRC, src)
     if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(spath), _newest_header()):
         return obj
-    log = subprocess.run([NVCC, *FLAGS, "-c", spath, "-o", obj], capture_output=True, text=True)
+    log = subprocess.run([NVCC, *FLAGS, *extra, "-c", spath, "-o", obj], capture_output=True, text=True)
     with open(obj + ".log", "w") as f:
         f.write(log.stdout + log.stderr)
     if log.returncode != 0:
@@ -44,17 +49,22 @@ def _compile(src: str, force: bool) -> str:
     return obj
 
 
-def build(force: bool = False) -> str:
+def build(force: bool = False, kprof: bool = False) -> str:
     srcs = sources()
+    out_dir, lib, extra = CSRC, LIB, ()
+    if kprof:
+        out_dir = os.path.join(HERE, "kprof")
+        os.makedirs(out_dir, exist_ok=True)
+        lib, extra = os.path.join(out_dir, "libinferno_attn.so"), ("-DINF_KPROF",)
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile(s, force), srcs))
-    if force or not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
-        r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcudart_static", "-ldl", "-lpthread", "-lrt"],
+        objs = list(ex.map(lambda s: _compile(s, force, out_dir, extra), srcs))
+    if force or not os.path.exists(lib) or any(os.path.getmtime(o) > os.path.getmtime(lib) for o in objs):
+        r = subprocess.run([NVCC, "-shared", "-o", lib, *objs, "-lcudart_static", "-ldl", "-lpthread", "-lrt"],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    print(build(force="--force" in sys.argv, kprof="--kprof" in sys.argv))

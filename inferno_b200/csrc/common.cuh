@@ -15,7 +15,8 @@
 // Bits of the device status word (ctx->status[0]); kernels OR them in and keep going safely.
 #define INF_STATUS_WAIT_TIMEOUT 1  // a bounded mbarrier wait gave up
 #define INF_STATUS_BAD_PAGE 2      // a page id outside the pool was refused
-#define INF_STATUS_BAD_LEN 4       // a length that does not fit the page table
+#define INF_STATUS_BAD_LEN 4       // a length that does not fit the page table or the size the launch was given
+#define INF_STATUS_BAD_SMEM 8      // the dynamic shared-memory base is not aligned as the tiles need
 
 typedef CUresult (*inf_tmap_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -174,10 +174,11 @@ int32_t inf_flush(inf_ctx* ctx) {
     int s = ctx->host_status[0];
     if (s != 0) {
         INF_CUDA(ctx, cudaMemsetAsync(ctx->status, 0, 16, ctx->stream));
-        return inf_fail(ctx, INF_E_BACKEND, "device status word 0x%x:%s%s%s", s,
+        return inf_fail(ctx, INF_E_BACKEND, "device status word 0x%x:%s%s%s%s", s,
                         (s & INF_STATUS_WAIT_TIMEOUT) ? " bounded wait gave up;" : "",
                         (s & INF_STATUS_BAD_PAGE) ? " page id outside the pool;" : "",
-                        (s & INF_STATUS_BAD_LEN) ? " length beyond the page table;" : "");
+                        (s & INF_STATUS_BAD_LEN) ? " length beyond the page table or max_len;" : "",
+                        (s & INF_STATUS_BAD_SMEM) ? " shared-memory base misaligned;" : "");
     }
     return INF_OK;
 }

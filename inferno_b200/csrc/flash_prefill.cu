@@ -172,7 +172,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int kvh = PAGED ? st[act0 ? 0 : 1].head / p.group : st[act0 ? 0 : 1].head;
 
     if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
-        if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        if (tid == 0) atomicOr(p.status, INF_STATUS_BAD_SMEM);
         return;
     }
     if (tid == 0) {

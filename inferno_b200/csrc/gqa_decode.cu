@@ -17,6 +17,9 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -83,8 +86,14 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     inf_pdl_release();
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kv_len = p.lens[b] + p.len_add;
+    int kv_len = p.lens[b] + p.len_add;
     if (kv_len <= 0) return;
+    // A length beyond what the launch was sized for (max_len -> max_chunks partial slots per sequence) is cut
+    // to that size and reported: no partial slot past the sequence's own is ever written.
+    if (kv_len > p.max_chunks * p.chunk) {
+        kv_len = p.max_chunks * p.chunk;
+        if (tid == 0 && blockIdx.x == 0 && kvh == 0) atomicOr(p.status, INF_STATUS_BAD_LEN);
+    }
     const int win_start = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
     const int first_chunk = win_start / p.chunk;
     const int cpc = p.chunks_per_cta;
@@ -93,7 +102,7 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     if (run_begin >= kv_len) return;
     const int run_end = min(kv_len, run_begin + cpc * p.chunk);
     if ((smem_u32(smem) & 1023u) != 0) {
-        if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        if (tid == 0) atomicOr(p.status, INF_STATUS_BAD_SMEM);
         return;
     }
 
@@ -371,15 +380,16 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
     inf_pdl_wait();
     inf_pdl_release();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-    const int kv_len = lens[b] + len_add;
+    int kv_len = lens[b] + len_add;
     const long long orow = ((long long)b * q_heads + h) * D + d;
     if (kv_len <= 0) {
         out[orow] = OutT(0.f);
         return;
     }
+    kv_len = min(kv_len, max_chunks * chunk);  // the partial kernel cut it the same way and raised the status word
     const int win_start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int first_chunk = win_start / chunk;
-    const int n = (kv_len + chunk - 1) / chunk - first_chunk;  // <= 512, checked on the host
+    const int n = (kv_len + chunk - 1) / chunk - first_chunk;  // <= max_chunks <= 512
     const long long prow0 = ((long long)b * max_chunks) * q_heads + h;
     float mloc = M_INIT;
     for (int c = d; c < n; c += D) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)c * q_heads) * 2]);
@@ -546,8 +556,10 @@ static __device__ __align__(256) unsigned char g_decode_static_scratch[INF_GQA_D
 
 namespace {
 constexpr int MAX_DEVICES = 64;
-void* g_static_scratch_ptr[MAX_DEVICES] = {};
-bool g_static_scratch_ready[MAX_DEVICES] = {};
+// Written once per device under the mutex, read afterwards through the atomic: two host threads making
+// their first call on one device at the same time both end up with the same, fully resolved pointer.
+std::atomic<void*> g_static_scratch_ptr[MAX_DEVICES];
+std::mutex g_static_scratch_mutex;
 }  // namespace
 
 extern "C" int32_t inf_gqa_decode_paged_static(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
@@ -566,23 +578,25 @@ extern "C" int32_t inf_gqa_decode_paged_static(inf_ctx* ctx, const void* q_f16, 
                         (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES);
     if (ctx->device < 0 || ctx->device >= MAX_DEVICES)
         return inf_fail(ctx, INF_E_ARG, "gqa_decode_static: device ordinal %d is out of range", ctx->device);
-    if (!g_static_scratch_ready[ctx->device]) {
+    void* scratch = g_static_scratch_ptr[ctx->device].load(std::memory_order_acquire);
+    if (!scratch) {
         // first call on this device: resolve the array's device address with this device current
-        int current = -1;
-        INF_CUDA(ctx, cudaGetDevice(&current));
-        if (current != ctx->device) INF_CUDA(ctx, cudaSetDevice(ctx->device));
-        void* ptr = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
-        if (current != ctx->device) cudaSetDevice(current);
-        if (e != cudaSuccess || !ptr)
-            return inf_fail(ctx, INF_E_BACKEND, "gqa_decode_static: cudaGetSymbolAddress failed: %s",
-                            cudaGetErrorString(e));
-        g_static_scratch_ptr[ctx->device] = ptr;
-        g_static_scratch_ready[ctx->device] = true;
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        scratch = g_static_scratch_ptr[ctx->device].load(std::memory_order_relaxed);
+        if (!scratch) {
+            int current = -1;
+            INF_CUDA(ctx, cudaGetDevice(&current));
+            if (current != ctx->device) INF_CUDA(ctx, cudaSetDevice(ctx->device));
+            cudaError_t e = cudaGetSymbolAddress(&scratch, g_decode_static_scratch);
+            if (current != ctx->device) cudaSetDevice(current);
+            if (e != cudaSuccess || !scratch)
+                return inf_fail(ctx, INF_E_BACKEND, "gqa_decode_static: cudaGetSymbolAddress failed: %s",
+                                cudaGetErrorString(e));
+            g_static_scratch_ptr[ctx->device].store(scratch, std::memory_order_release);
+        }
     }
     // Nothing in the array has to start at zero: every partial the combine kernel reads is written
     // by the partial kernel of the same call first.
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
-                                 out, out_dtype, g_static_scratch_ptr[ctx->device],
-                                 (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES, 0);
+                                 out, out_dtype, scratch, (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES, 0);
 }

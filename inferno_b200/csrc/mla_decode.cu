@@ -113,7 +113,11 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int t = blockIdx.y % p.tokens, hb = blockIdx.y / p.tokens;
     const int b = blockIdx.z;
     const int seq_rows = p.lens[b] + t + 1;                     // rows visible to this query token
-    const int kv_len = GATHER ? p.sel_counts[b] : seq_rows;  // keys this call attends to
+    int kv_len = GATHER ? p.sel_counts[b] : seq_rows;  // keys this call attends to
+    if (GATHER && kv_len > p.sel_stride) {  // a count beyond the list's row is cut to the row and reported
+        kv_len = p.sel_stride;
+        if (tid == 0 && split == 0) atomicOr(p.status, INF_STATUS_BAD_LEN);
+    }
     // this CTA's keys: rows [row_begin, row_end) of the sequence (contiguous form: whole pages) or of the list
     const int unit = GATHER ? GATHER_UNIT : PAGE;
     int u_begin, u_end;
@@ -123,7 +127,7 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int n = (row_end - row_begin + PAGE - 1) / PAGE;  // 64-row tiles
     if (n <= 0) return;
     if ((smem_u32(smem) & 1023u) != 0) {
-        if (tid == 0) atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
+        if (tid == 0) atomicOr(p.status, INF_STATUS_BAD_SMEM);
         return;
     }
     if (tid == 0) {
@@ -500,7 +504,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(512)
 mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, const int* __restrict__ counts, OutT* __restrict__ out, int tokens,
-                          int heads, int n_splits) {
+                          int heads, int n_splits, int sel_stride) {
     __shared__ float w[MAX_SPLITS];
     __shared__ float red[16];
     __shared__ float group_acc[7][LAT];
@@ -508,7 +512,13 @@ mla_decode_combine_kernel(const __half* __restrict__ part_acc, const float* __re
     inf_pdl_release();
     const int h = blockIdx.x, t = blockIdx.y % tokens, b = blockIdx.y / tokens;
     const int tid = threadIdx.x;
-    const int kv_len = counts ? counts[b] : lens[b] + t + 1;  // keys the partial kernel saw
+    int kv_len = counts ? counts[b] : lens[b] + t + 1;  // keys the partial kernel saw
+    if (counts) kv_len = min(kv_len, sel_stride);
+    if (kv_len <= 0) {  // no key at all (an empty list, a negative length): no partial was written; the output is zero
+        OutT* dst = out + ((((long long)b * tokens + t) * heads) + h) * LAT + tid;
+        *dst = OutT(0.f);
+        return;
+    }
     const int n_pages = (kv_len + (counts ? GATHER_UNIT : PAGE) - 1) / (counts ? GATHER_UNIT : PAGE);  // split units
     const int per = (n_pages + n_splits - 1) / n_splits;
     const int n_valid = (n_pages + per - 1) / per;  // splits [0, n_valid) did work
@@ -686,10 +696,10 @@ int inf_mla_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_mla_pool* p
     dim3 cgrid(heads, tokens * table->batch);
     if (out_dtype == INF_DTYPE_F32)
         INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<float>, cgrid, dim3(512), 0, ctx->stream, p.part_acc,
-                                     p.part_ml, table->lens, sel_counts, (float*)out, tokens, heads, n_splits));
+                                     p.part_ml, table->lens, sel_counts, (float*)out, tokens, heads, n_splits, sel_stride));
     else
         INF_CUDA(ctx, inf_launch_pdl(mla_decode_combine_kernel<__half>, cgrid, dim3(512), 0, ctx->stream, p.part_acc,
-                                     p.part_ml, table->lens, sel_counts, (__half*)out, tokens, heads, n_splits));
+                                     p.part_ml, table->lens, sel_counts, (__half*)out, tokens, heads, n_splits, sel_stride));
     INF_LAUNCH_CHECK(ctx, "mla_decode_combine_kernel");
     return INF_OK;
 }

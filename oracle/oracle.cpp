@@ -75,6 +75,15 @@ int orc_max_threads(void) {
 #endif
 }
 
+// Number of OpenMP threads later calls use (a launcher may have exported OMP_NUM_THREADS=1 for its workers).
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 uint16_t orc_f32_to_f16(float x) {
     uint32_t u = f32_bits(x);
     uint32_t sign = (u >> 16) & 0x8000u;

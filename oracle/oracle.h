@@ -140,6 +140,7 @@ void orc_causal_mha(const float* q, const float* k_nope, const float* k_rope, co
                     int threads);
 
 int orc_max_threads(void);
+void orc_set_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -61,6 +61,14 @@ def max_threads() -> int:
     return int(lib().orc_max_threads())
 
 
+def use_all_host_threads() -> int:
+    """Make later oracle calls use every core this process may run on, whatever OMP_NUM_THREADS says (torchrun
+    exports OMP_NUM_THREADS=1 to its workers).  Returns the thread count now in use."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_threads(C.c_int(n))
+    return max_threads()
+
+
 def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
     x = _f32(x)
     f = lib().orc_f32_to_f16

@@ -13,6 +13,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _worker(rank, world, uid_q, res_q):
+    import traceback
+    try:
+        _rank_body(rank, world, uid_q, res_q)
+    except Exception:  # report instead of leaving the parent to time out
+        res_q.put((rank, False, traceback.format_exc()))
+
+
+def _rank_body(rank, world, uid_q, res_q):
     import sys
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -41,7 +49,7 @@ def _worker(rank, world, uid_q, res_q):
                                                 v[:, kb:ke].contiguous(), scale)
     gathered = be.allgather_heads(local)
     be.device_flush()
-    res_q.put((rank, bool(torch.equal(gathered, full))))
+    res_q.put((rank, bool(torch.equal(gathered, full)), "gathered output differs from the single-GPU result"))
     be.close()
 
 
@@ -52,10 +60,6 @@ def test_head_sharded_prefill_allgather_matches_single_gpu():
     ctx = mp.get_context("spawn")
     uid_q, res_q = ctx.Queue(), ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, 2, uid_q, res_q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    results = [res_q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
-    assert all(ok for _, ok in results), results
+    from tests.workloads import collect_ranks
+    results = collect_ranks(procs, res_q, timeout=300)
+    assert sorted(r[0] for r in results) == [0, 1]

@@ -117,6 +117,107 @@ def test_decode_matches_oracle(be, lens, Hq, Hkv, chunk, window, use_gate):
     assert_close(out16.float().cpu().numpy(), want[:, 0], "fp16 output")
 
 
+def _decode_case(be, lens, Hq, Hkv, chunk, seed, theta=500000.0):
+    """Fused RoPE + append of the current token, then split-KV decode, against the oracle on the same bits."""
+    D, P = 128, 16
+    B = len(lens)
+    lens = [int(n) for n in lens]
+    pages = [(n + P - 1) // P for n in lens]
+    num_pages = sum(pages) + 64
+    pt = scatter_pages(pages, num_pages, seed)
+    past = [n - 1 for n in lens]
+    kp, vp = fill_gqa_pools(past, pt, num_pages, Hkv, P, D, seed)
+    q = orc.fill_normal((B, 1, Hq, D), seed + 11)
+    k = orc.fill_normal((B, 1, Hkv, D), seed + 12)
+    v = orc.fill_normal((B, 1, Hkv, D), seed + 13)
+    inv = orc.default_inv_freq(theta, 64)
+    pos = np.array(past, np.int32)
+    pool = be.prepare_kv_pool(num_pages, P, Hkv, D)
+    pool.k.copy_(dev(be, kp).view(torch.float16))
+    pool.v.copy_(dev(be, vp).view(torch.float16))
+    want = orc.gqa_paged_attention(orc.qk_norm_rope(q, None, inv, 64, 0, positions=pos),
+                                   orc.qk_norm_rope(k, None, inv, 64, 0, positions=pos), v, None, kp, vp, pt, past, P)
+    rope = be.prepare_rope_table(inv, 64, 1.0)
+    # no host mirrors: the launch is sized by max_len alone, as in a replayed CUDA graph
+    q16 = be.rope_append_gqa(dev(be, q, torch.float16), dev(be, k, torch.float16), dev(be, v, torch.float16), rope, pool,
+                             be.page_table(pt, past, validate_on_host=False))
+    outs = [be.gqa_decode_paged(q16[:, 0].contiguous(), pool, be.page_table(pt, lens, validate_on_host=False),
+                                max_len=max(lens), split_chunk=c) for c in chunk]
+    be.device_flush()
+    # appended V rows are copied, not computed: the pools agree bit for bit (kp / vp now hold the oracle's append)
+    assert np.array_equal(pool.v.cpu().numpy().view(np.uint16), vp)
+    kd = pool.k.cpu().numpy().view(np.uint16).astype(np.int32)
+    assert np.abs(kd - kp.astype(np.int32)).max() <= 1
+    return [assert_close(o.cpu().numpy(), want[:, 0], f"decode chunk {c}") for o, c in zip(outs, chunk)]
+
+
+def test_config3_full_size(be):
+    """Batch 32, 48 / 8 heads, contexts U{1024..16384} from the benchmark's own seeded draw, split-KV chunk 512,
+    16-token pages scattered through one pool, RoPE theta 5e5 + append of the current token.  Every sequence is
+    longer than 2048 keys' worth of one CTA or spans several CTAs of a run (f16_attention_kernels.metal:325-510)."""
+    from bench import decode_lens
+    lens = decode_lens(0, 32)
+    assert lens.min() >= 1024 and lens.max() <= 16384 and (lens > 2048).sum() >= 20
+    _decode_case(be, lens, 48, 8, [512], SEED0 + 3)
+
+
+def test_long_sequence_spans_several_ctas(be):
+    """One 5000-key sequence: three CTAs per KV head each stream a run of chunks; partial slots are indexed by
+    run * chunks_per_cta + chunk.  Chunk 64 (79 partials) and chunk 512 (10 partials)."""
+    _decode_case(be, [5000, 2049, 4096], 48, 8, [64, 512, 2048], SEED0 + 33)
+
+
+def test_length_beyond_max_len_is_cut_and_reported(be):
+    """lens[b] > max_len with no host mirror (what a replayed graph with stale sizes would do): the kernels cut the
+    sequence to what the launch was sized for, never touch another sequence's partials, and inf_flush reports it."""
+    from inferno_b200 import InfernoError
+    D, P, Hq, Hkv = 128, 16, 12, 2
+    lens = [300, 900, 200]
+    pages = [(n + P - 1) // P for n in lens]
+    pt = scatter_pages(pages, sum(pages) + 3, SEED0 + 61)
+    pool = be.prepare_kv_pool(sum(pages) + 3, P, Hkv, D)
+    g = torch.Generator(device=be.device).manual_seed(SEED0 + 62)
+    pool.k.normal_(0, 1, generator=g)
+    pool.v.normal_(0, 1, generator=g)
+    q = torch.randn((3, Hq, D), generator=g, device=be.device, dtype=torch.float16)
+    be.device_flush()
+    good = be.gqa_decode_paged(q, pool, be.page_table(pt, lens), max_len=900, split_chunk=64)
+    be.device_flush()
+    # the same launch sized for 320 keys: sequence 1 does not fit
+    bad = be.gqa_decode_paged(q, pool, be.page_table(pt, lens, validate_on_host=False), max_len=320, split_chunk=64)
+    with pytest.raises(InfernoError) as e:
+        be.device_flush()
+    assert "length beyond" in str(e.value)
+    good, bad = good.cpu().numpy(), bad.cpu().numpy()
+    assert np.all(np.isfinite(bad))
+    assert np.array_equal(bad[0], good[0]) and np.array_equal(bad[2], good[2])  # the neighbours are untouched
+    # sequence 1 was attended over its first 320 keys only
+    cut = be.gqa_decode_paged(q, pool, be.page_table(pt, [300, 320, 200]), max_len=320, split_chunk=64)
+    be.device_flush()
+    assert np.array_equal(bad[1], cut.cpu().numpy()[1])
+    # with the host mirror the same call is refused before any launch
+    with pytest.raises(InfernoError) as e:
+        be.gqa_decode_paged(q, pool, be.page_table(pt, lens), max_len=320, split_chunk=64)
+    assert e.value.kind == "ShapeMismatch"
+    be.device_flush()
+
+
+def test_bad_page_id_is_refused_on_the_device(be):
+    """A page id outside the pool, with no host mirror: the kernel reads zeros instead (no address is formed from
+    the id) and inf_flush reports it."""
+    from inferno_b200 import InfernoError
+    D, P, Hq, Hkv = 128, 16, 12, 2
+    pool = be.prepare_kv_pool(8, P, Hkv, D)
+    q = torch.randn((1, Hq, D), device=be.device, dtype=torch.float16)
+    out = be.gqa_decode_paged(q, pool, be.page_table([[0, 1, 99, 3]], [60], validate_on_host=False), max_len=64,
+                              split_chunk=64)
+    with pytest.raises(InfernoError) as e:
+        be.device_flush()
+    assert "page id outside" in str(e.value)
+    assert np.all(np.isfinite(out.cpu().numpy()))
+    be.device_flush()  # the status word was cleared by the failed flush
+
+
 def test_rmsnorm_rope_pair_matches_oracle(be):
     """laguna_qk_rms_norm_rope_pair_device on the reference's own test shapes (metal/rope.rs:621-710), tol 3e-5."""
     D, rotary, theta, factor, pos = 128, 64, 500000.0, 1.3465736, 7

@@ -118,3 +118,30 @@ def test_row_outside_the_sequence_is_reported(be):
     be.mla_decode_absorbed_selected(q, pool, table, sel, dev(be, np.array([3], np.int32)), 0.07)
     with pytest.raises(InfernoError):
         be.device_flush()
+
+
+def test_count_beyond_the_list_and_empty_list(be):
+    """counts[b] > selected_stride is cut to the stride and reported (the kernel never reads past a sequence's row of
+    the list); counts[b] == 0 gives a zero output row instead of a division by zero in the merge."""
+    from inferno_b200 import InfernoError
+    n, H = 500, 64
+    seed = SEED0 + 996
+    pt = scatter_pages([8, 8], 20, seed)
+    pool_np = fill_mla_pool([n, n], pt, 20, P, L + R, seed)
+    pool = be.prepare_mla_pool(20)
+    pool.rows.copy_(dev(be, pool_np).view(torch.float16))
+    table = be.page_table(pt, [n - 1, n - 1])
+    q = dev(be, orc.fill_normal((2, 1, H, L + R), seed + 1), torch.float16)
+    ids = np.sort(np.random.RandomState(seed).permutation(n)[:70]).astype(np.int32)
+    sel = dev(be, np.stack([ids, ids]))
+    scale = 1.0 / math.sqrt(192.0)
+    want = be.mla_decode_absorbed_selected(q, pool, table, sel, dev(be, np.array([70, 70], np.int32)), scale)
+    be.device_flush()
+    got = be.mla_decode_absorbed_selected(q, pool, table, sel, dev(be, np.array([0, 9999], np.int32)), scale)
+    with pytest.raises(InfernoError) as e:
+        be.device_flush()
+    assert "length beyond" in str(e.value)
+    got, want = got.cpu().numpy(), want.cpu().numpy()
+    assert np.all(got[0] == 0.0)
+    assert np.array_equal(got[1], want[1])
+    be.device_flush()

@@ -20,6 +20,14 @@ def _free_port():
 
 
 def _worker(rank, world, port, q_out):
+    import traceback
+    try:
+        _rank_body(rank, world, port, q_out)
+    except Exception:  # report instead of leaving the parent to time out
+        q_out.put((rank, False, traceback.format_exc()))
+
+
+def _rank_body(rank, world, port, q_out):
     import sys
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -42,7 +50,7 @@ def _worker(rank, world, port, q_out):
     mine[b:e] = 1
     dist.all_reduce(mine)
     ok_seq = bool((mine == 1).all())
-    q_out.put((rank, ok_heads, ok_seq))
+    q_out.put((rank, ok_heads and ok_seq, f"heads {ok_heads}, sequences {ok_seq}"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -54,11 +62,6 @@ def test_head_sharding_allgather_and_sequence_sharding_world2():
     q_out = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q_out)) for r in range(2)]
-    for p in procs:
-        p.start()
-    results = [q_out.get(timeout=120) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    from tests.workloads import collect_ranks
+    results = collect_ranks(procs, q_out, timeout=120)
     assert sorted(r[0] for r in results) == [0, 1]
-    assert all(r[1] and r[2] for r in results), results

@@ -66,3 +66,34 @@ def fill_mla_pool(lens, page_table, num_pages, page_size, width, seed, sigma=0.5
             t0, t1 = s * page_size, min(n, (s + 1) * page_size)
             pool[page_table[b, s], :t1 - t0] = rows[t0:t1]
     return pool
+
+
+def collect_ranks(procs, queue, timeout):
+    """Start `procs`, take one (rank, ok, detail) tuple per process from `queue`, and never leave a rank behind:
+    whatever happens (a rank that raised, one that blocks in a collective, a timeout here) every process still
+    alive at the end is terminated, then killed."""
+    import queue as queue_mod
+    results = []
+    try:
+        for p in procs:
+            p.start()
+        for _ in procs:
+            try:
+                r = queue.get(timeout=timeout)
+            except queue_mod.Empty:
+                raise AssertionError(f"a rank did not report within {timeout} s; got {results}")
+            results.append(r)
+            if not r[1]:
+                raise AssertionError(f"rank {r[0]} failed: {r[2]}")
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0, f"rank process exited with {p.exitcode}"
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+    return results
