@@ -11,9 +11,16 @@ resident in HBM; `e2e` is the same metric through the public API with host buffe
 device copy of the step's Q/K/V and a device -> host read of the output inside the timed region).
 Other workloads of the path are measured in the same run and reported under "workloads".
 
-With N > 1 (torchrun, one rank per GPU) sequences are sharded across ranks -- every rank owns its own
-batch and pages, no data-path collective -- and `value` is the sum over ranks divided by the slowest
-rank's time (weak scaling).
+With N > 1 (torchrun, one rank per GPU) the headline shards by sequence with fixed work per GPU -- every rank
+owns its own batch of 32 and its pages, no data-path collective -- and `value` is the sum over ranks divided by
+the slowest rank's time (weak scaling).  The same run also measures, under "workloads", the strong-scaled forms
+of the path: the batch of 32 split 32/N sequences per rank with the [32, 48, 128] output all-gathered, and both
+prefills head-sharded with the all-gather of the attention output inside the step.  Those gathers go through
+the library's own collective (inf_allgather_heads: NCCL behind the C ABI); torch.distributed only carries the
+rendezvous, the barriers and the reductions of the timings.
+
+Every timed figure is the median of several regions of exactly K steps, each region bracketed by a barrier and a
+synchronize on both sides and taken as the maximum over ranks.
 
 `--impl reference` times the CPU oracle (a scalar port of the reference's kernels; the reference is
 Rust + Metal and cannot be built here) on the host cores, on a bounded sample of the same workload.
@@ -103,23 +110,45 @@ def decode_lens(rank: int, batch: int = 32):
 
 
 class GqaDecodeB32:
-    """Paged GQA decode, batch 32 (the third benchmark configuration)."""
+    """Paged GQA decode, batch 32 (the third benchmark configuration).  Weak scaling: every rank owns its own batch
+    of 32 (different seeded lengths per rank).  Strong scaling (`strong=True`): rank 0's batch of 32 is split into
+    32/N sequences per rank and the [32, 48, 128] f32 output is all-gathered."""
     name = "gqa_decode_b32"
     metric, unit, bound = "attn_decode_hbm_gbs", "GB/s", "hbm"
     kernel = "gqa_decode_partial_kernel"
     launches_per_step = 3  # rope+append, split-KV partial, combine
-    traffic = 1.0319e9 + 15.2e6  # DRAM bytes read + written per launch, from an ncu capture
+    traffic = 1.0319e9 + 15.2e6  # DRAM bytes read + written per launch of the full batch, from an ncu capture
     B, Hq, Hkv, D, P, CHUNK, THETA = 32, 48, 8, 128, 16, 512, 500000.0
 
-    def __init__(self, be, rank):
+    @classmethod
+    def describe(cls, lens, strong=False):
+        units = float(np.asarray(lens, np.int64).sum()) * cls.Hkv * cls.D * 2 * 2
+        return {"workload": cls.name + ("_strong" if strong else ""), "batch": cls.B, "q_heads": cls.Hq,
+                "kv_heads": cls.Hkv, "head_dim": cls.D, "page_size": cls.P, "split_chunk": cls.CHUNK,
+                "context": "U{1024..16384} seeded", "sum_context": int(np.asarray(lens).sum()),
+                "rope_theta": cls.THETA, "kv_bytes_per_step": int(units),
+                "l2": "inputs larger than L2 (KV bytes per step >> 126 MB)",
+                "sharding": "by sequence, 32/N per rank, output all-gathered" if strong else "by sequence"}
+
+    def __init__(self, be, rank, world=1, strong=False):
         import torch
-        self.torch, self.be = torch, be
-        self.lens = decode_lens(rank, self.B)
+        from inferno_b200.sharding import shard_sequences
+        self.torch, self.be, self.world, self.strong = torch, be, world, strong
+        all_lens = decode_lens(0 if strong else rank, self.B)
+        if strong:
+            b0, b1 = shard_sequences(self.B, world, rank)
+            assert self.B % world == 0, "the gather wants equal blocks"
+            self.lens = all_lens[b0:b1]
+            self.name = self.name + "_strong"
+            self.scaling = "strong"
+        else:
+            self.lens = all_lens
+        Bl = self.Bl = len(self.lens)
         pages = (self.lens + self.P - 1) // self.P
         self.num_pages = int(pages.sum()) + 64
         g = torch.Generator(device="cpu").manual_seed(SEED + 5 + rank)
         perm = torch.randperm(self.num_pages, generator=g).to(torch.int32)
-        table = torch.full((self.B, int(pages.max())), 0, dtype=torch.int32)
+        table = torch.full((Bl, int(pages.max())), 0, dtype=torch.int32)
         o = 0
         for b, n in enumerate(pages):
             table[b, :n] = perm[o:o + n]
@@ -134,40 +163,45 @@ class GqaDecodeB32:
         self.rope = be.prepare_rope_table(inv.astype(np.float32), 64, 1.0)
         # q, k and v of a step are three views of one device buffer (and of one pinned host buffer), so that the
         # end-to-end step moves its inputs with a single host-to-device copy
-        nq, nk = self.B * self.Hq * self.D, self.B * self.Hkv * self.D
+        nq, nk = Bl * self.Hq * self.D, Bl * self.Hkv * self.D
         self.qkv = torch.randn((nq + 2 * nk,), generator=gd, device=be.device, dtype=torch.float16)
-        self.q = self.qkv[:nq].view(self.B, 1, self.Hq, self.D)
-        self.k = self.qkv[nq:nq + nk].view(self.B, 1, self.Hkv, self.D)
-        self.v = self.qkv[nq + nk:].view(self.B, 1, self.Hkv, self.D)
-        self.out = torch.empty((self.B, self.Hq, self.D), dtype=torch.float32, device=be.device)
+        self.q = self.qkv[:nq].view(Bl, 1, self.Hq, self.D)
+        self.k = self.qkv[nq:nq + nk].view(Bl, 1, self.Hkv, self.D)
+        self.v = self.qkv[nq + nk:].view(Bl, 1, self.Hkv, self.D)
+        self.out = torch.empty((Bl, self.Hq, self.D), dtype=torch.float32, device=be.device)
         self.hqkv = self.qkv.cpu().pin_memory()
         self.hq, self.hk, self.hv = self.hqkv[:nq], self.hqkv[nq:nq + nk], self.hqkv[nq + nk:]
-        self.hout = torch.empty((self.B, self.Hq, self.D), dtype=torch.float32).pin_memory()
+        self.collective = strong and world > 1
+        self.gather_bytes = self.out.numel() * 4 if self.collective else 0
+        self.gathered = torch.empty((world, Bl, self.Hq, self.D), dtype=torch.float32, device=be.device) if self.collective else None
+        result = self.gathered if self.collective else self.out
+        self.hout = torch.empty(result.shape, dtype=torch.float32).pin_memory()
         self.max_len = int(self.lens.max())
         self.i = 0
         self.units_per_step = float(self.lens.astype(np.int64).sum()) * self.Hkv * self.D * 2 * 2  # KV bytes
+        if strong:
+            self.traffic = None
         self.h2d = sum(t.numel() * t.element_size() for t in (self.hq, self.hk, self.hv))
         self.d2h = self.hout.numel() * 4
-        self.config = {"workload": self.name, "batch": self.B, "q_heads": self.Hq, "kv_heads": self.Hkv,
-                       "head_dim": self.D, "page_size": self.P, "split_chunk": self.CHUNK,
-                       "context": "U{1024..16384} seeded", "sum_context": int(self.lens.sum()),
-                       "rope_theta": self.THETA, "kv_bytes_per_step": int(self.units_per_step),
-                       "l2": "inputs larger than L2 (KV bytes per step >> 126 MB)", "sharding": "by sequence"}
+        self.config = self.describe(all_lens, strong)
 
     def step(self):
         q16 = self.be.rope_append_gqa(self.q, self.k, self.v, self.rope, self.pool, self.past)
-        self.be.gqa_decode_paged(q16.view(self.B, self.Hq, self.D), self.pool, self.full, self.max_len, self.CHUNK,
+        self.be.gqa_decode_paged(q16.view(self.Bl, self.Hq, self.D), self.pool, self.full, self.max_len, self.CHUNK,
                                  out=self.out)
+        if self.collective:
+            self.be.allgather_into(self.out, self.gathered)
 
     def step_e2e(self):
         self.qkv.copy_(self.hqkv, non_blocking=True)
         self.step()
-        self.hout.copy_(self.out, non_blocking=True)
+        self.hout.copy_(self.gathered if self.collective else self.out, non_blocking=True)
 
     # ---- CPU arm: the oracle on host arrays of the same shapes
-    def cpu_sample(self, rank=0, max_sequences=32):
+    @classmethod
+    def cpu_sample(cls, rank=0, max_sequences=32):
         from oracle import pyoracle as orc
-        c = self
+        c = cls
         lens = decode_lens(rank, c.B)[:max_sequences]
         pages = (lens + c.P - 1) // c.P
         num_pages = int(pages.sum()) + 8
@@ -243,11 +277,18 @@ class MlaDecode:
         self.flops_per_step = 2.0 * self.H * (self.L + self.R + self.L) * ctx_len
         self.h2d = self.hq.numel() * 2 + self.hx.numel() * 4
         self.d2h = self.hout.numel() * 4
-        self.config = {"workload": self.name, "batch": 1, "heads": self.H, "latent_dim": self.L, "rope_dim": self.R,
-                       "context": ctx_len, "page_size": self.P, "kv_sigma": 0.5, "scale": "1/sqrt(192)",
-                       "kv_bytes_per_step": int(self.units_per_step), "flops_per_step": self.flops_per_step,
-                       "l2": f"rotates through {self.n_caches} distinct caches ({self.n_caches * ctx_len * row_bytes / 1e6:.0f} MB > L2)",
-                       "sharding": "replicas"}
+        self.config = self.describe(ctx_len)
+
+    @classmethod
+    def describe(cls, ctx_len):
+        row_bytes = (cls.L + cls.R) * 2
+        n_caches = max(2, int(np.ceil(320e6 / (ctx_len * row_bytes))))
+        return {"workload": f"mla_decode_{ctx_len // 1024}k", "batch": 1, "heads": cls.H, "latent_dim": cls.L,
+                "rope_dim": cls.R, "context": ctx_len, "page_size": cls.P, "kv_sigma": 0.5, "scale": "1/sqrt(192)",
+                "kv_bytes_per_step": int(ctx_len * row_bytes),
+                "flops_per_step": 2.0 * cls.H * (cls.L + cls.R + cls.L) * ctx_len,
+                "l2": f"rotates through {n_caches} distinct caches ({n_caches * ctx_len * row_bytes / 1e6:.0f} MB > L2)",
+                "sharding": "replicas"}
 
     def step(self):
         t = self.tables[self.i % self.n_caches]
@@ -448,7 +489,7 @@ class DsaSparseDecode(MlaSelectedDecode):
 class GqaPrefill2k:
     """Causal GQA prefill, one 2048-token prompt, 48 q / 8 kv heads, fused RoPE + KV-append (fourth configuration).
     With N > 1 ranks the heads are sharded (48/N query heads with their 8/N KV heads per rank) and the output is
-    all-gathered over NCCL: strong scaling."""
+    all-gathered through the library's collective: strong scaling."""
     name = "gqa_prefill_2k"
     metric, unit, bound = "gqa_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_gqa_kernel"
@@ -457,10 +498,22 @@ class GqaPrefill2k:
     T, Hq, Hkv, D, P, THETA = 2048, 48, 8, 128, 16, 500000.0
     max_steps = 400
     N_SETS = 8
+    scaling = "strong"
 
-    def __init__(self, be, rank, world=1, dist=None):
+    @classmethod
+    def describe(cls, world=1):
+        set_mb = (cls.T * (cls.Hq + 2 * cls.Hkv) // world * cls.D * 2 * 2) / 1e6
+        return {"workload": cls.name, "tokens": cls.T, "q_heads": cls.Hq, "kv_heads": cls.Hkv,
+                "head_dim": cls.D, "page_size": cls.P, "rope_theta": cls.THETA, "causal": True,
+                "flops_per_step": 4.0 * cls.D * cls.Hq * cls.T * (cls.T + 1) / 2,
+                "append_bytes_per_step": cls.T * cls.Hkv * cls.D * 2 * 2,
+                "l2": f"rotates through {cls.N_SETS} distinct input sets and pools ({cls.N_SETS * set_mb:.0f} MB)",
+                "sharding": "heads" if world > 1 else "none",
+                "collective": "inf_allgather_heads (NCCL) of the output" if world > 1 else None}
+
+    def __init__(self, be, rank, world=1):
         import torch
-        self.torch, self.be, self.world, self.dist = torch, be, world, dist
+        self.torch, self.be, self.world = torch, be, world
         self.hq_local, self.hkv_local = self.Hq // world, self.Hkv // world
         pages = self.T // self.P
         gd = torch.Generator(device=be.device).manual_seed(SEED + 31 + rank)
@@ -476,30 +529,29 @@ class GqaPrefill2k:
             v = torch.randn((1, self.T, self.hkv_local, self.D), generator=gd, device=be.device, dtype=torch.float16)
             self.sets.append((pool, table, q, k, v))
         self.out = torch.empty((1, self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device)
-        self.gathered = torch.empty((world * self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device) if world > 1 else None
+        self.collective = world > 1
+        self.gather_bytes = self.out.numel() * 2 if world > 1 else 0
+        self.gathered = torch.empty((world, self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device) if world > 1 else None
         q, k, v = self.sets[0][2:]
         self.hq, self.hk, self.hv = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
-        self.hout = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
+        self.hout = torch.empty((self.gathered if world > 1 else self.out).shape, dtype=torch.float16).pin_memory()
         self.i = 0
         self.n_variants = self.N_SETS
         total_flops = 4.0 * self.D * self.Hq * self.T * (self.T + 1) / 2
         self.units_per_step = total_flops / world  # per rank; summed over ranks by the harness
         self.h2d = sum(t.numel() * 2 for t in (self.hq, self.hk, self.hv))
         self.d2h = self.hout.numel() * 2
-        set_mb = (self.T * (self.hq_local + 2 * self.hkv_local) * self.D * 2 * 2) / 1e6
-        self.config = {"workload": self.name, "tokens": self.T, "q_heads": self.Hq, "kv_heads": self.Hkv,
-                       "head_dim": self.D, "page_size": self.P, "rope_theta": self.THETA, "causal": True,
-                       "flops_per_step": total_flops, "append_bytes_per_step": self.T * self.Hkv * self.D * 2 * 2,
-                       "l2": f"rotates through {self.N_SETS} distinct input sets and pools ({self.N_SETS * set_mb:.0f} MB)",
-                       "sharding": "heads" if world > 1 else "none", "collective": "nccl all_gather of the output" if world > 1 else None}
+        self.config = self.describe(world)
+        if world == 1:
+            self._init_overlap(gd)
 
     def step(self):
         pool, table, q, k, v = self.sets[self.i % self.N_SETS]
         self.i += 1
         q16 = self.be.rope_append_gqa(q, k, v, self.rope, pool, table)
         self.be.gqa_prefill_paged(q16, pool, table, out=self.out)
-        if self.world > 1:
-            self.dist.all_gather_into_tensor(self.gathered, self.out.view(self.T, self.hq_local, self.D))
+        if self.collective:
+            self.be.allgather_into(self.out, self.gathered)
 
     def step_e2e(self):
         pool, table, q, k, v = self.sets[self.i % self.N_SETS]  # the same set step() is about to use
@@ -507,11 +559,54 @@ class GqaPrefill2k:
         k.copy_(self.hk, non_blocking=True)
         v.copy_(self.hv, non_blocking=True)
         self.step()
-        self.hout.copy_(self.out, non_blocking=True)
+        self.hout.copy_(self.gathered if self.collective else self.out, non_blocking=True)
 
-    def cpu_sample(self):
+    # ---- the same end-to-end step, head group by head group: every KV head with its six query heads has its own
+    # host buffers, device buffers and pool, so that the upload of group g + 1 and the download of group g - 1 run
+    # under the kernels of group g (three streams; the host layout is group-major)
+    def _init_overlap(self, gd):
+        torch, be = self.torch, self.be
+        self.overlap_groups = self.Hkv
+        grp, pages = self.Hq // self.Hkv, self.T // self.P
+        self.ov = []
+        for g in range(self.overlap_groups):
+            pool = be.prepare_kv_pool(pages + 4, self.P, 1, self.D)
+            perm = torch.randperm(pages + 4, generator=torch.Generator().manual_seed(SEED + 52 + g)).to(torch.int32)
+            table = be.page_table(perm[:pages].view(1, -1), [0], validate_on_host=False)
+            n_q, n_kv = self.T * grp * self.D, self.T * self.D
+            dev = torch.randn((n_q + 2 * n_kv,), generator=gd, device=be.device, dtype=torch.float16)
+            host = dev.cpu().pin_memory()
+            out = torch.empty((1, self.T, grp, self.D), dtype=torch.float16, device=be.device)
+            self.ov.append({"pool": pool, "table": table, "dev": dev, "host": host, "out": out,
+                            "q": dev[:n_q].view(1, self.T, grp, self.D), "k": dev[n_q:n_q + n_kv].view(1, self.T, 1, self.D),
+                            "v": dev[n_q + n_kv:].view(1, self.T, 1, self.D),
+                            "hout": torch.empty(out.shape, dtype=torch.float16).pin_memory(),
+                            "up": torch.cuda.Event(), "done": torch.cuda.Event()})
+        self.s_up, self.s_down = torch.cuda.Stream(be.device), torch.cuda.Stream(be.device)
+
+    def step_e2e_overlapped(self):
+        torch = self.torch
+        cur = torch.cuda.current_stream(self.be.device)
+        self.s_up.wait_stream(cur)
+        for o in self.ov:
+            with torch.cuda.stream(self.s_up):
+                o["dev"].copy_(o["host"], non_blocking=True)
+                o["up"].record(self.s_up)
+        for o in self.ov:
+            cur.wait_event(o["up"])
+            q16 = self.be.rope_append_gqa(o["q"], o["k"], o["v"], self.rope, o["pool"], o["table"])
+            self.be.gqa_prefill_paged(q16, o["pool"], o["table"], out=o["out"])
+            o["done"].record(cur)
+            self.s_down.wait_event(o["done"])
+            with torch.cuda.stream(self.s_down):
+                o["hout"].copy_(o["out"], non_blocking=True)
+        cur.wait_stream(self.s_up)
+        cur.wait_stream(self.s_down)
+
+    @classmethod
+    def cpu_sample(cls):
         from oracle import pyoracle as orc
-        c = self
+        c = cls
         q = orc.fill_normal((1, c.T, c.Hq, c.D), SEED + 33)
         k = orc.fill_normal((1, c.T, c.Hkv, c.D), SEED + 34)
         v = orc.fill_normal((1, c.T, c.Hkv, c.D), SEED + 35)
@@ -531,20 +626,30 @@ class GqaPrefill2k:
 
 class MlaPrefill32k:
     """Causal MLA prefill, 32768-token prompt, 64 heads, qk 128+64, v 128 (fifth configuration).  With N > 1
-    ranks the heads are sharded 64/N per rank and the [32768, 64, 128] output is all-gathered over NCCL."""
+    ranks the heads are sharded 64/N per rank and the [32768, 64, 128] output is all-gathered through the
+    library's collective."""
     name = "mla_prefill_32k"
     metric, unit, bound = "mla_prefill_tflops", "TFLOP/s", "tensor"
     kernel = "flash_prefill_mla_kernel"
     launches_per_step = 1
-    # ncu at 8192 tokens: 2.151 GB read + 0.138 GB written.  K/V re-streaming grows
-    # with tokens^2 and the output with tokens, so a full 32768-token launch is estimated at 16x / 4x of those.
-    traffic = 2.152e9 * 16 + 0.138e9 * 4
+    traffic = None  # set per prompt length in __init__, from an ncu capture at 8192 tokens
     T, H = 32768, 64
     max_steps = 3
+    max_regions = 5
+    scaling = "strong"
 
-    def __init__(self, be, rank, world=1, dist=None):
+    @classmethod
+    def describe(cls, world=1, tokens=None):
+        T = tokens or cls.T
+        return {"workload": cls.name if T == cls.T else f"mla_prefill_{T}", "tokens": T, "heads": cls.H, "qk_dim": 192,
+                "v_dim": 128, "causal": True, "flops_per_step": T * (T + 1) / 2 * cls.H * 2.0 * (192 + 128),
+                "l2": "inputs larger than L2 (2.4 GB of Q/K/V)" if T == cls.T else "inputs of this prompt length",
+                "sharding": "heads" if world > 1 else "none",
+                "collective": "inf_allgather_heads (NCCL) of the output" if world > 1 else None}
+
+    def __init__(self, be, rank, world=1):
         import torch
-        self.torch, self.be, self.world, self.dist = torch, be, world, dist
+        self.torch, self.be, self.world = torch, be, world
         hl = self.H // world
         self.hl = hl
         gd = torch.Generator(device=be.device).manual_seed(SEED + 41 + rank)
@@ -552,35 +657,75 @@ class MlaPrefill32k:
         self.kn = torch.randn((self.T, hl, 128), generator=gd, device=be.device, dtype=torch.float16)
         self.kr = torch.randn((self.T, 64), generator=gd, device=be.device, dtype=torch.float16)
         self.v = torch.randn((self.T, hl, 128), generator=gd, device=be.device, dtype=torch.float16)
-        self.gathered = torch.empty((world * self.T, hl, 128), dtype=torch.float16, device=be.device) if world > 1 else None
+        self.out = torch.empty((self.T, hl, 128), dtype=torch.float16, device=be.device)
+        self.collective = world > 1
+        self.gather_bytes = self.out.numel() * 2 if world > 1 else 0
+        self.gathered = torch.empty((world, self.T, hl, 128), dtype=torch.float16, device=be.device) if world > 1 else None
         self.host = [t.cpu().pin_memory() for t in (self.q, self.kn, self.kr, self.v)]
-        self.hout = torch.empty((self.T, hl, 128), dtype=torch.float16).pin_memory()
+        self.hout = torch.empty((self.gathered if world > 1 else self.out).shape, dtype=torch.float16).pin_memory()
         self.scale = 1.0 / float(np.sqrt(192.0))
         total_flops = self.T * (self.T + 1) / 2 * self.H * 2.0 * (192 + 128)
         self.units_per_step = total_flops / world
         self.h2d = sum(t.numel() * 2 for t in self.host)
         self.d2h = self.hout.numel() * 2
-        self.out = None
         self.i = 0
-        self.config = {"workload": self.name, "tokens": self.T, "heads": self.H, "qk_dim": 192, "v_dim": 128,
-                       "causal": True, "flops_per_step": total_flops,
-                       "l2": "inputs larger than L2 (2.4 GB of Q/K/V)", "sharding": "heads" if world > 1 else "none",
-                       "collective": "nccl all_gather of the output" if world > 1 else None}
+        self.config = self.describe(world, self.T)
+        if world == 1:
+            self._init_overlap(gd)
 
     def step(self):
-        self.out = self.be.causal_sequence_attention_device(self.q, self.kn, self.kr, self.v, self.scale)
-        if self.world > 1:
-            self.dist.all_gather_into_tensor(self.gathered, self.out)
+        self.be.causal_sequence_attention_device(self.q, self.kn, self.kr, self.v, self.scale, out=self.out)
+        if self.collective:
+            self.be.allgather_into(self.out, self.gathered)
 
     def step_e2e(self):
         for d, h in zip((self.q, self.kn, self.kr, self.v), self.host):
             d.copy_(h, non_blocking=True)
         self.step()
-        self.hout.copy_(self.out, non_blocking=True)
+        self.hout.copy_(self.gathered if self.collective else self.out, non_blocking=True)
 
-    def cpu_sample(self):
+    # ---- the same end-to-end step in groups of eight heads with a group-major host layout: the upload of group
+    # g + 1 and the download of group g - 1 run under the kernel of group g (three streams)
+    def _init_overlap(self, gd):
+        torch, be = self.torch, self.be
+        self.overlap_groups = G = 8
+        hg = self.hl // G
+        self.ov = []
+        for g in range(G):
+            dev = [torch.randn((self.T, hg, d), generator=gd, device=be.device, dtype=torch.float16) for d in (192, 128, 128)]
+            out = torch.empty((self.T, hg, 128), dtype=torch.float16, device=be.device)
+            self.ov.append({"dev": dev, "host": [t.cpu().pin_memory() for t in dev], "out": out,
+                            "hout": torch.empty(out.shape, dtype=torch.float16).pin_memory(),
+                            "up": torch.cuda.Event(), "done": torch.cuda.Event()})
+        self.s_up, self.s_down = torch.cuda.Stream(be.device), torch.cuda.Stream(be.device)
+
+    def step_e2e_overlapped(self):
+        torch = self.torch
+        cur = torch.cuda.current_stream(self.be.device)
+        self.s_up.wait_stream(cur)
+        with torch.cuda.stream(self.s_up):
+            self.kr.copy_(self.host[2], non_blocking=True)  # the rope tail every head shares goes up first
+        for o in self.ov:
+            with torch.cuda.stream(self.s_up):
+                for d, h in zip(o["dev"], o["host"]):
+                    d.copy_(h, non_blocking=True)
+                o["up"].record(self.s_up)
+        for o in self.ov:
+            cur.wait_event(o["up"])
+            q, kn, v = o["dev"]
+            self.be.causal_sequence_attention_device(q, kn, self.kr, v, self.scale, out=o["out"])
+            o["done"].record(cur)
+            self.s_down.wait_event(o["done"])
+            with torch.cuda.stream(self.s_down):
+                o["hout"].copy_(o["out"], non_blocking=True)
+        cur.wait_stream(self.s_up)
+        cur.wait_stream(self.s_down)
+
+    @classmethod
+    def cpu_sample(cls):
         from oracle import pyoracle as orc
-        T, H = self.T, 8  # 8 of the 64 heads, 48 sampled rows with their full causal key ranges
+        scale = 1.0 / float(np.sqrt(192.0))
+        T, H = cls.T, 8  # 8 of the 64 heads, 48 sampled rows with their full causal key ranges
         rows = np.sort(np.random.RandomState(SEED + 42).randint(0, T, size=48)).astype(np.int32)
         blk = np.random.RandomState(SEED + 43).standard_normal(1 << 22).astype(np.float16).astype(np.float32)
         q = np.resize(blk, T * H * 192).reshape(T, H, 192)
@@ -588,13 +733,15 @@ class MlaPrefill32k:
         kr = np.resize(blk[7:], T * 64).reshape(T, 64)
         v = np.resize(blk[13:], T * H * 128).reshape(T, H, 128)
         flops = float(np.sum(rows.astype(np.int64) + 1)) * H * 2.0 * (192 + 128)
-        run = lambda: orc.causal_mha(q, kn, kr, v, self.scale, rows=rows)
+        run = lambda: orc.causal_mha(q, kn, kr, v, scale, rows=rows)
         return run, flops, "48 sampled query rows x 8 of 64 heads, full causal key ranges (sampled)"
 
 
-def make_workload(name, be, rank, world=1, dist=None, tokens=0):
+def make_workload(name, be, rank, world=1, tokens=0):
     if name == "gqa_decode_b32":
-        return GqaDecodeB32(be, rank)
+        return GqaDecodeB32(be, rank, world)
+    if name == "gqa_decode_b32_strong":
+        return GqaDecodeB32(be, rank, world, strong=True)
     if name == "mla_decode_4k":
         return MlaDecode(be, rank, 4096)
     if name == "mla_decode_32k":
@@ -606,23 +753,24 @@ def make_workload(name, be, rank, world=1, dist=None, tokens=0):
     if name == "mla_absorbed_decode_32k":
         return MlaAbsorbedDecode(be, rank, 32768)
     if name == "gqa_prefill_2k":
-        return GqaPrefill2k(be, rank, world, dist)
+        return GqaPrefill2k(be, rank, world)
     if name == "mla_prefill_32k":
         wl = MlaPrefill32k.__new__(MlaPrefill32k)
         if tokens:
             wl.T = tokens  # smaller prompt for profiler captures; the name in `config` reflects it
-        wl.__init__(be, rank, world, dist)
-        if tokens:
-            wl.config["workload"] = f"mla_prefill_{tokens}"
             wl.max_steps = 50
+        wl.__init__(be, rank, world)
         return wl
     raise KeyError(name)
 
 
 WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "mla_selected_decode_32k",
-                  "dsa_sparse_decode_32k", "gqa_prefill_2k",
-                  "mla_prefill_32k"]
-STRONG = {"gqa_prefill_2k", "mla_prefill_32k"}  # head-sharded with an all-gather; the others replicate/shard by sequence
+                  "dsa_sparse_decode_32k", "gqa_prefill_2k", "mla_prefill_32k", "gqa_decode_b32_strong"]
+# head-sharded (or sequence-split) with an all-gather: strong scaling, the collective inside the step
+STRONG = {"gqa_prefill_2k", "mla_prefill_32k", "gqa_decode_b32_strong"}
+# what a multi-GPU run measures besides the weak-scaled headline: the sharded forms of the path
+MULTI_GPU_EXTRAS = ["gqa_decode_b32_strong", "gqa_prefill_2k", "mla_prefill_32k"]
+SINGLE_GPU_EXTRAS = [n for n in WORKLOAD_NAMES if n != "gqa_decode_b32_strong"]
 
 
 # ----------------------------------------------------------------------------- measurement
@@ -647,28 +795,39 @@ class GraphedStep:
         self.k += 1
 
 
-def timed(torch, dist, world, fn, steps, warmup):
-    """W warm-up steps, then K steps between barrier + synchronize, device time by CUDA events, max over ranks."""
+def timed(torch, dist, world, fn, steps, warmup, regions=1):
+    """W warm-up steps, then `regions` regions of exactly K steps, each between barrier + synchronize, device time
+    by CUDA events.  Returns (median over regions of the max over ranks, per-rank medians, all region maxima)."""
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize()
+    mine = []
+    for _ in range(regions):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        mine.append(a.elapsed_time(b))
     if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        fn()
-    b.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    ms = a.elapsed_time(b)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    return ms
+        t = torch.tensor(mine, dtype=torch.float64, device="cuda")
+        every = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        table = torch.stack(every).cpu().numpy()  # [rank][region]
+    else:
+        table = np.array([mine], dtype=np.float64)
+    region_max = table.max(axis=0)
+    return float(np.median(region_max)), [float(x) for x in np.median(table, axis=1)], [float(x) for x in region_max]
+
+
+def spread(values):
+    return {"min": float(min(values)), "median": float(statistics.median(values)), "max": float(max(values))}
 
 
 def kernel_time(be, torch, wl, steps):
@@ -703,9 +862,11 @@ def cpu_baseline(wl, budget_s=12.0):
             "sample": sample, "seconds_per_pass": best}
 
 
-def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, profile_steps=100, use_graph=True):
+def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, profile_steps=100, use_graph=True,
+            regions=10):
     steps = max(1, min(steps, getattr(wl, "max_steps", steps)))
     profile_steps = max(1, min(profile_steps, getattr(wl, "max_steps", profile_steps)))
+    regions = max(1, min(regions, getattr(wl, "max_regions", regions)))
     if use_graph:
         for _ in range(2):
             wl.step()
@@ -713,9 +874,8 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
         step, step_e2e = GraphedStep(be, wl, "step"), GraphedStep(be, wl, "step_e2e")
     else:
         step, step_e2e = wl.step, wl.step_e2e
-    wl.config["launch"] = "cuda graph replay (one per input set)" if use_graph else "eager"
-    ms = timed(torch, dist, world, step, steps, warmup)
-    ms_e2e = timed(torch, dist, world, step_e2e, steps, warmup)
+    ms, rank_ms, region_ms = timed(torch, dist, world, step, steps, warmup, regions)
+    ms_e2e, _, _ = timed(torch, dist, world, step_e2e, steps, warmup, regions)
     units = wl.units_per_step
     if world > 1:
         t = torch.tensor([units], dtype=torch.float64, device="cuda")
@@ -740,9 +900,39 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
     if wl.bound == "tensor" and achieved and peaks.get("tflops_sustained"):
         roof["frac_of_sustained_peak"] = achieved / peaks["tflops_sustained"]
     res = {"metric": wl.metric, "value": value, "unit": wl.unit, "steps": steps, "ms_per_step": ms / steps,
+           "regions": regions, "region_ms_per_step": spread([r / steps for r in region_ms]),
            "e2e": {"value": e2e, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                    "ms_per_step": ms_e2e / steps},
-           "roofline": roof, "gpu_launches": wl.launches_per_step * steps, "config": wl.config}
+           "roofline": roof, "gpu_launches": wl.launches_per_step * steps * regions, "config": wl.config,
+           "launch": "cuda graph replay (one per input set)" if use_graph else "eager",
+           "scaling": getattr(wl, "scaling", "weak")}
+    if hasattr(wl, "step_e2e_overlapped"):
+        # the same end-to-end step with the copies of one head group running under the kernels of its neighbours
+        for _ in range(2):
+            wl.step_e2e_overlapped()
+        ms_ov, _, _ = timed(torch, dist, world, wl.step_e2e_overlapped, steps, warmup, regions)
+        res["e2e_overlapped"] = {"value": total_units * steps / (ms_ov * 1e-3) * scale, "unit": wl.unit,
+                                 "ms_per_step": ms_ov / steps, "head_groups": wl.overlap_groups,
+                                 "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "launch": "eager, three streams"}
+    if world > 1:
+        # what every rank saw: its own median region time and its own kernel time
+        kt = torch.tensor([k_ms or 0.0], dtype=torch.float64, device="cuda")
+        every = [torch.empty_like(kt) for _ in range(world)]
+        dist.all_gather(every, kt)
+        res["per_rank"] = {"ms_per_step": spread([r / steps for r in rank_ms]),
+                           "kernel_ms": spread([float(x.item()) for x in every])}
+        if getattr(wl, "gather_bytes", 0):
+            wl.collective = False
+            ms_wo, _, _ = timed(torch, dist, world, wl.step, steps, warmup, regions)
+            wl.collective = True
+            ms_w = ms
+            if use_graph:  # compare like with like: the step with its collective, launched the same (eager) way
+                ms_w, _, _ = timed(torch, dist, world, wl.step, steps, warmup, regions)
+            res["collective"] = {"what": "inf_allgather_heads (NCCL all-gather behind the C ABI)",
+                                 "bytes_sent_per_rank": wl.gather_bytes,
+                                 "bytes_received_per_rank": wl.gather_bytes * (world - 1),
+                                 "ms_per_step_with": ms_w / steps, "ms_per_step_without": ms_wo / steps,
+                                 "ms_collective": (ms_w - ms_wo) / steps}
     if with_cpu and rank == 0:
         res["cpu_baseline"] = cpu_baseline(wl)
     return res
@@ -757,71 +947,86 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from inferno_b200 import CudaBackend
     be = CudaBackend(local_rank if world > 1 else 0)
+    if world > 1:
+        # the library's own communicator: rank 0 makes the id, torch.distributed only carries it to the others
+        box = [be.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        be.comm_init(box[0], rank, world)
     peaks = load_peaks()
     sampler = ClockSampler(local_rank if world > 1 else 0) if rank == 0 else None
-    wl = make_workload(args.workload, be, rank, world, dist, args.tokens)
-    graph_ok = lambda name: not args.no_graph and not (world > 1 and name in STRONG)  # NCCL stays eager
+    wl = make_workload(args.workload, be, rank, world, args.tokens)
+    graph_ok = lambda name: not args.no_graph and not (world > 1 and name in STRONG)  # steps with NCCL stay eager
     head = measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
                    with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps,
-                   use_graph=graph_ok(args.workload))
+                   use_graph=graph_ok(args.workload), regions=args.regions)
     extras = []
-    if args.extras or (world == 1 and not args.no_extras):
-        for name in WORKLOAD_NAMES:
+    if not args.no_extras:
+        names = MULTI_GPU_EXTRAS if world > 1 else SINGLE_GPU_EXTRAS
+        for name in names:
             if name == args.workload:
                 continue
             del wl
             torch.cuda.empty_cache()
-            wl = make_workload(name, be, rank, world, dist)
+            wl = make_workload(name, be, rank, world)
             extras.append(measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
                                   with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps,
-                                  use_graph=graph_ok(name)))
+                                  use_graph=graph_ok(name), regions=args.regions))
     be.device_flush()
     clocks = sampler.stop() if sampler else None
     if rank == 0:
         line = {"metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world,
                 "steps": head["steps"], "warmup": args.warmup, "ms_per_step": head["ms_per_step"],
-                "higher_is_better": True, "scaling": "strong" if args.workload in STRONG else "weak",
+                "higher_is_better": True, "scaling": head["scaling"],
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": head["config"],
                 "e2e": head["e2e"], "roofline": head["roofline"], "gpu_launches": head["gpu_launches"],
                 "clocks": clocks}
-        if "cpu_baseline" in head:
-            line["cpu_baseline"] = head["cpu_baseline"]
+        for k in ("regions", "region_ms_per_step", "launch", "per_rank", "collective", "e2e_overlapped", "cpu_baseline"):
+            if k in head:
+                line[k] = head[k]
         if extras:
-            keys = ("metric", "value", "unit", "steps", "ms_per_step", "e2e", "roofline", "gpu_launches", "config",
+            keys = ("metric", "value", "unit", "steps", "ms_per_step", "regions", "region_ms_per_step", "scaling", "e2e",
+                    "e2e_overlapped", "roofline", "gpu_launches", "config", "launch", "per_rank", "collective",
                     "cpu_baseline")
             line["workloads"] = [{k: e[k] for k in keys if k in e} for e in extras]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+        be.comm_destroy()
         dist.destroy_process_group()
 
 
-class _NoBackend:
-    """The CPU arm builds workload objects only for their cpu_sample(); it never touches a device."""
-
-
 def run_reference(args):
-    """The CPU arm: the oracle port on all host threads; rank 0 only, the other ranks exit at once."""
+    """The CPU arm: the oracle port on all host threads; rank 0 only, the other ranks exit at once.  One step is
+    one pass of the oracle over the bounded sample its `cpu_baseline.sample` names."""
     rank, _, world = dist_env()
     if rank != 0:
         return
     from oracle import pyoracle as orc
-    orc.use_all_host_threads()  # the same thread count at every N: a launcher's OMP_NUM_THREADS=1 does not apply
-    protos = {"gqa_decode_b32": GqaDecodeB32, "mla_decode_4k": MlaDecode, "mla_decode_32k": MlaDecode,
-              "gqa_prefill_2k": GqaPrefill2k, "mla_prefill_32k": MlaPrefill32k}
-    cls = protos[args.workload]
-    wl = cls.__new__(cls)  # no device set-up: only the shape constants and cpu_sample() are used
-    if cls is MlaDecode:
-        wl.ctx_len = 4096 if args.workload.endswith("4k") else 32768
+    cores = orc.use_all_host_threads()  # the same thread count at every N: a launcher's OMP_NUM_THREADS=1 does not apply
+    name = args.workload
+    if name in ("gqa_decode_b32", "gqa_decode_b32_strong"):
+        cls, config = GqaDecodeB32, GqaDecodeB32.describe(decode_lens(0), name.endswith("strong"))
+        run, units, sample = cls.cpu_sample()
+    elif name in ("mla_decode_4k", "mla_decode_32k"):
+        cls = MlaDecode
+        wl = cls.__new__(cls)  # no device set-up: only the shape constants and cpu_sample() are used
+        wl.ctx_len = 4096 if name.endswith("4k") else 32768
         wl.scale = 1.0 / float(np.sqrt(192.0))
         wl.units_per_step = float(wl.ctx_len) * (wl.L + wl.R) * 2
-    if cls is MlaPrefill32k:
-        wl.scale = 1.0 / float(np.sqrt(192.0))
-    run, units, sample = wl.cpu_sample()
-    warm = min(args.warmup, 1)
-    for _ in range(warm):
+        config = cls.describe(wl.ctx_len)
+        run, units, sample = wl.cpu_sample()
+    elif name == "gqa_prefill_2k":
+        cls, config = GqaPrefill2k, GqaPrefill2k.describe(world)
+        run, units, sample = cls.cpu_sample()
+    elif name == "mla_prefill_32k":
+        cls, config = MlaPrefill32k, MlaPrefill32k.describe(world)
+        run, units, sample = cls.cpu_sample()
+    else:
+        print(json.dumps({"impl": "reference", "unavailable": f"no CPU arm for workload {name}"}), flush=True)
+        return
+    for _ in range(args.warmup):
         run()
-    steps = max(1, min(args.steps, 5))
+    steps = args.steps
     t0 = time.perf_counter()
     for _ in range(steps):
         run()
@@ -829,12 +1034,11 @@ def run_reference(args):
     scale = 1e-9 if cls.unit == "GB/s" else 1e-12
     value = units * steps / dt * scale
     line = {"impl": "reference", "metric": cls.metric, "value": value, "unit": cls.unit, "n_gpus": world,
-            "steps": steps, "warmup": warm, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
-            "scaling": "strong" if args.workload in STRONG else "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "sample": sample,
-                       "note": "the reference is Rust + Metal and cannot be built here; this is the scalar CPU port of its kernels"},
-            "cpu_baseline": {"value": value, "unit": cls.unit, "cores": orc.max_threads(), "kind": "port", "sample": sample},
+            "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+            "scaling": "strong" if name in STRONG else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config,
+            "note": "the reference is Rust + Metal and cannot be built here; this is the scalar CPU port of its kernels",
+            "cpu_baseline": {"value": value, "unit": cls.unit, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": cls.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -847,17 +1051,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="gqa_decode_b32", choices=WORKLOAD_NAMES)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--extras", action="store_true", help="also measure the other workloads of the path (default at N=1)")
     ap.add_argument("--no-extras", action="store_true", help="only the selected workload")
+    ap.add_argument("--regions", type=int, default=10, help="timed regions of K steps each; the median is reported")
     ap.add_argument("--tokens", type=int, default=0, help="prompt length override for mla_prefill_32k (profiler captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg (profiler runs)")
     ap.add_argument("--profile-steps", type=int, default=100, help="launches timed per kernel for the roofline")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
+        # one oracle pass over the sample takes 0.3-2 s: bound the run to a couple of minutes whatever K and W say
+        args.steps, args.warmup = max(1, min(args.steps, 40)), max(0, min(args.warmup, 5))
         run_reference(args)
     else:
+        args.warmup = max(args.warmup, 3)
         run_ours(args)
 
 

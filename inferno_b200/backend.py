@@ -115,6 +115,16 @@ class CudaBackend:
         self._check(rc)
         return gathered.view(n, t, h, d).permute(1, 0, 2, 3).reshape(t, n * h, d)
 
+    def allgather_into(self, local_out: torch.Tensor, gathered: torch.Tensor) -> torch.Tensor:
+        """inf_allgather_heads without any allocation or layout change: `gathered` (contiguous, world x the bytes
+        of `local_out`) receives every rank's block in rank order, [world][...local shape...]; the consumer indexes
+        the rank-major layout itself."""
+        nbytes = local_out.numel() * local_out.element_size()
+        assert local_out.is_contiguous() and gathered.is_contiguous()
+        assert gathered.numel() * gathered.element_size() == self._comm_size * nbytes
+        self._check(self._lib.inf_allgather_heads(self._comm, _ptr(local_out), _ptr(gathered), nbytes))
+        return gathered
+
     def comm_destroy(self):
         if getattr(self, "_comm", None):
             self._lib.inf_comm_destroy(self._comm)
@@ -437,14 +447,15 @@ class CudaBackend:
             _ptr(out)))
         return out if ok else None
 
-    def causal_sequence_attention_device(self, q, k_nope, k_rope, v, scale: float, out_dtype=torch.float16):
+    def causal_sequence_attention_device(self, q, k_nope, k_rope, v, scale: float, out_dtype=torch.float16, out=None):
         """causal_sequence_attention_device (backend.rs:2028) for MLA prefill: q [T,H,dn+dr], k_nope [T,H,dn],
         k_rope [T,dr] shared by the heads (or None), v [T,H,dv]; any token/head strides, unit inner stride."""
         T, H, dqk = q.shape
         dn = k_nope.shape[2]
         dr = dqk - dn
         dv = v.shape[2]
-        out = torch.empty((T, H, dv), dtype=out_dtype, device=self.device)
+        if out is None:
+            out = torch.empty((T, H, dv), dtype=out_dtype, device=self.device)
         dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
         for t in (q, k_nope, v) + ((k_rope,) if k_rope is not None else ()):
             assert t.stride(-1) == 1 and t.dtype == torch.float16

@@ -1,26 +1,33 @@
 // Causal flash attention for prefill on tcgen05 / TMEM, fed by TMA.
 //
 // One CTA per SM runs TWO query streams of 128 rows each against one shared ring of 128-key K/V tiles,
-// so every K/V tile is fetched once for 256 query rows, and the MMA issue order is staggered by half a
-// tile between the streams: while one stream is in softmax the tensor pipe runs the other stream's
-// PV and next QK^T.  The two streams are either two query heads of the same KV group at the same rows
-// (GQA: identical causal structure, perfectly balanced) or two consecutive 128-row tiles of one head
-// (MHA / MLA prefill).
+// so every K/V tile is fetched once for 256 query rows.  The two streams are either two query heads of the
+// same KV group at the same rows (GQA: identical causal structure, perfectly balanced) or two consecutive
+// 128-row tiles of one head (MHA / MLA prefill).
 //
 // Twelve warps, specialised:
 //   warps 0-3   softmax + epilogue of stream 0; thread r owns query row r and TMEM lane r
 //   warps 4-7   the same for stream 1
-//   warp 8      TMA producer for Q and the K tiles
-//   warp 9      allocates TMEM and issues every tcgen05.mma
-//   warp 10     TMA producer for the V tiles            (warp 11 only pads the third warpgroup)
-// Per stream and 128-key tile: S = Q K^T  (SS MMA, M128 N128, both operands K-major, 128-byte swizzle;
-//                                          N = 128 keeps the operand traffic at the 128 B/clk the shared
-//                                          memory can feed, N = 64 would need 192 B/clk)
-//                              softmax in registers (two passes over S in 32-column chunks), P written back
-//                              to TMEM as packed fp16 over the first half of its own S columns
-//                              O += P V   (TS MMA, A = P from TMEM, B = V MN-major from its [key][dim] tile)
-// TMEM: 256 columns per stream (S/P in 0-127, O in 128-255).  O is rescaled lazily (only when a row
-// maximum grew by more than 2^8).
+//   warp 8      TMA producer for Q and the K ring (64-column blocks, returned one by one)
+//   warp 9      allocates TMEM; one thread issues every QK^T
+//   warp 10     TMA producer for the V ring
+//   warp 11     one thread issues every PV
+// After set-up setmaxnreg moves registers from warps 8-11 (40 each) to the softmax warpgroups (232 each), so
+// a whole 128-key S row lives in registers and the softmax is a single pass.
+// Per stream and 128-key tile:
+//   S = Q K^T    SS MMA, M128 N128 K16, both operands K-major with the 128-byte swizzle, into the ONE S buffer
+//                the two streams share; the softmax warpgroup copies its row out at once, which frees the
+//                buffer for the other stream's next QK^T
+//   softmax      row maximum, lazy rescale of O (only when a maximum grew by more than 2^8), exponentials;
+//                the streams take turns at the exponentials, which keeps them in anti-phase; P goes back to
+//                TMEM as packed fp16, each 64-key half handed to the PV issuer as soon as it is written
+//   O += P V     TS MMA, A = P from TMEM, B = V MN-major straight from its [key][dim] tile
+// TMEM (512 columns): S 128, then per stream P 64 (fp16 pairs) and O 128 (fp32).
+//
+// Work order: CTAs are numbered so that those in flight together share K/V: all query-tile pairs of a small
+// group of heads, latest (heaviest) rows first, before the next group.  With the head as the fast index the
+// CTAs in flight covered every head at two or three query tiles and their K/V working set was several
+// times the L2.
 //
 // Two instantiations: paged GQA prefill (head_dim 128; a K/V tile is eight 16-token page boxes addressed
 // through the page table; reference kernel f16_attention_kernels.metal:153-316) and dense MLA prefill
@@ -28,6 +35,8 @@
 // attention_kernels.metal:723-968 with no past, K laid out as in layout_kernels.metal:148-183).
 #include <cuda_fp16.h>
 #include <math.h>
+
+#include <stdlib.h>
 
 #include <algorithm>
 #include <vector>
@@ -52,6 +61,8 @@ constexpr uint32_t COL_S = 0, COL_STREAM0 = 128, STREAM_COLS = 192, COL_P = 0, C
 struct FlashParams {
     int tokens, q_heads, kv_heads, group, batch;
     int pair_heads;  // 1: streams are heads (2c, 2c+1) at the same rows; 0: streams are row tiles (2c, 2c+1) of one head
+    int grid_heads, grid_tiles;  // work items per batch entry: head (pair) count x query-tile (pair) count
+    int raster_heads;            // heads (pairs) whose work items are interleaved before the next group starts
     const int* pages;
     const int* lens;
     int max_pages, page_size, num_pages;
@@ -139,43 +150,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         p.kprof_cta[kp_cta * 5 + 1] = (long long)global_timer_ns();
     }
 #endif
-    const int b = blockIdx.z;
-    const int past = PAGED ? p.lens[b] : 0;
-    const int kv_total = past + p.tokens;
-    const int qtile = (int)gridDim.y - 1 - (int)blockIdx.y;  // heaviest (latest) query rows first
-
-    Stream st[2];
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-        st[s].head = p.pair_heads ? 2 * (int)blockIdx.x + s : (int)blockIdx.x;
-        st[s].q0 = p.pair_heads ? qtile * BM : (2 * qtile + s) * BM;
-        if (st[s].q0 < p.tokens && st[s].head < p.q_heads) {
-            const int q_last = min(st[s].q0 + BM, p.tokens) - 1;
-            st[s].kt_end = (past + q_last + 1 + BN - 1) / BN;
-            const int lo_key = p.window > 0 ? max(0, past + st[s].q0 + 1 - p.window) : 0;
-            st[s].kt_begin = lo_key / BN;
-        } else {
-            st[s].kt_begin = st[s].kt_end = 0;
-        }
-    }
-    const bool act0 = st[0].kt_end > st[0].kt_begin, act1 = st[1].kt_end > st[1].kt_begin;
-    if (!act0 && !act1) return;
-    const int kt_lo = act0 && act1 ? min(st[0].kt_begin, st[1].kt_begin) : (act0 ? st[0].kt_begin : st[1].kt_begin);
-    const int kt_hi = act0 && act1 ? max(st[0].kt_end, st[1].kt_end) : (act0 ? st[0].kt_end : st[1].kt_end);
-    const int n = kt_hi - kt_lo;
-    // Both streams start at the CTA's first key tile (with a sliding window the later rows' stream then sees one
-    // fully masked tile, which contributes exact zeros): an issuer that skipped leading tiles would have to test
-    // ring barriers whose phase it has not followed.
-    if (act0) st[0].kt_begin = kt_lo;
-    if (act1) st[1].kt_begin = kt_lo;
-    // both streams of a CTA read the same KV head (pair_heads pairs lie inside one KV group)
-    const int kvh = PAGED ? st[act0 ? 0 : 1].head / p.group : st[act0 ? 0 : 1].head;
-
-    if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base
-        if (tid == 0) atomicOr(p.status, INF_STATUS_BAD_SMEM);
-        return;
-    }
-    if (tid == 0) {
+    // Set-up that needs nothing from global memory comes first, so that under a programmatic dependent launch
+    // it overlaps the tail of the kernel before this one (the fused RoPE + append of the same prompt).
+    const bool smem_ok = (smem_u32(smem) & 1023u) == 0;  // the swizzled tiles need a 1024-byte aligned base
+    if (tid == 0 && smem_ok) {
         mbar_init(q_full, 1);
         for (int i = 0; i < KB; ++i) {
             mbar_init(&k_full[i], 1);
@@ -195,10 +173,60 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
+    if (warp == 8 && lane == 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
+    inf_pdl_wait();  // Q, the appended K/V rows and the page table come from work earlier in the stream
+    inf_pdl_release();
+
+    const int b = blockIdx.z;
+    const int past = PAGED ? p.lens[b] : 0;
+    const int kv_total = past + p.tokens;
+    // work item -> (head or head pair, query tile or tile pair): groups of raster_heads heads, inside a group the
+    // latest (heaviest) query rows first, the heads of the group side by side
+    int item_head, qtile;
+    {
+        const int per_group = p.raster_heads * p.grid_tiles;
+        const int grp = (int)blockIdx.x / per_group, within = (int)blockIdx.x % per_group;
+        const int g_heads = min(p.raster_heads, p.grid_heads - grp * p.raster_heads);
+        item_head = grp * p.raster_heads + within % g_heads;
+        qtile = p.grid_tiles - 1 - within / g_heads;
+    }
+
+    Stream st[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        st[s].head = p.pair_heads ? 2 * item_head + s : item_head;
+        st[s].q0 = p.pair_heads ? qtile * BM : (2 * qtile + s) * BM;
+        if (st[s].q0 < p.tokens && st[s].head < p.q_heads) {
+            const int q_last = min(st[s].q0 + BM, p.tokens) - 1;
+            st[s].kt_end = (past + q_last + 1 + BN - 1) / BN;
+            const int lo_key = p.window > 0 ? max(0, past + st[s].q0 + 1 - p.window) : 0;
+            st[s].kt_begin = lo_key / BN;
+        } else {
+            st[s].kt_begin = st[s].kt_end = 0;
+        }
+    }
+    const bool act0 = st[0].kt_end > st[0].kt_begin, act1 = st[1].kt_end > st[1].kt_begin;
+    const int kt_lo = act0 && act1 ? min(st[0].kt_begin, st[1].kt_begin) : (act0 ? st[0].kt_begin : st[1].kt_begin);
+    const int kt_hi = act0 && act1 ? max(st[0].kt_end, st[1].kt_end) : (act0 ? st[0].kt_end : st[1].kt_end);
+    // a CTA with nothing to do (no rows, or a misaligned shared-memory base) runs every role with zero tiles
+    const int n = (smem_ok && (act0 || act1)) ? kt_hi - kt_lo : 0;
+    if (n == 0) st[0].kt_begin = st[0].kt_end = st[1].kt_begin = st[1].kt_end = 0;
+    if (!smem_ok && tid == 0) atomicOr(p.status, INF_STATUS_BAD_SMEM);
+    // Both streams start at the CTA's first key tile (with a sliding window the later rows' stream then sees one
+    // fully masked tile, which contributes exact zeros): an issuer that skipped leading tiles would have to test
+    // ring barriers whose phase it has not followed.
+    if (n > 0 && act0) st[0].kt_begin = kt_lo;
+    if (n > 0 && act1) st[1].kt_begin = kt_lo;
+    // both streams of a CTA read the same KV head (pair_heads pairs lie inside one KV group)
+    const int kvh = PAGED ? st[act0 ? 0 : 1].head / p.group : st[act0 ? 0 : 1].head;
 #ifdef INF_KPROF
     if (tid == 0 && p.kprof_cta && kp_cta < 8192) p.kprof_cta[kp_cta * 5 + 2] = (long long)global_timer_ns();
 #endif
@@ -210,8 +238,6 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (warp == 8) {
         // ------------------------------------------------ Q + K producer
         if (lane == 0) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_k);
             mbar_arrive_expect_tx(q_full, (uint32_t)((act0 ? 1 : 0) + (act1 ? 1 : 0)) * L::Q_BYTES);
 #pragma unroll
             for (int s = 0; s < 2; ++s)
@@ -270,7 +296,6 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
     } else if (warp == 10) {
         // ------------------------------------------------ V producer
-        if (lane == 0) tma_prefetch_desc(&tm_v);
         const int oob_row = p.num_pages * p.kv_heads * p.page_size;
         for (int j = 0; j < n; ++j) {
             const int k0 = (kt_lo + j) * BN;
@@ -690,9 +715,17 @@ int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const C
         ctx->func_attr_done |= attr_bit;
     }
     const int q_tiles = (p.tokens + BM - 1) / BM;
-    dim3 grid(p.pair_heads ? p.q_heads / 2 : p.q_heads, p.pair_heads ? q_tiles : (q_tiles + 1) / 2, p.batch);
-#ifdef INF_KPROF
     FlashParams pp = p;
+    pp.grid_heads = p.pair_heads ? p.q_heads / 2 : p.q_heads;
+    pp.grid_tiles = p.pair_heads ? q_tiles : (q_tiles + 1) / 2;
+    // Work items of a group of heads run together so that the K/V they stream stay in L2.  Paged GQA prompts are
+    // short enough for every head's pages to fit; long dense prompts go head by head (at 32 768 tokens one head has
+    // 128 work items, so two neighbouring heads are in flight: 34 MB of K/V; measured 17.6 ms against 19.4 ms with
+    // every head in flight at once, 17.8 ms with groups of two or four).
+    pp.raster_heads = PAGED ? pp.grid_heads : 1;
+    if (const char* e = getenv("INF_PREFILL_RASTER_HEADS")) pp.raster_heads = std::max(1, std::min(pp.grid_heads, atoi(e)));
+    dim3 grid((unsigned)(pp.grid_heads * pp.grid_tiles), 1, p.batch);
+#ifdef INF_KPROF
     static long long* d_kprof = nullptr;
     if (!d_kprof) cudaMalloc(&d_kprof, 64 * sizeof(long long));
     cudaMemsetAsync(d_kprof, 0, 64 * sizeof(long long), ctx->stream);
@@ -754,7 +787,7 @@ int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const C
 #else
     {
         inf_prof_scope prof(ctx, name);
-        kernel<<<grid, NUM_THREADS, L::TOTAL, ctx->stream>>>(tq, tk, tk2, tv, p);
+        INF_CUDA(ctx, inf_launch_pdl(kernel, grid, dim3(NUM_THREADS), (size_t)L::TOTAL, ctx->stream, tq, tk, tk2, tv, pp));
     }
     INF_LAUNCH_CHECK(ctx, name);
     return INF_OK;
