@@ -906,7 +906,7 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
            "roofline": roof, "gpu_launches": wl.launches_per_step * steps * regions, "config": wl.config,
            "launch": "cuda graph replay (one per input set)" if use_graph else "eager",
            "scaling": getattr(wl, "scaling", "weak")}
-    if hasattr(wl, "step_e2e_overlapped"):
+    if getattr(wl, "overlap_groups", 0):
         # the same end-to-end step with the copies of one head group running under the kernels of its neighbours
         for _ in range(2):
             wl.step_e2e_overlapped()
