@@ -231,6 +231,72 @@ class GqaDecodeB32:
 
 
 
+class GqaDecodeB32Fp8(GqaDecodeB32):
+    """The batch-32 decode configuration over FP8 E4M3FN pages: the same sequences, half the KV bytes.  The current
+    token enters the softmax at full precision (its roped key and value travel beside the query); its FP8 copy is
+    appended by the same fused kernel."""
+    name = "gqa_decode_b32_fp8"
+    metric = "attn_decode_fp8_hbm_gbs"
+    kernel = "gqa_decode_partial_fp8_kernel"
+    traffic = None
+    KS, VS = 0.03, 0.03
+
+    def __init__(self, be, rank, world=1):
+        super().__init__(be, rank, world)
+        torch = self.torch
+        del self.pool
+        torch.cuda.empty_cache()
+        self.pool = be.prepare_kv_pool_fp8(self.num_pages, self.P, self.Hkv, self.KS, self.VS)
+        gd = torch.Generator(device=be.device).manual_seed(SEED + 8 + rank)
+        # bytes drawn uniformly from the codes below 0x78 in magnitude (finite values up to 240), both signs
+        for t in (self.pool.k, self.pool.v):
+            t.copy_(torch.randint(0, 0x78, t.shape, generator=gd, device=be.device, dtype=torch.uint8) |
+                    (torch.randint(0, 2, t.shape, generator=gd, device=be.device, dtype=torch.uint8) << 7))
+        self.cur_k = torch.empty((self.Bl, 1, self.Hkv, self.D), dtype=torch.float16, device=be.device)
+        self.cur_v = torch.empty_like(self.cur_k)
+        self.units_per_step = float(self.lens.astype(np.int64).sum()) * self.Hkv * self.D * 1 * 2  # KV bytes, one per value
+        self.config = dict(self.config, workload=self.name, kv_dtype="fp8 e4m3fn, one scale per tensor",
+                           kv_bytes_per_step=int(self.units_per_step))
+
+    def step(self):
+        q16, k16, v16 = self.be.rope_append_gqa_fp8(self.q, self.k, self.v, self.rope, self.pool, self.past,
+                                                     cur_k=self.cur_k, cur_v=self.cur_v)
+        self.be.gqa_decode_paged_fp8(q16.view(self.Bl, self.Hq, self.D), k16.view(self.Bl, self.Hkv, self.D),
+                                     v16.view(self.Bl, self.Hkv, self.D), self.pool, self.past, self.max_len, self.CHUNK,
+                                     out=self.out)
+
+    @classmethod
+    def cpu_sample(cls, rank=0, max_sequences=32):
+        from oracle import pyoracle as orc
+        c = cls
+        lens = decode_lens(rank, c.B)[:max_sequences]
+        pages = (lens + c.P - 1) // c.P
+        num_pages = int(pages.sum()) + 8
+        perm = np.random.RandomState(SEED + 9).permutation(num_pages).astype(np.int32)
+        table = np.zeros((len(lens), int(pages.max())), np.int32)
+        o = 0
+        for b, n in enumerate(pages):
+            table[b, :n] = perm[o:o + n]
+            o += int(n)
+        n_el = num_pages * c.Hkv * c.P * c.D
+        block = np.random.RandomState(SEED + 10).randint(0, 0x78, 1 << 22).astype(np.uint8)
+        kp = np.resize(block, n_el).reshape(num_pages, c.Hkv, c.P, c.D)
+        vp = np.resize(block[::-1], n_el).reshape(num_pages, c.Hkv, c.P, c.D)
+        q = orc.fill_normal((len(lens), 1, c.Hq, c.D), SEED + 11)
+        k = orc.fill_normal((len(lens), 1, c.Hkv, c.D), SEED + 12)
+        v = orc.fill_normal((len(lens), 1, c.Hkv, c.D), SEED + 13)
+        inv = orc.default_inv_freq(c.THETA, 64)
+        past = (lens - 1).astype(np.int32)
+        units = float(lens.astype(np.int64).sum()) * c.Hkv * c.D * 2
+
+        def run():
+            qr = orc.qk_norm_rope(q, None, inv, 64, 0, positions=past)
+            kr = orc.qk_norm_rope(k, None, inv, 64, 0, positions=past)
+            return orc.gqa_paged_attention_fp8(qr, kr, v, None, kp, vp, c.KS, c.VS, table, past, c.P)
+
+        return run, units, f"{len(lens)} of 32 sequences, all heads, full contexts"
+
+
 class MlaDecode:
     """Absorbed-MLA decode, batch 1, 64 heads over the paged 512+64 latent (second benchmark configuration)."""
     metric, unit, bound = "mla_decode_hbm_gbs", "GB/s", "hbm"
@@ -742,6 +808,8 @@ def make_workload(name, be, rank, world=1, tokens=0):
         return GqaDecodeB32(be, rank, world)
     if name == "gqa_decode_b32_strong":
         return GqaDecodeB32(be, rank, world, strong=True)
+    if name == "gqa_decode_b32_fp8":
+        return GqaDecodeB32Fp8(be, rank, world)
     if name == "mla_decode_4k":
         return MlaDecode(be, rank, 4096)
     if name == "mla_decode_32k":
@@ -764,7 +832,7 @@ def make_workload(name, be, rank, world=1, tokens=0):
     raise KeyError(name)
 
 
-WORKLOAD_NAMES = ["gqa_decode_b32", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "mla_selected_decode_32k",
+WORKLOAD_NAMES = ["gqa_decode_b32", "gqa_decode_b32_fp8", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "mla_selected_decode_32k",
                   "dsa_sparse_decode_32k", "gqa_prefill_2k", "mla_prefill_32k", "gqa_decode_b32_strong"]
 # head-sharded (or sequence-split) with an all-gather: strong scaling, the collective inside the step
 STRONG = {"gqa_prefill_2k", "mla_prefill_32k", "gqa_decode_b32_strong"}

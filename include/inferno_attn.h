@@ -298,13 +298,49 @@ int32_t inf_dsa_query_weights(inf_ctx* ctx, const float* hidden_states, const fl
                               int32_t batch, int32_t hidden_size, int32_t heads, int32_t head_dim, int32_t rope_dim,
                               int32_t position_offset, float theta, float* q_out, float* weights_out);
 
-/* FP8 E4M3FN KV storage of the Laguna safetensors cache (crates/backend/src/metal/kernels/
+/* FP8 E4M3FN KV pages: the paged replacement of LagunaFp8KvCache (prepare_laguna_fp8_kv_cache, crates/backend/src/
+ * metal/fp8_attention.rs; kernels fp8_attention_kernels.metal:70-263).  Same geometry as inf_kv_pool with one byte
+ * per value: stored byte = encode(x / scale), read value = decode(byte) * scale, one scale per tensor.  Pools hold
+ * encoder output only: the two NaN codes 0x7f / 0xff (which the encoder never writes and the scalar decode maps to
+ * zero) are not looked for by the attention kernel. */
+typedef struct inf_kv_pool_fp8 {
+    void* k; /* device uint8 [num_pages][kv_heads][page_size][head_dim] */
+    void* v;
+    int32_t num_pages, page_size, kv_heads, head_dim;
+    float key_scale, value_scale;
+} inf_kv_pool_fp8;
+int32_t inf_kv_pool_fp8_create(inf_ctx* ctx, int32_t num_pages, int32_t page_size, int32_t kv_heads, int32_t head_dim,
+                               float key_scale, float value_scale, inf_kv_pool_fp8* out);
+int32_t inf_kv_pool_fp8_destroy(inf_ctx* ctx, inf_kv_pool_fp8* pool);
+
+/* inf_rope_append_gqa for FP8 pages (append kernel fp8_attention_kernels.metal:227-263 fused with the RoPE): the
+ * roped keys and the values of the call's tokens are stored as encode(x / scale).  Attention reads the current
+ * tokens at full precision, not through the cache (fp8_attention_kernels.metal:155-163), so the same rows are
+ * also written as fp16 to cur_k_out_f16 / cur_v_out_f16 [batch, tokens, kv_heads, head_dim] (either may be NULL). */
+int32_t inf_rope_append_gqa_fp8(inf_ctx* ctx, const void* q, const void* k, const void* v, int32_t in_dtype,
+                                const float* q_norm_weight, const float* k_norm_weight, float eps,
+                                const inf_rope_table* rope, const inf_kv_pool_fp8* pool, const inf_page_table* table,
+                                int32_t tokens, int32_t q_heads, void* q_out_f16, void* cur_k_out_f16,
+                                void* cur_v_out_f16);
+
+/* Paged GQA decode over FP8 pages, split-KV: laguna_gated_gqa_fp8_attention_f32_kernel (fp8_attention_kernels.metal:
+ * 70-225) for one query token per sequence, generalised to a page table.  lens[b] = rows cached BEFORE the current
+ * token; those are read as decode(byte) * scale.  The current token's key (roped) and value are given as fp16
+ * [batch, kv_heads, head_dim] and enter the softmax at full precision, as in the reference; whether its FP8 copy
+ * has already been appended at slot lens[b] does not matter.  Window, gate, scale, max_len (>= max(lens) + 1),
+ * split_chunk and out as inf_gqa_decode_paged.  Halves the bytes a decode step moves. */
+int32_t inf_gqa_decode_paged_fp8(inf_ctx* ctx, const void* q_f16, const void* cur_k_f16, const void* cur_v_f16,
+                                 const inf_kv_pool_fp8* pool, const inf_page_table* table, int32_t q_heads,
+                                 int32_t max_len, int32_t split_chunk, int32_t sliding_window, const float* gate,
+                                 float scale, void* out, int32_t out_dtype);
+
+/* FP8 E4M3FN codec of the Laguna safetensors cache (crates/backend/src/metal/kernels/
  * fp8_attention_kernels.metal:11-54 codec, :227-263 append): stored byte = encode(x / scale), read value =
  * decode(byte) * scale, one scale per tensor.  Encode saturates at +-448, maps NaN and 0 to 0x00, rounds ties to
  * even, and below 2^-6 stores multiples of 2^-9; decode maps the two NaN codes to 0.  count values, device
  * pointers.  inf_kv_pool_from_fp8 dequantises whole FP8 K and V page arrays (same geometry as the pool,
- * [num_pages][kv_heads][page_size][head_dim] bytes) into the fp16 pool the attention kernels read; attention
- * directly over FP8 pages is not part of this library yet. */
+ * [num_pages][kv_heads][page_size][head_dim] bytes) into an fp16 pool (what a prefill over an FP8 cache with
+ * history reads: it is tensor-bound, so the byte count of its K/V does not set its time). */
 int32_t inf_fp8_e4m3fn_encode(inf_ctx* ctx, const float* input, int64_t count, float scale, void* output);
 int32_t inf_fp8_e4m3fn_decode(inf_ctx* ctx, const void* input, int64_t count, float scale, float* output);
 int32_t inf_kv_pool_from_fp8(inf_ctx* ctx, const void* k_fp8, const void* v_fp8, float key_scale, float value_scale,

@@ -37,6 +37,19 @@ class KvPool:
 
 
 @dataclass
+class KvPoolFp8:
+    """Caller-owned paged K/V storage in FP8 E4M3FN: uint8 [num_pages, kv_heads, page_size, head_dim] each, one
+    scale per tensor (stored byte = encode(x / scale))."""
+    k: torch.Tensor
+    v: torch.Tensor
+    desc: L.KvPoolFp8
+
+    @property
+    def page_size(self):
+        return self.desc.page_size
+
+
+@dataclass
 class MlaPool:
     """Caller-owned paged latent storage: fp16 [num_pages, page_size, latent_dim + rope_dim]."""
     rows: torch.Tensor
@@ -204,6 +217,20 @@ class CudaBackend:
         v = torch.zeros_like(k)
         return KvPool(k, v, L.KvPool(k.data_ptr(), v.data_ptr(), num_pages, page_size, kv_heads, head_dim))
 
+    def prepare_kv_pool_fp8(self, num_pages: int, page_size: int, kv_heads: int, key_scale: float, value_scale: float,
+                            head_dim: int = 128) -> KvPoolFp8:
+        """prepare_laguna_fp8_kv_cache (crates/backend/src/metal/fp8_attention.rs) for the paged layout; zero-filled."""
+        if page_size <= 0 or page_size % 16:
+            raise InfernoError(L.INF_E_CACHE, f"page_size must be a positive multiple of 16, got {page_size}")
+        if head_dim != 128:
+            raise InfernoError(L.INF_E_SHAPE, f"head_dim must be 128, got {head_dim}")
+        if not (key_scale > 0 and value_scale > 0):
+            raise InfernoError(L.INF_E_CONFIG, "FP8 scales must be positive and finite")
+        k = torch.zeros((num_pages, kv_heads, page_size, head_dim), dtype=torch.uint8, device=self.device)
+        v = torch.zeros_like(k)
+        return KvPoolFp8(k, v, L.KvPoolFp8(k.data_ptr(), v.data_ptr(), num_pages, page_size, kv_heads, head_dim,
+                                            key_scale, value_scale))
+
     def prepare_mla_pool(self, num_pages: int, page_size: int = 64, latent_dim: int = 512, rope_dim: int = 64) -> MlaPool:
         if page_size != 64:
             raise InfernoError(L.INF_E_CACHE, f"MLA page_size must be 64, got {page_size}")
@@ -249,6 +276,25 @@ class CudaBackend:
             _ptr(k_f32)))
         return (q_out, k_f32) if want_k_f32 else q_out
 
+    def rope_append_gqa_fp8(self, q, k, v, rope, pool: KvPoolFp8, table: PageTable, q_norm=None, k_norm=None, eps=1e-6,
+                            cur_k=None, cur_v=None):
+        """Fused per-head RMSNorm + half-split RoPE + paged append into FP8 pages.  Returns (roped q, roped k, v) as
+        fp16: attention reads the call's own tokens at full precision, not through the cache."""
+        B, T, Hq, D = q.shape
+        if q.dtype != k.dtype or q.dtype != v.dtype or q.dtype not in (torch.float32, torch.float16):
+            raise InfernoError(L.INF_E_DTYPE, "q/k/v must share dtype f32 or f16")
+        dt = L.DTYPE_F32 if q.dtype == torch.float32 else L.DTYPE_F16
+        q_out = torch.empty((B, T, Hq, D), dtype=torch.float16, device=self.device)
+        if cur_k is None:
+            cur_k = torch.empty(k.shape, dtype=torch.float16, device=self.device)
+        if cur_v is None:
+            cur_v = torch.empty(v.shape, dtype=torch.float16, device=self.device)
+        self._check(self._lib.inf_rope_append_gqa_fp8(
+            self._ctx, _ptr(q), _ptr(k), _ptr(v), dt, _ptr(q_norm), _ptr(k_norm), eps,
+            C.byref(rope) if rope is not None else None, C.byref(pool.desc), C.byref(table.desc), T, Hq, _ptr(q_out),
+            _ptr(cur_k), _ptr(cur_v)))
+        return q_out, cur_k, cur_v
+
     def rope_slice_device(self, x, rope_dim, position_offset, theta):  # backend.rs:1866
         B, T, H, R = x.shape
         out = torch.empty_like(x)
@@ -275,6 +321,20 @@ class CudaBackend:
         ok = self._check(self._lib.inf_gqa_decode_paged(self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc),
                                                         Hq, max_len, split_chunk, sliding_window, _ptr(gate), scale,
                                                         _ptr(out), dt))
+        return out if ok else None
+
+    def gqa_decode_paged_fp8(self, q_f16, cur_k_f16, cur_v_f16, pool: KvPoolFp8, table: PageTable, max_len: int,
+                             split_chunk: int = 512, sliding_window: int = 0, gate=None, scale: float = 0.0,
+                             out_dtype=torch.float32, out=None):
+        """Decode over FP8 pages: table.lens counts the rows cached BEFORE the current token, whose key and value
+        are given as fp16 [B, Hkv, D] and enter the softmax at full precision."""
+        B, Hq, D = q_f16.shape
+        if out is None:
+            out = torch.empty((B, Hq, D), dtype=out_dtype, device=self.device)
+        dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
+        ok = self._check(self._lib.inf_gqa_decode_paged_fp8(
+            self._ctx, _ptr(q_f16), _ptr(cur_k_f16), _ptr(cur_v_f16), C.byref(pool.desc), C.byref(table.desc), Hq,
+            max_len, split_chunk, sliding_window, _ptr(gate), scale, _ptr(out), dt))
         return out if ok else None
 
     def gqa_decode_paged_static(self, q_f16, pool: KvPool, table: PageTable, max_len: int, split_chunk: int = 512,

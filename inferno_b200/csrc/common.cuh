@@ -84,6 +84,9 @@ int inf_ensure_workspace(inf_ctx* ctx, size_t bytes);
 // strides in bytes for dims 1..rank-1.
 int inf_make_tmap(inf_ctx* ctx, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
                   const uint32_t* box, CUtensorMap* out);
+// The same for elements of elem_bytes bytes (1: bytes, e.g. FP8 pages; 2: fp16); dims and box count elements.
+int inf_make_tmap_typed(inf_ctx* ctx, const void* base, uint32_t rank, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box, CUtensorMap* out, uint32_t elem_bytes);
 
 #define INF_CHECK_CTX(ctx) \
     do {                   \

@@ -29,9 +29,14 @@ int inf_ensure_workspace(inf_ctx* ctx, size_t bytes) {
 
 int inf_make_tmap(inf_ctx* ctx, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
                   const uint32_t* box, CUtensorMap* out) {
+    return inf_make_tmap_typed(ctx, base, rank, dims, strides_bytes, box, out, 2);
+}
+
+int inf_make_tmap_typed(inf_ctx* ctx, const void* base, uint32_t rank, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box, CUtensorMap* out, uint32_t elem_bytes) {
     inf_tmap_key key{};
     key.base = base;
-    key.rank = rank;
+    key.rank = rank | (elem_bytes << 8);  // the element size is part of the identity of a cached descriptor
     for (uint32_t i = 0; i < rank; ++i) {
         key.dims[i] = dims[i];
         key.box[i] = box[i];
@@ -57,7 +62,8 @@ int inf_make_tmap(inf_ctx* ctx, const void* base, uint32_t rank, const uint64_t*
         if (i + 1 < rank) gstr[i] = strides_bytes[i];
     }
     CUtensorMap tm;
-    CUresult r = ctx->encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, rank, const_cast<void*>(base), gdim, gstr, bx, es,
+    const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = ctx->encode(&tm, dt, rank, const_cast<void*>(base), gdim, gstr, bx, es,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return inf_fail(ctx, INF_E_BACKEND, "cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -353,6 +359,40 @@ int32_t inf_kv_pool_create(inf_ctx* ctx, int32_t num_pages, int32_t page_size, i
 }
 
 int32_t inf_kv_pool_destroy(inf_ctx* ctx, inf_kv_pool* pool) {
+    INF_CHECK_CTX(ctx);
+    if (!pool) return INF_OK;
+    int rc = inf_free(ctx, pool->k);
+    int rc2 = inf_free(ctx, pool->v);
+    pool->k = pool->v = nullptr;
+    return rc != INF_OK ? rc : rc2;
+}
+
+int32_t inf_kv_pool_fp8_create(inf_ctx* ctx, int32_t num_pages, int32_t page_size, int32_t kv_heads, int32_t head_dim,
+                               float key_scale, float value_scale, inf_kv_pool_fp8* out) {
+    INF_CHECK_CTX(ctx);
+    if (!out) return inf_fail(ctx, INF_E_ARG, "fp8 kv pool: null output");
+    if (num_pages <= 0 || kv_heads <= 0) return inf_fail(ctx, INF_E_CACHE, "fp8 kv pool: sizes must be positive");
+    if (page_size <= 0 || page_size % 16 != 0)
+        return inf_fail(ctx, INF_E_CACHE, "fp8 kv pool: page_size must be a positive multiple of 16, got %d", page_size);
+    if (head_dim != 128) return inf_fail(ctx, INF_E_SHAPE, "fp8 kv pool: head_dim must be 128, got %d", head_dim);
+    // crates/backend/src/metal/fp8_attention.rs: the scales must be positive and finite
+    if (!(key_scale > 0.f) || !(value_scale > 0.f) || !isfinite(key_scale) || !isfinite(value_scale))
+        return inf_fail(ctx, INF_E_CONFIG, "fp8 kv pool: scales must be positive and finite");
+    size_t bytes = (size_t)num_pages * kv_heads * page_size * head_dim;
+    void *k = nullptr, *v = nullptr;
+    INF_CUDA(ctx, cudaMalloc(&k, bytes));
+    cudaError_t e = cudaMalloc(&v, bytes);
+    if (e != cudaSuccess) {
+        cudaFree(k);
+        return inf_fail(ctx, INF_E_BACKEND, "fp8 kv pool: cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    }
+    INF_CUDA(ctx, cudaMemsetAsync(k, 0, bytes, ctx->stream));  // byte 0 decodes to 0.0
+    INF_CUDA(ctx, cudaMemsetAsync(v, 0, bytes, ctx->stream));
+    *out = inf_kv_pool_fp8{k, v, num_pages, page_size, kv_heads, head_dim, key_scale, value_scale};
+    return INF_OK;
+}
+
+int32_t inf_kv_pool_fp8_destroy(inf_ctx* ctx, inf_kv_pool_fp8* pool) {
     INF_CHECK_CTX(ctx);
     if (!pool) return INF_OK;
     int rc = inf_free(ctx, pool->k);

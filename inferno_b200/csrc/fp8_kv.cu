@@ -1,48 +1,18 @@
 // FP8 E4M3FN KV storage of the Laguna cache (crates/backend/src/metal/kernels/fp8_attention_kernels.metal:11-54,
 // append kernel :227-263): a cached value is encode(x / scale) with one scale per tensor (key_scale, value_scale),
 // and decode(byte) * scale when read.  Built here: the exact codec, and the dequantisation of FP8 pages into the
-// fp16 pools the attention kernels read.  Attention directly over FP8 pages is not built.
+// fp16 pools.  The FP8 append and the decode attention that reads FP8 pages directly live with their fp16
+// counterparts (rope_append.cu, gqa_decode.cu).
 #include <cuda_fp16.h>
 #include <math.h>
 #include <stdint.h>
 
 #include "common.cuh"
+#include "fp8.cuh"
+
+using namespace inf;
 
 namespace {
-
-// laguna_fp8_e4m3fn_encode (fp8_attention_kernels.metal:29-54), with the exponent taken from the float's bits
-// instead of floor(log2()).
-__device__ __forceinline__ uint8_t fp8_e4m3fn_encode(float value) {
-    if (isnan(value) || value == 0.0f) return 0;
-    const uint32_t sign = value < 0.0f ? 0x80u : 0u;
-    const float mag = fminf(fabsf(value), 448.0f);
-    if (mag < 0.015625f) {  // below 2^-6, the smallest normal value: multiples of 2^-9
-        const uint32_t mant = (uint32_t)rintf(mag * 512.0f);
-        return (uint8_t)(sign | min(mant, 8u));
-    }
-    int e = (int)((__float_as_uint(mag) >> 23) & 0xffu) - 127;  // floor(log2(mag)) for a normal float
-    uint32_t exponent = (uint32_t)(e + 7);
-    const float normalized = mag * __uint_as_float((uint32_t)(127 - e) << 23);  // mag * 2^-e, in [1, 2), exact
-    uint32_t mant = (uint32_t)rintf((normalized - 1.0f) * 8.0f);  // ties to even
-    if (mant == 8u) {
-        mant = 0u;
-        exponent += 1u;
-    }
-    if (exponent > 15u || (exponent == 15u && mant > 6u)) {
-        exponent = 15u;
-        mant = 6u;
-    }
-    return (uint8_t)(sign | (exponent << 3) | mant);
-}
-
-// laguna_fp8_e4m3fn_decode (fp8_attention_kernels.metal:11-27)
-__device__ __forceinline__ float fp8_e4m3fn_decode(uint8_t bits) {
-    const uint32_t sign = bits >> 7, exponent = (bits >> 3) & 0x0fu, mant = bits & 0x07u;
-    if (exponent == 15u && mant == 7u) return 0.0f;
-    const float mag = exponent == 0u ? (float)mant * 0.001953125f
-                                     : (1.0f + (float)mant * 0.125f) * __uint_as_float((exponent + 120u) << 23);  // 2^(exponent-7)
-    return sign ? -mag : mag;
-}
 
 __global__ void fp8_encode_kernel(const float* __restrict__ in, uint8_t* __restrict__ out, long long n, float scale) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;

@@ -21,6 +21,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "fp8.cuh"
 #include "ptx.cuh"
 
 using namespace inf;
@@ -29,13 +30,22 @@ namespace {
 
 constexpr int D = 128;
 constexpr int TILE_KEYS = 64;
-constexpr int STAGES = 3;
-constexpr int HALF_BYTES = TILE_KEYS * 128;       // one [64 keys][64 dims] swizzled block
-constexpr int STAGE_BYTES = 4 * HALF_BYTES;       // K lo, K hi, V lo, V hi
+constexpr int BLOCK_BYTES = TILE_KEYS * 128;  // one [64 keys][128 bytes] swizzled block
 constexpr int CONSUMER_WARPS = 4;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int MAX_CHUNK = 2048;
 constexpr float M_INIT = -1.0e30f;
+
+// A stage holds 64 keys: fp16 pages as four blocks (K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127),
+// FP8 pages as two (a 128-dim row is 128 bytes, one block each for K and V).  Either way the ring is 96 KB.
+template <bool FP8>
+struct Ring {
+    static constexpr int BLOCKS = FP8 ? 2 : 4;
+    static constexpr int STAGE_BYTES = BLOCKS * BLOCK_BYTES;
+    static constexpr int STAGES = FP8 ? 6 : 3;
+    static constexpr int BYTES = STAGES * STAGE_BYTES;
+    static constexpr int V_BLOCK = FP8 ? 1 : 2;
+};
 
 struct DecodeParams {
     const __half* q;
@@ -45,7 +55,9 @@ struct DecodeParams {
     int chunk, window;
     int chunks_per_cta;  // consecutive chunks one CTA streams (chunks_per_cta * chunk <= 2048)
     int len_add;  // added to lens[b]: lets a caller that counts cached rows before the current token reuse its table
-    float scale_log2;
+    int cur_extra;  // 1 when the current token is not among the cached keys (FP8 form): it still counts for the window
+    float scale_log2;  // score scale (times the key scale of an FP8 pool) in the log2 domain
+    float v_scale;     // value scale of an FP8 pool, 1 otherwise; applied to the partial accumulators
     float* part_acc;
     float* part_ml;
     int max_chunks;
@@ -62,6 +74,11 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(addr));
 }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -73,14 +90,24 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // full across chunk boundaries while the consumers finish a chunk (merge the four warps, write its partial) and
 // start the next, so the per-chunk prologue and epilogue no longer drain the loads in flight.  Partials are still
 // one (max, sum, acc) triple per chunk of `chunk` keys, exactly what the combine kernel expects.
+//
+// FP8 pages: the same kernel with byte tiles.  mma.sync wants fp16 fragments, so bytes become fp16 pairs in
+// registers (one cvt per two values).  A sum does not care in which order its terms are taken, so the fragments
+// are laid out for the loads, not for the natural index order: in QK^T lane (g, qd) takes dims [32 qd, 32 qd + 32)
+// of key row g, two 16-byte loads, and the query fragments are permuted the same way; in PV the lane takes dims
+// [16 g, 16 g + 16) of the four key rows its P fragment covers, so accumulator column c of tile j is output dim
+// 16 c + j, which the merge step undoes when it writes the partial.
+template <bool FP8>
 __global__ void __launch_bounds__(THREADS, 2)
 gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           DecodeParams p) {
+    using R = Ring<FP8>;
+    constexpr int STAGES = R::STAGES, STAGE_BYTES = R::STAGE_BYTES;
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES];
     __shared__ int row_y[MAX_CHUNK / 16];
     __shared__ float warp_m[CONSUMER_WARPS][16], warp_l[CONSUMER_WARPS][16];
-    float* merge = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);  // [warp][group rows][128], not in the ring
+    float* merge = reinterpret_cast<float*>(smem + R::BYTES);  // [warp][group rows][128], not in the ring
 
     inf_pdl_wait();  // the appended K/V rows and the roped query come from the kernel before this one
     inf_pdl_release();
@@ -94,7 +121,8 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
         kv_len = p.max_chunks * p.chunk;
         if (tid == 0 && blockIdx.x == 0 && kvh == 0) atomicOr(p.status, INF_STATUS_BAD_LEN);
     }
-    const int win_start = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
+    const int seen = kv_len + p.cur_extra;  // keys the query sees, for the window
+    const int win_start = (p.window > 0 && seen > p.window) ? seen - p.window : 0;
     const int first_chunk = win_start / p.chunk;
     const int cpc = p.chunks_per_cta;
     const int run_chunk0 = (int)blockIdx.x * cpc;  // chunk index relative to first_chunk
@@ -161,14 +189,19 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                     const int remaining = key_end - (key_begin + t * TILE_KEYS);
                     const int nsub = min(4, (remaining + 15) / 16);
                     uint8_t* base = smem + s * STAGE_BYTES;
-                    mbar_arrive_expect_tx(&full_bar[s], (uint32_t)nsub * 4u * 2048u);
+                    mbar_arrive_expect_tx(&full_bar[s], (uint32_t)nsub * (uint32_t)R::BLOCKS * 2048u);
                     const int sub0 = (key_begin - run_begin) / 16 + t * 4;
                     for (int sub = 0; sub < nsub; ++sub) {
                         const int y = row_y[sub0 + sub];
-                        tma_load_2d(base + 0 * HALF_BYTES + sub * 2048, &tm_k, 0, y, &full_bar[s]);
-                        tma_load_2d(base + 1 * HALF_BYTES + sub * 2048, &tm_k, 64, y, &full_bar[s]);
-                        tma_load_2d(base + 2 * HALF_BYTES + sub * 2048, &tm_v, 0, y, &full_bar[s]);
-                        tma_load_2d(base + 3 * HALF_BYTES + sub * 2048, &tm_v, 64, y, &full_bar[s]);
+                        if (FP8) {
+                            tma_load_2d(base + 0 * BLOCK_BYTES + sub * 2048, &tm_k, 0, y, &full_bar[s]);
+                            tma_load_2d(base + 1 * BLOCK_BYTES + sub * 2048, &tm_v, 0, y, &full_bar[s]);
+                        } else {
+                            tma_load_2d(base + 0 * BLOCK_BYTES + sub * 2048, &tm_k, 0, y, &full_bar[s]);
+                            tma_load_2d(base + 1 * BLOCK_BYTES + sub * 2048, &tm_k, 64, y, &full_bar[s]);
+                            tma_load_2d(base + 2 * BLOCK_BYTES + sub * 2048, &tm_v, 0, y, &full_bar[s]);
+                            tma_load_2d(base + 3 * BLOCK_BYTES + sub * 2048, &tm_v, 64, y, &full_bar[s]);
+                        }
                     }
                 }
             }
@@ -184,11 +217,13 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
         const __half* qb = p.q + ((long long)b * p.q_heads + (long long)kvh * p.group) * D;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-            const int c0 = kk * 16 + qd * 2;
+            // dims behind fragment columns (2 qd, 2 qd + 1) and (2 qd + 8, 2 qd + 9) of k-step kk
+            const int c0 = FP8 ? 32 * qd + 4 * kk : kk * 16 + qd * 2;
+            const int c1 = FP8 ? c0 + 2 : c0 + 8;
             qa[kk][0] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0) : 0u;
             qa[kk][1] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0) : 0u;
-            qa[kk][2] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0 + 8) : 0u;
-            qa[kk][3] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0 + 8) : 0u;
+            qa[kk][2] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c1) : 0u;
+            qa[kk][3] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c1) : 0u;
         }
     }
     const uint32_t smem_base = smem_u32(smem);
@@ -222,11 +257,12 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                 if (edge) {
                     // slots of a page past the sequence end may hold anything: zero those V rows so that
                     // 0 * garbage cannot poison the accumulators
-                    for (int i = lane; i < 16 * 16; i += 32) {
-                        int r = i >> 4, ch = i & 15;
+                    constexpr int CH = FP8 ? 8 : 16;  // 16-byte chunks per V row
+                    for (int i = lane; i < 16 * CH; i += 32) {
+                        int r = i / CH, ch = i % CH;
                         int key = k0 + r;
                         if (key < lo || key >= key_end) {
-                            uint8_t* dst = smem + s * STAGE_BYTES + (2 + (ch >> 3)) * HALF_BYTES +
+                            uint8_t* dst = smem + s * STAGE_BYTES + (R::V_BLOCK + (ch >> 3)) * BLOCK_BYTES +
                                            (warp * 16 + r) * 128 + (ch & 7) * 16;
                             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
                         }
@@ -238,14 +274,28 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                 float sc[2][4];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-                {
+                if (FP8) {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const int krow = warp * 16 + nt * 8 + g;  // krow & 7 == g
+                        const uint4 c0 = lds128(stage + krow * 128 + (((2 * qd) ^ g) << 4));
+                        const uint4 c1 = lds128(stage + krow * 128 + (((2 * qd + 1) ^ g) << 4));
+                        const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) {
+                            uint32_t b0, b1;
+                            fp8x4_to_f16x4(w[kk], b0, b1);
+                            mma_16816(sc[nt], qa[kk], b0, b1);
+                        }
+                    }
+                } else {
                     const int mat = lane >> 3, rin = lane & 7;
                     const int krow = warp * 16 + (mat >> 1) * 8 + rin;
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
                         const int dchunk = kk * 2 + (mat & 1);
                         uint32_t r[4];
-                        ldsm_x4(stage + (dchunk >> 3) * HALF_BYTES + sw128_offset(krow, (dchunk & 7) * 8), r);
+                        ldsm_x4(stage + (dchunk >> 3) * BLOCK_BYTES + sw128_offset(krow, (dchunk & 7) * 8), r);
                         mma_16816(sc[0], qa[kk], r[0], r[1]);
                         mma_16816(sc[1], qa[kk], r[2], r[3]);
                     }
@@ -284,12 +334,15 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                         }
                     l_run[h] = l_run[h] * alpha[h] + sum;
                 }
+                // the accumulators only need rescaling when a row maximum moved, which becomes rare after the first tiles
+                if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    o[j][0] *= alpha[0];
-                    o[j][1] *= alpha[0];
-                    o[j][2] *= alpha[1];
-                    o[j][3] *= alpha[1];
+                    for (int j = 0; j < 16; ++j) {
+                        o[j][0] *= alpha[0];
+                        o[j][1] *= alpha[0];
+                        o[j][2] *= alpha[1];
+                        o[j][3] *= alpha[1];
+                    }
                 }
                 // ---- O += P V
                 uint32_t pa[4];
@@ -297,14 +350,37 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                 pa[1] = pack_half2(sc[0][2], sc[0][3]);
                 pa[2] = pack_half2(sc[1][0], sc[1][1]);
                 pa[3] = pack_half2(sc[1][2], sc[1][3]);
-                {
+                if (FP8) {
+                    // P's k columns of this lane are keys 2 qd, 2 qd + 1, 2 qd + 8, 2 qd + 9 of the warp's 16
+                    const uint32_t vb = stage + R::V_BLOCK * BLOCK_BYTES;
+                    const int r0 = warp * 16 + 2 * qd;
+                    const uint4 v0 = lds128(vb + r0 * 128 + ((g ^ (r0 & 7)) << 4));
+                    const uint4 v1 = lds128(vb + (r0 + 1) * 128 + ((g ^ ((r0 + 1) & 7)) << 4));
+                    const uint4 v2 = lds128(vb + (r0 + 8) * 128 + ((g ^ (r0 & 7)) << 4));
+                    const uint4 v3 = lds128(vb + (r0 + 9) * 128 + ((g ^ ((r0 + 1) & 7)) << 4));
+                    const uint32_t a[4] = {v0.x, v0.y, v0.z, v0.w}, bq[4] = {v1.x, v1.y, v1.z, v1.w};
+                    const uint32_t c[4] = {v2.x, v2.y, v2.z, v2.w}, dq[4] = {v3.x, v3.y, v3.z, v3.w};
+#pragma unroll
+                    for (int jw = 0; jw < 4; ++jw) {
+                        // bytes (row r0, row r0 + 1) side by side for dims 4 jw .. 4 jw + 3 of this lane's sixteen
+                        const uint32_t t01 = __byte_perm(a[jw], bq[jw], 0x5140), t23 = __byte_perm(a[jw], bq[jw], 0x7362);
+                        const uint32_t u01 = __byte_perm(c[jw], dq[jw], 0x5140), u23 = __byte_perm(c[jw], dq[jw], 0x7362);
+                        uint32_t b0[4], b1[4];
+                        fp8x4_to_f16x4(t01, b0[0], b0[1]);
+                        fp8x4_to_f16x4(t23, b0[2], b0[3]);
+                        fp8x4_to_f16x4(u01, b1[0], b1[1]);
+                        fp8x4_to_f16x4(u23, b1[2], b1[3]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) mma_16816(o[4 * jw + i], pa, b0[i], b1[i]);
+                    }
+                } else {
                     const int mat = lane >> 3, rin = lane & 7;
                     const int vrow = warp * 16 + (mat & 1) * 8 + rin;
 #pragma unroll
                     for (int jj = 0; jj < 8; ++jj) {
                         const int dchunk = jj * 2 + (mat >> 1);
                         uint32_t r[4];
-                        ldsm_x4_trans(stage + (2 + (dchunk >> 3)) * HALF_BYTES + sw128_offset(vrow, (dchunk & 7) * 8),
+                        ldsm_x4_trans(stage + (2 + (dchunk >> 3)) * BLOCK_BYTES + sw128_offset(vrow, (dchunk & 7) * 8),
                                       r);
                         mma_16816(o[2 * jj], pa, r[0], r[1]);
                         mma_16816(o[2 * jj + 1], pa, r[2], r[3]);
@@ -326,9 +402,18 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
             float* mw = merge + warp * p.group * D;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                if (g < p.group) *reinterpret_cast<float2*>(mw + g * D + j * 8 + qd * 2) = make_float2(o[j][0], o[j][1]);
-                if (g + 8 < p.group)
-                    *reinterpret_cast<float2*>(mw + (g + 8) * D + j * 8 + qd * 2) = make_float2(o[j][2], o[j][3]);
+                if (FP8) {  // accumulator column c of tile j is output dim 16 c + j
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int dim = 16 * (2 * qd + e) + j;
+                        if (g < p.group) mw[g * D + dim] = o[j][e];
+                        if (g + 8 < p.group) mw[(g + 8) * D + dim] = o[j][2 + e];
+                    }
+                } else {
+                    if (g < p.group) *reinterpret_cast<float2*>(mw + g * D + j * 8 + qd * 2) = make_float2(o[j][0], o[j][1]);
+                    if (g + 8 < p.group)
+                        *reinterpret_cast<float2*>(mw + (g + 8) * D + j * 8 + qd * 2) = make_float2(o[j][2], o[j][3]);
+                }
             }
             if (qd == 0) {
                 warp_m[warp][g] = m_run[0];
@@ -350,7 +435,7 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                     acc += sc * merge[(w * p.group + r) * D + tid];
                     L += sc * warp_l[w][r];
                 }
-                p.part_acc[(prow0 + r) * D + tid] = acc;
+                p.part_acc[(prow0 + r) * D + tid] = FP8 ? acc * p.v_scale : acc;
                 if (tid == 0) {
                     p.part_ml[(prow0 + r) * 2 + 0] = M;
                     p.part_ml[(prow0 + r) * 2 + 1] = L;
@@ -369,29 +454,47 @@ __device__ __forceinline__ float softplus_ref(float v) {
 }
 
 // Merge of the per-chunk partials.  The chunk weights are computed once in shared memory so that the
-// accumulation is a stream of independent coalesced loads.
+// accumulation is a stream of independent coalesced loads.  When cur_k / cur_v are given (FP8 pages), the current
+// token is not among the cached keys: its score q . k and its value enter here as one more term, at full precision
+// (fp8_attention_kernels.metal:155-163, 199-207).
 template <typename OutT>
 __global__ void __launch_bounds__(D)
 gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ lens, const float* __restrict__ gate, OutT* __restrict__ out,
-                          int q_heads, int max_chunks, int chunk, int window, int len_add) {
+                          int q_heads, int max_chunks, int chunk, int window, int len_add,
+                          const __half* __restrict__ q, const __half* __restrict__ cur_k,
+                          const __half* __restrict__ cur_v, int group, float cur_scale_log2) {
     __shared__ float w[MAX_CHUNK / TILE_KEYS * 16];  // up to 512 chunks
     __shared__ float red[4];
     inf_pdl_wait();
     inf_pdl_release();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const bool has_cur = cur_k != nullptr;
     int kv_len = lens[b] + len_add;
     const long long orow = ((long long)b * q_heads + h) * D + d;
-    if (kv_len <= 0) {
+    if (kv_len < 0 || (kv_len == 0 && !has_cur)) {
         out[orow] = OutT(0.f);
         return;
     }
     kv_len = min(kv_len, max_chunks * chunk);  // the partial kernel cut it the same way and raised the status word
-    const int win_start = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int seen = kv_len + (has_cur ? 1 : 0);
+    const int win_start = (window > 0 && seen > window) ? seen - window : 0;
     const int first_chunk = win_start / chunk;
-    const int n = (kv_len + chunk - 1) / chunk - first_chunk;  // <= max_chunks <= 512
+    const int n = max(0, (kv_len + chunk - 1) / chunk - first_chunk);  // <= max_chunks <= 512
     const long long prow0 = ((long long)b * max_chunks) * q_heads + h;
-    float mloc = M_INIT;
+    float s_cur = M_INIT, v_cur = 0.f;
+    if (has_cur) {
+        const long long krow = ((long long)b * (q_heads / group) + h / group) * D + d;
+        float prod = __half2float(q[orow]) * __half2float(cur_k[krow]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) prod += __shfl_xor_sync(0xffffffffu, prod, o);
+        if ((d & 31) == 0) red[d >> 5] = prod;
+        __syncthreads();
+        s_cur = (red[0] + red[1] + red[2] + red[3]) * cur_scale_log2;
+        v_cur = __half2float(cur_v[krow]);
+        __syncthreads();
+    }
+    float mloc = s_cur;
     for (int c = d; c < n; c += D) mloc = fmaxf(mloc, part_ml[(prow0 + (long long)c * q_heads) * 2]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
@@ -409,9 +512,10 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
     for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
     if ((d & 31) == 0) red[d >> 5] = lloc;
     __syncthreads();
-    const float L = red[0] + red[1] + red[2] + red[3];
+    const float w_cur = has_cur ? ex2_approx(s_cur - M) : 0.f;
+    const float L = red[0] + red[1] + red[2] + red[3] + w_cur;
     const float* src = part_acc + prow0 * D + d;
-    float acc = 0.f;
+    float acc = w_cur * v_cur;
 #pragma unroll 8
     for (int c = 0; c < n; ++c) acc += w[c] * src[(long long)c * q_heads * D];
     const float gain = (gate ? softplus_ref(gate[(long long)b * q_heads + h]) : 1.0f) / L;
@@ -420,9 +524,17 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
 
 }  // namespace
 
+// What distinguishes the FP8 form of a launch: byte pools with their scales, and the current token given separately.
+struct DecodeFp8 {
+    float key_scale, value_scale;
+    const void* cur_k;
+    const void* cur_v;
+};
+
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
-                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add);
+                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add,
+                          const DecodeFp8* fp8);
 
 extern "C" size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t max_len,
                                                  int32_t split_chunk) {
@@ -434,7 +546,8 @@ extern "C" size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads,
 // Shared by the allocating entry point below and by callers that bring their own scratch.
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
-                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add) {
+                          float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add,
+                          const DecodeFp8* fp8) {
     if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "gqa_decode: null pointer");
     if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "gqa_decode: pool has no storage");
     if (pool->head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: head_dim must be 128, got %d", pool->head_dim);
@@ -451,13 +564,17 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     if (sliding_window < 0) return inf_fail(ctx, INF_E_CONFIG, "gqa_decode: sliding_window must be >= 0");
     if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
         return inf_fail(ctx, INF_E_DTYPE, "gqa_decode: output dtype must be f32 or f16");
+    if (fp8 && (!fp8->cur_k || !fp8->cur_v)) return inf_fail(ctx, INF_E_ARG, "gqa_decode_fp8: null current key / value");
+    if (fp8 && (!(fp8->key_scale > 0.f) || !(fp8->value_scale > 0.f) || !isfinite(fp8->key_scale) || !isfinite(fp8->value_scale)))
+        return inf_fail(ctx, INF_E_CONFIG, "gqa_decode_fp8: scales must be positive and finite");
+    const int cur_extra = fp8 ? 1 : 0;  // the FP8 form counts cached rows; the current token comes on top
     int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, len_add, "gqa_decode");
     if (rc != INF_OK) return rc;
     if (table->host_lens)
         for (int b = 0; b < table->batch; ++b)
-            if (table->host_lens[b] + len_add > max_len)
+            if (table->host_lens[b] + len_add + cur_extra > max_len)
                 return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: sequence %d length %d exceeds max_len %d", b,
-                                table->host_lens[b], max_len);
+                                table->host_lens[b] + cur_extra, max_len);
     // with a window only ceil(window/chunk)+1 chunks can be visible
     int max_chunks = (max_len + split_chunk - 1) / split_chunk;
     if (max_chunks > 512)
@@ -469,15 +586,17 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
                         need);
 
     const uint64_t rows_total = (uint64_t)pool->num_pages * pool->kv_heads * pool->page_size;
+    const uint32_t elem = fp8 ? 1u : 2u;
     uint64_t dims[2] = {(uint64_t)D, rows_total};
-    uint64_t strides[1] = {(uint64_t)D * 2};
-    uint32_t box[2] = {64, 16};
+    uint64_t strides[1] = {(uint64_t)D * elem};
+    uint32_t box[2] = {fp8 ? 128u : 64u, 16};  // 128 bytes wide either way
     CUtensorMap tm_k, tm_v;
-    rc = inf_make_tmap(ctx, pool->k, 2, dims, strides, box, &tm_k);
+    rc = inf_make_tmap_typed(ctx, pool->k, 2, dims, strides, box, &tm_k, elem);
     if (rc != INF_OK) return rc;
-    rc = inf_make_tmap(ctx, pool->v, 2, dims, strides, box, &tm_v);
+    rc = inf_make_tmap_typed(ctx, pool->v, 2, dims, strides, box, &tm_v, elem);
     if (rc != INF_OK) return rc;
 
+    const float base_scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
     DecodeParams p;
     p.q = (const __half*)q_f16;
     p.pages = table->pages;
@@ -491,34 +610,48 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     p.chunk = split_chunk;
     p.window = sliding_window;
     p.len_add = len_add;
-    p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf((float)D)) * 1.4426950408889634f;
+    p.cur_extra = cur_extra;
+    p.scale_log2 = base_scale * (fp8 ? fp8->key_scale * FP8_CVT_GAIN : 1.0f) * 1.4426950408889634f;
+    p.v_scale = fp8 ? fp8->value_scale * FP8_CVT_GAIN : 1.0f;
     p.part_acc = (float*)scratch;
     p.part_ml = p.part_acc + (size_t)table->batch * max_chunks * q_heads * D;
     p.max_chunks = max_chunks;
     p.chunks_per_cta = MAX_CHUNK / split_chunk;
     p.status = ctx->status;
 
-    const size_t smem = STAGES * STAGE_BYTES + (size_t)CONSUMER_WARPS * group * D * sizeof(float);
-    if (!(ctx->func_attr_done & 1u)) {
-        INF_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)(STAGES * STAGE_BYTES + CONSUMER_WARPS * 16 * D * sizeof(float))));
-        ctx->func_attr_done |= 1u;
+    const size_t ring = fp8 ? Ring<true>::BYTES : Ring<false>::BYTES;
+    const size_t smem = ring + (size_t)CONSUMER_WARPS * group * D * sizeof(float);
+    const uint32_t attr_bit = fp8 ? 32u : 1u;
+    if (!(ctx->func_attr_done & attr_bit)) {
+        const int limit = (int)(ring + CONSUMER_WARPS * 16 * D * sizeof(float));
+        if (fp8)
+            INF_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit));
+        else
+            INF_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit));
+        ctx->func_attr_done |= attr_bit;
     }
     dim3 grid((max_chunks + p.chunks_per_cta - 1) / p.chunks_per_cta, pool->kv_heads, table->batch);
     {
-        inf_prof_scope prof(ctx, "gqa_decode_partial_kernel");
-        INF_CUDA(ctx, inf_launch_pdl(gqa_decode_partial_kernel, grid, dim3(THREADS), smem, ctx->stream, tm_k, tm_v, p));
+        inf_prof_scope prof(ctx, fp8 ? "gqa_decode_partial_fp8_kernel" : "gqa_decode_partial_kernel");
+        if (fp8)
+            INF_CUDA(ctx, inf_launch_pdl(gqa_decode_partial_kernel<true>, grid, dim3(THREADS), smem, ctx->stream, tm_k, tm_v, p));
+        else
+            INF_CUDA(ctx, inf_launch_pdl(gqa_decode_partial_kernel<false>, grid, dim3(THREADS), smem, ctx->stream, tm_k, tm_v, p));
     }
     INF_LAUNCH_CHECK(ctx, "gqa_decode_partial_kernel");
     dim3 cgrid(q_heads, table->batch);
+    const __half* cq = fp8 ? (const __half*)q_f16 : nullptr;
+    const __half* ck = fp8 ? (const __half*)fp8->cur_k : nullptr;
+    const __half* cv = fp8 ? (const __half*)fp8->cur_v : nullptr;
+    const float cur_scale_log2 = base_scale * 1.4426950408889634f;
     if (out_dtype == INF_DTYPE_F32)
         INF_CUDA(ctx, inf_launch_pdl(gqa_decode_combine_kernel<float>, cgrid, dim3(D), 0, ctx->stream, p.part_acc, p.part_ml,
                                      table->lens, gate, (float*)out, q_heads, max_chunks, split_chunk, sliding_window,
-                                     len_add));
+                                     len_add, cq, ck, cv, group, cur_scale_log2));
     else
         INF_CUDA(ctx, inf_launch_pdl(gqa_decode_combine_kernel<__half>, cgrid, dim3(D), 0, ctx->stream, p.part_acc,
                                      p.part_ml, table->lens, gate, (__half*)out, q_heads, max_chunks, split_chunk,
-                                     sliding_window, len_add));
+                                     sliding_window, len_add, cq, ck, cv, group, cur_scale_log2));
     INF_LAUNCH_CHECK(ctx, "gqa_decode_combine_kernel");
     return INF_OK;
 }
@@ -534,7 +667,23 @@ extern "C" int32_t inf_gqa_decode_paged(inf_ctx* ctx, const void* q_f16, const i
     int rc = inf_ensure_workspace(ctx, need);
     if (rc != INF_OK) return rc;
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
-                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0);
+                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0, nullptr);
+}
+
+extern "C" int32_t inf_gqa_decode_paged_fp8(inf_ctx* ctx, const void* q_f16, const void* cur_k_f16, const void* cur_v_f16,
+                                            const inf_kv_pool_fp8* pool, const inf_page_table* table, int32_t q_heads,
+                                            int32_t max_len, int32_t split_chunk, int32_t sliding_window,
+                                            const float* gate, float scale, void* out, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    if (!table || !pool) return inf_fail(ctx, INF_E_ARG, "gqa_decode_fp8: null pool or page table");
+    size_t need = inf_gqa_decode_workspace_bytes(table->batch, q_heads, D, max_len, split_chunk);
+    if (need == 0) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode_fp8: sizes must be positive");
+    int rc = inf_ensure_workspace(ctx, need);
+    if (rc != INF_OK) return rc;
+    const inf_kv_pool shape = {pool->k, pool->v, pool->num_pages, pool->page_size, pool->kv_heads, pool->head_dim};
+    const DecodeFp8 fp8 = {pool->key_scale, pool->value_scale, cur_k_f16, cur_v_f16};
+    return inf_gqa_decode_launch(ctx, q_f16, &shape, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
+                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0, &fp8);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -598,5 +747,5 @@ extern "C" int32_t inf_gqa_decode_paged_static(inf_ctx* ctx, const void* q_f16, 
     // Nothing in the array has to start at zero: every partial the combine kernel reads is written
     // by the partial kernel of the same call first.
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
-                                 out, out_dtype, scratch, (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES, 0);
+                                 out, out_dtype, scratch, (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES, 0, nullptr);
 }

@@ -8,6 +8,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "fp8.cuh"
 
 namespace {
 
@@ -119,14 +120,18 @@ __device__ __forceinline__ void st8_as_f16(__half* p, const float (&x)[8]) {
     *reinterpret_cast<uint4*>(p) = raw;
 }
 
-template <typename T>
+// FP8: the pools hold E4M3FN bytes, stored byte = encode(x / scale) with one scale per tensor
+// (fp8_attention_kernels.metal:227-263); the roped keys and the values of the call's tokens are also written out as
+// fp16 (cur_k_out / cur_v_out), because attention reads the current tokens at full precision, not through the cache.
+template <typename T, bool FP8>
 __global__ void __launch_bounds__(256)
 rope_append_gqa_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                        const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ inv_freq,
-                       int rotary_dim, float factor, float eps, __half* __restrict__ k_pool, __half* __restrict__ v_pool,
+                       int rotary_dim, float factor, float eps, void* __restrict__ k_pool, void* __restrict__ v_pool,
                        int num_pages, int page_size, const int* __restrict__ pages, const int* __restrict__ lens,
                        int max_pages, int tokens, int q_heads, int kv_heads, __half* __restrict__ q_out,
-                       float* __restrict__ k_f32_out, int* __restrict__ status) {
+                       float* __restrict__ k_f32_out, int* __restrict__ status, float key_scale, float value_scale,
+                       __half* __restrict__ cur_k_out, __half* __restrict__ cur_v_out) {
     __shared__ float2 s_cs[64];  // (cos, sin) * factor of the token's angles
     inf_pdl_wait();  // the pages may still be read by the attention kernels of the previous step
     inf_pdl_release();
@@ -214,8 +219,20 @@ rope_append_gqa_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
             o[0] = make_float4(x[0], x[1], x[2], x[3]);
             o[1] = make_float4(x[4], x[5], x[6], x[7]);
         }
-        if (page_row >= 0)
-            st8_as_f16((kind == 1 ? k_pool : v_pool) + (page_row + (long long)head * page_size) * D + d0, x);
+        if (FP8) {
+            __half* cur = kind == 1 ? cur_k_out : cur_v_out;
+            if (cur) st8_as_f16(cur + in_row * D + d0, x);
+            if (page_row >= 0) {
+                const float scale = kind == 1 ? key_scale : value_scale;
+                uint32_t w[2] = {0u, 0u};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j >> 2] |= (uint32_t)inf::fp8_e4m3fn_encode(__fdiv_rn(x[j], scale)) << (8 * (j & 3));
+                uint8_t* pool8 = reinterpret_cast<uint8_t*>(kind == 1 ? k_pool : v_pool);
+                *reinterpret_cast<uint2*>(pool8 + (page_row + (long long)head * page_size) * D + d0) = make_uint2(w[0], w[1]);
+            }
+        } else if (page_row >= 0) {
+            st8_as_f16(reinterpret_cast<__half*>(kind == 1 ? k_pool : v_pool) + (page_row + (long long)head * page_size) * D + d0, x);
+        }
     }
 }
 
@@ -379,14 +396,19 @@ int32_t inf_laguna_qk_rms_norm_rope_pair(inf_ctx* ctx, const float* q, const flo
     return INF_OK;
 }
 
-int32_t inf_rope_append_gqa(inf_ctx* ctx, const void* q, const void* k, const void* v, int32_t in_dtype,
-                            const float* qw, const float* kw, float eps, const inf_rope_table* rope,
-                            const inf_kv_pool* pool, const inf_page_table* table, int32_t tokens, int32_t q_heads,
-                            void* q_out_f16, float* k_f32_out) {
-    INF_CHECK_CTX(ctx);
+}  // extern "C"
+
+// The fp16 and the FP8 entry points differ only in the pool's element type.
+static int rope_append_gqa_any(inf_ctx* ctx, const void* q, const void* k, const void* v, int32_t in_dtype,
+                               const float* qw, const float* kw, float eps, const inf_rope_table* rope,
+                               const inf_kv_pool* pool, bool fp8, float key_scale, float value_scale,
+                               const inf_page_table* table, int32_t tokens, int32_t q_heads, void* q_out_f16,
+                               float* k_f32_out, void* cur_k_out, void* cur_v_out) {
     if (!q || !k || !v || !pool || !table || !q_out_f16) return inf_fail(ctx, INF_E_ARG, "rope_append_gqa: null pointer");
     if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "rope_append_gqa: pool has no storage");
     if (pool->head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "rope_append_gqa: head_dim must be 128");
+    if (fp8 && (!(key_scale > 0.f) || !(value_scale > 0.f) || !isfinite(key_scale) || !isfinite(value_scale)))
+        return inf_fail(ctx, INF_E_CONFIG, "rope_append_gqa: FP8 scales must be positive and finite");
     if (tokens <= 0 || q_heads <= 0 || q_heads % pool->kv_heads != 0)
         return inf_fail(ctx, INF_E_SHAPE, "rope_append_gqa: q_heads %d must be a positive multiple of kv_heads %d",
                         q_heads, pool->kv_heads);
@@ -406,19 +428,41 @@ int32_t inf_rope_append_gqa(inf_ctx* ctx, const void* q, const void* k, const vo
     const float* inv = rope ? rope->inv_freq : nullptr;
     int rd = rope ? rope->rotary_dim : 64;
     float factor = rope ? rope->attention_factor : 1.0f;
-    if (in_dtype == INF_DTYPE_F32)
-        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<float>, grid, dim3(256), 0, ctx->stream,
-                                     (const float*)q, (const float*)k, (const float*)v, qw, kw, inv, rd, factor, eps,
-                                     (__half*)pool->k, (__half*)pool->v, pool->num_pages, pool->page_size, table->pages,
-                                     table->lens, table->max_pages, tokens, q_heads, pool->kv_heads, (__half*)q_out_f16,
-                                     k_f32_out, ctx->status));
-    else
-        INF_CUDA(ctx, inf_launch_pdl(rope_append_gqa_kernel<__half>, grid, dim3(256), 0, ctx->stream,
-                                     (const __half*)q, (const __half*)k, (const __half*)v, qw, kw, inv, rd, factor, eps,
-                                     (__half*)pool->k, (__half*)pool->v, pool->num_pages, pool->page_size, table->pages,
-                                     table->lens, table->max_pages, tokens, q_heads, pool->kv_heads, (__half*)q_out_f16,
-                                     k_f32_out, ctx->status));
+    auto launch = [&](auto kernel, auto* tq, auto* tk, auto* tv) {
+        return inf_launch_pdl(kernel, grid, dim3(256), 0, ctx->stream, tq, tk, tv, qw, kw, inv, rd, factor, eps, pool->k,
+                              pool->v, pool->num_pages, pool->page_size, table->pages, table->lens, table->max_pages,
+                              tokens, q_heads, pool->kv_heads, (__half*)q_out_f16, k_f32_out, ctx->status, key_scale,
+                              value_scale, (__half*)cur_k_out, (__half*)cur_v_out);
+    };
+    const float *qf = (const float*)q, *kf = (const float*)k, *vf = (const float*)v;
+    const __half *qh = (const __half*)q, *kh = (const __half*)k, *vh = (const __half*)v;
+    if (in_dtype == INF_DTYPE_F32 && !fp8) INF_CUDA(ctx, launch(rope_append_gqa_kernel<float, false>, qf, kf, vf));
+    if (in_dtype == INF_DTYPE_F32 && fp8) INF_CUDA(ctx, launch(rope_append_gqa_kernel<float, true>, qf, kf, vf));
+    if (in_dtype == INF_DTYPE_F16 && !fp8) INF_CUDA(ctx, launch(rope_append_gqa_kernel<__half, false>, qh, kh, vh));
+    if (in_dtype == INF_DTYPE_F16 && fp8) INF_CUDA(ctx, launch(rope_append_gqa_kernel<__half, true>, qh, kh, vh));
     return INF_OK;
+}
+
+extern "C" {
+
+int32_t inf_rope_append_gqa(inf_ctx* ctx, const void* q, const void* k, const void* v, int32_t in_dtype,
+                            const float* qw, const float* kw, float eps, const inf_rope_table* rope,
+                            const inf_kv_pool* pool, const inf_page_table* table, int32_t tokens, int32_t q_heads,
+                            void* q_out_f16, float* k_f32_out) {
+    INF_CHECK_CTX(ctx);
+    return rope_append_gqa_any(ctx, q, k, v, in_dtype, qw, kw, eps, rope, pool, false, 1.f, 1.f, table, tokens, q_heads,
+                               q_out_f16, k_f32_out, nullptr, nullptr);
+}
+
+int32_t inf_rope_append_gqa_fp8(inf_ctx* ctx, const void* q, const void* k, const void* v, int32_t in_dtype,
+                                const float* qw, const float* kw, float eps, const inf_rope_table* rope,
+                                const inf_kv_pool_fp8* pool, const inf_page_table* table, int32_t tokens,
+                                int32_t q_heads, void* q_out_f16, void* cur_k_out_f16, void* cur_v_out_f16) {
+    INF_CHECK_CTX(ctx);
+    if (!pool) return inf_fail(ctx, INF_E_ARG, "rope_append_gqa_fp8: null pool");
+    const inf_kv_pool shape = {pool->k, pool->v, pool->num_pages, pool->page_size, pool->kv_heads, pool->head_dim};
+    return rope_append_gqa_any(ctx, q, k, v, in_dtype, qw, kw, eps, rope, &shape, true, pool->key_scale, pool->value_scale,
+                               table, tokens, q_heads, q_out_f16, nullptr, cur_k_out_f16, cur_v_out_f16);
 }
 
 int32_t inf_rope_slice(inf_ctx* ctx, const float* input, float* output, int32_t batch, int32_t tokens, int32_t heads,

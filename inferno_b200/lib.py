@@ -39,6 +39,11 @@ class KvPool(C.Structure):
                 ("kv_heads", C.c_int32), ("head_dim", C.c_int32)]
 
 
+class KvPoolFp8(C.Structure):
+    _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("num_pages", C.c_int32), ("page_size", C.c_int32),
+                ("kv_heads", C.c_int32), ("head_dim", C.c_int32), ("key_scale", C.c_float), ("value_scale", C.c_float)]
+
+
 class MlaPool(C.Structure):
     _fields_ = [("rows", C.c_void_p), ("num_pages", C.c_int32), ("page_size", C.c_int32), ("latent_dim", C.c_int32),
                 ("rope_dim", C.c_int32)]
@@ -82,6 +87,12 @@ SIGNATURES = {
                                               _P, _P]),
     "inf_rope_append_gqa": (_I, [_P, _P, _P, _P, _I, _P, _P, _F, C.POINTER(RopeTable), C.POINTER(KvPool),
                                  C.POINTER(PageTable), _I, _I, _P, _P]),
+    "inf_kv_pool_fp8_create": (_I, [_P, _I, _I, _I, _I, _F, _F, C.POINTER(KvPoolFp8)]),
+    "inf_kv_pool_fp8_destroy": (_I, [_P, C.POINTER(KvPoolFp8)]),
+    "inf_rope_append_gqa_fp8": (_I, [_P, _P, _P, _P, _I, _P, _P, _F, C.POINTER(RopeTable), C.POINTER(KvPoolFp8),
+                                     C.POINTER(PageTable), _I, _I, _P, _P, _P]),
+    "inf_gqa_decode_paged_fp8": (_I, [_P, _P, _P, _P, C.POINTER(KvPoolFp8), C.POINTER(PageTable), _I, _I, _I, _I, _P, _F,
+                                      _P, _I]),
     "inf_rope_slice": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F]),
     "inf_mla_kv_postprocess_append": (_I, [_P, _P, _P, _F, _F, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _P, _P]),
     "inf_gqa_decode_paged": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _I, _P, _F, _P, _I]),

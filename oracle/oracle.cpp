@@ -514,6 +514,105 @@ void orc_gqa_paged_attention(const float* query, const float* cur_key, const flo
     }
 }
 
+// ---- FP8 E4M3FN pages -------------------------------------------------------------------------------
+// kernels/fp8_attention_kernels.metal:11-27
+float orc_fp8_e4m3fn_decode(uint8_t bits) {
+    uint32_t sign = bits >> 7, exponent = (bits >> 3) & 0x0fu, mantissa = bits & 0x07u;
+    if (exponent == 15u && mantissa == 7u) return 0.0f;
+    float magnitude = exponent == 0u ? (float)mantissa * 0.001953125f
+                                     : (1.0f + (float)mantissa * 0.125f) * exp2f((float)((int)exponent - 7));
+    return sign == 0u ? magnitude : -magnitude;
+}
+
+// kernels/fp8_attention_kernels.metal:29-54
+uint8_t orc_fp8_e4m3fn_encode(float value) {
+    if (std::isnan(value) || value == 0.0f) return 0;
+    uint32_t sign = value < 0.0f ? 0x80u : 0u;
+    float magnitude = std::min(fabsf(value), 448.0f);
+    if (magnitude < 0.015625f) {
+        uint32_t mantissa = (uint32_t)nearbyintf(magnitude * 512.0f);
+        return (uint8_t)(sign | std::min(mantissa, 8u));
+    }
+    int unbiased = (int)floorf(log2f(magnitude));
+    uint32_t exponent = (uint32_t)(unbiased + 7);
+    float normalized = magnitude * exp2f((float)(-unbiased));
+    uint32_t mantissa = (uint32_t)nearbyintf((normalized - 1.0f) * 8.0f);
+    if (mantissa == 8u) {
+        mantissa = 0u;
+        exponent += 1u;
+    }
+    if (exponent > 15u || (exponent == 15u && mantissa > 6u)) {
+        exponent = 15u;
+        mantissa = 6u;
+    }
+    return (uint8_t)(sign | (exponent << 3) | mantissa);
+}
+
+// kernels/fp8_attention_kernels.metal:70-225 (attention) and :227-263 (append), over pages: cached rows are
+// decode(byte) * scale, the current chunk's rows are f32, the append stores encode(x / scale) afterwards.
+void orc_gqa_paged_attention_fp8(const float* query, const float* cur_key, const float* cur_value, const float* gate,
+                                 uint8_t* k_pool, uint8_t* v_pool, float key_scale, float value_scale,
+                                 const int32_t* page_table, int max_pages, const int32_t* past_tokens, float* output,
+                                 int batch, int q_heads, int kv_heads, int head_dim, int page_size, int q_tokens,
+                                 int sliding_window, int fuse_append, float scale, int threads) {
+    int heads_per_kv = q_heads / kv_heads;
+    if (scale <= 0.0f) scale = 1.0f / sqrtf((float)head_dim);
+    int64_t rows = (int64_t)batch * q_tokens * q_heads;
+    (void)threads;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(threads > 0 ? threads : orc_max_threads())
+    for (int64_t row = 0; row < rows; ++row) {
+        int qh = (int)(row % q_heads);
+        int qt = (int)((row / q_heads) % q_tokens);
+        int b = (int)(row / ((int64_t)q_heads * q_tokens));
+        int kvh = qh / heads_per_kv;
+        int past = past_tokens[b];
+        int abs_q = past + qt;
+        int visible_start = (sliding_window == 0 || abs_q + 1 <= sliding_window) ? 0 : abs_q + 1 - sliding_window;
+        int past_start = std::min(past, visible_start);
+        int past_count = past - past_start;
+        int current_start = visible_start > past ? visible_start - past : 0;
+        int current_count = qt - current_start + 1;
+        int key_count = past_count + current_count;
+        const float* q = query + row * head_dim;
+        std::vector<float> acc(head_dim, 0.0f), kf(head_dim), vf(head_dim);
+        Online st;
+        for (int lk = 0; lk < key_count; ++lk) {
+            const float *kp, *vp;
+            if (lk < past_count) {
+                int64_t idx = paged_row(page_table, max_pages, b, past_start + lk, page_size, kv_heads, kvh, head_dim);
+                for (int d = 0; d < head_dim; ++d) {
+                    kf[d] = orc_fp8_e4m3fn_decode(k_pool[idx + d]) * key_scale;
+                    vf[d] = orc_fp8_e4m3fn_decode(v_pool[idx + d]) * value_scale;
+                }
+                kp = kf.data();
+                vp = vf.data();
+            } else {
+                int ct = current_start + lk - past_count;
+                int64_t idx = (((int64_t)b * q_tokens + ct) * kv_heads + kvh) * head_dim;
+                kp = cur_key + idx;
+                vp = cur_value + idx;
+            }
+            st.step(dotf(q, kp, head_dim) * scale, vp, acc.data(), head_dim);
+        }
+        float g = gate ? softplus(gate[((int64_t)b * q_tokens + qt) * q_heads + qh]) : 1.0f;
+        float gain = g / st.running_sum;
+        for (int d = 0; d < head_dim; ++d) output[row * head_dim + d] = acc[d] * gain;
+    }
+    if (fuse_append) {
+        for (int b = 0; b < batch; ++b)
+            for (int t = 0; t < q_tokens; ++t)
+                for (int h = 0; h < kv_heads; ++h) {
+                    int64_t src = (((int64_t)b * q_tokens + t) * kv_heads + h) * head_dim;
+                    int64_t dst =
+                        paged_row(page_table, max_pages, b, past_tokens[b] + t, page_size, kv_heads, h, head_dim);
+                    for (int d = 0; d < head_dim; ++d) {
+                        k_pool[dst + d] = orc_fp8_e4m3fn_encode(cur_key[src + d] / key_scale);
+                        v_pool[dst + d] = orc_fp8_e4m3fn_encode(cur_value[src + d] / value_scale);
+                    }
+                }
+    }
+}
+
 void orc_linearize_paged(const uint16_t* pool, const int32_t* page_table, int max_pages, uint16_t* out, int batch,
                          int kv_heads, int tokens, int page_size, int head_dim) {
     for (int b = 0; b < batch; ++b)

@@ -98,6 +98,17 @@ void orc_gqa_paged_attention(const float* query, const float* cur_key, const flo
                              int head_dim, int page_size, int q_tokens, int sliding_window, int fuse_append,
                              float scale /* <=0: 1/sqrt(head_dim) */, int threads);
 
+/* The same over FP8 E4M3FN pages (kernels/fp8_attention_kernels.metal:70-225 attention, :227-263 append; codec
+ * :11-54): pools are uint8 [num_pages][kv_heads][page_size][head_dim], a cached value reads decode(byte) * scale,
+ * the current chunk's rows are f32, and the append stores encode(x / scale). */
+float orc_fp8_e4m3fn_decode(uint8_t bits);
+uint8_t orc_fp8_e4m3fn_encode(float value);
+void orc_gqa_paged_attention_fp8(const float* query, const float* cur_key, const float* cur_value, const float* gate,
+                                 uint8_t* k_pool, uint8_t* v_pool, float key_scale, float value_scale,
+                                 const int32_t* page_table, int max_pages, const int32_t* past_tokens, float* output,
+                                 int batch, int q_heads, int kv_heads, int head_dim, int page_size, int q_tokens,
+                                 int sliding_window, int fuse_append, float scale, int threads);
+
 /* Gather logical rows back out of the pool: out [batch][kv_heads][tokens][head_dim] (layout_kernels.metal:205-232
  * generalised to a page table). */
 void orc_linearize_paged(const uint16_t* pool, const int32_t* page_table, int max_pages, uint16_t* out, int batch,

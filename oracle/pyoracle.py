@@ -322,6 +322,36 @@ def q8_rows_decode(payload, dim):
     return (p[:, 4:].view(np.int8).astype(np.float32) * scale[:, None]).astype(np.float32)
 
 
+def gqa_paged_attention_fp8(q, k, v, gate, k_pool, v_pool, key_scale, value_scale, page_table, past_tokens, page_size,
+                            sliding_window=0, fuse_append=True, scale=0.0, threads=0):
+    """laguna_gated_gqa_fp8_attention (fp8_attention_kernels.metal:70-263) over pages: q [B,T,Hq,D]; k, v [B,T,Hkv,D]
+    f32; pools uint8 [pages,Hkv,P,D] (modified in place when appending)."""
+    q, k, v, gate = _f32(q), _f32(k), _f32(v), _f32(gate)
+    B, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+    pt = _i32(page_table)
+    past = _i32(past_tokens)
+    out = np.empty_like(q)
+    lib().orc_gqa_paged_attention_fp8(_p(q), _p(k), _p(v), _p(gate), _p(k_pool, np.uint8), _p(v_pool, np.uint8),
+                                      C.c_float(key_scale), C.c_float(value_scale), _p(pt), C.c_int(pt.shape[1]),
+                                      _p(past), _p(out), C.c_int(B), C.c_int(Hq), C.c_int(Hkv), C.c_int(D),
+                                      C.c_int(page_size), C.c_int(T), C.c_int(sliding_window),
+                                      C.c_int(int(fuse_append)), C.c_float(scale), C.c_int(threads))
+    return out
+
+
+def fp8_codec_c(values=None, bits=None):
+    """The C restatement of the codec, element by element (pins it against the numpy statement below)."""
+    L = lib()
+    L.orc_fp8_e4m3fn_decode.restype = C.c_float
+    L.orc_fp8_e4m3fn_decode.argtypes = [C.c_uint8]
+    L.orc_fp8_e4m3fn_encode.restype = C.c_uint8
+    L.orc_fp8_e4m3fn_encode.argtypes = [C.c_float]
+    if bits is not None:
+        return np.array([L.orc_fp8_e4m3fn_decode(int(b)) for b in np.asarray(bits).ravel()], np.float32)
+    return np.array([L.orc_fp8_e4m3fn_encode(float(x)) for x in np.asarray(values, np.float32).ravel()], np.uint8)
+
+
 def fp8_e4m3fn_decode(bits):
     """laguna_fp8_e4m3fn_decode (crates/backend/src/metal/kernels/fp8_attention_kernels.metal:11-27): uint8 -> f32."""
     b = np.asarray(bits, dtype=np.uint8).astype(np.int32)

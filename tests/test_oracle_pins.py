@@ -443,3 +443,78 @@ def test_dsa_decode_topk_matches_the_reference_known_answers():
     c0, s0, f1 = math.cos(1.0), math.sin(1.0), 1.0 / math.sqrt(10000.0)
     want = [1 * c0 - 2 * s0, 3 * math.cos(f1) - 4 * math.sin(f1), 2 * c0 + 1 * s0, 4 * math.cos(f1) + 3 * math.sin(f1), 9.0]
     assert np.allclose(r, want, atol=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# FP8 E4M3FN cache: crates/backend/src/metal/fp8_attention.rs tests, replayed on the paged oracle
+# ---------------------------------------------------------------------------------------------------------------
+def test_fp8_codec_c_restatement_equals_the_numpy_statement():
+    bits = np.arange(256, dtype=np.uint8)
+    assert np.array_equal(orc.fp8_codec_c(bits=bits).view(np.uint32), orc.fp8_e4m3fn_decode(bits).view(np.uint32))
+    grid = np.sort(orc.fp8_e4m3fn_decode(np.arange(127, dtype=np.uint8)))
+    x = np.concatenate([grid, (grid[:-1] + grid[1:]) / 2, -grid, orc.fill_normal((4000,), 99, 3.0, False),
+                        np.array([0.0, -0.0, np.nan, 448.0, 449.0, 1e9, -1e9, 464.0, 1.1, 2.0 ** -10, 1e-30], np.float32)])
+    assert np.array_equal(orc.fp8_codec_c(values=x), orc.fp8_e4m3fn_encode(x))
+    assert orc.fp8_codec_c(values=[1.1])[0] == 0x39 and orc.fp8_codec_c(bits=[0x39])[0] == np.float32(1.125)
+
+
+def _fp8_paged(pages, P=16, Hkv=8, D=128):
+    return (np.zeros((pages, Hkv, P, D), np.uint8), np.zeros((pages, Hkv, P, D), np.uint8),
+            np.arange(pages, dtype=np.int32)[None])
+
+
+def test_fp8_global_prefill_append_and_decode():
+    """fp8_attention.rs:489-561: zero queries, values 1.1 and 3.0 prefilled (causal means 1.1 and 2.05), then a decode
+    with value 5.0: the two cached values come back through FP8 (1.1 -> 1.125), the current one is f32."""
+    Hq, Hkv, D = 48, 8, 128
+    kp, vp, pt = _fp8_paged(2)
+    q = np.zeros((1, 2, Hq, D), np.float32)
+    k = np.zeros((1, 2, Hkv, D), np.float32)
+    v = np.zeros((1, 2, Hkv, D), np.float32)
+    v[0, 0], v[0, 1] = 1.1, 3.0
+    gate = np.zeros((1, 2, Hq), np.float32)
+    out = orc.gqa_paged_attention_fp8(q, k, v, gate, kp, vp, 1.0, 1.0, pt, [0], 16)
+    ln2 = np.float32(np.log(2.0))
+    assert np.abs(out[0, 0] - 1.1 * ln2).max() <= 1e-4 and np.abs(out[0, 1] - 2.05 * ln2).max() <= 1e-4
+    out = orc.gqa_paged_attention_fp8(q[:, :1], k[:, :1], np.full((1, 1, Hkv, D), 5.0, np.float32), gate[:, :1], kp, vp,
+                                      1.0, 1.0, pt, [2], 16)
+    assert np.abs(out - (1.125 + 3.0 + 5.0) / 3.0 * ln2).max() <= 1e-4
+    assert vp[0, 0, 0, 0] == 0x39 and vp[0, 0, 2, 0] == orc.fp8_e4m3fn_encode(np.float32([5.0]))[0]
+
+
+def test_fp8_sliding_window_over_a_full_ring():
+    """fp8_attention.rs:563-625: 511 cached rows of value 1.0 (byte 0x38), window 512, two tokens 3.0 and 5.0, then a
+    decode of 7.0: 514/512, 518/512 and 524/512 times softplus(0)."""
+    Hq, Hkv, D, W = 72, 8, 128, 512
+    kp, vp, pt = _fp8_paged(40)
+    for t in range(511):
+        vp[t // 16, :, t % 16] = 0x38
+    q = np.zeros((1, 2, Hq, D), np.float32)
+    k = np.zeros((1, 2, Hkv, D), np.float32)
+    v = np.zeros((1, 2, Hkv, D), np.float32)
+    v[0, 0], v[0, 1] = 3.0, 5.0
+    gate = np.zeros((1, 2, Hq), np.float32)
+    ln2 = np.float32(np.log(2.0))
+    out = orc.gqa_paged_attention_fp8(q, k, v, gate, kp, vp, 1.0, 1.0, pt, [511], 16, sliding_window=W)
+    assert np.abs(out[0, 0] - 514.0 / 512.0 * ln2).max() <= 1e-4 and np.abs(out[0, 1] - 518.0 / 512.0 * ln2).max() <= 1e-4
+    out = orc.gqa_paged_attention_fp8(q[:, :1], k[:, :1], np.full((1, 1, Hkv, D), 7.0, np.float32), gate[:, :1], kp, vp,
+                                      1.0, 1.0, pt, [513], 16, sliding_window=W)
+    assert np.abs(out - 524.0 / 512.0 * ln2).max() <= 1e-4
+
+
+def test_fp8_sliding_prefill_longer_than_the_window():
+    """fp8_attention.rs:429-487: 513 tokens of value 2.0 (the first one 100.0) through a 512 window: the last row sees
+    only 2.0; a decode of 4.0 then sees 511 x 2.0 and itself."""
+    Hq, Hkv, D, W, T = 72, 8, 128, 512, 513
+    kp, vp, pt = _fp8_paged(40)
+    q = np.zeros((1, T, Hq, D), np.float32)
+    k = np.zeros((1, T, Hkv, D), np.float32)
+    v = np.full((1, T, Hkv, D), 2.0, np.float32)
+    v[0, 0] = 100.0
+    gate = np.zeros((1, T, Hq), np.float32)
+    ln2 = np.float32(np.log(2.0))
+    out = orc.gqa_paged_attention_fp8(q, k, v, gate, kp, vp, 1.0, 1.0, pt, [0], 16, sliding_window=W)
+    assert abs(out[0, T - 1, 0, 0] - 2.0 * ln2) < 1e-3
+    out = orc.gqa_paged_attention_fp8(q[:, :1], k[:, :1], np.full((1, 1, Hkv, D), 4.0, np.float32), gate[:, :1], kp, vp,
+                                      1.0, 1.0, pt, [T], 16, sliding_window=W)
+    assert abs(out[0, 0, 0, 0] - ((W - 1) * 2.0 + 4.0) / W * ln2) < 1e-3
