@@ -59,7 +59,9 @@ int32_t inf_ctx_destroy(inf_ctx* ctx);
 /* Re-target the context at another cudaStream_t (NULL is not accepted; (void*)1 names the default stream).
  * Pending work stays on the old stream.  A caller that captures a decode step into a CUDA graph points the
  * context at its capture stream first; the scratch workspace must already be large enough (run the step
- * once before capturing) because growing it allocates. */
+ * once before capturing) because growing it allocates, which a capture forbids.  A graph keeps the workspace
+ * address it was captured with: when a later, larger call outgrows the workspace the old buffer is kept alive
+ * until inf_ctx_destroy, so the graph stays valid (it then shares nothing with the new buffer). */
 int32_t inf_ctx_set_stream(inf_ctx* ctx, void* stream);
 const char* inf_last_error(inf_ctx* ctx);
 /* device_values_supported (backend.rs:1060). */
@@ -152,10 +154,24 @@ int32_t inf_paged_index_free_pages(inf_paged_index* index);
 int32_t inf_paged_index_release(inf_paged_index* index, int32_t seq);
 int32_t inf_paged_index_checkpoint(inf_paged_index* index, int32_t seq);
 int32_t inf_paged_index_restore(inf_paged_index* index, int32_t seq);
+/* The sliding-window ring on pages (reference: a sliding layer's cache is 512 slots, slot = position % capacity,
+ * crates/backend/src/metal/f16_attention.rs:120-210; 36 of 48 Laguna layers are sliding).  Pages that lie wholly
+ * below first_visible -- the lowest row any future query of the sequence can see, i.e. next position + 1 - window --
+ * go back to the free list; logical positions stay, the released page-table slots read -1, and the attention kernels
+ * never resolve a page below the window.  A checkpoint older than first_visible forbids the trim (INF_E_CACHE).
+ * released_pages (optional) receives the number of pages returned. */
+int32_t inf_paged_index_trim(inf_paged_index* index, int32_t seq, int32_t first_visible, int32_t* released_pages);
 int32_t inf_paged_index_arrays(inf_paged_index* index, const int32_t** pages, const int32_t** lens,
                                int32_t* max_seqs, int32_t* max_pages);
 
 /* ---- RoPE and KV append ----------------------------------------------------------- */
+/* qk_rms_norm_rope_device (backend.rs:1238; kernel qk_rms_norm_half_split_rope_f32_kernel, rope_kernels.metal:113):
+ * per-head RMSNorm (weight NULL = no norm) then half-split RoPE of one tensor [batch, tokens, heads, head_dim],
+ * f32 in / f32 out; position of a row = position_offset + its token index. */
+int32_t inf_qk_rms_norm_rope(inf_ctx* ctx, const float* input, const float* norm_weight, float eps,
+                             int32_t position_offset, const inf_rope_table* rope, int32_t batch, int32_t tokens,
+                             int32_t heads, int32_t head_dim, float* output);
+
 /* laguna_qk_rms_norm_rope_pair_device (backend.rs:1252; kernel rope_kernels.metal:167):
  * per-head RMSNorm (weight NULL = no norm) then half-split RoPE, f32 in / f32 out.
  * q [batch, tokens, q_heads, head_dim], k [batch, tokens, kv_heads, head_dim]. */
@@ -263,6 +279,27 @@ int32_t inf_mla_decode_absorbed_selected(inf_ctx* ctx, const void* q_f16, const 
                                          const inf_page_table* table, const int32_t* selected,
                                          const int32_t* selected_counts, int32_t selected_stride, int32_t heads,
                                          float scale, void* out, int32_t out_dtype);
+
+/* The expanded-head forms of the selected-row attention (f32 at the boundary, heads-major layouts as the reference's).
+ * inf_selected_decode_attention: selected_decode_attention_device (backend.rs:2001, 7814; kernel
+ *   fused_selected_decode_attention_f32_kernel, kernels/attention_kernels.metal:605-721, and its f16-KV twin): q
+ *   [batch, heads, 1, head_dim], selected_k [batch, heads, selected_tokens, head_dim], selected_v [.., value_dim] in
+ *   selected_dtype (INF_DTYPE_F32 or INF_DTYPE_F16), current_k / current_v f32 [batch, heads, 1, dim]; the softmax
+ *   runs over the selected rows plus, when include_current_kv, the current token; scale 1/sqrt(head_dim); out
+ *   [batch, heads, 1, value_dim].  selected_tokens == 0 is INF_E_BACKEND like the reference.
+ * inf_selected_sequence_attention: selected_sequence_attention_device (backend.rs:2015, 7930; kernel
+ *   fused_selected_sequence_attention_f32_kernel, :723-968): causal attention of query_tokens rows (a speculative
+ *   batch, or a first prompt chunk with past_tokens == 0) over past_k / past_v [batch, heads, past_tokens, dim] plus
+ *   current rows 0..t; all f32; out [batch, heads, query_tokens, value_dim].
+ * More than 4096 visible keys (the reference kernel's limit) or dims above 256 return INF_UNSUPPORTED. */
+int32_t inf_selected_decode_attention(inf_ctx* ctx, const float* q, const void* selected_k, const void* selected_v,
+                                      int32_t selected_dtype, const float* current_k, const float* current_v,
+                                      int32_t batch, int32_t heads, int32_t selected_tokens, int32_t head_dim,
+                                      int32_t value_dim, int32_t include_current_kv, float* out);
+int32_t inf_selected_sequence_attention(inf_ctx* ctx, const float* q, const float* past_k, const float* past_v,
+                                        const float* current_k, const float* current_v, int32_t batch, int32_t heads,
+                                        int32_t past_tokens, int32_t query_tokens, int32_t head_dim, int32_t value_dim,
+                                        float* out);
 
 /* DSA indexer, the step before inf_mla_decode_absorbed_selected.
  * inf_dsa_scores (kernel dsa_scores_f32_kernel, crates/backend/src/metal/kernels/dsa_kernels.metal:137-176):

@@ -252,6 +252,13 @@ class CudaBackend:
         return PageTable(dp, dl, desc, hp, hl)
 
     # ------------------------------------------------------------------ RoPE + append
+    def qk_rms_norm_rope_device(self, x, norm_weight, eps, position_offset, table):  # backend.rs:1238
+        B, T, H, D = x.shape
+        out = torch.empty_like(x)
+        ok = self._check(self._lib.inf_qk_rms_norm_rope(self._ctx, _ptr(x), _ptr(norm_weight), eps, position_offset,
+                                                        C.byref(table), B, T, H, D, _ptr(out)))
+        return out if ok else None
+
     def laguna_qk_rms_norm_rope_pair_device(self, q, k, q_norm, k_norm, eps, position_offset, table):  # backend.rs:1252
         B, T, Hq, D = q.shape
         Hkv = k.shape[2]
@@ -393,6 +400,34 @@ class CudaBackend:
         ok = self._check(self._lib.inf_mla_decode_absorbed_selected(
             self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc), _ptr(selected), _ptr(selected_counts),
             selected.shape[1], H, scale, _ptr(out), dt))
+        return out if ok else None
+
+    def selected_decode_attention_device(self, q, selected_k, selected_v, current_k, current_v, include_current_kv: bool):
+        """selected_decode_attention_device (backend.rs:2001): q [B,H,1,D] f32, selected_k/v [B,H,S,D/Dv] f32 or fp16,
+        current_k/v [B,H,1,D/Dv] f32 -> [B,H,1,Dv] f32."""
+        B, H, T, D = q.shape
+        S, Dv = selected_k.shape[2], selected_v.shape[3]
+        if selected_k.dtype != selected_v.dtype:
+            raise InfernoError(L.INF_E_BACKEND, "device selected decode attention selected KV dtype mismatch")
+        if T != 1:
+            raise InfernoError(L.INF_E_SHAPE, "device_selected_decode_attention_query_tokens: expected [1]")
+        dt = L.DTYPE_F32 if selected_k.dtype == torch.float32 else L.DTYPE_F16
+        out = torch.empty((B, H, 1, Dv), dtype=torch.float32, device=self.device)
+        ok = self._check(self._lib.inf_selected_decode_attention(
+            self._ctx, _ptr(q), _ptr(selected_k), _ptr(selected_v), dt, _ptr(current_k), _ptr(current_v), B, H, S, D, Dv,
+            int(include_current_kv), _ptr(out)))
+        return out if ok else None
+
+    def selected_sequence_attention_device(self, q, past_k, past_v, current_k, current_v):
+        """selected_sequence_attention_device (backend.rs:2015): causal rows over past + current, all f32,
+        [B,H,T,D] / [B,H,P,D] layouts -> [B,H,T,Dv]."""
+        B, H, T, D = q.shape
+        P = past_k.shape[2] if past_k is not None else 0
+        Dv = current_v.shape[3]
+        out = torch.empty((B, H, T, Dv), dtype=torch.float32, device=self.device)
+        ok = self._check(self._lib.inf_selected_sequence_attention(
+            self._ctx, _ptr(q), _ptr(past_k) if P else None, _ptr(past_v) if P else None, _ptr(current_k),
+            _ptr(current_v), B, H, P, T, D, Dv, _ptr(out)))
         return out if ok else None
 
     def dsa_scores(self, q, weights, past_keys, current_key, out=None):

@@ -44,6 +44,7 @@ struct inf_ctx {
     std::string err;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
+    std::vector<void*> retired_workspaces;  // outgrown workspaces, kept until destroy: captured graphs may name them
     size_t dsa_scores_smem = 0;  // dynamic shared memory the tensor-core index-score kernel has been allowed so far
     int* status = nullptr;       // device int32[4]
     int* host_status = nullptr;  // pinned int32[4]
@@ -77,8 +78,8 @@ struct inf_prof_scope {
 };
 
 int inf_fail(inf_ctx* ctx, int code, const char* fmt, ...);
-// Grows (never shrinks) the context's scratch buffer.  Allocation is synchronous with respect to
-// the stream: the old buffer is released only after the stream has drained.
+// Grows (never shrinks) the context's scratch buffer.  An outgrown buffer is kept until the context is destroyed,
+// so work already enqueued -- or a CUDA graph captured earlier -- that names it stays valid.
 int inf_ensure_workspace(inf_ctx* ctx, size_t bytes);
 // fp16 tiled tensor map with the 128-byte swizzle, rank 2 or 3.  dims/strides innermost first;
 // strides in bytes for dims 1..rank-1.
@@ -135,5 +136,8 @@ inline cudaError_t inf_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 #endif
 
 // Host-side range check of the page-table entries a launch may touch (needs the host mirrors).
+// window / query_tokens: with a sliding window, page slots wholly below the lowest key the first of the call's
+// query_tokens rows can see are not checked (they may have been trimmed away).  append_only: the call writes its
+// extra_tokens rows and reads nothing else, so only their pages are checked.
 int inf_validate_table(inf_ctx* ctx, const inf_page_table* t, int num_pages, int page_size, int extra_tokens,
-                       const char* what);
+                       const char* what, int window = 0, int query_tokens = 1, bool append_only = false);

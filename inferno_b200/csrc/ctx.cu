@@ -17,12 +17,15 @@ int inf_fail(inf_ctx* ctx, int code, const char* fmt, ...) {
 
 int inf_ensure_workspace(inf_ctx* ctx, size_t bytes) {
     if (bytes <= ctx->workspace_bytes) return INF_OK;
-    INF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->workspace) INF_CUDA(ctx, cudaFree(ctx->workspace));
-    ctx->workspace = nullptr;
-    ctx->workspace_bytes = 0;
+    // A CUDA graph captured earlier keeps the address it was captured with, so an outgrown workspace is retired,
+    // not freed: it lives until the context is destroyed.  Growth is by at least a factor of two, which bounds
+    // the retired buffers by the size of the live one.
     size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-    INF_CUDA(ctx, cudaMalloc(&ctx->workspace, want));
+    if (want < 2 * ctx->workspace_bytes) want = 2 * ctx->workspace_bytes;
+    void* fresh = nullptr;
+    INF_CUDA(ctx, cudaMalloc(&fresh, want));
+    if (ctx->workspace) ctx->retired_workspaces.push_back(ctx->workspace);
+    ctx->workspace = fresh;
     ctx->workspace_bytes = want;
     return INF_OK;
 }
@@ -74,7 +77,7 @@ int inf_make_tmap_typed(inf_ctx* ctx, const void* base, uint32_t rank, const uin
 }
 
 int inf_validate_table(inf_ctx* ctx, const inf_page_table* t, int num_pages, int page_size, int extra_tokens,
-                       const char* what) {
+                       const char* what, int window, int query_tokens, bool append_only) {
     if (!t || !t->pages || !t->lens) return inf_fail(ctx, INF_E_ARG, "%s: null page table", what);
     if (t->batch <= 0 || t->max_pages <= 0)
         return inf_fail(ctx, INF_E_SHAPE, "%s: batch %d / max_pages %d must be positive", what, t->batch, t->max_pages);
@@ -86,7 +89,12 @@ int inf_validate_table(inf_ctx* ctx, const inf_page_table* t, int num_pages, int
                             len, (long long)t->max_pages * page_size);
         if (!t->host_pages) continue;
         int used = (int)((len + page_size - 1) / page_size);
-        for (int p = 0; p < used; ++p) {
+        // with a sliding window the pages wholly below the first query row's lowest visible key are never read and
+        // may have been returned to the pool (inf_paged_index_trim): their slots are not checked; an append only
+        // touches the pages of its own tokens
+        long long lowest = append_only ? t->host_lens[b] : (window > 0 ? len - query_tokens + 1 - window : 0);
+        int first = lowest > 0 ? (int)(lowest / page_size) : 0;
+        for (int p = first; p < used; ++p) {
             int id = t->host_pages[(size_t)b * t->max_pages + p];
             if (id < 0 || id >= num_pages)
                 return inf_fail(ctx, INF_E_CACHE, "%s: sequence %d page slot %d holds page id %d outside [0,%d)", what,
@@ -150,6 +158,7 @@ int32_t inf_ctx_destroy(inf_ctx* ctx) {
         cudaEventDestroy(r.b);
     }
     if (ctx->workspace) cudaFree(ctx->workspace);
+    for (void* w : ctx->retired_workspaces) cudaFree(w);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);

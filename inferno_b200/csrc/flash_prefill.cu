@@ -225,6 +225,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // ring barriers whose phase it has not followed.
     if (n > 0 && act0) st[0].kt_begin = kt_lo;
     if (n > 0 && act1) st[1].kt_begin = kt_lo;
+    // lowest key any row of this CTA can see: 16-token page tiles wholly below it are masked for every row and may
+    // have been returned to the pool, so they are requested as zeros without looking at the page table
+    const int q0_min = act0 && act1 ? min(st[0].q0, st[1].q0) : (act0 ? st[0].q0 : st[1].q0);
+    const int lo_visible = p.window > 0 ? max(0, past + q0_min + 1 - p.window) : 0;
     // both streams of a CTA read the same KV head (pair_heads pairs lie inside one KV group)
     const int kvh = PAGED ? st[act0 ? 0 : 1].head / p.group : st[act0 ? 0 : 1].head;
 #ifdef INF_KPROF
@@ -256,7 +260,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (PAGED && lane < 8) {
                 const int token = k0 + lane * 16;
                 const int slot = token / p.page_size;
-                if (token < kv_total && slot < p.max_pages) {
+                if (token < kv_total && token + 16 > lo_visible && slot < p.max_pages) {
                     const int page = p.pages[(long long)b * p.max_pages + slot];
                     if (page >= 0 && page < p.num_pages)
                         y = (page * p.kv_heads + kvh) * p.page_size + token % p.page_size;
@@ -304,7 +308,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (PAGED && lane < 8) {
                 const int token = k0 + lane * 16;
                 const int slot = token / p.page_size;
-                if (token < kv_total && slot < p.max_pages) {
+                if (token < kv_total && token + 16 > lo_visible && slot < p.max_pages) {
                     const int page = p.pages[(long long)b * p.max_pages + slot];
                     if (page >= 0 && page < p.num_pages) y = (page * p.kv_heads + kvh) * p.page_size + token % p.page_size;
                 }
@@ -811,7 +815,7 @@ int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* p
     if (sliding_window < 0) return inf_fail(ctx, INF_E_CONFIG, "gqa_prefill: sliding_window must be >= 0");
     if (out_dtype != INF_DTYPE_F32 && out_dtype != INF_DTYPE_F16)
         return inf_fail(ctx, INF_E_DTYPE, "gqa_prefill: output dtype must be f32 or f16");
-    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "gqa_prefill");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "gqa_prefill", sliding_window, tokens);
     if (rc != INF_OK) return rc;
 
     CUtensorMap tq, tk, tv;

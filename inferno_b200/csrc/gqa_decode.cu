@@ -148,7 +148,9 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
             int token = run_begin + i * 16;
             int slot = token / p.page_size;
             int y = oob_row;
-            if (slot < p.max_pages) {
+            if (token + 16 <= win_start) {
+                // wholly below the window: every key is masked, and the page may have been returned to the pool
+            } else if (slot < p.max_pages) {
                 int page = p.pages[(long long)b * p.max_pages + slot];
                 if (page >= 0 && page < p.num_pages)
                     y = (page * p.kv_heads + kvh) * p.page_size + token % p.page_size;
@@ -568,7 +570,7 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     if (fp8 && (!(fp8->key_scale > 0.f) || !(fp8->value_scale > 0.f) || !isfinite(fp8->key_scale) || !isfinite(fp8->value_scale)))
         return inf_fail(ctx, INF_E_CONFIG, "gqa_decode_fp8: scales must be positive and finite");
     const int cur_extra = fp8 ? 1 : 0;  // the FP8 form counts cached rows; the current token comes on top
-    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, len_add, "gqa_decode");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, len_add, "gqa_decode", sliding_window, 1);
     if (rc != INF_OK) return rc;
     if (table->host_lens)
         for (int b = 0; b < table->batch; ++b)

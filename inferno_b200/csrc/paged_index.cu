@@ -15,7 +15,8 @@ struct inf_paged_index {
     int num_pages, page_size, max_seqs, max_pages;
     std::vector<int32_t> table;  // [max_seqs][max_pages], -1 = unmapped
     std::vector<int32_t> lens;   // [max_seqs]
-    std::vector<int32_t> mapped; // pages mapped per sequence
+    std::vector<int32_t> mapped; // page slots in use per sequence: slots [trimmed, mapped) hold pages
+    std::vector<int32_t> trimmed;  // leading page slots whose pages went back to the pool (inf_paged_index_trim)
     std::vector<int32_t> checkpoint;  // saved length per sequence, -1 = none
     std::vector<int32_t> free_list;   // stack of free physical pages (lowest id on top at start)
     std::string err;
@@ -42,6 +43,7 @@ int32_t inf_paged_index_create(int32_t num_pages, int32_t page_size, int32_t max
     p->table.assign((size_t)max_seqs * max_pages_per_seq, -1);
     p->lens.assign(max_seqs, 0);
     p->mapped.assign(max_seqs, 0);
+    p->trimmed.assign(max_seqs, 0);
     p->checkpoint.assign(max_seqs, -1);
     p->free_list.resize(num_pages);
     for (int i = 0; i < num_pages; ++i) p->free_list[i] = num_pages - 1 - i;  // pop() yields 0, 1, 2, ...
@@ -86,6 +88,8 @@ int32_t inf_paged_index_locate(inf_paged_index* p, int32_t seq, int32_t token, i
     if (token < 0 || token >= p->lens[seq])
         return pi_fail(p, INF_E_CACHE, "token index " + std::to_string(token) + " is outside cached token count " +
                                            std::to_string(p->lens[seq]));
+    if (token / p->page_size < p->trimmed[seq])
+        return pi_fail(p, INF_E_CACHE, "token index " + std::to_string(token) + " lies in a page that was trimmed away");
     if (page) *page = p->table[(size_t)seq * p->max_pages + token / p->page_size];
     if (offset) *offset = token % p->page_size;
     return INF_OK;
@@ -98,7 +102,7 @@ int32_t inf_paged_index_len(inf_paged_index* p, int32_t seq) {
 
 int32_t inf_paged_index_page_count(inf_paged_index* p, int32_t seq) {
     if (!p || seq < 0 || seq >= p->max_seqs) return -1;
-    return p->mapped[seq];
+    return p->mapped[seq] - p->trimmed[seq];
 }
 
 int32_t inf_paged_index_free_pages(inf_paged_index* p) { return p ? (int32_t)p->free_list.size() : -1; }
@@ -108,16 +112,45 @@ static void pi_truncate(inf_paged_index* p, int seq, int new_len) {
     while (p->mapped[seq] > keep) {
         --p->mapped[seq];
         int32_t& slot = p->table[(size_t)seq * p->max_pages + p->mapped[seq]];
-        p->free_list.push_back(slot);
+        if (slot >= 0) p->free_list.push_back(slot);
         slot = -1;
     }
+    if (p->trimmed[seq] > p->mapped[seq]) p->trimmed[seq] = p->mapped[seq];
     p->lens[seq] = new_len;
+}
+
+// The sliding-window ring on pages (the reference bounds a sliding layer's cache at 512 slots and overwrites slot
+// abs % capacity, crates/backend/src/metal/f16_attention.rs:120-210): once no future query can see a row, its page
+// goes back to the pool.  Logical positions do not move: the page-table slots of the released pages become -1 and
+// the kernels, which mask everything below the window, never resolve them.
+int32_t inf_paged_index_trim(inf_paged_index* p, int32_t seq, int32_t first_visible, int32_t* released_pages) {
+    if (!p) return INF_E_ARG;
+    if (seq < 0 || seq >= p->max_seqs) return pi_fail(p, INF_E_CACHE, "sequence index out of range");
+    if (first_visible < 0) return pi_fail(p, INF_E_CACHE, "first visible token must not be negative");
+    if (first_visible > p->lens[seq]) first_visible = p->lens[seq];
+    if (p->checkpoint[seq] >= 0 && first_visible > p->checkpoint[seq])
+        return pi_fail(p, INF_E_CACHE, "trim would release rows a checkpoint at " + std::to_string(p->checkpoint[seq]) +
+                                           " tokens still covers; drop or renew the checkpoint first");
+    const int upto = first_visible / p->page_size;  // pages wholly below the first visible token
+    int released = 0;
+    while (p->trimmed[seq] < upto && p->trimmed[seq] < p->mapped[seq]) {
+        int32_t& slot = p->table[(size_t)seq * p->max_pages + p->trimmed[seq]];
+        if (slot >= 0) {
+            p->free_list.push_back(slot);
+            ++released;
+        }
+        slot = -1;
+        ++p->trimmed[seq];
+    }
+    if (released_pages) *released_pages = released;
+    return INF_OK;
 }
 
 int32_t inf_paged_index_release(inf_paged_index* p, int32_t seq) {
     if (!p) return INF_E_ARG;
     if (seq < 0 || seq >= p->max_seqs) return pi_fail(p, INF_E_CACHE, "sequence index out of range");
     pi_truncate(p, seq, 0);
+    p->trimmed[seq] = 0;
     p->checkpoint[seq] = -1;
     return INF_OK;
 }
@@ -134,6 +167,8 @@ int32_t inf_paged_index_restore(inf_paged_index* p, int32_t seq) {
     if (seq < 0 || seq >= p->max_seqs) return pi_fail(p, INF_E_CACHE, "sequence index out of range");
     if (p->checkpoint[seq] < 0) return pi_fail(p, INF_E_CACHE, "sequence has no checkpoint");
     if (p->checkpoint[seq] > p->lens[seq]) return pi_fail(p, INF_E_CACHE, "checkpoint is ahead of the sequence");
+    if (p->checkpoint[seq] < (long long)p->trimmed[seq] * p->page_size)
+        return pi_fail(p, INF_E_CACHE, "checkpoint lies below the rows that were trimmed away");
     pi_truncate(p, seq, p->checkpoint[seq]);
     return INF_OK;
 }

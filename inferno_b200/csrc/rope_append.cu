@@ -375,6 +375,24 @@ int check_rope(inf_ctx* ctx, const inf_rope_table* rope) {
 
 extern "C" {
 
+int32_t inf_qk_rms_norm_rope(inf_ctx* ctx, const float* input, const float* norm_weight, float eps,
+                             int32_t position_offset, const inf_rope_table* rope, int32_t batch, int32_t tokens,
+                             int32_t heads, int32_t head_dim, float* output) {
+    INF_CHECK_CTX(ctx);
+    if (!input || !rope || !output) return inf_fail(ctx, INF_E_ARG, "qk_rms_norm_rope: null pointer");
+    if (head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "qk_rms_norm_rope: head_dim must be 128, got %d", head_dim);
+    if (batch <= 0 || tokens <= 0 || heads <= 0) return inf_fail(ctx, INF_E_SHAPE, "qk_rms_norm_rope: sizes must be positive");
+    int rc = check_rope(ctx, rope);
+    if (rc != INF_OK) return rc;
+    // the pair kernel with an empty K side: one warp per head row
+    const long long rows = (long long)batch * tokens * heads;
+    qk_norm_rope_pair_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx->stream>>>(
+        input, nullptr, norm_weight, nullptr, rope->inv_freq, output, nullptr, rows, 0, tokens, heads, 1, rope->rotary_dim,
+        position_offset, eps, rope->attention_factor);
+    INF_LAUNCH_CHECK(ctx, "qk_norm_rope_pair_kernel");
+    return INF_OK;
+}
+
 int32_t inf_laguna_qk_rms_norm_rope_pair(inf_ctx* ctx, const float* q, const float* k, const float* qw,
                                          const float* kw, float eps, int32_t position_offset,
                                          const inf_rope_table* rope, int32_t batch, int32_t tokens, int32_t q_heads,
@@ -418,7 +436,7 @@ static int rope_append_gqa_any(inf_ctx* ctx, const void* q, const void* k, const
         int rc = check_rope(ctx, rope);
         if (rc != INF_OK) return rc;
     }
-    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "rope_append_gqa");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "rope_append_gqa", 0, 1, true);
     if (rc != INF_OK) return rc;
     const long long bt = (long long)table->batch * tokens;
     if (bt > 0x7fffffffLL) return inf_fail(ctx, INF_E_SHAPE, "rope_append_gqa: batch x tokens exceeds the launch grid");
@@ -491,7 +509,7 @@ int32_t inf_mla_kv_postprocess_append(inf_ctx* ctx, const float* input, const fl
     if (tokens <= 0) return inf_fail(ctx, INF_E_SHAPE, "mla_kv_postprocess: tokens must be positive");
     if (pool->rope_dim > 128 || (pool->rope_dim & 1)) return inf_fail(ctx, INF_E_SHAPE, "rope_dim must be even and <= 128");
     if (!(theta > 0.0f) || !isfinite(theta)) return inf_fail(ctx, INF_E_CONFIG, "rope theta must be positive");
-    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "mla_kv_postprocess");
+    int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, tokens, "mla_kv_postprocess", 0, 1, true);
     if (rc != INF_OK) return rc;
     InvFreq64 f;
     host_inv_freq_glm(theta, pool->rope_dim, &f);

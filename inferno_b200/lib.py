@@ -83,6 +83,7 @@ SIGNATURES = {
     "inf_kv_pool_destroy": (_I, [_P, C.POINTER(KvPool)]),
     "inf_mla_pool_create": (_I, [_P, _I, _I, _I, _I, C.POINTER(MlaPool)]),
     "inf_mla_pool_destroy": (_I, [_P, C.POINTER(MlaPool)]),
+    "inf_qk_rms_norm_rope": (_I, [_P, _P, _P, _F, _I, C.POINTER(RopeTable), _I, _I, _I, _I, _P]),
     "inf_laguna_qk_rms_norm_rope_pair": (_I, [_P, _P, _P, _P, _P, _F, _I, C.POINTER(RopeTable), _I, _I, _I, _I, _I,
                                               _P, _P]),
     "inf_rope_append_gqa": (_I, [_P, _P, _P, _P, _I, _P, _P, _F, C.POINTER(RopeTable), C.POINTER(KvPool),
@@ -105,6 +106,8 @@ SIGNATURES = {
     "inf_mla_decode_absorbed": (_I, [_P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _I, _I, _F, _P, _I]),
     "inf_mla_decode_absorbed_selected": (_I, [_P, _P, C.POINTER(MlaPool), C.POINTER(PageTable), _P, _P, _I, _I, _F, _P,
                                               _I]),
+    "inf_selected_decode_attention": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "inf_selected_sequence_attention": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "inf_dsa_scores": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "inf_dsa_topk": (_I, [_P, _P, _I, _I, _I, _P, _I]),
     "inf_dsa_index_key": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P]),
@@ -135,6 +138,7 @@ SIGNATURES = {
     "inf_paged_index_page_count": (_I, [_P, _I]),
     "inf_paged_index_free_pages": (_I, [_P]),
     "inf_paged_index_release": (_I, [_P, _I]),
+    "inf_paged_index_trim": (_I, [_P, _I, _I, C.POINTER(_I)]),
     "inf_paged_index_checkpoint": (_I, [_P, _I]),
     "inf_paged_index_restore": (_I, [_P, _I]),
     "inf_paged_index_arrays": (_I, [_P, C.POINTER(_P), C.POINTER(_P), C.POINTER(_I), C.POINTER(_I)]),

@@ -63,10 +63,18 @@ class PagedIndex:
         """[(physical_page_id, start_token, token_count, free_slots)] like PagedKvCache::page_stats."""
         n, P = self.cached_tokens(seq), self.page_size
         pages, _ = self.arrays()
-        return [(int(pages[seq, i]), i * P, min(P, n - i * P), P - min(P, n - i * P)) for i in range(self.page_count(seq))]
+        return [(int(pages[seq, i]), i * P, min(P, n - i * P), P - min(P, n - i * P))
+                for i in range((n + P - 1) // P) if pages[seq, i] >= 0]
 
     def release(self, seq: int):
         self._check(self._lib.inf_paged_index_release(self._h, seq))
+
+    def trim(self, seq: int, first_visible: int) -> int:
+        """Return the pages wholly below `first_visible` (the lowest row a future query can see under the sliding
+        window) to the pool; logical positions stay.  Returns the number of pages released."""
+        n = C.c_int32()
+        self._check(self._lib.inf_paged_index_trim(self._h, seq, first_visible, C.byref(n)))
+        return n.value
 
     def checkpoint(self, seq: int):
         self._check(self._lib.inf_paged_index_checkpoint(self._h, seq))

@@ -613,6 +613,38 @@ void orc_gqa_paged_attention_fp8(const float* query, const float* cur_key, const
     }
 }
 
+// kernels/attention_kernels.metal:605-721 (decode: T = 1, include_current flag) and :723-968 (sequence: row t sees
+// the selected rows and current rows 0..t): every score, the maximum, the denominator, then the weighted sum.
+void orc_selected_attention_f32(const float* q, const float* sel_k, const float* sel_v, const float* cur_k,
+                                const float* cur_v, float* out, int batch, int heads, int S, int T, int D, int Dv,
+                                int include_current) {
+    const float scale = 1.0f / sqrtf((float)D);
+    const int64_t rows = (int64_t)batch * heads * T;
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < rows; ++row) {
+        const int t = (int)(row % T);
+        const int64_t bh = row / T;
+        const int visible = S + (include_current ? t + 1 : 0);
+        std::vector<float> scores(visible);
+        float mx = -3.4028234663852886e+38f;
+        for (int key = 0; key < visible; ++key) {
+            const float* kr = key < S ? sel_k + (bh * S + key) * D : cur_k + (bh * T + (key - S)) * D;
+            scores[key] = dotf(q + row * D, kr, D) * scale;
+            mx = std::max(mx, scores[key]);
+        }
+        float denom = 0.0f;
+        for (int key = 0; key < visible; ++key) denom += expf(scores[key] - mx);
+        for (int d = 0; d < Dv; ++d) {
+            float sum = 0.0f;
+            for (int key = 0; key < visible; ++key) {
+                const float* vr = key < S ? sel_v + (bh * S + key) * Dv : cur_v + (bh * T + (key - S)) * Dv;
+                sum += expf(scores[key] - mx) / denom * vr[d];
+            }
+            out[row * Dv + d] = sum;
+        }
+    }
+}
+
 void orc_linearize_paged(const uint16_t* pool, const int32_t* page_table, int max_pages, uint16_t* out, int batch,
                          int kv_heads, int tokens, int page_size, int head_dim) {
     for (int b = 0; b < batch; ++b)

@@ -141,6 +141,13 @@ void orc_mla_absorbed_paged(const float* q, const float* cur_rows /* [batch,T,L+
                             int batch, int heads, int q_tokens, int page_size, int latent_dim, int rope_dim,
                             float scale, int fuse_append, int threads);
 
+/* ---- selected-row attention over expanded heads (DSA), kernels/attention_kernels.metal:605-721 and :723-968 ----
+ * q [B,H,T,D]; sel_k [B,H,S,D], sel_v [B,H,S,Dv]; cur_k [B,H,T,D], cur_v [B,H,T,Dv]; row t sees the S selected rows
+ * and, when include_current, current rows 0..t.  out [B,H,T,Dv]. */
+void orc_selected_attention_f32(const float* q, const float* sel_k, const float* sel_v, const float* cur_k,
+                                const float* cur_v, float* out, int batch, int heads, int S, int T, int D, int Dv,
+                                int include_current);
+
 /* ---- a10: causal attention over expanded heads (MLA prefill) ------------- */
 /* kernels/attention_kernels.metal:723-968 with zero past (backend.rs:8050-8067); K = [k_nope | shared rope
  * tail] as built by combine_rope_tail (kernels/layout_kernels.metal:148-183, rope_head_count == 1).

@@ -322,6 +322,20 @@ def q8_rows_decode(payload, dim):
     return (p[:, 4:].view(np.int8).astype(np.float32) * scale[:, None]).astype(np.float32)
 
 
+def selected_attention(q, sel_k, sel_v, cur_k, cur_v, include_current=True):
+    """kernels/attention_kernels.metal:605-721 / :723-968: q [B,H,T,D], sel_k [B,H,S,D], sel_v [B,H,S,Dv] (or None for
+    S = 0), cur_k [B,H,T,D], cur_v [B,H,T,Dv] -> [B,H,T,Dv]."""
+    q, cur_k, cur_v = _f32(q), _f32(cur_k), _f32(cur_v)
+    B, H, T, D = q.shape
+    Dv = cur_v.shape[3]
+    S = 0 if sel_k is None else sel_k.shape[2]
+    sel_k, sel_v = _f32(sel_k), _f32(sel_v)
+    out = np.empty((B, H, T, Dv), np.float32)
+    lib().orc_selected_attention_f32(_p(q), _p(sel_k), _p(sel_v), _p(cur_k), _p(cur_v), _p(out), C.c_int(B), C.c_int(H),
+                                     C.c_int(S), C.c_int(T), C.c_int(D), C.c_int(Dv), C.c_int(int(include_current)))
+    return out
+
+
 def gqa_paged_attention_fp8(q, k, v, gate, k_pool, v_pool, key_scale, value_scale, page_table, past_tokens, page_size,
                             sliding_window=0, fuse_append=True, scale=0.0, threads=0):
     """laguna_gated_gqa_fp8_attention (fp8_attention_kernels.metal:70-263) over pages: q [B,T,Hq,D]; k, v [B,T,Hkv,D]

@@ -230,6 +230,9 @@ def test_rmsnorm_rope_pair_matches_oracle(be):
     qo, ko = be.laguna_qk_rms_norm_rope_pair_device(dev(be, qv), dev(be, kv), dev(be, qw), dev(be, kw), 1e-6, pos, table)
     assert np.max(np.abs(qo.cpu().numpy() - orc.qk_norm_rope(qv, qw, inv, rotary, pos, 1e-6, factor))) <= 3e-5
     assert np.max(np.abs(ko.cpu().numpy() - orc.qk_norm_rope(kv, kw, inv, rotary, pos, 1e-6, factor))) <= 3e-5
+    # the single-tensor form of the same kernel (qk_rms_norm_rope_device, rope_kernels.metal:113)
+    one = be.qk_rms_norm_rope_device(dev(be, qv), dev(be, qw), 1e-6, pos, table)
+    assert np.array_equal(one.cpu().numpy(), qo.cpu().numpy())
     # sliding-layer convention: rotary 128, theta 1e4
     inv2 = orc.default_inv_freq(10000.0, 128)
     t2 = be.prepare_rope_table(inv2, 128, 1.0)

@@ -115,3 +115,41 @@ def test_sharding_helpers():
     assert cover[0] == (0, 4) and cover[-1] == (28, 32)
     cover = [shard_sequences(10, 4, r) for r in range(4)]
     assert cover == [(0, 3), (3, 6), (6, 8), (8, 10)]
+
+
+def test_trim_returns_pages_below_the_window_and_keeps_positions():
+    """The sliding-window ring on pages: a 512-token window over a growing sequence holds a bounded number of pages
+    (the reference's sliding cache is 512 slots, metal/f16_attention.rs:120-210)."""
+    from inferno_b200 import InfernoError
+    from inferno_b200.paged import PagedIndex
+    P, W = 16, 512
+    idx = PagedIndex(num_pages=40, page_size=P, max_seqs=2, max_pages_per_seq=256)
+    idx.append(0, 600)
+    assert idx.page_count(0) == 38 and idx.free_pages() == 2
+    released = idx.trim(0, 600 + 1 - W)          # the next query sits at position 600
+    assert released == (600 + 1 - W) // P == 5 and idx.free_pages() == 7 and idx.page_count(0) == 33
+    pages, lens = idx.arrays()
+    assert lens[0] == 600 and (pages[0, :5] == -1).all() and (pages[0, 5:38] >= 0).all()
+    assert idx.token_location(0, 599)[1] == 599 % P       # logical positions did not move
+    with pytest.raises(InfernoError) as e:
+        idx.token_location(0, 10)
+    assert "trimmed" in str(e.value)
+    # decoding on: the sequence grows to 3000 tokens inside a 40-page pool
+    for pos in range(600, 3000):
+        idx.append(0, 1)
+        idx.trim(0, pos + 2 - W)
+        assert idx.page_count(0) <= W // P + 2
+    assert idx.cached_tokens(0) == 3000 and idx.trim(0, 0) == 0
+    # a checkpoint pins its rows: trimming past it is refused, restoring below the trimmed rows too
+    idx.checkpoint(0)
+    idx.append(0, 64)
+    with pytest.raises(InfernoError) as e:
+        idx.trim(0, 3010)
+    assert "checkpoint" in str(e.value)
+    idx.restore(0)
+    assert idx.cached_tokens(0) == 3000
+    idx.release(0)
+    assert idx.free_pages() == 40 and idx.page_count(0) == 0
+    idx.append(0, 5)
+    assert idx.token_location(0, 0)[1] == 0
+    idx.close()

@@ -518,3 +518,51 @@ def test_fp8_sliding_prefill_longer_than_the_window():
     out = orc.gqa_paged_attention_fp8(q[:, :1], k[:, :1], np.full((1, 1, Hkv, D), 4.0, np.float32), gate[:, :1], kp, vp,
                                       1.0, 1.0, pt, [T], 16, sliding_window=W)
     assert abs(out[0, 0, 0, 0] - ((W - 1) * 2.0 + 4.0) / W * ln2) < 1e-3
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# selected-row attention over expanded heads: metal/attention.rs:2413-2740, closed-form inputs, tolerance 1e-5
+# ---------------------------------------------------------------------------------------------------------------
+def _ramp(n, div):
+    return ((np.arange(n, dtype=np.float32) + np.float32(1.0)) / np.float32(div)).astype(np.float32)
+
+
+def numpy_selected_attention(q, sel_k, sel_v, cur_k, cur_v, include_current=True):
+    """Independent statement (cpu_attention_scores / causal_softmax / values, metal/attention.rs): float64 throughout."""
+    B, H, T, D = q.shape
+    S = 0 if sel_k is None else sel_k.shape[2]
+    out = np.zeros((B, H, T, cur_v.shape[3]))
+    for b in range(B):
+        for h in range(H):
+            for t in range(T):
+                ks = [sel_k[b, h]] if S else []
+                vs = [sel_v[b, h]] if S else []
+                if include_current:
+                    ks.append(cur_k[b, h, :t + 1])
+                    vs.append(cur_v[b, h, :t + 1])
+                K, V = np.concatenate(ks).astype(np.float64), np.concatenate(vs).astype(np.float64)
+                s = K @ q[b, h, t].astype(np.float64) / np.sqrt(D)
+                p = np.exp(s - s.max())
+                out[b, h, t] = (p / p.sum()) @ V
+    return out.astype(np.float32)
+
+
+def selected_attention_cases():
+    B, H, D, Dv = 1, 2, 4, 3
+    yield ("decode, 4 selected + current (attention.rs:2413)", _ramp(B * H * D, 10).reshape(B, H, 1, D),
+           _ramp(B * H * 4 * D, 20).reshape(B, H, 4, D), _ramp(B * H * 4 * Dv, 30).reshape(B, H, 4, Dv),
+           _ramp(B * H * D, 40).reshape(B, H, 1, D), _ramp(B * H * Dv, 50).reshape(B, H, 1, Dv), True)
+    yield ("sequence, 3 past + 8 rows (attention.rs:2564)", _ramp(B * H * 8 * D, 10).reshape(B, H, 8, D),
+           _ramp(B * H * 3 * D, 20).reshape(B, H, 3, D), _ramp(B * H * 3 * Dv, 30).reshape(B, H, 3, Dv),
+           _ramp(B * H * 8 * D, 40).reshape(B, H, 8, D), _ramp(B * H * 8 * Dv, 50).reshape(B, H, 8, Dv), True)
+    yield ("current-only prefill chunk (attention.rs:2668)", _ramp(B * H * 8 * D, 10).reshape(B, H, 8, D), None, None,
+           _ramp(B * H * 8 * D, 20).reshape(B, H, 8, D), _ramp(B * H * 8 * Dv, 30).reshape(B, H, 8, Dv), True)
+    yield ("decode without the current token", _ramp(B * H * D, 10).reshape(B, H, 1, D),
+           _ramp(B * H * 4 * D, 20).reshape(B, H, 4, D), _ramp(B * H * 4 * Dv, 30).reshape(B, H, 4, Dv),
+           _ramp(B * H * D, 40).reshape(B, H, 1, D), _ramp(B * H * Dv, 50).reshape(B, H, 1, Dv), False)
+
+
+def test_selected_attention_reference_cases():
+    for name, q, sk, sv, ck, cv, inc in selected_attention_cases():
+        got = orc.selected_attention(q, sk, sv, ck, cv, inc)
+        assert np.abs(got - numpy_selected_attention(q, sk, sv, ck, cv, inc)).max() <= 1e-5, name
