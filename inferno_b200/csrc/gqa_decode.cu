@@ -97,7 +97,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // of key row g, two 16-byte loads, and the query fragments are permuted the same way; in PV the lane takes dims
 // [16 g, 16 g + 16) of the four key rows its P fragment covers, so accumulator column c of tile j is output dim
 // 16 c + j, which the merge step undoes when it writes the partial.
-template <bool FP8>
+template <bool FP8, int NT>
 __global__ void __launch_bounds__(THREADS, 2)
 gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           DecodeParams p) {
@@ -212,20 +212,25 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     }
 
     // ---------------- consumers ----------------
+    // Keys are the M rows of the MMAs and the group's query heads the N columns: S^T[16 keys x 8 heads] = K Q^T and
+    // O^T[128 dims x 8 heads] += V^T P^T.  A group of up to eight heads fills one 8-wide tile (NT = 1) instead of
+    // six of sixteen M rows, which halves the MMAs and the accumulator registers; nine to sixteen heads take two.
     const int g = lane >> 2, qd = lane & 3;
-    // Q fragments: rows = query heads of this KV group (zero beyond the group)
-    uint32_t qa[8][4];
+    // Q^T as the B operand: lane (g, qd) holds head g (and g + 8), two dim pairs per k-step
+    uint32_t qb[NT][8][2];
     {
-        const __half* qb = p.q + ((long long)b * p.q_heads + (long long)kvh * p.group) * D;
+        const __half* q0 = p.q + ((long long)b * p.q_heads + (long long)kvh * p.group) * D;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-            // dims behind fragment columns (2 qd, 2 qd + 1) and (2 qd + 8, 2 qd + 9) of k-step kk
-            const int c0 = FP8 ? 32 * qd + 4 * kk : kk * 16 + qd * 2;
-            const int c1 = FP8 ? c0 + 2 : c0 + 8;
-            qa[kk][0] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c0) : 0u;
-            qa[kk][1] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c0) : 0u;
-            qa[kk][2] = g < p.group ? *reinterpret_cast<const uint32_t*>(qb + g * D + c1) : 0u;
-            qa[kk][3] = g + 8 < p.group ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * D + c1) : 0u;
+        for (int nt = 0; nt < NT; ++nt) {
+            const int head = nt * 8 + g;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                // dims behind fragment rows (2 qd, 2 qd + 1) and (2 qd + 8, 2 qd + 9) of k-step kk
+                const int c0 = FP8 ? 32 * qd + 4 * kk : kk * 16 + qd * 2;
+                const int c1 = FP8 ? c0 + 2 : c0 + 8;
+                qb[nt][kk][0] = head < p.group ? *reinterpret_cast<const uint32_t*>(q0 + head * D + c0) : 0u;
+                qb[nt][kk][1] = head < p.group ? *reinterpret_cast<const uint32_t*>(q0 + head * D + c1) : 0u;
+            }
         }
     }
     const uint32_t smem_base = smem_u32(smem);
@@ -239,10 +244,15 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
         const int tile0 = (lo - key_begin) / TILE_KEYS;
         const int n_tiles = (key_end - key_begin + TILE_KEYS - 1) / TILE_KEYS;
 
-        float o[16][4];
-        float m_run[2] = {M_INIT, M_INIT}, l_run[2] = {0.f, 0.f};
+        float o[NT][8][4];  // tile j: dims (d(j, g), d(j, g + 8)) x heads (2 qd, 2 qd + 1)
+        float m_run[NT][2], l_run[NT][2];  // per head 2 qd + e; the sums are partial over this lane's keys
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+        for (int nt = 0; nt < NT; ++nt) {
+            m_run[nt][0] = m_run[nt][1] = M_INIT;
+            l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[nt][j][0] = o[nt][j][1] = o[nt][j][2] = o[nt][j][3] = 0.f;
+        }
 
         for (int t = tile0; t < n_tiles; ++t, ++it) {
             const int s = it % STAGES;
@@ -272,120 +282,119 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                     wrote_smem = true;
                     __syncwarp();
                 }
-                // ---- S = Q K^T for 16 keys
-                float sc[2][4];
+                // ---- S^T = K Q^T for 16 keys: rows g and g + 8 are keys, columns 2 qd, 2 qd + 1 heads
+                float sc[NT][4];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+                for (int nt = 0; nt < NT; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
                 if (FP8) {
-#pragma unroll
-                    for (int nt = 0; nt < 2; ++nt) {
-                        const int krow = warp * 16 + nt * 8 + g;  // krow & 7 == g
-                        const uint4 c0 = lds128(stage + krow * 128 + (((2 * qd) ^ g) << 4));
-                        const uint4 c1 = lds128(stage + krow * 128 + (((2 * qd + 1) ^ g) << 4));
-                        const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-#pragma unroll
-                        for (int kk = 0; kk < 8; ++kk) {
-                            uint32_t b0, b1;
-                            fp8x4_to_f16x4(w[kk], b0, b1);
-                            mma_16816(sc[nt], qa[kk], b0, b1);
-                        }
-                    }
-                } else {
-                    const int mat = lane >> 3, rin = lane & 7;
-                    const int krow = warp * 16 + (mat >> 1) * 8 + rin;
+                    // lane (g, qd) takes bytes [32 qd, 32 qd + 32) of key rows g and g + 8 (row & 7 == g)
+                    const uint32_t r_lo = stage + (warp * 16 + g) * 128, r_hi = r_lo + 8 * 128;
+                    const uint32_t x0 = ((2 * qd) ^ g) << 4, x1 = ((2 * qd + 1) ^ g) << 4;
+                    const uint4 a0 = lds128(r_lo + x0), a1 = lds128(r_lo + x1);
+                    const uint4 b0 = lds128(r_hi + x0), b1 = lds128(r_hi + x1);
+                    const uint32_t wl[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    const uint32_t wh[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
-                        const int dchunk = kk * 2 + (mat & 1);
-                        uint32_t r[4];
-                        ldsm_x4(stage + (dchunk >> 3) * BLOCK_BYTES + sw128_offset(krow, (dchunk & 7) * 8), r);
-                        mma_16816(sc[0], qa[kk], r[0], r[1]);
-                        mma_16816(sc[1], qa[kk], r[2], r[3]);
+                        uint32_t ka[4];
+                        fp8x4_to_f16x4(wl[kk], ka[0], ka[2]);
+                        fp8x4_to_f16x4(wh[kk], ka[1], ka[3]);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_16816(sc[nt], ka, qb[nt][kk][0], qb[nt][kk][1]);
+                    }
+                } else {
+                    const int krow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const int dchunk = kk * 2 + (lane >> 4);
+                        uint32_t ka[4];
+                        ldsm_x4(stage + (dchunk >> 3) * BLOCK_BYTES + sw128_offset(krow, (dchunk & 7) * 8), ka);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_16816(sc[nt], ka, qb[nt][kk][0], qb[nt][kk][1]);
                     }
                 }
-                // ---- online softmax (log2 domain); rows g and g+8
+                // ---- online softmax (log2 domain) per head; this lane holds keys k0 + g and k0 + g + 8
+                const bool dead_lo = edge && (k0 + g < lo || k0 + g >= key_end);
+                const bool dead_hi = edge && (k0 + g + 8 < lo || k0 + g + 8 >= key_end);
+                uint32_t pb[NT][2];
+                bool moved = false;
+                float alpha[NT][2];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) sc[nt][e] *= p.scale_log2;
-                if (edge) {
+                    if (dead_lo) sc[nt][0] = sc[nt][1] = -INFINITY;
+                    if (dead_hi) sc[nt][2] = sc[nt][3] = -INFINITY;
 #pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            int key = k0 + nt * 8 + qd * 2 + (e & 1);
-                            if (key < lo || key >= key_end) sc[nt][e] = -INFINITY;
-                        }
-                }
-                float alpha[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    float mx = fmaxf(fmaxf(sc[0][2 * h], sc[0][2 * h + 1]), fmaxf(sc[1][2 * h], sc[1][2 * h + 1]));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    float m_new = fmaxf(m_run[h], mx);
-                    alpha[h] = ex2_approx(m_run[h] - m_new);
-                    m_run[h] = m_new;
-                    float sum = 0.f;
-#pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            float pv = ex2_approx(sc[nt][2 * h + e] - m_new);
-                            sc[nt][2 * h + e] = pv;
-                            sum += pv;
-                        }
-                    l_run[h] = l_run[h] * alpha[h] + sum;
-                }
-                // the accumulators only need rescaling when a row maximum moved, which becomes rare after the first tiles
-                if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        o[j][0] *= alpha[0];
-                        o[j][1] *= alpha[0];
-                        o[j][2] *= alpha[1];
-                        o[j][3] *= alpha[1];
+                    for (int e = 0; e < 2; ++e) {
+                        float mx = fmaxf(sc[nt][e], sc[nt][2 + e]);
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                        const float m_new = fmaxf(m_run[nt][e], mx);
+                        alpha[nt][e] = ex2_approx(m_run[nt][e] - m_new);
+                        moved |= m_new != m_run[nt][e];
+                        m_run[nt][e] = m_new;
+                        const float p_lo = ex2_approx(sc[nt][e] - m_new), p_hi = ex2_approx(sc[nt][2 + e] - m_new);
+                        sc[nt][e] = p_lo;
+                        sc[nt][2 + e] = p_hi;
+                        l_run[nt][e] = l_run[nt][e] * alpha[nt][e] + p_lo + p_hi;
                     }
+                    // P^T as the B operand of PV: the 8 x 8 blocks (keys g | g + 8) x heads transposed across the warp
+                    uint32_t lo8 = pack_half2(sc[nt][0], sc[nt][1]), hi8 = pack_half2(sc[nt][2], sc[nt][3]);
+                    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb[nt][0]) : "r"(lo8));
+                    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb[nt][1]) : "r"(hi8));
                 }
-                // ---- O += P V
-                uint32_t pa[4];
-                pa[0] = pack_half2(sc[0][0], sc[0][1]);
-                pa[1] = pack_half2(sc[0][2], sc[0][3]);
-                pa[2] = pack_half2(sc[1][0], sc[1][1]);
-                pa[3] = pack_half2(sc[1][2], sc[1][3]);
+                // the accumulators only need rescaling when a maximum moved, which becomes rare after the first tiles
+                if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            o[nt][j][0] *= alpha[nt][0];
+                            o[nt][j][1] *= alpha[nt][1];
+                            o[nt][j][2] *= alpha[nt][0];
+                            o[nt][j][3] *= alpha[nt][1];
+                        }
+                }
+                // ---- O^T += V^T P^T
                 if (FP8) {
-                    // P's k columns of this lane are keys 2 qd, 2 qd + 1, 2 qd + 8, 2 qd + 9 of the warp's 16
+                    // lane (g, qd) takes dims [16 g, 16 g + 16) of key rows 2 qd, 2 qd + 1, 2 qd + 8, 2 qd + 9: tile j
+                    // covers dims 16 g + 2 j (fragment row g) and 16 g + 2 j + 1 (fragment row g + 8)
                     const uint32_t vb = stage + R::V_BLOCK * BLOCK_BYTES;
                     const int r0 = warp * 16 + 2 * qd;
                     const uint4 v0 = lds128(vb + r0 * 128 + ((g ^ (r0 & 7)) << 4));
                     const uint4 v1 = lds128(vb + (r0 + 1) * 128 + ((g ^ ((r0 + 1) & 7)) << 4));
                     const uint4 v2 = lds128(vb + (r0 + 8) * 128 + ((g ^ (r0 & 7)) << 4));
                     const uint4 v3 = lds128(vb + (r0 + 9) * 128 + ((g ^ ((r0 + 1) & 7)) << 4));
-                    const uint32_t a[4] = {v0.x, v0.y, v0.z, v0.w}, bq[4] = {v1.x, v1.y, v1.z, v1.w};
-                    const uint32_t c[4] = {v2.x, v2.y, v2.z, v2.w}, dq[4] = {v3.x, v3.y, v3.z, v3.w};
+                    const uint32_t ra[4] = {v0.x, v0.y, v0.z, v0.w}, rb[4] = {v1.x, v1.y, v1.z, v1.w};
+                    const uint32_t rc[4] = {v2.x, v2.y, v2.z, v2.w}, rd[4] = {v3.x, v3.y, v3.z, v3.w};
 #pragma unroll
-                    for (int jw = 0; jw < 4; ++jw) {
-                        // bytes (row r0, row r0 + 1) side by side for dims 4 jw .. 4 jw + 3 of this lane's sixteen
-                        const uint32_t t01 = __byte_perm(a[jw], bq[jw], 0x5140), t23 = __byte_perm(a[jw], bq[jw], 0x7362);
-                        const uint32_t u01 = __byte_perm(c[jw], dq[jw], 0x5140), u23 = __byte_perm(c[jw], dq[jw], 0x7362);
-                        uint32_t b0[4], b1[4];
-                        fp8x4_to_f16x4(t01, b0[0], b0[1]);
-                        fp8x4_to_f16x4(t23, b0[2], b0[3]);
-                        fp8x4_to_f16x4(u01, b1[0], b1[1]);
-                        fp8x4_to_f16x4(u23, b1[2], b1[3]);
+                    for (int w = 0; w < 4; ++w) {
+                        // bytes of two key rows side by side: [a0 b0 a1 b1] and [a2 b2 a3 b3]
+                        const uint32_t t01 = __byte_perm(ra[w], rb[w], 0x5140), t23 = __byte_perm(ra[w], rb[w], 0x7362);
+                        const uint32_t u01 = __byte_perm(rc[w], rd[w], 0x5140), u23 = __byte_perm(rc[w], rd[w], 0x7362);
+                        uint32_t va[4], vc[4];
+                        fp8x4_to_f16x4(t01, va[0], va[1]);
+                        fp8x4_to_f16x4(u01, va[2], va[3]);
+                        fp8x4_to_f16x4(t23, vc[0], vc[1]);
+                        fp8x4_to_f16x4(u23, vc[2], vc[3]);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) mma_16816(o[4 * jw + i], pa, b0[i], b1[i]);
+                        for (int nt = 0; nt < NT; ++nt) {
+                            mma_16816(o[nt][2 * w], va, pb[nt][0], pb[nt][1]);
+                            mma_16816(o[nt][2 * w + 1], vc, pb[nt][0], pb[nt][1]);
+                        }
                     }
                 } else {
                     const int mat = lane >> 3, rin = lane & 7;
-                    const int vrow = warp * 16 + (mat & 1) * 8 + rin;
+                    const int vrow = warp * 16 + (mat >> 1) * 8 + rin;
 #pragma unroll
-                    for (int jj = 0; jj < 8; ++jj) {
-                        const int dchunk = jj * 2 + (mat >> 1);
-                        uint32_t r[4];
-                        ldsm_x4_trans(stage + (2 + (dchunk >> 3)) * BLOCK_BYTES + sw128_offset(vrow, (dchunk & 7) * 8),
-                                      r);
-                        mma_16816(o[2 * jj], pa, r[0], r[1]);
-                        mma_16816(o[2 * jj + 1], pa, r[2], r[3]);
+                    for (int j = 0; j < 8; ++j) {
+                        const int dchunk = 2 * j + (mat & 1);
+                        uint32_t va[4];
+                        ldsm_x4_trans(stage + (2 + (dchunk >> 3)) * BLOCK_BYTES + sw128_offset(vrow, (dchunk & 7) * 8), va);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_16816(o[nt][j], va, pb[nt][0], pb[nt][1]);
                     }
                 }
             }
@@ -393,35 +402,32 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[s]);
         }
-        // row sums live spread over the quad
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-        }
         // ---------------- merge the four warps of this chunk through their own shared-memory buffer ----------------
         {
             float* mw = merge + warp * p.group * D;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                if (FP8) {  // accumulator column c of tile j is output dim 16 c + j
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int dim = 16 * (2 * qd + e) + j;
-                        if (g < p.group) mw[g * D + dim] = o[j][e];
-                        if (g + 8 < p.group) mw[(g + 8) * D + dim] = o[j][2 + e];
+                for (int e = 0; e < 2; ++e) {
+                    // the row sums are spread over the eight lanes that share qd
+                    float l = l_run[nt][e];
+                    l += __shfl_xor_sync(0xffffffffu, l, 4);
+                    l += __shfl_xor_sync(0xffffffffu, l, 8);
+                    l += __shfl_xor_sync(0xffffffffu, l, 16);
+                    const int head = nt * 8 + 2 * qd + e;
+                    if (head < p.group) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int d_lo = FP8 ? 16 * g + 2 * j : 16 * j + g, d_hi = FP8 ? d_lo + 1 : d_lo + 8;
+                            mw[head * D + d_lo] = o[nt][j][e];
+                            mw[head * D + d_hi] = o[nt][j][2 + e];
+                        }
+                        if (g == 0) {
+                            warp_m[warp][head] = m_run[nt][e];
+                            warp_l[warp][head] = l;
+                        }
                     }
-                } else {
-                    if (g < p.group) *reinterpret_cast<float2*>(mw + g * D + j * 8 + qd * 2) = make_float2(o[j][0], o[j][1]);
-                    if (g + 8 < p.group)
-                        *reinterpret_cast<float2*>(mw + (g + 8) * D + j * 8 + qd * 2) = make_float2(o[j][2], o[j][3]);
                 }
-            }
-            if (qd == 0) {
-                warp_m[warp][g] = m_run[0];
-                warp_m[warp][g + 8] = m_run[1];
-                warp_l[warp][g] = l_run[0];
-                warp_l[warp][g + 8] = l_run[1];
             }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four consumer warps only
@@ -623,22 +629,20 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
 
     const size_t ring = fp8 ? Ring<true>::BYTES : Ring<false>::BYTES;
     const size_t smem = ring + (size_t)CONSUMER_WARPS * group * D * sizeof(float);
-    const uint32_t attr_bit = fp8 ? 32u : 1u;
+    // four instantiations: fp16 or FP8 pages, one or two 8-head tiles per KV group
+    void (*kernel)(CUtensorMap, CUtensorMap, DecodeParams) =
+        fp8 ? (group <= 8 ? gqa_decode_partial_kernel<true, 1> : gqa_decode_partial_kernel<true, 2>)
+            : (group <= 8 ? gqa_decode_partial_kernel<false, 1> : gqa_decode_partial_kernel<false, 2>);
+    const uint32_t attr_bit = (fp8 ? 32u : 1u) << (group <= 8 ? 0 : 6);  // bits 0, 5, 6, 11
     if (!(ctx->func_attr_done & attr_bit)) {
         const int limit = (int)(ring + CONSUMER_WARPS * 16 * D * sizeof(float));
-        if (fp8)
-            INF_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit));
-        else
-            INF_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit));
+        INF_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, limit));
         ctx->func_attr_done |= attr_bit;
     }
     dim3 grid((max_chunks + p.chunks_per_cta - 1) / p.chunks_per_cta, pool->kv_heads, table->batch);
     {
         inf_prof_scope prof(ctx, fp8 ? "gqa_decode_partial_fp8_kernel" : "gqa_decode_partial_kernel");
-        if (fp8)
-            INF_CUDA(ctx, inf_launch_pdl(gqa_decode_partial_kernel<true>, grid, dim3(THREADS), smem, ctx->stream, tm_k, tm_v, p));
-        else
-            INF_CUDA(ctx, inf_launch_pdl(gqa_decode_partial_kernel<false>, grid, dim3(THREADS), smem, ctx->stream, tm_k, tm_v, p));
+        INF_CUDA(ctx, inf_launch_pdl(kernel, grid, dim3(THREADS), smem, ctx->stream, tm_k, tm_v, p));
     }
     INF_LAUNCH_CHECK(ctx, "gqa_decode_partial_kernel");
     dim3 cgrid(q_heads, table->batch);
