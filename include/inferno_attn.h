@@ -71,6 +71,12 @@ int32_t inf_device_values_supported(inf_ctx* ctx);
 int32_t inf_flush(inf_ctx* ctx);
 /* device_submit (backend.rs:1072): launches are already asynchronous; checks arguments only. */
 int32_t inf_submit(inf_ctx* ctx);
+/* Diagnostic for the failure path (no counterpart in the reference).  Every wait inside the kernels is bounded: a
+ * load that never arrives makes the waiting warps give up after two seconds, the kernel then runs to its normal end
+ * and inf_flush reports "bounded wait gave up" (INF_E_BACKEND); the context stays usable.  This call makes the NEXT
+ * inf_gqa_decode_paged* launch of the context lose the loads of tile number `tile` (counted from 0) of its first
+ * CTA, so that a test can watch that happen.  The affected output rows are undefined. */
+int32_t inf_debug_drop_next_load(inf_ctx* ctx, int32_t tile);
 /* device_profile_boundary (backend.rs:1080; GPU time per command buffer, metal/batch.rs:161-170):
  * while enabled, every op records a CUDA event pair around its dominant kernel.  inf_profile_read waits
  * for the stream, returns the summed device time and launch count of the kernel called `kernel_name`
@@ -457,6 +463,35 @@ int32_t inf_comm_unique_id(inf_ctx* ctx, void* id_out);
 int32_t inf_comm_init(inf_ctx* ctx, const void* id, int32_t rank, int32_t nranks, inf_comm** out);
 int32_t inf_comm_destroy(inf_comm* comm);
 int32_t inf_allgather_heads(inf_comm* comm, const void* send, void* recv, size_t bytes);
+
+/* The all-gather fused into the prefill kernels.  Every rank holds its own copy of the gathered tensor
+ * [tokens][all heads][dim]; a rank's kernel stores each finished output tile into its own copy and, with plain
+ * stores over NVLink, into the other ranks' copies, so the exchange rides under the attention tile by tile and no
+ * collective follows the kernel -- only inf_comm_barrier, after which every rank's copy is complete.  A consumer
+ * must not let the next call overwrite a copy a peer may still be reading: alternate two gathered tensors, or put
+ * a barrier before the call as well.  (No counterpart in the reference.)
+ *   inf_peer_export: INF_PEER_HANDLE_BYTES describing `device_ptr` (any pointer inside a cudaMalloc allocation of this
+ *     process) for another process of the same box; the host carries the bytes to the peers by any means.
+ *   inf_peer_open / inf_peer_close: map / unmap a peer's export into this process (cudaIpcOpenMemHandle).
+ *   inf_comm_barrier: stream-ordered barrier over the communicator's ranks (a four-byte NCCL all-reduce).
+ *   inf_mla_prefill_causal_peers / inf_gqa_prefill_paged_peers: the prefill entry points with up to INF_MAX_PEERS
+ *     peer outputs; `out` and every peer pointer already point at this rank's first head inside a gathered tensor
+ *     whose token stride is o_ts (out_token_stride) elements. */
+#define INF_MAX_PEERS 7
+#define INF_PEER_HANDLE_BYTES 72
+int32_t inf_peer_export(inf_ctx* ctx, const void* device_ptr, void* handle_out);
+int32_t inf_peer_open(inf_ctx* ctx, const void* handle, void** peer_ptr);
+int32_t inf_peer_close(inf_ctx* ctx, void* peer_ptr, const void* handle);
+int32_t inf_comm_barrier(inf_comm* comm);
+int32_t inf_mla_prefill_causal_peers(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs, const void* k_nope,
+                                     int64_t kn_ts, int64_t kn_hs, const void* k_rope, int64_t kr_ts, const void* v,
+                                     int64_t v_ts, int64_t v_hs, int32_t tokens, int32_t heads, int32_t nope_dim,
+                                     int32_t rope_dim, int32_t v_dim, float scale, void* out, int64_t o_ts, int64_t o_hs,
+                                     int32_t out_dtype, void* const* peer_outs, int32_t n_peers);
+int32_t inf_gqa_prefill_paged_peers(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                    const inf_page_table* table, int32_t tokens, int32_t q_heads, int32_t sliding_window,
+                                    const float* gate, float scale, void* out, int32_t out_dtype,
+                                    int64_t out_token_stride, void* const* peer_outs, int32_t n_peers);
 
 #ifdef __cplusplus
 }

@@ -138,12 +138,44 @@ class CudaBackend:
         self._check(self._lib.inf_allgather_heads(self._comm, _ptr(local_out), _ptr(gathered), nbytes))
         return gathered
 
+    def comm_barrier(self):
+        """Stream-ordered barrier over the communicator's ranks (after it, every rank's earlier work has finished)."""
+        self._check(self._lib.inf_comm_barrier(self._comm))
+
+    # ---- the all-gather fused into the prefill kernels: peers' copies of the gathered tensor, mapped into this process
+    def peer_export(self, t: torch.Tensor) -> bytes:
+        """Bytes that let another process of this box map the allocation `t` lives in (its storage must come from
+        cudaMalloc, which is what torch's default allocator uses)."""
+        buf = C.create_string_buffer(L.PEER_HANDLE_BYTES)
+        self._check(self._lib.inf_peer_export(self._ctx, C.c_void_p(t.data_ptr()), buf))
+        return buf.raw
+
+    def peer_open(self, handle: bytes) -> int:
+        """Device address, valid in this process, of the tensor a peer exported."""
+        p = C.c_void_p()
+        self._check(self._lib.inf_peer_open(self._ctx, C.create_string_buffer(handle, L.PEER_HANDLE_BYTES), C.byref(p)))
+        self._peer_maps = getattr(self, "_peer_maps", [])
+        self._peer_maps.append((p.value, handle))
+        return p.value
+
+    def peer_close_all(self):
+        for ptr, handle in getattr(self, "_peer_maps", []):
+            self._lib.inf_peer_close(self._ctx, C.c_void_p(ptr), C.create_string_buffer(handle, L.PEER_HANDLE_BYTES))
+        self._peer_maps = []
+
+    @staticmethod
+    def _peer_array(peers, byte_offset):
+        arr = (C.c_void_p * max(1, len(peers)))(*[C.c_void_p(p + byte_offset) for p in peers])
+        return arr
+
     def comm_destroy(self):
         if getattr(self, "_comm", None):
             self._lib.inf_comm_destroy(self._comm)
             self._comm = None
 
     def close(self):
+        if getattr(self, "_ctx", None):
+            self.peer_close_all()
         self.comm_destroy()
         if getattr(self, "_ctx", None):
             self._lib.inf_ctx_destroy(self._ctx)
@@ -360,13 +392,22 @@ class CudaBackend:
         return out if ok else None
 
     def gqa_prefill_paged(self, q_f16, pool: KvPool, table: PageTable, sliding_window: int = 0, gate=None,
-                          scale: float = 0.0, out_dtype=torch.float16, out=None):
+                          scale: float = 0.0, out_dtype=torch.float16, out=None, peers=None):
+        """`peers`: device addresses (peer_open) of the other ranks' copies of the gathered tensor `out` is a head
+        slice of ([B, T, Hq, D] view with the gathered tensor's token stride): every output tile is also stored there."""
         B, T, Hq, D = q_f16.shape
         if out is None:
             out = torch.empty((B, T, Hq, D), dtype=out_dtype, device=self.device)
         dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
-        ok = self._check(self._lib.inf_gqa_prefill_paged(self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc),
-                                                         T, Hq, sliding_window, _ptr(gate), scale, _ptr(out), dt))
+        if peers is None:
+            ok = self._check(self._lib.inf_gqa_prefill_paged(self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc),
+                                                             T, Hq, sliding_window, _ptr(gate), scale, _ptr(out), dt))
+            return out if ok else None
+        assert out.stride(3) == 1 and out.stride(2) == D and out.stride(0) == T * out.stride(1)
+        arr = self._peer_array(peers, out.storage_offset() * out.element_size())
+        ok = self._check(self._lib.inf_gqa_prefill_paged_peers(
+            self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc), T, Hq, sliding_window, _ptr(gate), scale,
+            C.c_void_p(out.data_ptr()), dt, out.stride(1), arr, len(peers)))
         return out if ok else None
 
     def laguna_gated_gqa_f16_attention_device(self, q, k, v, gate, pool: KvPool, table: PageTable, max_len: int,
@@ -542,7 +583,8 @@ class CudaBackend:
             _ptr(out)))
         return out if ok else None
 
-    def causal_sequence_attention_device(self, q, k_nope, k_rope, v, scale: float, out_dtype=torch.float16, out=None):
+    def causal_sequence_attention_device(self, q, k_nope, k_rope, v, scale: float, out_dtype=torch.float16, out=None,
+                                         peers=None):
         """causal_sequence_attention_device (backend.rs:2028) for MLA prefill: q [T,H,dn+dr], k_nope [T,H,dn],
         k_rope [T,dr] shared by the heads (or None), v [T,H,dv]; any token/head strides, unit inner stride."""
         T, H, dqk = q.shape
@@ -554,11 +596,16 @@ class CudaBackend:
         dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
         for t in (q, k_nope, v) + ((k_rope,) if k_rope is not None else ()):
             assert t.stride(-1) == 1 and t.dtype == torch.float16
-        ok = self._check(self._lib.inf_mla_prefill_causal(
-            self._ctx, C.c_void_p(q.data_ptr()), q.stride(0), q.stride(1), C.c_void_p(k_nope.data_ptr()),
-            k_nope.stride(0), k_nope.stride(1), C.c_void_p(k_rope.data_ptr()) if k_rope is not None else None,
-            k_rope.stride(0) if k_rope is not None else 0, C.c_void_p(v.data_ptr()), v.stride(0), v.stride(1), T, H,
-            dn, dr, dv, scale, _ptr(out), out.stride(0), out.stride(1), dt))
+        common = (self._ctx, C.c_void_p(q.data_ptr()), q.stride(0), q.stride(1), C.c_void_p(k_nope.data_ptr()),
+                  k_nope.stride(0), k_nope.stride(1), C.c_void_p(k_rope.data_ptr()) if k_rope is not None else None,
+                  k_rope.stride(0) if k_rope is not None else 0, C.c_void_p(v.data_ptr()), v.stride(0), v.stride(1), T, H,
+                  dn, dr, dv, scale, C.c_void_p(out.data_ptr()), out.stride(0), out.stride(1), dt)
+        if peers is None:
+            ok = self._check(self._lib.inf_mla_prefill_causal(*common))
+        else:
+            # `out` is this rank's head slice of a gathered [T, all heads, dv] tensor; peers are the other ranks' copies
+            arr = self._peer_array(peers, out.storage_offset() * out.element_size())
+            ok = self._check(self._lib.inf_mla_prefill_causal_peers(*common, arr, len(peers)))
         return out if ok else None
 
     def paged_decode_attention_resident_device(self, q, paged_k, cur_k, paged_v, cur_v, past_tokens: int, page_size: int):

@@ -50,6 +50,7 @@ struct inf_ctx {
     int* host_status = nullptr;  // pinned int32[4]
     inf_tmap_encode_fn encode = nullptr;
     std::vector<std::pair<inf_tmap_key, CUtensorMap>> tmaps;
+    int debug_drop_tile = -1;  // diagnostic: see inf_debug_drop_next_load
     uint32_t func_attr_done = 0;  // one bit per kernel whose dynamic shared-memory limit has been raised
     // optional per-kernel timing (inf_profile_enable): event pairs around named kernels
     bool prof_on = false;

@@ -72,6 +72,11 @@ struct FlashParams {
     void* out;
     int out_f16;
     long long o_ts, o_hs, o_bs;  // element strides of the output: token, head, batch
+    // Head-sharded runs: the same output rows are also stored into the other ranks' copies of the gathered tensor
+    // (peer memory over NVLink, plain stores), same strides as `out`: the all-gather happens tile by tile in the
+    // epilogue instead of as a collective after the kernel.
+    void* peer_out[INF_MAX_PEERS];
+    int n_peers;
     int* status;
 #ifdef INF_KPROF
     long long* kprof;      // debug builds only: cycle counters of CTA (0,0,0)
@@ -650,9 +655,12 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         const int row_l = rr * 2 + (lane >> 4);
                         const int row_g = me.q0 + (warp & 3) * 32 + row_l;
                         const uint4 v = *reinterpret_cast<const uint4*>(stage + row_l * 256 + ((chunk ^ (row_l & 15)) << 4));
-                        if (row_g < p.tokens)
-                            *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + (long long)b * p.o_bs +
-                                                      (long long)row_g * p.o_ts + (long long)me.head * p.o_hs + chunk * 8) = v;
+                        if (row_g < p.tokens) {
+                            const long long off = (long long)b * p.o_bs + (long long)row_g * p.o_ts + (long long)me.head * p.o_hs + chunk * 8;
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + off) = v;
+                            for (int pr = 0; pr < p.n_peers; ++pr)
+                                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.peer_out[pr]) + off) = v;
+                        }
                     }
                 } else {
 #pragma unroll
@@ -671,14 +679,19 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                     v.z = pack_half2(__uint_as_float(o[i + 4]) * gain, __uint_as_float(o[i + 5]) * gain);
                                     v.w = pack_half2(__uint_as_float(o[i + 6]) * gain, __uint_as_float(o[i + 7]) * gain);
                                     *reinterpret_cast<uint4*>(dst + i) = v;
+                                    for (int pr = 0; pr < p.n_peers; ++pr)
+                                        *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.peer_out[pr]) + obase + c * 32 + i) = v;
                                 }
                             } else {
                                 float* dst = reinterpret_cast<float*>(p.out) + obase + c * 32;
 #pragma unroll
-                                for (int i = 0; i < 32; i += 4)
-                                    *reinterpret_cast<float4*>(dst + i) =
-                                        make_float4(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain,
-                                                    __uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                                for (int i = 0; i < 32; i += 4) {
+                                    const float4 v = make_float4(__uint_as_float(o[i]) * gain, __uint_as_float(o[i + 1]) * gain,
+                                                                 __uint_as_float(o[i + 2]) * gain, __uint_as_float(o[i + 3]) * gain);
+                                    *reinterpret_cast<float4*>(dst + i) = v;
+                                    for (int pr = 0; pr < p.n_peers; ++pr)
+                                        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.peer_out[pr]) + obase + c * 32 + i) = v;
+                                }
                             }
                         }
                     }
@@ -801,9 +814,28 @@ int launch_flash(inf_ctx* ctx, uint32_t attr_bit, const CUtensorMap& tq, const C
 }  // namespace
 
 // Shared with the fused operator entry point.
+// Where the rows go when the heads are sharded over ranks: the token stride of the gathered tensor (elements) and the
+// other ranks' copies of it, each already offset to this rank's first head like `out` itself.
+struct PrefillPeers {
+    long long token_stride;
+    void* const* outs;
+    int count;
+};
+
+static int check_peers(inf_ctx* ctx, const PrefillPeers* peers, const char* what) {
+    if (!peers) return INF_OK;
+    if (peers->count < 0 || peers->count > INF_MAX_PEERS)
+        return inf_fail(ctx, INF_E_CONFIG, "%s: %d peers, at most %d are supported", what, peers->count, INF_MAX_PEERS);
+    if (peers->count > 0 && !peers->outs) return inf_fail(ctx, INF_E_ARG, "%s: null peer list", what);
+    for (int i = 0; i < peers->count; ++i)
+        if (!peers->outs[i] || (reinterpret_cast<uintptr_t>(peers->outs[i]) & 15u))
+            return inf_fail(ctx, INF_E_ARG, "%s: peer output %d is null or not 16-byte aligned", what, i);
+    return INF_OK;
+}
+
 int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                            int tokens, int q_heads, int sliding_window, const float* gate, float scale, void* out,
-                           int out_dtype) {
+                           int out_dtype, const PrefillPeers* peers) {
     if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "gqa_prefill: null pointer");
     if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "gqa_prefill: pool has no storage");
     if (pool->head_dim != 128) return inf_fail(ctx, INF_E_SHAPE, "gqa_prefill: head_dim must be 128, got %d", pool->head_dim);
@@ -854,7 +886,17 @@ int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* p
     p.out_f16 = out_dtype == INF_DTYPE_F16;
     p.o_hs = 128;
     p.o_ts = (long long)q_heads * 128;
-    p.o_bs = (long long)tokens * q_heads * 128;
+    if (peers) {
+        rc = check_peers(ctx, peers, "gqa_prefill");
+        if (rc != INF_OK) return rc;
+        if (peers->token_stride < (long long)q_heads * 128 || peers->token_stride % 8)
+            return inf_fail(ctx, INF_E_SHAPE, "gqa_prefill: output token stride %lld must be a multiple of 8 and at least %d",
+                            peers->token_stride, q_heads * 128);
+        p.o_ts = peers->token_stride;
+        p.n_peers = peers->count;
+        for (int i = 0; i < peers->count; ++i) p.peer_out[i] = peers->outs[i];
+    }
+    p.o_bs = (long long)tokens * p.o_ts;
     p.status = ctx->status;
     return launch_flash<128, 128, 6, 2, true>(ctx, 2u, tq, tk, tk, tv, p, "flash_prefill_gqa_kernel");
 }
@@ -865,15 +907,24 @@ extern "C" int32_t inf_gqa_prefill_paged(inf_ctx* ctx, const void* q_f16, const 
                                          int32_t out_dtype) {
     INF_CHECK_CTX(ctx);
     return inf_gqa_prefill_launch(ctx, q_f16, pool, table, tokens, q_heads, sliding_window, gate, scale, out,
-                                  out_dtype);
+                                  out_dtype, nullptr);
 }
 
-extern "C" int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs, const void* k_nope,
-                                          int64_t kn_ts, int64_t kn_hs, const void* k_rope, int64_t kr_ts,
-                                          const void* v, int64_t v_ts, int64_t v_hs, int32_t tokens, int32_t heads,
-                                          int32_t nope_dim, int32_t rope_dim, int32_t v_dim, float scale, void* out,
-                                          int64_t o_ts, int64_t o_hs, int32_t out_dtype) {
+extern "C" int32_t inf_gqa_prefill_paged_peers(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                               const inf_page_table* table, int32_t tokens, int32_t q_heads,
+                                               int32_t sliding_window, const float* gate, float scale, void* out,
+                                               int32_t out_dtype, int64_t out_token_stride, void* const* peer_outs,
+                                               int32_t n_peers) {
     INF_CHECK_CTX(ctx);
+    const PrefillPeers peers = {out_token_stride, peer_outs, n_peers};
+    return inf_gqa_prefill_launch(ctx, q_f16, pool, table, tokens, q_heads, sliding_window, gate, scale, out,
+                                  out_dtype, &peers);
+}
+
+static int mla_prefill_any(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs, const void* k_nope, int64_t kn_ts,
+                           int64_t kn_hs, const void* k_rope, int64_t kr_ts, const void* v, int64_t v_ts, int64_t v_hs,
+                           int32_t tokens, int32_t heads, int32_t nope_dim, int32_t rope_dim, int32_t v_dim, float scale,
+                           void* out, int64_t o_ts, int64_t o_hs, int32_t out_dtype, const PrefillPeers* peers) {
     if (!q || !k_nope || !v || !out) return inf_fail(ctx, INF_E_ARG, "mla_prefill: null pointer");
     if (tokens <= 0 || heads <= 0) return inf_fail(ctx, INF_E_SHAPE, "mla_prefill: sizes must be positive");
     if (nope_dim != 128 || v_dim != 128 || (rope_dim != 64 && rope_dim != 0)) return INF_UNSUPPORTED;
@@ -928,7 +979,36 @@ extern "C" int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q
     p.o_ts = o_ts;
     p.o_hs = o_hs;
     p.o_bs = 0;
+    if (peers) {
+        rc = check_peers(ctx, peers, "mla_prefill");
+        if (rc != INF_OK) return rc;
+        if ((o_ts % 8) || (o_hs % 8)) return inf_fail(ctx, INF_E_SHAPE, "mla_prefill: output strides must be multiples of 8");
+        p.n_peers = peers->count;
+        for (int i = 0; i < peers->count; ++i) p.peer_out[i] = peers->outs[i];
+    }
     p.status = ctx->status;
     if (rope_dim) return launch_flash<192, 128, 4, 2, false>(ctx, 4u, tq, tk, tk2, tv, p, "flash_prefill_mla_kernel");
     return launch_flash<128, 128, 6, 2, false>(ctx, 8u, tq, tk, tk2, tv, p, "flash_prefill_mha_kernel");
+}
+
+extern "C" int32_t inf_mla_prefill_causal(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs, const void* k_nope,
+                                          int64_t kn_ts, int64_t kn_hs, const void* k_rope, int64_t kr_ts,
+                                          const void* v, int64_t v_ts, int64_t v_hs, int32_t tokens, int32_t heads,
+                                          int32_t nope_dim, int32_t rope_dim, int32_t v_dim, float scale, void* out,
+                                          int64_t o_ts, int64_t o_hs, int32_t out_dtype) {
+    INF_CHECK_CTX(ctx);
+    return mla_prefill_any(ctx, q, q_ts, q_hs, k_nope, kn_ts, kn_hs, k_rope, kr_ts, v, v_ts, v_hs, tokens, heads, nope_dim,
+                           rope_dim, v_dim, scale, out, o_ts, o_hs, out_dtype, nullptr);
+}
+
+extern "C" int32_t inf_mla_prefill_causal_peers(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs,
+                                                const void* k_nope, int64_t kn_ts, int64_t kn_hs, const void* k_rope,
+                                                int64_t kr_ts, const void* v, int64_t v_ts, int64_t v_hs, int32_t tokens,
+                                                int32_t heads, int32_t nope_dim, int32_t rope_dim, int32_t v_dim,
+                                                float scale, void* out, int64_t o_ts, int64_t o_hs, int32_t out_dtype,
+                                                void* const* peer_outs, int32_t n_peers) {
+    INF_CHECK_CTX(ctx);
+    const PrefillPeers peers = {o_ts, peer_outs, n_peers};
+    return mla_prefill_any(ctx, q, q_ts, q_hs, k_nope, kn_ts, kn_hs, k_rope, kr_ts, v, v_ts, v_hs, tokens, heads, nope_dim,
+                           rope_dim, v_dim, scale, out, o_ts, o_hs, out_dtype, &peers);
 }

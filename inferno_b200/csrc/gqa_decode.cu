@@ -62,6 +62,7 @@ struct DecodeParams {
     float* part_ml;
     int max_chunks;
     int* status;
+    int drop_tile;  // diagnostic (inf_debug_drop_next_load): the producer skips this tile's loads; -1 = none
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
@@ -188,6 +189,7 @@ gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
                         ok = false;
                         break;
                     }
+                    if (it == p.drop_tile && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) continue;
                     const int remaining = key_end - (key_begin + t * TILE_KEYS);
                     const int nsub = min(4, (remaining + 15) / 16);
                     uint8_t* base = smem + s * STAGE_BYTES;
@@ -626,6 +628,8 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     p.max_chunks = max_chunks;
     p.chunks_per_cta = MAX_CHUNK / split_chunk;
     p.status = ctx->status;
+    p.drop_tile = ctx->debug_drop_tile;
+    ctx->debug_drop_tile = -1;  // one launch only
 
     const size_t ring = fp8 ? Ring<true>::BYTES : Ring<false>::BYTES;
     const size_t smem = ring + (size_t)CONSUMER_WARPS * group * D * sizeof(float);
@@ -659,6 +663,12 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
                                      p.part_ml, table->lens, gate, (__half*)out, q_heads, max_chunks, split_chunk,
                                      sliding_window, len_add, cq, ck, cv, group, cur_scale_log2));
     INF_LAUNCH_CHECK(ctx, "gqa_decode_combine_kernel");
+    return INF_OK;
+}
+
+extern "C" int32_t inf_debug_drop_next_load(inf_ctx* ctx, int32_t tile) {
+    INF_CHECK_CTX(ctx);
+    ctx->debug_drop_tile = tile;
     return INF_OK;
 }
 

@@ -11,7 +11,7 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
                           const struct DecodeFp8* fp8);
 int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                            int tokens, int q_heads, int sliding_window, const float* gate, float scale, void* out,
-                           int out_dtype);
+                           int out_dtype, const struct PrefillPeers* peers);
 
 namespace {
 
@@ -123,7 +123,7 @@ int32_t inf_laguna_gated_gqa_f16_attention(inf_ctx* ctx, const float* q, const f
         return inf_gqa_decode_launch(ctx, q16, pool, table, q_heads, max_len, chunk, sliding_window, gate, 0.f, out,
                                      INF_DTYPE_F32, (char*)ctx->workspace + q_bytes, dec_bytes, 1, nullptr);
     return inf_gqa_prefill_launch(ctx, q16, pool, table, tokens, q_heads, sliding_window, gate, 0.f, out,
-                                  INF_DTYPE_F32);
+                                  INF_DTYPE_F32, nullptr);
 }
 
 int32_t inf_paged_decode_attention_resident(inf_ctx* ctx, const float* q, const void* paged_k_f16, const float* cur_k,

@@ -16,6 +16,7 @@ INF_UNSUPPORTED = 1
 INF_E_BACKEND, INF_E_SHAPE, INF_E_CONFIG, INF_E_CACHE, INF_E_DTYPE, INF_E_ARG = -1, -2, -3, -4, -5, -6
 DTYPE_F32, DTYPE_F16 = 0, 1
 GQA_DECODE_STATIC_SCRATCH_BYTES = 32 << 20
+MAX_PEERS, PEER_HANDLE_BYTES = 7, 72
 
 ERROR_NAMES = {INF_E_BACKEND: "Backend", INF_E_SHAPE: "ShapeMismatch", INF_E_CONFIG: "Config", INF_E_CACHE: "Cache",
                INF_E_DTYPE: "DType", INF_E_ARG: "Argument"}
@@ -68,6 +69,7 @@ SIGNATURES = {
     "inf_device_values_supported": (_I, [_P]),
     "inf_flush": (_I, [_P]),
     "inf_submit": (_I, [_P]),
+    "inf_debug_drop_next_load": (_I, [_P, _I]),
     "inf_profile_enable": (_I, [_P, _I]),
     "inf_profile_read": (_I, [_P, C.c_char_p, C.POINTER(C.c_double), C.POINTER(_I)]),
     "inf_alloc": (_I, [_P, C.c_size_t, C.POINTER(_P)]),
@@ -129,6 +131,14 @@ SIGNATURES = {
     "inf_comm_init": (_I, [_P, _P, _I, _I, C.POINTER(_P)]),
     "inf_comm_destroy": (_I, [_P]),
     "inf_allgather_heads": (_I, [_P, _P, _P, C.c_size_t]),
+    "inf_comm_barrier": (_I, [_P]),
+    "inf_peer_export": (_I, [_P, _P, _P]),
+    "inf_peer_open": (_I, [_P, _P, C.POINTER(_P)]),
+    "inf_peer_close": (_I, [_P, _P, _P]),
+    "inf_mla_prefill_causal_peers": (_I, [_P, _P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P, _L,
+                                          _L, _I, _P, _I]),
+    "inf_gqa_prefill_paged_peers": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _P, _F, _P, _I, _L,
+                                         _P, _I]),
     "inf_paged_index_create": (_I, [_I, _I, _I, _I, C.POINTER(_P)]),
     "inf_paged_index_destroy": (_I, [_P]),
     "inf_paged_index_last_error": (C.c_char_p, [_P]),

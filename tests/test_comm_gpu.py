@@ -53,6 +53,97 @@ def _rank_body(rank, world, uid_q, res_q):
     be.close()
 
 
+def _fused_worker(rank, world, uid_q, inboxes, res_q):
+    import traceback
+    try:
+        _fused_body(rank, world, uid_q, inboxes, res_q)
+    except Exception:
+        res_q.put((rank, False, traceback.format_exc()))
+
+
+def _fused_body(rank, world, uid_q, inboxes, res_q):
+    """The all-gather fused into the prefill kernels: every rank stores its heads into its own and, over NVLink,
+    into the peers' copies of the gathered tensor; after the barrier each copy must equal the single-GPU result."""
+    import sys
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import numpy as np
+    import torch
+    from inferno_b200 import CudaBackend
+    from inferno_b200.sharding import shard_heads
+    torch.cuda.set_device(rank)
+    be = CudaBackend(rank)
+    if rank == 0:
+        uid = be.comm_unique_id()
+        for _ in range(world - 1):
+            uid_q.put(uid)
+    else:
+        uid = uid_q.get(timeout=120)
+    be.comm_init(uid, rank, world)
+    g = torch.Generator(device=be.device).manual_seed(4321)
+    scale = 1.0 / math.sqrt(192.0)
+    # ---- dense MLA prefill: gathered [T, H, 128]
+    T, H = 300, 8
+    q = torch.randn((T, H, 192), generator=g, device=be.device, dtype=torch.float16)
+    kn = torch.randn((T, H, 128), generator=g, device=be.device, dtype=torch.float16)
+    kr = torch.randn((T, 64), generator=g, device=be.device, dtype=torch.float16)
+    v = torch.randn((T, H, 128), generator=g, device=be.device, dtype=torch.float16)
+    gathered = torch.zeros((T, H, 128), dtype=torch.float16, device=be.device)
+    # ---- paged GQA prefill: gathered [1, T2, Hq, 128]
+    T2, Hq, Hkv, P = 200, 12, 4, 16
+    q2 = torch.randn((1, T2, Hq, 128), generator=g, device=be.device, dtype=torch.float16)
+    k2 = torch.randn((1, T2, Hkv, 128), generator=g, device=be.device, dtype=torch.float16)
+    v2 = torch.randn((1, T2, Hkv, 128), generator=g, device=be.device, dtype=torch.float16)
+    gathered2 = torch.zeros((1, T2, Hq, 128), dtype=torch.float16, device=be.device)
+    torch.cuda.synchronize()
+    mine = (be.peer_export(gathered), be.peer_export(gathered2))
+    for r in range(world):
+        if r != rank:
+            inboxes[r].put((rank, mine))
+    theirs = dict(inboxes[rank].get(timeout=120) for _ in range(world - 1))
+    peers = [be.peer_open(theirs[r][0]) for r in sorted(theirs)]
+    peers2 = [be.peer_open(theirs[r][1]) for r in sorted(theirs)]
+    be.comm_barrier()            # every copy exists and is zero before anybody stores into it
+    be.device_flush()
+
+    full = be.causal_sequence_attention_device(q, kn, kr, v, scale)
+    qb, qe, kb, ke = shard_heads(H, H, world, rank)
+    be.causal_sequence_attention_device(q[:, qb:qe].contiguous(), kn[:, kb:ke].contiguous(), kr, v[:, kb:ke].contiguous(),
+                                        scale, out=gathered[:, qb:qe], peers=peers)
+
+    pages = (T2 + P - 1) // P
+    table_np = np.arange(pages, dtype=np.int32)[None]
+    pool_full = be.prepare_kv_pool(pages, P, Hkv)
+    q16 = be.rope_append_gqa(q2, k2, v2, None, pool_full, be.page_table(table_np, [0]))
+    full2 = be.gqa_prefill_paged(q16, pool_full, be.page_table(table_np, [0]))
+    qb2, qe2, kb2, ke2 = shard_heads(Hq, Hkv, world, rank)
+    pool = be.prepare_kv_pool(pages, P, ke2 - kb2)
+    q16l = be.rope_append_gqa(q2[:, :, qb2:qe2].contiguous(), k2[:, :, kb2:ke2].contiguous(), v2[:, :, kb2:ke2].contiguous(),
+                              None, pool, be.page_table(table_np, [0]))
+    be.gqa_prefill_paged(q16l, pool, be.page_table(table_np, [0]), out=gathered2[:, :, qb2:qe2], peers=peers2)
+    be.comm_barrier()
+    be.device_flush()
+    ok = bool(torch.equal(gathered, full)) and bool(torch.equal(gathered2, full2))
+    be.comm_barrier()            # nobody unmaps a copy a peer's kernel could still be writing
+    be.device_flush()
+    res_q.put((rank, ok, "a gathered copy differs from the single-GPU result"))
+    be.close()
+
+
+def test_prefill_with_the_gather_fused_into_its_epilogue_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from tests.workloads import collect_ranks
+    ctx = mp.get_context("spawn")
+    world = 2
+    uid_q, res_q = ctx.Queue(), ctx.Queue()
+    inboxes = [ctx.Queue() for _ in range(world)]
+    procs = [ctx.Process(target=_fused_worker, args=(r, world, uid_q, inboxes, res_q)) for r in range(world)]
+    results = collect_ranks(procs, res_q, timeout=300)
+    assert sorted(r[0] for r in results) == list(range(world))
+
+
 def test_head_sharded_prefill_allgather_matches_single_gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -218,6 +218,32 @@ def test_bad_page_id_is_refused_on_the_device(be):
     be.device_flush()  # the status word was cleared by the failed flush
 
 
+def test_bounded_wait_gives_up_and_the_context_survives(be):
+    """A load that never arrives: the consumers' wait runs out (two seconds), the kernel leaves through its normal
+    end, inf_flush names the cause, and the very next call on the same context is correct again."""
+    import time
+    from inferno_b200 import InfernoError
+    D, P, Hq, Hkv = 128, 16, 12, 2
+    pool = be.prepare_kv_pool(12, P, Hkv, D)
+    g = torch.Generator(device=be.device).manual_seed(SEED0 + 71)
+    pool.k.normal_(0, 1, generator=g)
+    pool.v.normal_(0, 1, generator=g)
+    q = torch.randn((1, Hq, D), generator=g, device=be.device, dtype=torch.float16)
+    table = be.page_table(np.arange(12, dtype=np.int32)[None], [180])
+    good = be.gqa_decode_paged(q, pool, table, max_len=180, split_chunk=64)
+    be.device_flush()
+    be._check(be._lib.inf_debug_drop_next_load(be._ctx, 1))  # the second 64-key tile of CTA (0, 0, 0) never lands
+    t0 = time.time()
+    be.gqa_decode_paged(q, pool, table, max_len=180, split_chunk=64)
+    with pytest.raises(InfernoError) as e:
+        be.device_flush()
+    assert "bounded wait gave up" in str(e.value)
+    assert 1.0 < time.time() - t0 < 30.0
+    again = be.gqa_decode_paged(q, pool, table, max_len=180, split_chunk=64)
+    be.device_flush()
+    assert np.array_equal(again.cpu().numpy(), good.cpu().numpy())
+
+
 def test_rmsnorm_rope_pair_matches_oracle(be):
     """laguna_qk_rms_norm_rope_pair_device on the reference's own test shapes (metal/rope.rs:621-710), tol 3e-5."""
     D, rotary, theta, factor, pos = 128, 64, 500000.0, 1.3465736, 7
