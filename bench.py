@@ -575,9 +575,10 @@ class GqaPrefill2k:
                 "append_bytes_per_step": cls.T * cls.Hkv * cls.D * 2 * 2,
                 "l2": f"rotates through {cls.N_SETS} distinct input sets and pools ({cls.N_SETS * set_mb:.0f} MB)",
                 "sharding": "heads" if world > 1 else "none",
-                "collective": "inf_allgather_heads (NCCL) of the output" if world > 1 else None}
+                "collective": "all-gather of the output fused into the kernel's epilogue (peer stores over NVLink) + barrier"
+                              if world > 1 else None}
 
-    def __init__(self, be, rank, world=1):
+    def __init__(self, be, rank, world=1, dist=None):
         import torch
         self.torch, self.be, self.world = torch, be, world
         self.hq_local, self.hkv_local = self.Hq // world, self.Hkv // world
@@ -598,6 +599,11 @@ class GqaPrefill2k:
         self.collective = world > 1
         self.gather_bytes = self.out.numel() * 2 if world > 1 else 0
         self.gathered = torch.empty((world, self.T, self.hq_local, self.D), dtype=torch.float16, device=be.device) if world > 1 else None
+        self.exchange = "fused"   # how the heads get to every rank: "fused" (peer stores in the epilogue), "nccl", "none"
+        if world > 1:
+            self.full = [torch.zeros((1, self.T, self.Hq, self.D), dtype=torch.float16, device=be.device) for _ in range(2)]
+            self.peers = [map_peers(be, dist, t) for t in self.full]
+            self.mine = [t[:, :, rank * self.hq_local:(rank + 1) * self.hq_local] for t in self.full]
         q, k, v = self.sets[0][2:]
         self.hq, self.hk, self.hv = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
         self.hout = torch.empty((self.gathered if world > 1 else self.out).shape, dtype=torch.float16).pin_memory()
@@ -615,9 +621,17 @@ class GqaPrefill2k:
         pool, table, q, k, v = self.sets[self.i % self.N_SETS]
         self.i += 1
         q16 = self.be.rope_append_gqa(q, k, v, self.rope, pool, table)
+        if self.collective and self.exchange == "fused":
+            # the two gathered tensors alternate: a peer may still read the one the previous step filled
+            self.result = self.full[self.i & 1]
+            self.be.gqa_prefill_paged(q16, pool, table, out=self.mine[self.i & 1], peers=self.peers[self.i & 1])
+            self.be.comm_barrier()
+            return
         self.be.gqa_prefill_paged(q16, pool, table, out=self.out)
-        if self.collective:
+        self.result = self.out
+        if self.collective and self.exchange == "nccl":
             self.be.allgather_into(self.out, self.gathered)
+            self.result = self.gathered
 
     def step_e2e(self):
         pool, table, q, k, v = self.sets[self.i % self.N_SETS]  # the same set step() is about to use
@@ -625,7 +639,7 @@ class GqaPrefill2k:
         k.copy_(self.hk, non_blocking=True)
         v.copy_(self.hv, non_blocking=True)
         self.step()
-        self.hout.copy_(self.gathered if self.collective else self.out, non_blocking=True)
+        self.hout.view(-1).copy_(self.result.view(-1), non_blocking=True)
 
     # ---- the same end-to-end step, head group by head group: every KV head with its six query heads has its own
     # host buffers, device buffers and pool, so that the upload of group g + 1 and the download of group g - 1 run
@@ -711,9 +725,10 @@ class MlaPrefill32k:
                 "v_dim": 128, "causal": True, "flops_per_step": T * (T + 1) / 2 * cls.H * 2.0 * (192 + 128),
                 "l2": "inputs larger than L2 (2.4 GB of Q/K/V)" if T == cls.T else "inputs of this prompt length",
                 "sharding": "heads" if world > 1 else "none",
-                "collective": "inf_allgather_heads (NCCL) of the output" if world > 1 else None}
+                "collective": "all-gather of the output fused into the kernel's epilogue (peer stores over NVLink) + barrier"
+                              if world > 1 else None}
 
-    def __init__(self, be, rank, world=1):
+    def __init__(self, be, rank, world=1, dist=None):
         import torch
         self.torch, self.be, self.world = torch, be, world
         hl = self.H // world
@@ -727,6 +742,11 @@ class MlaPrefill32k:
         self.collective = world > 1
         self.gather_bytes = self.out.numel() * 2 if world > 1 else 0
         self.gathered = torch.empty((world, self.T, hl, 128), dtype=torch.float16, device=be.device) if world > 1 else None
+        self.exchange = "fused"   # "fused" (peer stores in the epilogue), "nccl", "none"
+        if world > 1:
+            self.full = [torch.zeros((self.T, self.H, 128), dtype=torch.float16, device=be.device) for _ in range(2)]
+            self.peers = [map_peers(be, dist, t) for t in self.full]
+            self.mine = [t[:, rank * hl:(rank + 1) * hl] for t in self.full]
         self.host = [t.cpu().pin_memory() for t in (self.q, self.kn, self.kr, self.v)]
         self.hout = torch.empty((self.gathered if world > 1 else self.out).shape, dtype=torch.float16).pin_memory()
         self.scale = 1.0 / float(np.sqrt(192.0))
@@ -740,15 +760,25 @@ class MlaPrefill32k:
             self._init_overlap(gd)
 
     def step(self):
+        self.i += 1
+        if self.collective and self.exchange == "fused":
+            # the two gathered tensors alternate: a peer may still read the one the previous step filled
+            self.result = self.full[self.i & 1]
+            self.be.causal_sequence_attention_device(self.q, self.kn, self.kr, self.v, self.scale, out=self.mine[self.i & 1],
+                                                     peers=self.peers[self.i & 1])
+            self.be.comm_barrier()
+            return
         self.be.causal_sequence_attention_device(self.q, self.kn, self.kr, self.v, self.scale, out=self.out)
-        if self.collective:
+        self.result = self.out
+        if self.collective and self.exchange == "nccl":
             self.be.allgather_into(self.out, self.gathered)
+            self.result = self.gathered
 
     def step_e2e(self):
         for d, h in zip((self.q, self.kn, self.kr, self.v), self.host):
             d.copy_(h, non_blocking=True)
         self.step()
-        self.hout.copy_(self.gathered if self.collective else self.out, non_blocking=True)
+        self.hout.view(-1).copy_(self.result.view(-1), non_blocking=True)
 
     # ---- the same end-to-end step in groups of eight heads with a group-major host layout: the upload of group
     # g + 1 and the download of group g - 1 run under the kernel of group g (three streams)
@@ -803,7 +833,17 @@ class MlaPrefill32k:
         return run, flops, "48 sampled query rows x 8 of 64 heads, full causal key ranges (sampled)"
 
 
-def make_workload(name, be, rank, world=1, tokens=0):
+def map_peers(be, dist, tensor):
+    """Every rank exports `tensor` (its copy of a gathered output) and maps the other ranks' copies: the device
+    addresses, in rank order without this rank, that the fused-gather prefill stores into.  torch.distributed only
+    carries the 72-byte handles."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    handles = [None] * world
+    dist.all_gather_object(handles, be.peer_export(tensor))
+    return [be.peer_open(handles[r]) for r in range(world) if r != rank]
+
+
+def make_workload(name, be, rank, world=1, tokens=0, dist=None):
     if name == "gqa_decode_b32":
         return GqaDecodeB32(be, rank, world)
     if name == "gqa_decode_b32_strong":
@@ -821,13 +861,13 @@ def make_workload(name, be, rank, world=1, tokens=0):
     if name == "mla_absorbed_decode_32k":
         return MlaAbsorbedDecode(be, rank, 32768)
     if name == "gqa_prefill_2k":
-        return GqaPrefill2k(be, rank, world)
+        return GqaPrefill2k(be, rank, world, dist)
     if name == "mla_prefill_32k":
         wl = MlaPrefill32k.__new__(MlaPrefill32k)
         if tokens:
             wl.T = tokens  # smaller prompt for profiler captures; the name in `config` reflects it
             wl.max_steps = 50
-        wl.__init__(be, rank, world)
+        wl.__init__(be, rank, world, dist)
         return wl
     raise KeyError(name)
 
@@ -990,17 +1030,32 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
         res["per_rank"] = {"ms_per_step": spread([r / steps for r in rank_ms]),
                            "kernel_ms": spread([float(x.item()) for x in every])}
         if getattr(wl, "gather_bytes", 0):
-            wl.collective = False
-            ms_wo, _, _ = timed(torch, dist, world, wl.step, steps, warmup, regions)
-            wl.collective = True
-            ms_w = ms
-            if use_graph:  # compare like with like: the step with its collective, launched the same (eager) way
-                ms_w, _, _ = timed(torch, dist, world, wl.step, steps, warmup, regions)
-            res["collective"] = {"what": "inf_allgather_heads (NCCL all-gather behind the C ABI)",
-                                 "bytes_sent_per_rank": wl.gather_bytes,
-                                 "bytes_received_per_rank": wl.gather_bytes * (world - 1),
-                                 "ms_per_step_with": ms_w / steps, "ms_per_step_without": ms_wo / steps,
-                                 "ms_collective": (ms_w - ms_wo) / steps}
+            def eager_ms(mode):
+                if hasattr(wl, "exchange"):
+                    wl.exchange = mode
+                else:
+                    wl.collective = mode != "none"
+                t_ms, _, _ = timed(torch, dist, world, wl.step, steps, warmup, regions)
+                return t_ms / steps
+            coll = {"bytes_sent_per_rank_to_each_peer": wl.gather_bytes,
+                    "bytes_received_per_rank": wl.gather_bytes * (world - 1)}
+            if hasattr(wl, "exchange"):
+                coll["what"] = ("the step stores its tiles into every rank's gathered tensor from the kernel's epilogue "
+                                "(peer stores over NVLink) and ends with inf_comm_barrier; beside it, the same step with "
+                                "inf_allgather_heads (NCCL) after the kernel, and with no exchange at all")
+                coll["ms_per_step_fused_gather"] = eager_ms("fused")
+                coll["ms_per_step_nccl_allgather"] = eager_ms("nccl")
+                coll["ms_per_step_without"] = eager_ms("none")
+                wl.exchange = "fused"
+                coll["ms_exchange_fused"] = coll["ms_per_step_fused_gather"] - coll["ms_per_step_without"]
+                coll["ms_exchange_nccl"] = coll["ms_per_step_nccl_allgather"] - coll["ms_per_step_without"]
+            else:
+                coll["what"] = "inf_allgather_heads (NCCL all-gather behind the C ABI) after the kernels"
+                coll["ms_per_step_with"] = eager_ms("nccl")
+                coll["ms_per_step_without"] = eager_ms("none")
+                wl.collective = True
+                coll["ms_collective"] = coll["ms_per_step_with"] - coll["ms_per_step_without"]
+            res["collective"] = coll
     if with_cpu and rank == 0:
         res["cpu_baseline"] = cpu_baseline(wl)
     return res
@@ -1022,7 +1077,7 @@ def run_ours(args):
         be.comm_init(box[0], rank, world)
     peaks = load_peaks()
     sampler = ClockSampler(local_rank if world > 1 else 0) if rank == 0 else None
-    wl = make_workload(args.workload, be, rank, world, args.tokens)
+    wl = make_workload(args.workload, be, rank, world, args.tokens, dist)
     graph_ok = lambda name: not args.no_graph and not (world > 1 and name in STRONG)  # steps with NCCL stay eager
     head = measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
                    with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps,
@@ -1035,7 +1090,7 @@ def run_ours(args):
                 continue
             del wl
             torch.cuda.empty_cache()
-            wl = make_workload(name, be, rank, world)
+            wl = make_workload(name, be, rank, world, 0, dist)
             extras.append(measure(be, torch, dist, world, rank, wl, args.steps, args.warmup, peaks,
                                   with_cpu=(world == 1 and not args.no_cpu), profile_steps=args.profile_steps,
                                   use_graph=graph_ok(name), regions=args.regions))
