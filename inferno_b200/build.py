@@ -59,7 +59,8 @@ def build(force: bool = False, kprof: bool = False) -> str:
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(lambda s: _compile(s, force, out_dir, extra), srcs))
     if force or not os.path.exists(lib) or any(os.path.getmtime(o) > os.path.getmtime(lib) for o in objs):
-        r = subprocess.run([NVCC, "-shared", "-o", lib, *objs, "-lcudart_static", "-ldl", "-lpthread", "-lrt"],
+        r = subprocess.run([NVCC, "-shared", "-o", lib, *objs, "-lcudart_static", "-ldl", "-lpthread", "-lrt",
+                            "-Xlinker", "--no-undefined"],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

@@ -4,6 +4,8 @@
 #include <dlfcn.h>
 #include <string.h>
 
+#include <vector>
+
 #include "common.cuh"
 
 namespace {
@@ -58,12 +60,103 @@ const char* nccl_err(nccl_result_t r) { return g_nccl.GetErrorString ? g_nccl.Ge
 
 }  // namespace
 
+constexpr int FLAG_SLOTS = 64;   // [0, 32): arrival values written by the peers; [32]: this rank's epoch
+constexpr int EPOCH_SLOT = 32;
+constexpr int MAX_RANKS = INF_MAX_PEERS + 1;
+
+struct PeerFlags {
+    int* of[MAX_RANKS];  // every rank's flag array as mapped into this process (own entry: the local array)
+};
+
 struct inf_comm {
     inf_ctx* ctx;
     nccl_comm_t comm;
     int rank, nranks;
-    int* token = nullptr;  // device int the barrier reduces
+    int* token = nullptr;  // device int the NCCL form of the barrier reduces
+    int* flags = nullptr;  // this rank's flag array (FLAG_SLOTS ints), written by the peers' barrier kernels
+    PeerFlags peers = {};
+    bool p2p = false;      // the peers' flag arrays are mapped: the barrier is one small kernel, no NCCL call
 };
+
+// One CTA, one thread per rank.  Thread r tells rank r "I have arrived at barrier number e" with a store into r's
+// flag array over NVLink and waits until r has said the same here.  Everything this rank's stream ran before the
+// barrier -- kernels that stored into the peers' memory included -- has completed before this kernel starts, and the
+// system-wide fence orders those stores before the flag.  The wait is bounded: a rank that never arrives turns into
+// the status word's time-out bit, not into a hung GPU.  Each rank's kernel runs on its own GPU.
+__global__ void comm_barrier_kernel(int* mine, PeerFlags peers, int rank, int world, int* status) {
+    __shared__ int e_s;
+    const int r = threadIdx.x;
+    if (r == 0) e_s = mine[EPOCH_SLOT] + 1;
+    __syncthreads();
+    const int e = e_s;
+    if (r < world && r != rank) {
+        __threadfence_system();
+        volatile int* there = peers.of[r] + rank;
+        *there = e;
+        __threadfence_system();
+        volatile int* here = mine + r;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        while (*here < e) {
+            __nanosleep(32);
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 2000000000ull) {
+                atomicOr(status, INF_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (r == 0) mine[EPOCH_SLOT] = e;
+}
+
+static int peer_export_impl(inf_ctx* ctx, const void* device_ptr, void* handle_out);
+static int peer_open_impl(inf_ctx* ctx, const void* handle, void** peer_ptr);
+
+// Exchange the flag arrays' handles over NCCL itself and map them.  Any failure leaves the NCCL barrier in place.
+void setup_p2p_barrier(inf_comm* c) {
+    inf_ctx* ctx = c->ctx;
+    if (c->nranks > MAX_RANKS || c->nranks < 2) return;
+    if (cudaMalloc(&c->flags, FLAG_SLOTS * sizeof(int)) != cudaSuccess) return;
+    cudaMemset(c->flags, 0, FLAG_SLOTS * sizeof(int));
+    char mine[INF_PEER_HANDLE_BYTES];
+    if (peer_export_impl(ctx, c->flags, mine) != INF_OK) return;
+    char *d_send = nullptr, *d_recv = nullptr;
+    if (cudaMalloc(&d_send, INF_PEER_HANDLE_BYTES) != cudaSuccess ||
+        cudaMalloc(&d_recv, (size_t)INF_PEER_HANDLE_BYTES * c->nranks) != cudaSuccess)
+        return;
+    std::vector<char> all((size_t)INF_PEER_HANDLE_BYTES * c->nranks);
+    bool ok = cudaMemcpy(d_send, mine, INF_PEER_HANDLE_BYTES, cudaMemcpyHostToDevice) == cudaSuccess &&
+              g_nccl.AllGather(d_send, d_recv, INF_PEER_HANDLE_BYTES, /*ncclInt8*/ 0, c->comm, ctx->stream) == 0 &&
+              cudaStreamSynchronize(ctx->stream) == cudaSuccess &&
+              cudaMemcpy(all.data(), d_recv, all.size(), cudaMemcpyDeviceToHost) == cudaSuccess;
+    cudaFree(d_send);
+    cudaFree(d_recv);
+    if (!ok) return;
+    int mapped = 0;
+    for (int r = 0; r < c->nranks; ++r) {
+        if (r == c->rank) {
+            c->peers.of[r] = c->flags;
+            continue;
+        }
+        void* p = nullptr;
+        if (peer_open_impl(ctx, all.data() + (size_t)r * INF_PEER_HANDLE_BYTES, &p) == INF_OK) {
+            c->peers.of[r] = (int*)p;
+            ++mapped;
+        }
+    }
+    // every rank must come to the same decision: agree through one more reduction (min over ranks)
+    int* d_ok = c->token;
+    int mine_ok = mapped == c->nranks - 1 ? 1 : 0, all_ok = 0;
+    if (cudaMemcpy(d_ok, &mine_ok, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
+        g_nccl.AllReduce(d_ok, d_ok, 1, /*ncclInt32*/ 2, /*ncclMin*/ 3, c->comm, ctx->stream) == 0 &&
+        cudaStreamSynchronize(ctx->stream) == cudaSuccess &&
+        cudaMemcpy(&all_ok, d_ok, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess)
+        c->p2p = all_ok == 1;
+    cudaMemset(c->token, 0, sizeof(int));
+}
 
 extern "C" {
 
@@ -99,6 +192,7 @@ int32_t inf_comm_init(inf_ctx* ctx, const void* id, int32_t rank, int32_t nranks
         delete comm;
         return inf_fail(ctx, INF_E_BACKEND, "comm_init: could not allocate the barrier token");
     }
+    setup_p2p_barrier(comm);
     *out = comm;
     return INF_OK;
 }
@@ -108,6 +202,9 @@ int32_t inf_comm_destroy(inf_comm* comm) {
     cudaStreamSynchronize(comm->ctx->stream);
     if (g_nccl.CommDestroy) g_nccl.CommDestroy(comm->comm);
     if (comm->token) cudaFree(comm->token);
+    for (int r = 0; r < comm->nranks && r < MAX_RANKS; ++r)
+        if (r != comm->rank && comm->peers.of[r]) cudaIpcCloseMemHandle(comm->peers.of[r]);
+    if (comm->flags) cudaFree(comm->flags);
     delete comm;
     return INF_OK;
 }
@@ -125,7 +222,12 @@ int32_t inf_allgather_heads(inf_comm* comm, const void* send, void* recv, size_t
 int32_t inf_comm_barrier(inf_comm* comm) {
     if (!comm) return INF_E_ARG;
     inf_ctx* ctx = comm->ctx;
-    // a four-byte all-reduce on the context's stream: when it has run on a rank, every rank's earlier work on its own
+    if (comm->p2p) {
+        comm_barrier_kernel<<<1, 32, 0, ctx->stream>>>(comm->flags, comm->peers, comm->rank, comm->nranks, ctx->status);
+        INF_LAUNCH_CHECK(ctx, "comm_barrier_kernel");
+        return INF_OK;
+    }
+    // otherwise a four-byte all-reduce on the context's stream: when it has run on a rank, every rank's earlier work on its own
     // stream -- kernels that stored into this rank's memory included -- has finished
     nccl_result_t r = g_nccl.AllReduce(comm->token, comm->token, 1, /*ncclInt32*/ 2, /*ncclMax*/ 2, comm->comm, ctx->stream);
     if (r != 0) return inf_fail(ctx, INF_E_BACKEND, "ncclAllReduce (barrier) failed: %s", nccl_err(r));
@@ -134,6 +236,17 @@ int32_t inf_comm_barrier(inf_comm* comm) {
 
 int32_t inf_peer_export(inf_ctx* ctx, const void* device_ptr, void* handle_out) {
     INF_CHECK_CTX(ctx);
+    return peer_export_impl(ctx, device_ptr, handle_out);
+}
+
+int32_t inf_peer_open(inf_ctx* ctx, const void* handle, void** peer_ptr) {
+    INF_CHECK_CTX(ctx);
+    return peer_open_impl(ctx, handle, peer_ptr);
+}
+
+}  // extern "C"
+
+static int peer_export_impl(inf_ctx* ctx, const void* device_ptr, void* handle_out) {
     if (!device_ptr || !handle_out) return inf_fail(ctx, INF_E_ARG, "peer_export: null pointer");
     // the handle names the whole allocation the pointer lies in; the offset inside it travels with the handle
     CUdeviceptr base = 0;
@@ -155,8 +268,7 @@ int32_t inf_peer_export(inf_ctx* ctx, const void* device_ptr, void* handle_out) 
     return INF_OK;
 }
 
-int32_t inf_peer_open(inf_ctx* ctx, const void* handle, void** peer_ptr) {
-    INF_CHECK_CTX(ctx);
+static int peer_open_impl(inf_ctx* ctx, const void* handle, void** peer_ptr) {
     if (!handle || !peer_ptr) return inf_fail(ctx, INF_E_ARG, "peer_open: null pointer");
     *peer_ptr = nullptr;
     INF_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -170,6 +282,8 @@ int32_t inf_peer_open(inf_ctx* ctx, const void* handle, void** peer_ptr) {
     *peer_ptr = (char*)base + offset;
     return INF_OK;
 }
+
+extern "C" {
 
 int32_t inf_peer_close(inf_ctx* ctx, void* peer_ptr, const void* handle) {
     INF_CHECK_CTX(ctx);
