@@ -1043,6 +1043,7 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
                 coll["what"] = ("the step stores its tiles into every rank's gathered tensor from the kernel's epilogue "
                                 "(peer stores over NVLink) and ends with inf_comm_barrier; beside it, the same step with "
                                 "inf_allgather_heads (NCCL) after the kernel, and with no exchange at all")
+                coll["barrier"] = "peer-flag kernel" if be.comm_barrier_is_p2p() else "nccl all-reduce"
                 coll["ms_per_step_fused_gather"] = eager_ms("fused")
                 coll["ms_per_step_nccl_allgather"] = eager_ms("nccl")
                 coll["ms_per_step_without"] = eager_ms("none")

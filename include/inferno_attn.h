@@ -473,7 +473,9 @@ int32_t inf_allgather_heads(inf_comm* comm, const void* send, void* recv, size_t
  *   inf_peer_export: INF_PEER_HANDLE_BYTES describing `device_ptr` (any pointer inside a cudaMalloc allocation of this
  *     process) for another process of the same box; the host carries the bytes to the peers by any means.
  *   inf_peer_open / inf_peer_close: map / unmap a peer's export into this process (cudaIpcOpenMemHandle).
- *   inf_comm_barrier: stream-ordered barrier over the communicator's ranks (a four-byte NCCL all-reduce).
+ *   inf_comm_barrier: stream-ordered barrier over the communicator's ranks: one small kernel per rank that writes an
+ *     arrival flag into every peer's flag array over NVLink and waits, with a time limit, for theirs (the arrays are
+ *     exchanged and mapped at inf_comm_init; if that is not possible, a four-byte NCCL all-reduce instead).
  *   inf_mla_prefill_causal_peers / inf_gqa_prefill_paged_peers: the prefill entry points with up to INF_MAX_PEERS
  *     peer outputs; `out` and every peer pointer already point at this rank's first head inside a gathered tensor
  *     whose token stride is o_ts (out_token_stride) elements. */
@@ -483,6 +485,9 @@ int32_t inf_peer_export(inf_ctx* ctx, const void* device_ptr, void* handle_out);
 int32_t inf_peer_open(inf_ctx* ctx, const void* handle, void** peer_ptr);
 int32_t inf_peer_close(inf_ctx* ctx, void* peer_ptr, const void* handle);
 int32_t inf_comm_barrier(inf_comm* comm);
+/* 1 when inf_comm_barrier is the peer-flag kernel (every rank could map every other rank's flag array at
+ * inf_comm_init), 0 when it falls back to the NCCL all-reduce. */
+int32_t inf_comm_barrier_is_p2p(inf_comm* comm);
 int32_t inf_mla_prefill_causal_peers(inf_ctx* ctx, const void* q, int64_t q_ts, int64_t q_hs, const void* k_nope,
                                      int64_t kn_ts, int64_t kn_hs, const void* k_rope, int64_t kr_ts, const void* v,
                                      int64_t v_ts, int64_t v_hs, int32_t tokens, int32_t heads, int32_t nope_dim,

@@ -138,6 +138,9 @@ class CudaBackend:
         self._check(self._lib.inf_allgather_heads(self._comm, _ptr(local_out), _ptr(gathered), nbytes))
         return gathered
 
+    def comm_barrier_is_p2p(self) -> bool:
+        return bool(self._lib.inf_comm_barrier_is_p2p(self._comm))
+
     def comm_barrier(self):
         """Stream-ordered barrier over the communicator's ranks (after it, every rank's earlier work has finished)."""
         self._check(self._lib.inf_comm_barrier(self._comm))

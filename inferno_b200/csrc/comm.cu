@@ -219,6 +219,8 @@ int32_t inf_allgather_heads(inf_comm* comm, const void* send, void* recv, size_t
     return INF_OK;
 }
 
+int32_t inf_comm_barrier_is_p2p(inf_comm* comm) { return comm && comm->p2p ? 1 : 0; }
+
 int32_t inf_comm_barrier(inf_comm* comm) {
     if (!comm) return INF_E_ARG;
     inf_ctx* ctx = comm->ctx;

@@ -132,6 +132,7 @@ SIGNATURES = {
     "inf_comm_destroy": (_I, [_P]),
     "inf_allgather_heads": (_I, [_P, _P, _P, C.c_size_t]),
     "inf_comm_barrier": (_I, [_P]),
+    "inf_comm_barrier_is_p2p": (_I, [_P]),
     "inf_peer_export": (_I, [_P, _P, _P]),
     "inf_peer_open": (_I, [_P, _P, C.POINTER(_P)]),
     "inf_peer_close": (_I, [_P, _P, _P]),

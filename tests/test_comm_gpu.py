@@ -103,6 +103,7 @@ def _fused_body(rank, world, uid_q, inboxes, res_q):
     theirs = dict(inboxes[rank].get(timeout=120) for _ in range(world - 1))
     peers = [be.peer_open(theirs[r][0]) for r in sorted(theirs)]
     peers2 = [be.peer_open(theirs[r][1]) for r in sorted(theirs)]
+    assert be.comm_barrier_is_p2p(), "the peers' flag arrays could not be mapped: the barrier fell back to NCCL"
     be.comm_barrier()            # every copy exists and is zero before anybody stores into it
     be.device_flush()
 
