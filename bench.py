@@ -126,7 +126,7 @@ class GqaDecodeB32:
         return {"workload": cls.name + ("_strong" if strong else ""), "batch": cls.B, "q_heads": cls.Hq,
                 "kv_heads": cls.Hkv, "head_dim": cls.D, "page_size": cls.P, "split_chunk": cls.CHUNK,
                 "context": "U{1024..16384} seeded", "sum_context": int(np.asarray(lens).sum()),
-                "rope_theta": cls.THETA, "kv_bytes_per_step": int(units),
+                "rope_theta": cls.THETA, "output": "fp16, fp32 accumulation", "kv_bytes_per_step": int(units),
                 "l2": "inputs larger than L2 (KV bytes per step >> 126 MB)",
                 "sharding": "by sequence, 32/N per rank, output all-gathered" if strong else "by sequence"}
 
@@ -168,21 +168,22 @@ class GqaDecodeB32:
         self.q = self.qkv[:nq].view(Bl, 1, self.Hq, self.D)
         self.k = self.qkv[nq:nq + nk].view(Bl, 1, self.Hkv, self.D)
         self.v = self.qkv[nq + nk:].view(Bl, 1, self.Hkv, self.D)
-        self.out = torch.empty((Bl, self.Hq, self.D), dtype=torch.float32, device=be.device)
+        # fp16 output with fp32 accumulation: the precision the stated tolerance is written for
+        self.out = torch.empty((Bl, self.Hq, self.D), dtype=torch.float16, device=be.device)
         self.hqkv = self.qkv.cpu().pin_memory()
         self.hq, self.hk, self.hv = self.hqkv[:nq], self.hqkv[nq:nq + nk], self.hqkv[nq + nk:]
         self.collective = strong and world > 1
-        self.gather_bytes = self.out.numel() * 4 if self.collective else 0
-        self.gathered = torch.empty((world, Bl, self.Hq, self.D), dtype=torch.float32, device=be.device) if self.collective else None
+        self.gather_bytes = self.out.numel() * 2 if self.collective else 0
+        self.gathered = torch.empty((world, Bl, self.Hq, self.D), dtype=torch.float16, device=be.device) if self.collective else None
         result = self.gathered if self.collective else self.out
-        self.hout = torch.empty(result.shape, dtype=torch.float32).pin_memory()
+        self.hout = torch.empty(result.shape, dtype=torch.float16).pin_memory()
         self.max_len = int(self.lens.max())
         self.i = 0
         self.units_per_step = float(self.lens.astype(np.int64).sum()) * self.Hkv * self.D * 2 * 2  # KV bytes
         if strong:
             self.traffic = None
         self.h2d = sum(t.numel() * t.element_size() for t in (self.hq, self.hk, self.hv))
-        self.d2h = self.hout.numel() * 4
+        self.d2h = self.hout.numel() * 2
         self.config = self.describe(all_lens, strong)
 
     def step(self):
@@ -295,6 +296,68 @@ class GqaDecodeB32Fp8(GqaDecodeB32):
             return orc.gqa_paged_attention_fp8(qr, kr, v, None, kp, vp, c.KS, c.VS, table, past, c.P)
 
         return run, units, f"{len(lens)} of 32 sequences, all heads, full contexts"
+
+
+class GlmPagedDecode:
+    """paged_decode_attention_resident_device at the GLM expanded layout: MHA decode, 64 heads, key and value dim
+    256, 4095 cached keys + the current token, fp16 cache [pages][batch][heads][page][dim] in identity page order.
+    No sharing between heads: 268 MB of K and V rows stream once."""
+    name = "glm_paged_decode_4k"
+    metric, unit, bound = "glm_paged_decode_hbm_gbs", "GB/s", "hbm"
+    kernel = "glm_paged_decode_split_kernel"
+    launches_per_step = 2
+    traffic = None
+    B, H, D, DV, P, PAST = 1, 64, 256, 256, 64, 4095
+    max_steps = 200
+
+    def __init__(self, be, rank):
+        import torch
+        self.torch, self.be = torch, be
+        gd = torch.Generator(device=be.device).manual_seed(SEED + 61 + rank)
+        pages = (self.PAST + self.P - 1) // self.P
+        self.n_variants = 2  # two caches of 268 MB in rotation: more than L2
+        self.pk = [torch.randn((pages, self.B, self.H, self.P, self.D), generator=gd, device=be.device, dtype=torch.float16)
+                   for _ in range(2)]
+        self.pv = [torch.randn((pages, self.B, self.H, self.P, self.DV), generator=gd, device=be.device, dtype=torch.float16)
+                   for _ in range(2)]
+        n = self.B * self.H
+        self.inputs = torch.randn((n * (2 * self.D + self.DV),), generator=gd, device=be.device, dtype=torch.float32)
+        self.q = self.inputs[:n * self.D].view(self.B, self.H, self.D)
+        self.ck = self.inputs[n * self.D:2 * n * self.D].view(self.B, self.H, self.D)
+        self.cv = self.inputs[2 * n * self.D:].view(self.B, self.H, self.DV)
+        self.hinputs = self.inputs.cpu().pin_memory()
+        self.out = None
+        self.hout = torch.empty((self.B, self.H, self.DV), dtype=torch.float32).pin_memory()
+        self.i = 0
+        self.units_per_step = float(self.PAST) * self.B * self.H * (self.D + self.DV) * 2
+        self.h2d, self.d2h = self.hinputs.numel() * 4, self.hout.numel() * 4
+        self.config = {"workload": self.name, "batch": self.B, "heads": self.H, "head_dim": self.D, "value_dim": self.DV,
+                       "cached_keys": self.PAST, "page_size": self.P, "kv_bytes_per_step": int(self.units_per_step),
+                       "l2": "rotates through 2 caches (537 MB > L2)", "sharding": "replicas"}
+
+    def step(self):
+        v = self.i % 2
+        self.i += 1
+        self.out = self.be.paged_decode_attention_resident_device(self.q, self.pk[v], self.ck, self.pv[v], self.cv,
+                                                                  self.PAST, self.P)
+
+    def step_e2e(self):
+        self.inputs.copy_(self.hinputs, non_blocking=True)
+        self.step()
+        self.hout.copy_(self.out, non_blocking=True)
+
+    def cpu_sample(self):
+        from oracle import pyoracle as orc
+        rng = np.random.RandomState(SEED + 62)
+        pages = (self.PAST + self.P - 1) // self.P
+        blk = rng.standard_normal(1 << 22).astype(np.float16).view(np.uint16)
+        pk = np.resize(blk, pages * self.B * self.H * self.P * self.D).reshape(pages, self.B, self.H, self.P, self.D)
+        pv = np.resize(blk[::-1], pages * self.B * self.H * self.P * self.DV).reshape(pages, self.B, self.H, self.P, self.DV)
+        q = rng.standard_normal((self.B, self.H, self.D)).astype(np.float32)
+        ck = rng.standard_normal((self.B, self.H, self.D)).astype(np.float32)
+        cv = rng.standard_normal((self.B, self.H, self.DV)).astype(np.float32)
+        run = lambda: orc.paged_decode_mha_f16(q, pk, ck, pv, cv, self.PAST, self.P)
+        return run, self.units_per_step, "whole workload (64 heads, 4095 cached keys)"
 
 
 class MlaDecode:
@@ -850,6 +913,8 @@ def make_workload(name, be, rank, world=1, tokens=0, dist=None):
         return GqaDecodeB32(be, rank, world, strong=True)
     if name == "gqa_decode_b32_fp8":
         return GqaDecodeB32Fp8(be, rank, world)
+    if name == "glm_paged_decode_4k":
+        return GlmPagedDecode(be, rank)
     if name == "mla_decode_4k":
         return MlaDecode(be, rank, 4096)
     if name == "mla_decode_32k":
@@ -872,7 +937,7 @@ def make_workload(name, be, rank, world=1, tokens=0, dist=None):
     raise KeyError(name)
 
 
-WORKLOAD_NAMES = ["gqa_decode_b32", "gqa_decode_b32_fp8", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "mla_selected_decode_32k",
+WORKLOAD_NAMES = ["gqa_decode_b32", "gqa_decode_b32_fp8", "glm_paged_decode_4k", "mla_decode_4k", "mla_decode_32k", "mla_absorbed_decode_32k", "mla_selected_decode_32k",
                   "dsa_sparse_decode_32k", "gqa_prefill_2k", "mla_prefill_32k", "gqa_decode_b32_strong"]
 # head-sharded (or sequence-split) with an all-gather: strong scaling, the collective inside the step
 STRONG = {"gqa_prefill_2k", "mla_prefill_32k", "gqa_decode_b32_strong"}

@@ -42,7 +42,7 @@ template <bool FP8>
 struct Ring {
     static constexpr int BLOCKS = FP8 ? 2 : 4;
     static constexpr int STAGE_BYTES = BLOCKS * BLOCK_BYTES;
-    static constexpr int STAGES = FP8 ? 2 : 3;
+    static constexpr int STAGES = 3;
     static constexpr int BYTES = STAGES * STAGE_BYTES;
     static constexpr int V_BLOCK = FP8 ? 1 : 2;
 };
@@ -99,7 +99,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // [16 g, 16 g + 16) of the four key rows its P fragment covers, so accumulator column c of tile j is output dim
 // 16 c + j, which the merge step undoes when it writes the partial.
 template <bool FP8, int NT>
-__global__ void __launch_bounds__(THREADS, (FP8 && NT == 1) ? 4 : 2)
+__global__ void __launch_bounds__(THREADS, (FP8 && NT == 1) ? 3 : 2)
 gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           DecodeParams p) {
     using R = Ring<FP8>;

@@ -3,6 +3,8 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
@@ -94,6 +96,180 @@ glm_paged_decode_kernel(const float* __restrict__ q, const __half* __restrict__ 
     }
 }
 
+// The same operator split over the keys, for dims that are multiples of 64 (the GLM layout is 256 / 256): MHA decode
+// shares nothing between heads, so it is a pure stream over the head's K and V rows and the only question is how many
+// bytes are in flight.  One CTA per (split of the cached keys, head, sequence); eight lanes own one key -- each lane
+// KC (VC) 16-byte pieces of its K (V) row, pieces of neighbouring lanes adjacent in memory -- so a warp reads four
+// whole rows per load instruction and the dot product closes with three shuffles; the 32 lane groups of a CTA keep
+// their own online softmax and merge once at the end.  A second kernel merges the splits and adds the current token,
+// which the reference also takes from its f32 buffers, not from the cache (attention_kernels.metal:374-387).
+constexpr int GS_THREADS = 256;
+constexpr int GS_GROUPS = GS_THREADS / 8;
+
+template <int KC, int VC>
+__global__ void __launch_bounds__(GS_THREADS)
+glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restrict__ pk, const __half* __restrict__ pv,
+                              float* __restrict__ part_acc, float* __restrict__ part_ml, int batch, int heads, int past,
+                              int page_size, int keys_per_split, int splits) {
+    constexpr int dim = KC * 64, vdim = VC * 64;
+    const int split = blockIdx.x, row = blockIdx.y, head = row % heads, b = row / heads;
+    const int tid = threadIdx.x, group = tid >> 3, gl = tid & 7;
+    const int k_begin = split * keys_per_split, k_end = min(past, k_begin + keys_per_split);
+    const float scale = 1.0f / sqrtf((float)dim);
+    float qf[KC][8], acc[VC][8];
+#pragma unroll
+    for (int c = 0; c < KC; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qf[c][i] = q[(size_t)row * dim + (c * 8 + gl) * 8 + i] * scale;
+#pragma unroll
+    for (int c = 0; c < VC; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+    float m = NEG_BIG, l = 0.f;
+    const size_t row_base = ((size_t)b * heads + head) * page_size;            // + page * batch * heads * page_size
+    const size_t page_stride = (size_t)batch * heads * page_size;
+    for (int key = k_begin + group; key < k_end; key += GS_GROUPS) {
+        const int page = key / page_size, off = key - page * page_size;
+        const size_t r = (size_t)page * page_stride + row_base + off;
+        uint4 kraw[KC], vraw[VC];
+#pragma unroll
+        for (int c = 0; c < KC; ++c) kraw[c] = __ldg(reinterpret_cast<const uint4*>(pk + r * dim + (c * 8 + gl) * 8));
+#pragma unroll
+        for (int c = 0; c < VC; ++c) vraw[c] = __ldg(reinterpret_cast<const uint4*>(pv + r * vdim + (c * 8 + gl) * 8));
+        float dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < KC; ++c) {
+            const __half2* h = reinterpret_cast<const __half2*>(&kraw[c]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                dot = fmaf(qf[c][2 * i], f.x, dot);
+                dot = fmaf(qf[c][2 * i + 1], f.y, dot);
+            }
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        const float mn = fmaxf(m, dot);
+        const float rs = l == 0.f ? 0.f : expf(m - mn);
+        const float w = expf(dot - mn);
+        l = l * rs + w;
+        m = mn;
+#pragma unroll
+        for (int c = 0; c < VC; ++c) {
+            const __half2* h = reinterpret_cast<const __half2*>(&vraw[c]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                acc[c][2 * i] = fmaf(acc[c][2 * i], rs, w * f.x);
+                acc[c][2 * i + 1] = fmaf(acc[c][2 * i + 1], rs, w * f.y);
+            }
+        }
+    }
+    // merge the 32 groups of the CTA, 8 at a time through shared memory
+    __shared__ float sm[GS_GROUPS], sl[GS_GROUPS];
+    __shared__ float sacc[8][vdim];
+    if (gl == 0) {
+        sm[group] = m;
+        sl[group] = l;
+    }
+    __syncthreads();
+    float M = NEG_BIG;
+    for (int g = 0; g < GS_GROUPS; ++g)
+        if (sl[g] > 0.f) M = fmaxf(M, sm[g]);
+    float L = 0.f;
+    for (int g = 0; g < GS_GROUPS; ++g)
+        if (sl[g] > 0.f) L += sl[g] * expf(sm[g] - M);
+    const float mine = l > 0.f ? expf(m - M) : 0.f;
+    float total[(vdim + GS_THREADS - 1) / GS_THREADS];
+#pragma unroll
+    for (int i = 0; i < (vdim + GS_THREADS - 1) / GS_THREADS; ++i) total[i] = 0.f;
+    for (int round = 0; round < GS_GROUPS / 8; ++round) {
+        __syncthreads();
+        if (group / 8 == round) {
+#pragma unroll
+            for (int c = 0; c < VC; ++c)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sacc[group & 7][(c * 8 + gl) * 8 + i] = acc[c][i] * mine;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < (vdim + GS_THREADS - 1) / GS_THREADS; ++i) {
+            const int d = tid + i * GS_THREADS;
+            if (d < vdim)
+#pragma unroll
+                for (int g = 0; g < 8; ++g) total[i] += sacc[g][d];
+        }
+    }
+    const size_t prow = (size_t)row * splits + split;
+#pragma unroll
+    for (int i = 0; i < (vdim + GS_THREADS - 1) / GS_THREADS; ++i) {
+        const int d = tid + i * GS_THREADS;
+        if (d < vdim) part_acc[prow * vdim + d] = total[i];
+    }
+    if (tid == 0) {
+        part_ml[prow * 2] = M;
+        part_ml[prow * 2 + 1] = L;
+    }
+}
+
+// Merge of the splits plus the current token (its key and value in f32).  One CTA of 256 threads per (batch, head).
+__global__ void __launch_bounds__(256)
+glm_paged_decode_merge_kernel(const float* __restrict__ q, const float* __restrict__ cur_k,
+                              const float* __restrict__ cur_v, const float* __restrict__ part_acc,
+                              const float* __restrict__ part_ml, float* __restrict__ out, int dim, int vdim, int splits) {
+    __shared__ float red[8];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    float dot = 0.f;
+    for (int d = tid; d < dim; d += 256) dot += q[(size_t)row * dim + d] * cur_k[(size_t)row * dim + d];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if ((tid & 31) == 0) red[tid >> 5] = dot;
+    __syncthreads();
+    const float s_cur = (red[0] + red[1] + red[2] + red[3] + red[4] + red[5] + red[6] + red[7]) / sqrtf((float)dim);
+    float M = s_cur;
+    for (int s = 0; s < splits; ++s)
+        if (part_ml[((size_t)row * splits + s) * 2 + 1] > 0.f) M = fmaxf(M, part_ml[((size_t)row * splits + s) * 2]);
+    const float w_cur = expf(s_cur - M);
+    float L = w_cur;
+    for (int s = 0; s < splits; ++s) {
+        const float ls = part_ml[((size_t)row * splits + s) * 2 + 1];
+        if (ls > 0.f) L += ls * expf(part_ml[((size_t)row * splits + s) * 2] - M);
+    }
+    for (int d = tid; d < vdim; d += 256) {
+        float a = w_cur * cur_v[(size_t)row * vdim + d];
+        for (int s = 0; s < splits; ++s) {
+            const float ls = part_ml[((size_t)row * splits + s) * 2 + 1];
+            if (ls > 0.f) a += part_acc[((size_t)row * splits + s) * vdim + d] * expf(part_ml[((size_t)row * splits + s) * 2] - M);
+        }
+        out[(size_t)row * vdim + d] = a / L;
+    }
+}
+
+template <int KC, int VC>
+int launch_glm_split(inf_ctx* ctx, const float* q, const void* pk, const float* cur_k, const void* pv, const float* cur_v,
+                     int batch, int heads, int past, int page_size, float* out) {
+    const int rows = batch * heads;
+    int splits = (4 * ctx->sm_count + rows - 1) / rows;
+    splits = std::max(1, std::min(splits, (past + 255) / 256));
+    const int keys_per_split = ((past + splits - 1) / splits + GS_GROUPS - 1) / GS_GROUPS * GS_GROUPS;
+    splits = (past + keys_per_split - 1) / keys_per_split;
+    const size_t acc_bytes = (size_t)rows * splits * VC * 64 * sizeof(float);
+    int rc = inf_ensure_workspace(ctx, acc_bytes + (size_t)rows * splits * 2 * sizeof(float));
+    if (rc != INF_OK) return rc;
+    float* part_acc = (float*)ctx->workspace;
+    float* part_ml = (float*)((char*)ctx->workspace + acc_bytes);
+    {
+        inf_prof_scope prof(ctx, "glm_paged_decode_split_kernel");
+        glm_paged_decode_split_kernel<KC, VC><<<dim3(splits, rows), GS_THREADS, 0, ctx->stream>>>(
+            q, (const __half*)pk, (const __half*)pv, part_acc, part_ml, batch, heads, past, page_size, keys_per_split, splits);
+    }
+    INF_LAUNCH_CHECK(ctx, "glm_paged_decode_split_kernel");
+    glm_paged_decode_merge_kernel<<<rows, 256, 0, ctx->stream>>>(q, cur_k, cur_v, part_acc, part_ml, out, KC * 64, VC * 64, splits);
+    INF_LAUNCH_CHECK(ctx, "glm_paged_decode_merge_kernel");
+    return INF_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -139,6 +315,16 @@ int32_t inf_paged_decode_attention_resident(inf_ctx* ctx, const float* q, const 
     if (head_dim <= 0 || value_dim <= 0 || head_dim % 32 || value_dim % 32 || head_dim > GLM_MAX_DIM ||
         value_dim > GLM_MAX_DIM)
         return INF_UNSUPPORTED;
+    // the key-split form wants dims that are multiples of 64, 16-byte aligned caches and enough keys to split
+    if (past_tokens >= 256 && head_dim % 64 == 0 && value_dim % 64 == 0 &&
+        !(((uintptr_t)paged_k_f16 | (uintptr_t)paged_v_f16) & 15u)) {
+#define GLM_CASE(KC_, VC_)                                                                                      \
+    if (head_dim == KC_ * 64 && value_dim == VC_ * 64)                                                          \
+        return launch_glm_split<KC_, VC_>(ctx, q, paged_k_f16, cur_k, paged_v_f16, cur_v, batch, heads, past_tokens, \
+                                          page_size, out);
+        GLM_CASE(4, 4) GLM_CASE(3, 2) GLM_CASE(4, 2) GLM_CASE(2, 2) GLM_CASE(1, 1)
+#undef GLM_CASE
+    }
     glm_paged_decode_kernel<<<batch * heads, GLM_THREADS, 0, ctx->stream>>>(
         q, (const __half*)paged_k_f16, cur_k, (const __half*)paged_v_f16, cur_v, out, batch, heads, past_tokens,
         page_size, head_dim, value_dim);

@@ -99,6 +99,28 @@ def test_decode_step_matches_nonuniform_cpu_reference(be, sliding, q_heads, toke
     assert np.all(np.abs(got - want) <= np.maximum(2e-3, np.abs(want) * 2e-3))  # the reference tolerance
 
 
+@pytest.mark.parametrize("B,H,Dk,Dv,P,past", [
+    (2, 64, 256, 256, 128, 300),    # the key-split kernel, two splits
+    (1, 64, 256, 256, 64, 4095),    # the GLM expanded layout at the reference kernel's limit of 4096 keys
+    (3, 5, 192, 128, 16, 1000),     # 192 / 128 dims, ragged last split
+    (2, 4, 96, 32, 16, 700),        # dims that are not multiples of 64: the one-CTA-per-row kernel
+    (1, 8, 256, 256, 128, 100),     # too few keys to split
+])
+def test_glm_paged_f16_decode_sizes(be, B, H, Dk, Dv, P, past):
+    rng = np.random.default_rng(past)
+    pages = (past + P - 1) // P
+    pk = (rng.standard_normal((pages, B, H, P, Dk)) * 0.5).astype(np.float16)
+    pv = (rng.standard_normal((pages, B, H, P, Dv)) * 0.5).astype(np.float16)
+    q = rng.standard_normal((B, H, Dk)).astype(np.float32)
+    ck = rng.standard_normal((B, H, Dk)).astype(np.float32)
+    cv = rng.standard_normal((B, H, Dv)).astype(np.float32)
+    want = orc.paged_decode_mha_f16(q, pk.view(np.uint16), ck, pv.view(np.uint16), cv, past, P)
+    out = be.paged_decode_attention_resident_device(dev(be, q), torch.from_numpy(pk).to(be.device), dev(be, ck),
+                                                    torch.from_numpy(pv).to(be.device), dev(be, cv), past, P)
+    be.device_flush()
+    assert np.max(np.abs(out.cpu().numpy() - want)) <= 2e-5
+
+
 def test_glm_paged_f16_decode_matches_oracle(be):
     B, H, Dk, Dv, P, past = 2, 64, 256, 256, 128, 300
     rng = np.random.default_rng(11)
