@@ -126,6 +126,7 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
     float m = NEG_BIG, l = 0.f;
+    const unsigned gmask = 0xffu << (tid & 24);  // the eight lanes of this group inside their warp
     const size_t row_base = ((size_t)b * heads + head) * page_size;            // + page * batch * heads * page_size
     const size_t page_stride = (size_t)batch * heads * page_size;
     for (int key = k_begin + group; key < k_end; key += GS_GROUPS) {
@@ -147,9 +148,10 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
                 dot = fmaf(qf[c][2 * i + 1], f.y, dot);
             }
         }
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        // only the eight lanes of this key's group take part: the four groups of a warp may run different trip counts
+        dot += __shfl_xor_sync(gmask, dot, 1);
+        dot += __shfl_xor_sync(gmask, dot, 2);
+        dot += __shfl_xor_sync(gmask, dot, 4);
         const float mn = fmaxf(m, dot);
         const float rs = l == 0.f ? 0.f : expf(m - mn);
         const float w = expf(dot - mn);
