@@ -252,7 +252,8 @@ template <int KC, int VC>
 int launch_glm_split(inf_ctx* ctx, const float* q, const void* pk, const float* cur_k, const void* pv, const float* cur_v,
                      int batch, int heads, int past, int page_size, float* out) {
     const int rows = batch * heads;
-    int splits = (4 * ctx->sm_count + rows - 1) / rows;
+    // two CTAs fit an SM (118 registers x 256 threads): aim at two full waves, never more CTAs than that
+    int splits = (4 * ctx->sm_count) / rows;
     splits = std::max(1, std::min(splits, (past + 255) / 256));
     const int keys_per_split = ((past + splits - 1) / splits + GS_GROUPS - 1) / GS_GROUPS * GS_GROUPS;
     splits = (past + keys_per_split - 1) / keys_per_split;

