@@ -112,7 +112,8 @@ def decode_lens(rank: int, batch: int = 32):
 class GqaDecodeB32:
     """Paged GQA decode, batch 32 (the third benchmark configuration).  Weak scaling: every rank owns its own batch
     of 32 (different seeded lengths per rank).  Strong scaling (`strong=True`): rank 0's batch of 32 is split into
-    32/N sequences per rank and the [32, 48, 128] f32 output is all-gathered."""
+    32/N sequences per rank and the [32, 48, 128] fp16 output is gathered on every rank: the combine kernel stores
+    each row into every rank's copy (peer stores), and inf_comm_barrier ends the step."""
     name = "gqa_decode_b32"
     metric, unit, bound = "attn_decode_hbm_gbs", "GB/s", "hbm"
     kernel = "gqa_decode_partial_kernel"
@@ -130,7 +131,7 @@ class GqaDecodeB32:
                 "l2": "inputs larger than L2 (KV bytes per step >> 126 MB)",
                 "sharding": "by sequence, 32/N per rank, output all-gathered" if strong else "by sequence"}
 
-    def __init__(self, be, rank, world=1, strong=False):
+    def __init__(self, be, rank, world=1, strong=False, dist=None):
         import torch
         from inferno_b200.sharding import shard_sequences
         self.torch, self.be, self.world, self.strong = torch, be, world, strong
@@ -158,7 +159,7 @@ class GqaDecodeB32:
         self.pool.k.normal_(0, 1, generator=gd)
         self.pool.v.normal_(0, 1, generator=gd)
         self.past = be.page_table(table, self.lens - 1, validate_on_host=False)
-        self.full = be.page_table(table, self.lens, validate_on_host=False)
+        self.table_full = be.page_table(table, self.lens, validate_on_host=False)
         inv = 1.0 / np.power(np.float32(self.THETA), (2 * np.arange(32)).astype(np.float32) / np.float32(64))
         self.rope = be.prepare_rope_table(inv.astype(np.float32), 64, 1.0)
         # q, k and v of a step are three views of one device buffer (and of one pinned host buffer), so that the
@@ -175,6 +176,13 @@ class GqaDecodeB32:
         self.collective = strong and world > 1
         self.gather_bytes = self.out.numel() * 2 if self.collective else 0
         self.gathered = torch.empty((world, Bl, self.Hq, self.D), dtype=torch.float16, device=be.device) if self.collective else None
+        if self.collective:
+            self.exchange = "fused"   # "fused" (peer stores in the combine kernel), "nccl", "none"
+            # two gathered outputs alternate: a peer may still read the one the previous step filled
+            self.n_variants = 2
+            self.full = [torch.zeros((self.B, self.Hq, self.D), dtype=torch.float16, device=be.device) for _ in range(2)]
+            self.peers = [map_peers(be, dist, t) for t in self.full]
+            self.mine = [t[b0:b1] for t in self.full]
         result = self.gathered if self.collective else self.out
         self.hout = torch.empty(result.shape, dtype=torch.float16).pin_memory()
         self.max_len = int(self.lens.max())
@@ -188,15 +196,24 @@ class GqaDecodeB32:
 
     def step(self):
         q16 = self.be.rope_append_gqa(self.q, self.k, self.v, self.rope, self.pool, self.past)
-        self.be.gqa_decode_paged(q16.view(self.Bl, self.Hq, self.D), self.pool, self.full, self.max_len, self.CHUNK,
+        self.i += 1
+        if self.collective and self.exchange == "fused":
+            self.result = self.full[self.i & 1]
+            self.be.gqa_decode_paged(q16.view(self.Bl, self.Hq, self.D), self.pool, self.table_full, self.max_len,
+                                     self.CHUNK, out=self.mine[self.i & 1], peers=self.peers[self.i & 1])
+            self.be.comm_barrier()
+            return
+        self.be.gqa_decode_paged(q16.view(self.Bl, self.Hq, self.D), self.pool, self.table_full, self.max_len, self.CHUNK,
                                  out=self.out)
-        if self.collective:
+        self.result = self.out
+        if self.collective and self.exchange == "nccl":
             self.be.allgather_into(self.out, self.gathered)
+            self.result = self.gathered
 
     def step_e2e(self):
         self.qkv.copy_(self.hqkv, non_blocking=True)
         self.step()
-        self.hout.copy_(self.gathered if self.collective else self.out, non_blocking=True)
+        self.hout.view(-1).copy_(self.result.view(-1), non_blocking=True)
 
     # ---- CPU arm: the oracle on host arrays of the same shapes
     @classmethod
@@ -265,6 +282,7 @@ class GqaDecodeB32Fp8(GqaDecodeB32):
         self.be.gqa_decode_paged_fp8(q16.view(self.Bl, self.Hq, self.D), k16.view(self.Bl, self.Hkv, self.D),
                                      v16.view(self.Bl, self.Hkv, self.D), self.pool, self.past, self.max_len, self.CHUNK,
                                      out=self.out)
+        self.result = self.out
 
     @classmethod
     def cpu_sample(cls, rank=0, max_sequences=32):
@@ -913,7 +931,7 @@ def make_workload(name, be, rank, world=1, tokens=0, dist=None):
     if name == "gqa_decode_b32":
         return GqaDecodeB32(be, rank, world)
     if name == "gqa_decode_b32_strong":
-        return GqaDecodeB32(be, rank, world, strong=True)
+        return GqaDecodeB32(be, rank, world, strong=True, dist=dist)
     if name == "gqa_decode_b32_fp8":
         return GqaDecodeB32Fp8(be, rank, world)
     if name == "glm_paged_decode_4k":
@@ -1110,9 +1128,9 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
             coll = {"bytes_sent_per_rank_to_each_peer": wl.gather_bytes,
                     "bytes_received_per_rank": wl.gather_bytes * (world - 1)}
             if hasattr(wl, "exchange"):
-                coll["what"] = ("the step stores its tiles into every rank's gathered tensor from the kernel's epilogue "
-                                "(peer stores over NVLink) and ends with inf_comm_barrier; beside it, the same step with "
-                                "inf_allgather_heads (NCCL) after the kernel, and with no exchange at all")
+                coll["what"] = ("the step's last kernel stores its output into every rank's gathered tensor (peer stores "
+                                "over NVLink, tile by tile) and the step ends with inf_comm_barrier; beside it, the same "
+                                "step with inf_allgather_heads (NCCL) after the kernel, and with no exchange at all")
                 coll["barrier"] = "peer-flag kernel" if be.comm_barrier_is_p2p() else "nccl all-reduce"
                 coll["ms_per_step_fused_gather"] = eager_ms("fused")
                 coll["ms_per_step_nccl_allgather"] = eager_ms("nccl")

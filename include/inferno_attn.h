@@ -478,7 +478,10 @@ int32_t inf_allgather_heads(inf_comm* comm, const void* send, void* recv, size_t
  *     exchanged and mapped at inf_comm_init; if that is not possible, a four-byte NCCL all-reduce instead).
  *   inf_mla_prefill_causal_peers / inf_gqa_prefill_paged_peers: the prefill entry points with up to INF_MAX_PEERS
  *     peer outputs; `out` and every peer pointer already point at this rank's first head inside a gathered tensor
- *     whose token stride is o_ts (out_token_stride) elements. */
+ *     whose token stride is o_ts (out_token_stride) elements.
+ *   inf_gqa_decode_paged_peers: inf_gqa_decode_paged for a batch sharded by sequence; `out` and every peer pointer
+ *     point at this rank's first sequence inside a gathered [all sequences][q_heads][128] output, and the combine
+ *     kernel stores each output row into all of them. */
 #define INF_MAX_PEERS 7
 #define INF_PEER_HANDLE_BYTES 72
 int32_t inf_peer_export(inf_ctx* ctx, const void* device_ptr, void* handle_out);
@@ -497,6 +500,10 @@ int32_t inf_gqa_prefill_paged_peers(inf_ctx* ctx, const void* q_f16, const inf_k
                                     const inf_page_table* table, int32_t tokens, int32_t q_heads, int32_t sliding_window,
                                     const float* gate, float scale, void* out, int32_t out_dtype,
                                     int64_t out_token_stride, void* const* peer_outs, int32_t n_peers);
+int32_t inf_gqa_decode_paged_peers(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                   const inf_page_table* table, int32_t q_heads, int32_t max_len, int32_t split_chunk,
+                                   int32_t sliding_window, const float* gate, float scale, void* out,
+                                   int32_t out_dtype, void* const* peer_outs, int32_t n_peers);
 
 #ifdef __cplusplus
 }

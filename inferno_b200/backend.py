@@ -355,14 +355,24 @@ class CudaBackend:
 
     # ------------------------------------------------------------------ attention
     def gqa_decode_paged(self, q_f16, pool: KvPool, table: PageTable, max_len: int, split_chunk: int = 512,
-                         sliding_window: int = 0, gate=None, scale: float = 0.0, out_dtype=torch.float32, out=None):
+                         sliding_window: int = 0, gate=None, scale: float = 0.0, out_dtype=torch.float32, out=None,
+                         peers=None):
+        """`peers`: device addresses (peer_open) of the other ranks' copies of the gathered [all sequences, Hq, D]
+        output that `out` is this rank's block of rows of: every output row is also stored there."""
         B, Hq, D = q_f16.shape
         if out is None:
             out = torch.empty((B, Hq, D), dtype=out_dtype, device=self.device)
         dt = L.DTYPE_F32 if out.dtype == torch.float32 else L.DTYPE_F16
-        ok = self._check(self._lib.inf_gqa_decode_paged(self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc),
-                                                        Hq, max_len, split_chunk, sliding_window, _ptr(gate), scale,
-                                                        _ptr(out), dt))
+        if peers is None:
+            ok = self._check(self._lib.inf_gqa_decode_paged(self._ctx, _ptr(q_f16), C.byref(pool.desc),
+                                                            C.byref(table.desc), Hq, max_len, split_chunk,
+                                                            sliding_window, _ptr(gate), scale, _ptr(out), dt))
+            return out if ok else None
+        assert out.is_contiguous()
+        arr = self._peer_array(peers, out.storage_offset() * out.element_size())
+        ok = self._check(self._lib.inf_gqa_decode_paged_peers(
+            self._ctx, _ptr(q_f16), C.byref(pool.desc), C.byref(table.desc), Hq, max_len, split_chunk, sliding_window,
+            _ptr(gate), scale, _ptr(out), dt, arr, len(peers)))
         return out if ok else None
 
     def gqa_decode_paged_fp8(self, q_f16, cur_k_f16, cur_v_f16, pool: KvPoolFp8, table: PageTable, max_len: int,

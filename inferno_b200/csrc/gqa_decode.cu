@@ -38,11 +38,15 @@ constexpr float M_INIT = -1.0e30f;
 
 // A stage holds 64 keys: fp16 pages as four blocks (K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127),
 // FP8 pages as two (a 128-dim row is 128 bytes, one block each for K and V).  Either way the ring is 96 KB.
+#ifndef INF_FP8_STAGES
+#define INF_FP8_STAGES 3   // ring depth and resident CTAs per SM of the FP8 instantiation (build-time experiment knobs)
+#define INF_FP8_CTAS 3
+#endif
 template <bool FP8>
 struct Ring {
     static constexpr int BLOCKS = FP8 ? 2 : 4;
     static constexpr int STAGE_BYTES = BLOCKS * BLOCK_BYTES;
-    static constexpr int STAGES = 3;
+    static constexpr int STAGES = FP8 ? INF_FP8_STAGES : 3;
     static constexpr int BYTES = STAGES * STAGE_BYTES;
     static constexpr int V_BLOCK = FP8 ? 1 : 2;
 };
@@ -99,7 +103,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // [16 g, 16 g + 16) of the four key rows its P fragment covers, so accumulator column c of tile j is output dim
 // 16 c + j, which the merge step undoes when it writes the partial.
 template <bool FP8, int NT>
-__global__ void __launch_bounds__(THREADS, (FP8 && NT == 1) ? 3 : 2)
+__global__ void __launch_bounds__(THREADS, (FP8 && NT == 1) ? INF_FP8_CTAS : 2)
 gqa_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           DecodeParams p) {
     using R = Ring<FP8>;
@@ -463,6 +467,13 @@ __device__ __forceinline__ float softplus_ref(float v) {
     return logf(1.0f + expf(v));
 }
 
+// The other ranks' copies of the gathered output when the batch is sharded by sequence, each already offset to this
+// rank's first sequence like `out` itself (peer memory mapped into this process; plain stores).
+struct DecodePeerOuts {
+    void* out[INF_MAX_PEERS];
+    int count;
+};
+
 // Merge of the per-chunk partials.  The chunk weights are computed once in shared memory so that the
 // accumulation is a stream of independent coalesced loads.  When cur_k / cur_v are given (FP8 pages), the current
 // token is not among the cached keys: its score q . k and its value enter here as one more term, at full precision
@@ -473,7 +484,7 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
                           const int* __restrict__ lens, const float* __restrict__ gate, OutT* __restrict__ out,
                           int q_heads, int max_chunks, int chunk, int window, int len_add,
                           const __half* __restrict__ q, const __half* __restrict__ cur_k,
-                          const __half* __restrict__ cur_v, int group, float cur_scale_log2) {
+                          const __half* __restrict__ cur_v, int group, float cur_scale_log2, DecodePeerOuts peers) {
     __shared__ float w[MAX_CHUNK / TILE_KEYS * 16];  // up to 512 chunks
     __shared__ float red[4];
     inf_pdl_wait();
@@ -484,6 +495,7 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
     const long long orow = ((long long)b * q_heads + h) * D + d;
     if (kv_len < 0 || (kv_len == 0 && !has_cur)) {
         out[orow] = OutT(0.f);
+        for (int pr = 0; pr < peers.count; ++pr) reinterpret_cast<OutT*>(peers.out[pr])[orow] = OutT(0.f);
         return;
     }
     kv_len = min(kv_len, max_chunks * chunk);  // the partial kernel cut it the same way and raised the status word
@@ -529,7 +541,10 @@ gqa_decode_combine_kernel(const float* __restrict__ part_acc, const float* __res
 #pragma unroll 8
     for (int c = 0; c < n; ++c) acc += w[c] * src[(long long)c * q_heads * D];
     const float gain = (gate ? softplus_ref(gate[(long long)b * q_heads + h]) : 1.0f) / L;
-    out[orow] = OutT(acc * gain);
+    const OutT o = OutT(acc * gain);
+    out[orow] = o;
+    // a batch sharded by sequence: the row also goes into the other ranks' copies of the gathered output
+    for (int pr = 0; pr < peers.count; ++pr) reinterpret_cast<OutT*>(peers.out[pr])[orow] = o;
 }
 
 }  // namespace
@@ -544,7 +559,7 @@ struct DecodeFp8 {
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
                           float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add,
-                          const DecodeFp8* fp8);
+                          const DecodeFp8* fp8, void* const* peer_outs, int n_peers);
 
 extern "C" size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads, int32_t head_dim, int32_t max_len,
                                                  int32_t split_chunk) {
@@ -557,7 +572,7 @@ extern "C" size_t inf_gqa_decode_workspace_bytes(int32_t batch, int32_t q_heads,
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
                           float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add,
-                          const DecodeFp8* fp8) {
+                          const DecodeFp8* fp8, void* const* peer_outs, int n_peers) {
     if (!q_f16 || !pool || !table || !out) return inf_fail(ctx, INF_E_ARG, "gqa_decode: null pointer");
     if (!pool->k || !pool->v) return inf_fail(ctx, INF_E_ARG, "gqa_decode: pool has no storage");
     if (pool->head_dim != D) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: head_dim must be 128, got %d", pool->head_dim);
@@ -577,6 +592,16 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     if (fp8 && (!fp8->cur_k || !fp8->cur_v)) return inf_fail(ctx, INF_E_ARG, "gqa_decode_fp8: null current key / value");
     if (fp8 && (!(fp8->key_scale > 0.f) || !(fp8->value_scale > 0.f) || !isfinite(fp8->key_scale) || !isfinite(fp8->value_scale)))
         return inf_fail(ctx, INF_E_CONFIG, "gqa_decode_fp8: scales must be positive and finite");
+    if (n_peers < 0 || n_peers > INF_MAX_PEERS)
+        return inf_fail(ctx, INF_E_CONFIG, "gqa_decode: %d peers, at most %d are supported", n_peers, INF_MAX_PEERS);
+    if (n_peers > 0 && !peer_outs) return inf_fail(ctx, INF_E_ARG, "gqa_decode: null peer list");
+    DecodePeerOuts peers;
+    peers.count = n_peers;
+    for (int i = 0; i < INF_MAX_PEERS; ++i) {
+        peers.out[i] = i < n_peers ? peer_outs[i] : nullptr;
+        if (i < n_peers && (!peers.out[i] || (reinterpret_cast<uintptr_t>(peers.out[i]) & 3u)))
+            return inf_fail(ctx, INF_E_ARG, "gqa_decode: peer output %d is null or misaligned", i);
+    }
     const int cur_extra = fp8 ? 1 : 0;  // the FP8 form counts cached rows; the current token comes on top
     int rc = inf_validate_table(ctx, table, pool->num_pages, pool->page_size, len_add, "gqa_decode", sliding_window, 1);
     if (rc != INF_OK) return rc;
@@ -657,11 +682,11 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     if (out_dtype == INF_DTYPE_F32)
         INF_CUDA(ctx, inf_launch_pdl(gqa_decode_combine_kernel<float>, cgrid, dim3(D), 0, ctx->stream, p.part_acc, p.part_ml,
                                      table->lens, gate, (float*)out, q_heads, max_chunks, split_chunk, sliding_window,
-                                     len_add, cq, ck, cv, group, cur_scale_log2));
+                                     len_add, cq, ck, cv, group, cur_scale_log2, peers));
     else
         INF_CUDA(ctx, inf_launch_pdl(gqa_decode_combine_kernel<__half>, cgrid, dim3(D), 0, ctx->stream, p.part_acc,
                                      p.part_ml, table->lens, gate, (__half*)out, q_heads, max_chunks, split_chunk,
-                                     sliding_window, len_add, cq, ck, cv, group, cur_scale_log2));
+                                     sliding_window, len_add, cq, ck, cv, group, cur_scale_log2, peers));
     INF_LAUNCH_CHECK(ctx, "gqa_decode_combine_kernel");
     return INF_OK;
 }
@@ -683,7 +708,25 @@ extern "C" int32_t inf_gqa_decode_paged(inf_ctx* ctx, const void* q_f16, const i
     int rc = inf_ensure_workspace(ctx, need);
     if (rc != INF_OK) return rc;
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
-                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0, nullptr);
+                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0, nullptr, nullptr, 0);
+}
+
+// The same decode for a batch sharded by sequence over the GPUs of one box: `out` points at this rank's rows inside
+// its own copy of the gathered [all sequences][q_heads][128] output and peer_outs[i] at the same rows inside rank i's
+// copy (inf_peer_open), so the combine kernel's stores are the all-gather.  inf_comm_barrier ends the step.
+extern "C" int32_t inf_gqa_decode_paged_peers(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool,
+                                              const inf_page_table* table, int32_t q_heads, int32_t max_len,
+                                              int32_t split_chunk, int32_t sliding_window, const float* gate,
+                                              float scale, void* out, int32_t out_dtype, void* const* peer_outs,
+                                              int32_t n_peers) {
+    INF_CHECK_CTX(ctx);
+    if (!table) return inf_fail(ctx, INF_E_ARG, "gqa_decode: null page table");
+    size_t need = inf_gqa_decode_workspace_bytes(table->batch, q_heads, D, max_len, split_chunk);
+    if (need == 0) return inf_fail(ctx, INF_E_SHAPE, "gqa_decode: sizes must be positive");
+    int rc = inf_ensure_workspace(ctx, need);
+    if (rc != INF_OK) return rc;
+    return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
+                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0, nullptr, peer_outs, n_peers);
 }
 
 extern "C" int32_t inf_gqa_decode_paged_fp8(inf_ctx* ctx, const void* q_f16, const void* cur_k_f16, const void* cur_v_f16,
@@ -699,7 +742,7 @@ extern "C" int32_t inf_gqa_decode_paged_fp8(inf_ctx* ctx, const void* q_f16, con
     const inf_kv_pool shape = {pool->k, pool->v, pool->num_pages, pool->page_size, pool->kv_heads, pool->head_dim};
     const DecodeFp8 fp8 = {pool->key_scale, pool->value_scale, cur_k_f16, cur_v_f16};
     return inf_gqa_decode_launch(ctx, q_f16, &shape, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
-                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0, &fp8);
+                                 out, out_dtype, ctx->workspace, ctx->workspace_bytes, 0, &fp8, nullptr, 0);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -763,5 +806,5 @@ extern "C" int32_t inf_gqa_decode_paged_static(inf_ctx* ctx, const void* q_f16, 
     // Nothing in the array has to start at zero: every partial the combine kernel reads is written
     // by the partial kernel of the same call first.
     return inf_gqa_decode_launch(ctx, q_f16, pool, table, q_heads, max_len, split_chunk, sliding_window, gate, scale,
-                                 out, out_dtype, scratch, (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES, 0, nullptr);
+                                 out, out_dtype, scratch, (size_t)INF_GQA_DECODE_STATIC_SCRATCH_BYTES, 0, nullptr, nullptr, 0);
 }

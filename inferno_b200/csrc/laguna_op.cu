@@ -10,7 +10,7 @@
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
                           float scale, void* out, int out_dtype, void* scratch, size_t scratch_bytes, int len_add,
-                          const struct DecodeFp8* fp8);
+                          const struct DecodeFp8* fp8, void* const* peer_outs, int n_peers);
 int inf_gqa_prefill_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                            int tokens, int q_heads, int sliding_window, const float* gate, float scale, void* out,
                            int out_dtype, const struct PrefillPeers* peers);
@@ -103,11 +103,19 @@ glm_paged_decode_kernel(const float* __restrict__ q, const __half* __restrict__ 
 // whole rows per load instruction and the dot product closes with three shuffles; the 32 lane groups of a CTA keep
 // their own online softmax and merge once at the end.  A second kernel merges the splits and adds the current token,
 // which the reference also takes from its f32 buffers, not from the cache (attention_kernels.metal:374-387).
-constexpr int GS_THREADS = 256;
+#ifndef INF_GLM_THREADS
+// Threads per CTA, resident CTAs per SM, and whether a lane group requests its next key's rows before it works on the
+// current one.  Measured on the 64-head, 4 095-key case: 256 x 2 without prefetch 53.2 us, 128 x 3 with prefetch
+// (163 registers) 52.5 us, 128 x 4 without (128 registers) 51.1 us.
+#define INF_GLM_THREADS 128
+#define INF_GLM_CTAS 4
+#define INF_GLM_PREFETCH 0
+#endif
+constexpr int GS_THREADS = INF_GLM_THREADS;
 constexpr int GS_GROUPS = GS_THREADS / 8;
 
 template <int KC, int VC>
-__global__ void __launch_bounds__(GS_THREADS)
+__global__ void __launch_bounds__(GS_THREADS, INF_GLM_CTAS)
 glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restrict__ pk, const __half* __restrict__ pv,
                               float* __restrict__ part_acc, float* __restrict__ part_ml, int batch, int heads, int past,
                               int page_size, int keys_per_split, int splits) {
@@ -129,14 +137,26 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
     const unsigned gmask = 0xffu << (tid & 24);  // the eight lanes of this group inside their warp
     const size_t row_base = ((size_t)b * heads + head) * page_size;            // + page * batch * heads * page_size
     const size_t page_stride = (size_t)batch * heads * page_size;
-    for (int key = k_begin + group; key < k_end; key += GS_GROUPS) {
+    uint4 kraw[KC], vraw[VC];
+    auto request = [&](int key, uint4 (&kr)[KC], uint4 (&vr)[VC]) {
         const int page = key / page_size, off = key - page * page_size;
         const size_t r = (size_t)page * page_stride + row_base + off;
-        uint4 kraw[KC], vraw[VC];
 #pragma unroll
-        for (int c = 0; c < KC; ++c) kraw[c] = __ldg(reinterpret_cast<const uint4*>(pk + r * dim + (c * 8 + gl) * 8));
+        for (int c = 0; c < KC; ++c) kr[c] = __ldg(reinterpret_cast<const uint4*>(pk + r * dim + (c * 8 + gl) * 8));
 #pragma unroll
-        for (int c = 0; c < VC; ++c) vraw[c] = __ldg(reinterpret_cast<const uint4*>(pv + r * vdim + (c * 8 + gl) * 8));
+        for (int c = 0; c < VC; ++c) vr[c] = __ldg(reinterpret_cast<const uint4*>(pv + r * vdim + (c * 8 + gl) * 8));
+    };
+#if INF_GLM_PREFETCH
+    if (k_begin + group < k_end) request(k_begin + group, kraw, vraw);
+#endif
+    for (int key = k_begin + group; key < k_end; key += GS_GROUPS) {
+#if INF_GLM_PREFETCH
+        uint4 knext[KC], vnext[VC];
+        const bool more = key + GS_GROUPS < k_end;
+        if (more) request(key + GS_GROUPS, knext, vnext);
+#else
+        request(key, kraw, vraw);
+#endif
         float dot = 0.f;
 #pragma unroll
         for (int c = 0; c < KC; ++c) {
@@ -167,6 +187,14 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
                 acc[c][2 * i + 1] = fmaf(acc[c][2 * i + 1], rs, w * f.y);
             }
         }
+#if INF_GLM_PREFETCH
+        if (more) {
+#pragma unroll
+            for (int c = 0; c < KC; ++c) kraw[c] = knext[c];
+#pragma unroll
+            for (int c = 0; c < VC; ++c) vraw[c] = vnext[c];
+        }
+#endif
     }
     // merge the 32 groups of the CTA, 8 at a time through shared memory
     __shared__ float sm[GS_GROUPS], sl[GS_GROUPS];
@@ -252,8 +280,8 @@ template <int KC, int VC>
 int launch_glm_split(inf_ctx* ctx, const float* q, const void* pk, const float* cur_k, const void* pv, const float* cur_v,
                      int batch, int heads, int past, int page_size, float* out) {
     const int rows = batch * heads;
-    // two CTAs fit an SM (118 registers x 256 threads): aim at two full waves, never more CTAs than that
-    int splits = (4 * ctx->sm_count) / rows;
+    // aim at two full waves of the CTAs an SM holds, never more CTAs than that
+    int splits = (2 * INF_GLM_CTAS * ctx->sm_count) / rows;
     splits = std::max(1, std::min(splits, (past + 255) / 256));
     const int keys_per_split = ((past + splits - 1) / splits + GS_GROUPS - 1) / GS_GROUPS * GS_GROUPS;
     splits = (past + keys_per_split - 1) / keys_per_split;
@@ -300,7 +328,7 @@ int32_t inf_laguna_gated_gqa_f16_attention(inf_ctx* ctx, const float* q, const f
     if (rc != INF_OK) return rc;
     if (tokens == 1)
         return inf_gqa_decode_launch(ctx, q16, pool, table, q_heads, max_len, chunk, sliding_window, gate, 0.f, out,
-                                     INF_DTYPE_F32, (char*)ctx->workspace + q_bytes, dec_bytes, 1, nullptr);
+                                     INF_DTYPE_F32, (char*)ctx->workspace + q_bytes, dec_bytes, 1, nullptr, nullptr, 0);
     return inf_gqa_prefill_launch(ctx, q16, pool, table, tokens, q_heads, sliding_window, gate, 0.f, out,
                                   INF_DTYPE_F32, nullptr);
 }

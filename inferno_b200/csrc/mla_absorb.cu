@@ -61,13 +61,23 @@ q8_0_heads_matvec_kernel(const uint8_t* __restrict__ weights, const float* __res
 
 // The same product for out_features % 32 == 0 (every shape of the absorbed-MLA path): a CTA owns 32 consecutive
 // output features of one head, whose weight rows are one contiguous, 16-byte aligned run of 32 * 34 * blocks
-// bytes.  The run is staged in shared memory with 16-byte loads (every byte of the matrix crosses HBM once, with
-// many independent requests in flight), then each warp reduces four of the rows against the input rows, lane =
-// value inside a block as in the reference kernel.  Optionally the CTAs with blockIdx.x == 0 also convert the
-// head's `tail` f32 values per input row into fp16 columns [tail_col0, tail_col0 + tail_n) of the output row
-// (the RoPE part of the absorbed query).
+// bytes.  The run is read with 16-byte loads (every byte of the matrix crosses HBM once, with many independent
+// requests in flight) and taken apart on its way into shared memory: the quants of a row become one contiguous,
+// 16-byte aligned int8 row, the block scales a separate fp16 table (everything in a Q8_0 row is 2-byte aligned, so
+// the scatter works on 16-bit units).  Then G lanes share a weight row, each lane taking 16 consecutive quants (half
+// a block) per step with one 16-byte load; int8 -> f32 goes through the 2^23 trick on the integer and FP32 pipes
+// (I2F would run at a quarter of their rate), and the lanes of a row meet with log2(G) shuffles.  Optionally the CTAs
+// with blockIdx.x == 0 also convert the head's `tail` f32 values per input row into fp16 columns
+// [tail_col0, tail_col0 + tail_n) of the output row (the RoPE part of the absorbed query).
 constexpr int TILE_ROWS = 32;
-template <typename OutT>
+
+__device__ __forceinline__ float q8_byte_to_float(uint32_t biased_word, int byte) {
+    // biased_word holds q + 128 in each byte: 0x4B0000uu is 2^23 + u exactly
+    const uint32_t bits = __byte_perm(biased_word, 0x4B000000u, 0x7650 - 0 + byte);  // bytes {u, 00, 00, 4B}
+    return __uint_as_float(bits) - 8388736.0f;
+}
+
+template <typename OutT, int G>
 __global__ void __launch_bounds__(MV_WARPS * 32)
 q8_0_heads_matvec_tile_kernel(const uint8_t* __restrict__ weights, const float* __restrict__ input,
                               OutT* __restrict__ out, int rows, int heads, int in_features, int out_features,
@@ -75,14 +85,41 @@ q8_0_heads_matvec_tile_kernel(const uint8_t* __restrict__ weights, const float* 
     extern __shared__ __align__(16) uint8_t tile[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int o0 = blockIdx.x * TILE_ROWS;
-    // the weights never change: stage them before waiting for the kernel that produces the input rows
     const int head = blockIdx.y;
     const int row0 = blockIdx.z * MV_ROWS;
     const int blocks_per_row = in_features / Q8_BLOCK_VALUES;
-    const int row_bytes = blocks_per_row * Q8_BLOCK_BYTES;
-    const uint4* src = reinterpret_cast<const uint4*>(weights + ((size_t)head * out_features + o0) * row_bytes);
-    const int n16 = TILE_ROWS * row_bytes / 16;
-    for (int i = threadIdx.x; i < n16; i += MV_WARPS * 32) reinterpret_cast<uint4*>(tile)[i] = src[i];
+    const int row_units = blocks_per_row * (Q8_BLOCK_BYTES / 2);  // 16-bit units per weight row
+    int8_t* quants = reinterpret_cast<int8_t*>(tile);                                         // [32][in_features]
+    __half* scales = reinterpret_cast<__half*>(tile + (size_t)TILE_ROWS * in_features);      // [32][blocks_per_row]
+    // the weights never change: stage them before waiting for the kernel that produces the input rows
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(
+            weights + ((size_t)head * out_features + o0) * blocks_per_row * Q8_BLOCK_BYTES);
+        const int n16 = TILE_ROWS * row_units / 8;
+        unsigned short* q16 = reinterpret_cast<unsigned short*>(quants);
+        unsigned short* s16 = reinterpret_cast<unsigned short*>(scales);
+        for (int i = threadIdx.x; i < n16; i += MV_WARPS * 32) {
+            const uint4 v = src[i];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            const int g = i * 8;
+            int row = g / row_units;
+            const int u = g - row * row_units;
+            int blk = u / 17, pos = u - blk * 17;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const unsigned short unit = (unsigned short)(w[k >> 1] >> ((k & 1) * 16));
+                if (pos == 0) s16[row * blocks_per_row + blk] = unit;
+                else q16[(row * in_features + blk * Q8_BLOCK_VALUES) / 2 + pos - 1] = unit;
+                if (++pos == 17) {
+                    pos = 0;
+                    if (++blk == blocks_per_row) {
+                        blk = 0;
+                        ++row;
+                    }
+                }
+            }
+        }
+    }
     inf_pdl_wait();
     inf_pdl_release();
     if (tail && blockIdx.x == 0) {
@@ -92,28 +129,46 @@ q8_0_heads_matvec_tile_kernel(const uint8_t* __restrict__ weights, const float* 
                     OutT(tail[((size_t)(row0 + r) * heads + head) * tail_n + d]);
     }
     __syncthreads();
-#pragma unroll
-    for (int i = 0; i < TILE_ROWS / MV_WARPS; ++i) {
-        const int lr = warp * (TILE_ROWS / MV_WARPS) + i;
-        const uint8_t* wrow = tile + lr * row_bytes;
+    constexpr int ROWS_PER_PASS = 32 / G;                       // weight rows a warp works on at once
+    constexpr int PASSES = TILE_ROWS / (MV_WARPS * ROWS_PER_PASS);
+    const int gl = lane % G, sub = lane / G;
+    const int chunks = in_features / 16;                        // 16-quant steps per weight row
+#pragma unroll 1
+    for (int pass = 0; pass < PASSES; ++pass) {
+        const int lr = (pass * MV_WARPS + warp) * ROWS_PER_PASS + sub;
         float sum[MV_ROWS];
 #pragma unroll
         for (int r = 0; r < MV_ROWS; ++r) sum[r] = 0.f;
-        for (int blk = 0; blk < blocks_per_row; ++blk) {
-            const uint8_t* bp = wrow + blk * Q8_BLOCK_BYTES;
-            const float d = __half2float(*reinterpret_cast<const __half*>(bp));  // block starts are 2-byte aligned
-            const float w = d * (float)(signed char)bp[2 + lane];
+        for (int c = gl; c < chunks; c += G) {
+            const uint4 qv = *reinterpret_cast<const uint4*>(quants + (size_t)lr * in_features + c * 16);
+            const float d = __half2float(scales[lr * blocks_per_row + (c >> 1)]);
+            const uint32_t qw[4] = {qv.x ^ 0x80808080u, qv.y ^ 0x80808080u, qv.z ^ 0x80808080u, qv.w ^ 0x80808080u};
+            float wf[16];
 #pragma unroll
-            for (int r = 0; r < MV_ROWS; ++r)
-                if (row0 + r < rows)
-                    sum[r] = fmaf(input[((size_t)(row0 + r) * heads + head) * in_features + blk * Q8_BLOCK_VALUES + lane],
-                                  w, sum[r]);
+            for (int i = 0; i < 16; ++i) wf[i] = q8_byte_to_float(qw[i >> 2], i & 3);
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; ++r) {
+                if (row0 + r < rows) {
+                    const float4* xp = reinterpret_cast<const float4*>(
+                        input + ((size_t)(row0 + r) * heads + head) * in_features + c * 16);
+                    float part = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 x = __ldg(xp + i);
+                        part = fmaf(x.x, wf[4 * i], part);
+                        part = fmaf(x.y, wf[4 * i + 1], part);
+                        part = fmaf(x.z, wf[4 * i + 2], part);
+                        part = fmaf(x.w, wf[4 * i + 3], part);
+                    }
+                    sum[r] = fmaf(part, d, sum[r]);
+                }
+            }
         }
 #pragma unroll
         for (int r = 0; r < MV_ROWS; ++r) {
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], off);
-            if (lane == 0 && row0 + r < rows)
+            for (int off = G / 2; off > 0; off >>= 1) sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], off);
+            if (gl == 0 && row0 + r < rows)
                 out[((size_t)(row0 + r) * heads + head) * out_stride + o0 + lr] = OutT(sum[r]);
         }
     }
@@ -163,11 +218,16 @@ int launch_matvec(inf_ctx* ctx, const void* weights, const float* input, OutT* o
                   int out_features, long long out_stride, const char* name, const float* tail = nullptr, int tail_n = 0,
                   int tail_col0 = 0) {
     const size_t tile_bytes = (size_t)TILE_ROWS * (in_features / Q8_BLOCK_VALUES) * Q8_BLOCK_BYTES;
-    const bool tiled = out_features % TILE_ROWS == 0 && tile_bytes <= 48 * 1024 && ((uintptr_t)weights & 15) == 0;
+    const bool tiled = out_features % TILE_ROWS == 0 && tile_bytes <= 48 * 1024 && ((uintptr_t)weights & 15) == 0 &&
+                       ((uintptr_t)input & 15) == 0;
     inf_prof_scope prof(ctx, name);
     if (tiled) {
         dim3 grid(out_features / TILE_ROWS, heads, (rows + MV_ROWS - 1) / MV_ROWS);
-        INF_CUDA(ctx, inf_launch_pdl(q8_0_heads_matvec_tile_kernel<OutT>, grid, dim3(MV_WARPS * 32), tile_bytes, ctx->stream,
+        // lanes that share a weight row: as many as it has 16-quant steps, between 8 and 32
+        const int chunks = in_features / 16;
+        auto kernel = chunks > 16 ? q8_0_heads_matvec_tile_kernel<OutT, 32>
+                                  : (chunks > 8 ? q8_0_heads_matvec_tile_kernel<OutT, 16> : q8_0_heads_matvec_tile_kernel<OutT, 8>);
+        INF_CUDA(ctx, inf_launch_pdl(kernel, grid, dim3(MV_WARPS * 32), tile_bytes, ctx->stream,
                                      (const uint8_t*)weights, input, out, rows, heads, in_features, out_features,
                                      out_stride, tail, tail_n, tail_col0));
     } else {

@@ -99,6 +99,8 @@ SIGNATURES = {
     "inf_rope_slice": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F]),
     "inf_mla_kv_postprocess_append": (_I, [_P, _P, _P, _F, _F, C.POINTER(MlaPool), C.POINTER(PageTable), _I, _P, _P]),
     "inf_gqa_decode_paged": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _I, _P, _F, _P, _I]),
+    "inf_gqa_decode_paged_peers": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _I, _P, _F, _P, _I,
+                                        _P, _I]),
     "inf_gqa_decode_workspace_bytes": (C.c_size_t, [_I, _I, _I, _I, _I]),
     "inf_gqa_decode_paged_static": (_I, [_P, _P, C.POINTER(KvPool), C.POINTER(PageTable), _I, _I, _I, _I, _P, _F, _P,
                                          _I]),

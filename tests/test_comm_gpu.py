@@ -62,8 +62,9 @@ def _fused_worker(rank, world, uid_q, inboxes, res_q):
 
 
 def _fused_body(rank, world, uid_q, inboxes, res_q):
-    """The all-gather fused into the prefill kernels: every rank stores its heads into its own and, over NVLink,
-    into the peers' copies of the gathered tensor; after the barrier each copy must equal the single-GPU result."""
+    """The all-gather fused into the kernels: every rank stores its heads (prefill) or its sequences (decode) into
+    its own and, over NVLink, into the peers' copies of the gathered tensor; after the barrier each copy must equal
+    the single-GPU result."""
     import sys
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -95,14 +96,20 @@ def _fused_body(rank, world, uid_q, inboxes, res_q):
     k2 = torch.randn((1, T2, Hkv, 128), generator=g, device=be.device, dtype=torch.float16)
     v2 = torch.randn((1, T2, Hkv, 128), generator=g, device=be.device, dtype=torch.float16)
     gathered2 = torch.zeros((1, T2, Hq, 128), dtype=torch.float16, device=be.device)
+    # ---- paged GQA decode sharded by sequence: gathered [B3, Hq, 128]
+    B3 = 4
+    lens3 = np.array([700, 33, 2049, 1200], np.int32)
+    q3 = torch.randn((B3, Hq, 128), generator=g, device=be.device, dtype=torch.float16)
+    gathered3 = torch.zeros((B3, Hq, 128), dtype=torch.float16, device=be.device)
     torch.cuda.synchronize()
-    mine = (be.peer_export(gathered), be.peer_export(gathered2))
+    mine = (be.peer_export(gathered), be.peer_export(gathered2), be.peer_export(gathered3))
     for r in range(world):
         if r != rank:
             inboxes[r].put((rank, mine))
     theirs = dict(inboxes[rank].get(timeout=120) for _ in range(world - 1))
     peers = [be.peer_open(theirs[r][0]) for r in sorted(theirs)]
     peers2 = [be.peer_open(theirs[r][1]) for r in sorted(theirs)]
+    peers3 = [be.peer_open(theirs[r][2]) for r in sorted(theirs)]
     assert be.comm_barrier_is_p2p(), "the peers' flag arrays could not be mapped: the barrier fell back to NCCL"
     be.comm_barrier()            # every copy exists and is zero before anybody stores into it
     be.device_flush()
@@ -122,9 +129,22 @@ def _fused_body(rank, world, uid_q, inboxes, res_q):
     q16l = be.rope_append_gqa(q2[:, :, qb2:qe2].contiguous(), k2[:, :, kb2:ke2].contiguous(), v2[:, :, kb2:ke2].contiguous(),
                               None, pool, be.page_table(table_np, [0]))
     be.gqa_prefill_paged(q16l, pool, be.page_table(table_np, [0]), out=gathered2[:, :, qb2:qe2], peers=peers2)
+
+    from inferno_b200.sharding import shard_sequences
+    from tests.workloads import scatter_pages
+    pages3 = (lens3 + P - 1) // P
+    table3 = scatter_pages(list(pages3), int(pages3.sum()) + 5, 99)
+    pool3 = be.prepare_kv_pool(int(pages3.sum()) + 5, P, Hkv)
+    gk = torch.Generator(device=be.device).manual_seed(77)   # the same cache on every rank
+    pool3.k.normal_(0, 1, generator=gk)
+    pool3.v.normal_(0, 1, generator=gk)
+    full3 = be.gqa_decode_paged(q3, pool3, be.page_table(table3, lens3), int(lens3.max()), 512, out_dtype=torch.float16)
+    b0, b1 = shard_sequences(B3, world, rank)
+    be.gqa_decode_paged(q3[b0:b1], pool3, be.page_table(table3[b0:b1], lens3[b0:b1]), int(lens3.max()), 512,
+                        out=gathered3[b0:b1], peers=peers3)
     be.comm_barrier()
     be.device_flush()
-    ok = bool(torch.equal(gathered, full)) and bool(torch.equal(gathered2, full2))
+    ok = bool(torch.equal(gathered, full)) and bool(torch.equal(gathered2, full2)) and bool(torch.equal(gathered3, full3))
     be.comm_barrier()            # nobody unmaps a copy a peer's kernel could still be writing
     be.device_flush()
     res_q.put((rank, ok, "a gathered copy differs from the single-GPU result"))

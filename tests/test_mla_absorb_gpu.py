@@ -55,7 +55,8 @@ def test_packed_q8_heads_closed_form(be):
     np.testing.assert_allclose(orc.q8_0_heads_matvec(w, x, 2, 32, 2), want, rtol=1e-6, atol=1e-5)
 
 
-@pytest.mark.parametrize("rows,heads,fin,fout", [(1, 64, 192, 512), (3, 5, 64, 40), (9, 64, 512, 256)])
+@pytest.mark.parametrize("rows,heads,fin,fout", [(1, 64, 192, 512), (3, 5, 64, 40), (9, 64, 512, 256),
+                                                 (2, 3, 128, 64), (1, 2, 1024, 32), (5, 4, 32, 96)])
 def test_packed_q8_heads_matches_oracle(be, rows, heads, fin, fout):
     seed = SEED0 + 800 + rows
     w = q8_0_weights(heads, fout, fin, seed, 0.01)
