@@ -129,14 +129,17 @@ class GqaDecodeB32:
                 "context": "U{1024..16384} seeded", "sum_context": int(np.asarray(lens).sum()),
                 "rope_theta": cls.THETA, "output": "fp16, fp32 accumulation", "kv_bytes_per_step": int(units),
                 "l2": "inputs larger than L2 (KV bytes per step >> 126 MB)",
-                "sharding": "by sequence, 32/N per rank, output all-gathered" if strong else "by sequence"}
+                "sharding": "by sequence, 32/N per rank in blocks balanced by context length, output gathered on every rank"
+                            if strong else "by sequence"}
 
     def __init__(self, be, rank, world=1, strong=False, dist=None):
         import torch
-        from inferno_b200.sharding import shard_sequences
+        from inferno_b200.sharding import balanced_sequence_order, shard_sequences
         self.torch, self.be, self.world, self.strong = torch, be, world, strong
         all_lens = decode_lens(0 if strong else rank, self.B)
         if strong:
+            # the batch is put in an order whose equal blocks hold about the same number of cached keys
+            all_lens = all_lens[balanced_sequence_order(all_lens, world)]
             b0, b1 = shard_sequences(self.B, world, rank)
             assert self.B % world == 0, "the gather wants equal blocks"
             self.lens = all_lens[b0:b1]

@@ -86,6 +86,9 @@ struct inf_comm {
 __global__ void comm_barrier_kernel(int* mine, PeerFlags peers, int rank, int world, int* status) {
     __shared__ int e_s;
     const int r = threadIdx.x;
+    // launched as a programmatic dependent: resident while the kernel before it drains, and past this point only when
+    // that kernel has completed and its stores (into the peers' memory too) have been performed
+    inf_pdl_wait();
     if (r == 0) e_s = mine[EPOCH_SLOT] + 1;
     __syncthreads();
     const int e = e_s;
@@ -93,7 +96,6 @@ __global__ void comm_barrier_kernel(int* mine, PeerFlags peers, int rank, int wo
         __threadfence_system();
         volatile int* there = peers.of[r] + rank;
         *there = e;
-        __threadfence_system();
         volatile int* here = mine + r;
         unsigned long long t0;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -106,7 +108,9 @@ __global__ void comm_barrier_kernel(int* mine, PeerFlags peers, int rank, int wo
                 break;
             }
         }
-        __threadfence_system();
+        // what the peers stored before their flags already lies in this GPU's memory; the kernels after this one start
+        // with cold L1 caches, so a device-scope fence is all that is left to do
+        __threadfence();
     }
     __syncthreads();
     if (r == 0) mine[EPOCH_SLOT] = e;
@@ -225,7 +229,8 @@ int32_t inf_comm_barrier(inf_comm* comm) {
     if (!comm) return INF_E_ARG;
     inf_ctx* ctx = comm->ctx;
     if (comm->p2p) {
-        comm_barrier_kernel<<<1, 32, 0, ctx->stream>>>(comm->flags, comm->peers, comm->rank, comm->nranks, ctx->status);
+        INF_CUDA(ctx, inf_launch_pdl(comm_barrier_kernel, dim3(1), dim3(32), 0, ctx->stream, comm->flags, comm->peers,
+                                     comm->rank, comm->nranks, ctx->status));
         INF_LAUNCH_CHECK(ctx, "comm_barrier_kernel");
         return INF_OK;
     }

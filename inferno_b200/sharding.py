@@ -31,6 +31,44 @@ def shard_sequences(batch: int, world: int, rank: int):
     return begin, begin + base + (1 if rank < extra else 0)
 
 
+def balanced_sequence_order(lengths, world: int):
+    """Order of a batch in which the contiguous blocks of shard_sequences hold about the same number of cached keys.
+
+    Decode time is proportional to the keys a rank streams, so a batch split in arrival order leaves every rank
+    waiting for the one that drew the long contexts.  Longest first, each sequence goes to the rank with the fewest
+    keys so far that still has room in its block, then single exchanges with the fullest rank; the result lists rank 0's sequences, then rank 1's, and so on."""
+    n = len(lengths)
+    if world <= 0:
+        raise ValueError(f"bad world size {world}")
+    room = [shard_sequences(n, world, r)[1] - shard_sequences(n, world, r)[0] for r in range(world)]
+    load = [0] * world
+    owned = [[] for _ in range(world)]
+    for i in sorted(range(n), key=lambda i: (-int(lengths[i]), i)):
+        r = min((r for r in range(world) if len(owned[r]) < room[r]), key=lambda r: (load[r], r))
+        owned[r].append(i)
+        load[r] += int(lengths[i])
+    # exchange single sequences between the fullest rank and the others while that lowers the larger of the two loads
+    for _ in range(4 * n):
+        hi = max(range(world), key=lambda r: (load[r], -r))
+        best = None
+        for lo in range(world):
+            if lo == hi:
+                continue
+            for a in owned[hi]:
+                for b in owned[lo]:
+                    d = int(lengths[a]) - int(lengths[b])
+                    if d > 0 and load[lo] + d < load[hi] and (best is None or max(load[hi] - d, load[lo] + d) < best[0]):
+                        best = (max(load[hi] - d, load[lo] + d), lo, a, b, d)
+        if best is None:
+            break
+        _, lo, a, b, d = best
+        owned[hi][owned[hi].index(a)] = b
+        owned[lo][owned[lo].index(b)] = a
+        load[hi] -= d
+        load[lo] += d
+    return [i for r in range(world) for i in sorted(owned[r])]
+
+
 def allgather_heads(local_out: torch.Tensor, group=None) -> torch.Tensor:
     """local_out [tokens, heads/N, dim] on every rank -> [tokens, heads, dim] (heads in rank order).
 

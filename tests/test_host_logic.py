@@ -117,6 +117,23 @@ def test_sharding_helpers():
     assert cover == [(0, 3), (3, 6), (6, 8), (8, 10)]
 
 
+def test_balanced_sequence_order_evens_out_the_keys_per_rank():
+    from inferno_b200.sharding import balanced_sequence_order, shard_sequences
+    rng = np.random.RandomState(5)
+    for world in (1, 2, 4, 8):
+        lens = rng.randint(1024, 16385, size=32)
+        order = balanced_sequence_order(lens, world)
+        assert sorted(order) == list(range(32))          # a permutation
+        loads = [int(lens[order[slice(*shard_sequences(32, world, r))]].sum()) for r in range(world)]
+        plain = [int(lens[slice(*shard_sequences(32, world, r))].sum()) for r in range(world)]
+        assert max(loads) <= max(plain)
+        assert max(loads) - min(loads) <= 16384 // 4      # far inside one long sequence
+    # ragged block sizes keep their sizes
+    order = balanced_sequence_order([5, 1, 9, 7, 3, 8, 2, 6, 4, 10], 4)
+    assert sorted(order) == list(range(10)) and len(order) == 10
+    assert balanced_sequence_order([], 3) == []
+
+
 def test_trim_returns_pages_below_the_window_and_keeps_positions():
     """The sliding-window ring on pages: a 512-token window over a growing sequence holds a bounded number of pages
     (the reference's sliding cache is 512 slots, metal/f16_attention.rs:120-210)."""
