@@ -12,12 +12,15 @@ device copy of the step's Q/K/V and a device -> host read of the output inside t
 Other workloads of the path are measured in the same run and reported under "workloads".
 
 With N > 1 (torchrun, one rank per GPU) the headline shards by sequence with fixed work per GPU -- every rank
-owns its own batch of 32 and its pages, no data-path collective -- and `value` is the sum over ranks divided by
-the slowest rank's time (weak scaling).  The same run also measures, under "workloads", the strong-scaled forms
-of the path: the batch of 32 split 32/N sequences per rank with the [32, 48, 128] output all-gathered, and both
-prefills head-sharded with the all-gather of the attention output inside the step.  Those gathers go through
-the library's own collective (inf_allgather_heads: NCCL behind the C ABI); torch.distributed only carries the
-rendezvous, the barriers and the reductions of the timings.
+owns its own batch of 32 (the same 32 context lengths, its own pages), no data-path collective -- and `value` is
+the sum over ranks divided by the slowest rank's time (weak scaling).  The same run also measures, under
+"workloads", the strong-scaled forms of the path: the batch of 32 split 32/N sequences per rank (blocks balanced
+by context length) with the [32, 48, 128] output gathered on every rank, and both prefills head-sharded with the
+gather of the attention output inside the step.  The gather is fused into the kernels (their last stores go into
+every rank's copy of the gathered tensor over NVLink, inf_comm_barrier ends the step); the same steps with the
+library's NCCL all-gather (inf_allgather_heads) and with no exchange at all are timed beside it under
+"collective".  torch.distributed only carries the rendezvous, the peer-memory handles, the barriers and the
+reductions of the timings.
 
 Every timed figure is the median of several regions of exactly K steps, each region bracketed by a barrier and a
 synchronize on both sides and taken as the maximum over ranks.
@@ -111,7 +114,7 @@ def decode_lens(rank: int, batch: int = 32):
 
 class GqaDecodeB32:
     """Paged GQA decode, batch 32 (the third benchmark configuration).  Weak scaling: every rank owns its own batch
-    of 32 (different seeded lengths per rank).  Strong scaling (`strong=True`): rank 0's batch of 32 is split into
+    of 32 (the same seeded context lengths on every rank, its own pages and values).  Strong scaling (`strong=True`): rank 0's batch of 32 is split into
     32/N sequences per rank and the [32, 48, 128] fp16 output is gathered on every rank: the combine kernel stores
     each row into every rank's copy (peer stores), and inf_comm_barrier ends the step."""
     name = "gqa_decode_b32"
@@ -136,7 +139,9 @@ class GqaDecodeB32:
         import torch
         from inferno_b200.sharding import balanced_sequence_order, shard_sequences
         self.torch, self.be, self.world, self.strong = torch, be, world, strong
-        all_lens = decode_lens(0 if strong else rank, self.B)
+        # weak scaling keeps the work per GPU fixed: every rank draws the same 32 context lengths (its pages, page
+        # order and values are its own)
+        all_lens = decode_lens(0, self.B)
         if strong:
             # the batch is put in an order whose equal blocks hold about the same number of cached keys
             all_lens = all_lens[balanced_sequence_order(all_lens, world)]
@@ -185,6 +190,7 @@ class GqaDecodeB32:
             self.n_variants = 2
             self.full = [torch.zeros((self.B, self.Hq, self.D), dtype=torch.float16, device=be.device) for _ in range(2)]
             self.peers = [map_peers(be, dist, t) for t in self.full]
+            use_fused_exchange(self, be)
             self.mine = [t[b0:b1] for t in self.full]
         result = self.gathered if self.collective else self.out
         self.hout = torch.empty(result.shape, dtype=torch.float16).pin_memory()
@@ -687,6 +693,7 @@ class GqaPrefill2k:
         if world > 1:
             self.full = [torch.zeros((1, self.T, self.Hq, self.D), dtype=torch.float16, device=be.device) for _ in range(2)]
             self.peers = [map_peers(be, dist, t) for t in self.full]
+            use_fused_exchange(self, be)
             self.mine = [t[:, :, rank * self.hq_local:(rank + 1) * self.hq_local] for t in self.full]
         q, k, v = self.sets[0][2:]
         self.hq, self.hk, self.hv = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
@@ -830,6 +837,7 @@ class MlaPrefill32k:
         if world > 1:
             self.full = [torch.zeros((self.T, self.H, 128), dtype=torch.float16, device=be.device) for _ in range(2)]
             self.peers = [map_peers(be, dist, t) for t in self.full]
+            use_fused_exchange(self, be)
             self.mine = [t[:, rank * hl:(rank + 1) * hl] for t in self.full]
         self.host = [t.cpu().pin_memory() for t in (self.q, self.kn, self.kr, self.v)]
         self.hout = torch.empty((self.gathered if world > 1 else self.out).shape, dtype=torch.float16).pin_memory()
@@ -922,12 +930,32 @@ class MlaPrefill32k:
 
 def map_peers(be, dist, tensor):
     """Every rank exports `tensor` (its copy of a gathered output) and maps the other ranks' copies: the device
-    addresses, in rank order without this rank, that the fused-gather prefill stores into.  torch.distributed only
-    carries the 72-byte handles."""
+    addresses, in rank order without this rank, that the fused gather stores into.  torch.distributed only carries
+    the 72-byte handles.  None on every rank when any rank could not map a peer (no peer access between the GPUs):
+    the workload then gathers with the library's NCCL collective instead."""
+    import torch
     world, rank = dist.get_world_size(), dist.get_rank()
     handles = [None] * world
-    dist.all_gather_object(handles, be.peer_export(tensor))
-    return [be.peer_open(handles[r]) for r in range(world) if r != rank]
+    mapped, ok = None, 1
+    try:
+        dist.all_gather_object(handles, be.peer_export(tensor))
+        mapped = [be.peer_open(handles[r]) for r in range(world) if r != rank]
+    except Exception as e:  # InfernoError from the export / open calls
+        sys.stderr.write(f"rank {rank}: peer mapping failed ({e}); gathering with NCCL\n")
+        ok = 0
+    agreed = torch.tensor([ok], dtype=torch.int32, device="cuda")
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+    return mapped if int(agreed.item()) == 1 else None
+
+
+def use_fused_exchange(wl, be):
+    """Called by the sharded workloads after map_peers: falls back to the NCCL gather when the peers are not mapped."""
+    if any(p is None for p in wl.peers) or not wl.peers:
+        wl.exchange = "nccl"
+        wl.fused_ok = False
+    else:
+        wl.exchange = "fused"
+        wl.fused_ok = True
 
 
 def make_workload(name, be, rank, world=1, tokens=0, dist=None):
@@ -995,6 +1023,10 @@ class GraphedStep:
 def timed(torch, dist, world, fn, steps, warmup, regions=1):
     """W warm-up steps, then `regions` regions of exactly K steps, each between barrier + synchronize, device time
     by CUDA events.  Returns (median over regions of the max over ranks, per-rank medians, all region maxima)."""
+    if world > 1:
+        # the ranks enter the warm-up together: a step that ends in the peer-flag barrier waits at most two seconds
+        torch.cuda.synchronize()
+        dist.barrier()
     for _ in range(warmup):
         fn()
     mine = []
@@ -1135,11 +1167,16 @@ def measure(be, torch, dist, world, rank, wl, steps, warmup, peaks, with_cpu, pr
                                 "over NVLink, tile by tile) and the step ends with inf_comm_barrier; beside it, the same "
                                 "step with inf_allgather_heads (NCCL) after the kernel, and with no exchange at all")
                 coll["barrier"] = "peer-flag kernel" if be.comm_barrier_is_p2p() else "nccl all-reduce"
-                coll["ms_per_step_fused_gather"] = eager_ms("fused")
+                fused_ok = getattr(wl, "fused_ok", True)
+                if fused_ok:
+                    coll["ms_per_step_fused_gather"] = eager_ms("fused")
+                else:
+                    coll["fused_gather"] = "unavailable: the peers' memory could not be mapped; the step gathers with NCCL"
                 coll["ms_per_step_nccl_allgather"] = eager_ms("nccl")
                 coll["ms_per_step_without"] = eager_ms("none")
-                wl.exchange = "fused"
-                coll["ms_exchange_fused"] = coll["ms_per_step_fused_gather"] - coll["ms_per_step_without"]
+                wl.exchange = "fused" if fused_ok else "nccl"
+                if fused_ok:
+                    coll["ms_exchange_fused"] = coll["ms_per_step_fused_gather"] - coll["ms_per_step_without"]
                 coll["ms_exchange_nccl"] = coll["ms_per_step_nccl_allgather"] - coll["ms_per_step_without"]
             else:
                 coll["what"] = "inf_allgather_heads (NCCL all-gather behind the C ABI) after the kernels"

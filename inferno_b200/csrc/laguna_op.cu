@@ -6,6 +6,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* pool, const inf_page_table* table,
                           int q_heads, int max_len, int split_chunk, int sliding_window, const float* gate,
@@ -243,6 +244,182 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
     }
 }
 
+// The same split with the rows brought in by the copy engine instead of by the threads' own loads: when pages hold a
+// multiple of 16 keys, 16 consecutive keys of a head are one contiguous run of K rows and one of V rows, and a producer
+// thread keeps a ring of such tiles full with bulk copies (cp.async.bulk) while four consumer warps -- 16 lane groups,
+// one key each per tile -- read their slices from shared memory.  The bytes in flight no longer depend on registers.
+#ifndef INF_GLM_RING_STAGES
+#define INF_GLM_RING_STAGES 4
+#define INF_GLM_RING_CTAS 3
+#endif
+// Waves of resident CTAs the grid aims at.  Measured on the 64-head, 4 095-key case (kernel time): four stages, three
+// CTAs per SM, two waves 50.0 us; one wave 48.8 us; three waves 53.6 us; six stages, two CTAs per SM 51.5 us; eight
+// stages, one CTA per SM 65.1 us.
+#ifndef INF_GLM_RING_WAVES
+#define INF_GLM_RING_WAVES 1
+#endif
+constexpr int GR_KEYS = 16;
+constexpr int GR_STAGES = INF_GLM_RING_STAGES;
+constexpr int GR_CONSUMERS = 128;
+constexpr int GR_THREADS = GR_CONSUMERS + 32;
+
+template <int KC, int VC>
+__global__ void __launch_bounds__(GR_THREADS, INF_GLM_RING_CTAS)
+glm_paged_decode_ring_kernel(const float* __restrict__ q, const __half* __restrict__ pk, const __half* __restrict__ pv,
+                             float* __restrict__ part_acc, float* __restrict__ part_ml, int batch, int heads, int past,
+                             int page_size, int keys_per_split, int splits, int* __restrict__ status) {
+    constexpr int dim = KC * 64, vdim = VC * 64;
+    constexpr int K_BYTES = GR_KEYS * dim * 2, V_BYTES = GR_KEYS * vdim * 2, STAGE_BYTES = K_BYTES + V_BYTES;
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ uint64_t full[GR_STAGES], empty[GR_STAGES];
+    __shared__ float sm[GR_KEYS], sl[GR_KEYS];
+    __shared__ float sacc[8][vdim];
+    const int split = blockIdx.x, row = blockIdx.y, head = row % heads, b = row / heads;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int k_begin = split * keys_per_split, k_end = min(past, k_begin + keys_per_split);
+    const int n_tiles = k_end > k_begin ? (k_end - k_begin + GR_KEYS - 1) / GR_KEYS : 0;
+    if (tid == 0) {
+        for (int i = 0; i < GR_STAGES; ++i) {
+            inf::mbar_init(&full[i], 1);
+            inf::mbar_init(&empty[i], GR_CONSUMERS / 32);
+        }
+        inf::mbar_fence_init();
+    }
+    __syncthreads();
+    const size_t row_base = ((size_t)b * heads + head) * page_size;  // + page * batch * heads * page_size
+    const size_t page_stride = (size_t)batch * heads * page_size;
+    float acc[VC][8];
+#pragma unroll
+    for (int c = 0; c < VC; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+    float m = NEG_BIG, l = 0.f;
+    const int group = tid >> 3, gl = tid & 7;
+    if (warp == GR_CONSUMERS / 32) {
+        // ---- producer: one thread; a 16-key tile never straddles a page (pages hold a multiple of 16 keys and the
+        //      splits start at multiples of 16)
+        if (lane == 0) {
+            for (int t = 0; t < n_tiles; ++t) {
+                const int s = t % GR_STAGES;
+                if (t >= GR_STAGES && !inf::mbar_wait(&empty[s], ((uint32_t)(t / GR_STAGES - 1)) & 1u)) {
+                    atomicOr(status, INF_STATUS_WAIT_TIMEOUT);
+                    break;
+                }
+                const int key0 = k_begin + t * GR_KEYS;
+                const int valid = min(GR_KEYS, k_end - key0);
+                const int page = key0 / page_size, off = key0 - page * page_size;
+                const size_t r = (size_t)page * page_stride + row_base + off;
+                uint8_t* dst = ring + s * STAGE_BYTES;
+                inf::mbar_arrive_expect_tx(&full[s], (uint32_t)valid * (dim + vdim) * 2);
+                inf::bulk_load_1d(dst, pk + r * dim, (uint32_t)valid * dim * 2, &full[s]);
+                inf::bulk_load_1d(dst + K_BYTES, pv + r * vdim, (uint32_t)valid * vdim * 2, &full[s]);
+            }
+        }
+    } else {
+        const float scale = 1.0f / sqrtf((float)dim);
+        float qf[KC][8];
+#pragma unroll
+        for (int c = 0; c < KC; ++c)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qf[c][i] = q[(size_t)row * dim + (c * 8 + gl) * 8 + i] * scale;
+        const unsigned gmask = 0xffu << (tid & 24);  // the eight lanes of this group inside their warp
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int s = t % GR_STAGES;
+            if (ok && !inf::mbar_wait(&full[s], ((uint32_t)(t / GR_STAGES)) & 1u)) ok = false;
+            const int key = k_begin + t * GR_KEYS + group;
+            if (ok && key < k_end) {
+                const uint8_t* krow = ring + s * STAGE_BYTES + group * (dim * 2) + gl * 16;
+                const uint8_t* vrow = ring + s * STAGE_BYTES + K_BYTES + group * (vdim * 2) + gl * 16;
+                float dot = 0.f;
+#pragma unroll
+                for (int c = 0; c < KC; ++c) {
+                    const uint4 kraw = *reinterpret_cast<const uint4*>(krow + c * 128);
+                    const __half2* h = reinterpret_cast<const __half2*>(&kraw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __half22float2(h[i]);
+                        dot = fmaf(qf[c][2 * i], f.x, dot);
+                        dot = fmaf(qf[c][2 * i + 1], f.y, dot);
+                    }
+                }
+                // only the eight lanes of this key's group take part: in the last tile some groups have no key
+                dot += __shfl_xor_sync(gmask, dot, 1);
+                dot += __shfl_xor_sync(gmask, dot, 2);
+                dot += __shfl_xor_sync(gmask, dot, 4);
+                const float mn = fmaxf(m, dot);
+                const float rs = l == 0.f ? 0.f : expf(m - mn);
+                const float w = expf(dot - mn);
+                l = l * rs + w;
+                m = mn;
+#pragma unroll
+                for (int c = 0; c < VC; ++c) {
+                    const uint4 vraw = *reinterpret_cast<const uint4*>(vrow + c * 128);
+                    const __half2* h = reinterpret_cast<const __half2*>(&vraw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __half22float2(h[i]);
+                        acc[c][2 * i] = fmaf(acc[c][2 * i], rs, w * f.x);
+                        acc[c][2 * i + 1] = fmaf(acc[c][2 * i + 1], rs, w * f.y);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) inf::mbar_arrive(&empty[s]);  // the warp's four groups have read the tile
+        }
+        if (!ok && lane == 0) atomicOr(status, INF_STATUS_WAIT_TIMEOUT);
+    }
+    // merge the 16 groups of the CTA, 8 at a time through shared memory (the producer warp only keeps the barriers company)
+    const bool consumer = tid < GR_CONSUMERS;
+    if (consumer && gl == 0) {
+        sm[group] = m;
+        sl[group] = l;
+    }
+    __syncthreads();
+    float M = NEG_BIG;
+    for (int g = 0; g < GR_KEYS; ++g)
+        if (sl[g] > 0.f) M = fmaxf(M, sm[g]);
+    float L = 0.f;
+    for (int g = 0; g < GR_KEYS; ++g)
+        if (sl[g] > 0.f) L += sl[g] * expf(sm[g] - M);
+    const float mine = (consumer && l > 0.f) ? expf(m - M) : 0.f;
+    constexpr int PER = (vdim + GR_CONSUMERS - 1) / GR_CONSUMERS;
+    float total[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) total[i] = 0.f;
+    for (int round = 0; round < GR_KEYS / 8; ++round) {
+        __syncthreads();
+        if (consumer && group / 8 == round) {
+#pragma unroll
+            for (int c = 0; c < VC; ++c)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sacc[group & 7][(c * 8 + gl) * 8 + i] = acc[c][i] * mine;
+        }
+        __syncthreads();
+        if (consumer) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = tid + i * GR_CONSUMERS;
+                if (d < vdim)
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) total[i] += sacc[g][d];
+            }
+        }
+    }
+    const size_t prow = (size_t)row * splits + split;
+    if (consumer) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = tid + i * GR_CONSUMERS;
+            if (d < vdim) part_acc[prow * vdim + d] = total[i];
+        }
+    }
+    if (tid == 0) {
+        part_ml[prow * 2] = M;
+        part_ml[prow * 2 + 1] = L;
+    }
+}
+
 // Merge of the splits plus the current token (its key and value in f32).  One CTA of 256 threads per (batch, head).
 __global__ void __launch_bounds__(256)
 glm_paged_decode_merge_kernel(const float* __restrict__ q, const float* __restrict__ cur_k,
@@ -280,8 +457,9 @@ template <int KC, int VC>
 int launch_glm_split(inf_ctx* ctx, const float* q, const void* pk, const float* cur_k, const void* pv, const float* cur_v,
                      int batch, int heads, int past, int page_size, float* out) {
     const int rows = batch * heads;
+    const bool use_ring = page_size % GR_KEYS == 0;
     // aim at two full waves of the CTAs an SM holds, never more CTAs than that
-    int splits = (2 * INF_GLM_CTAS * ctx->sm_count) / rows;
+    int splits = ((use_ring ? INF_GLM_RING_WAVES * INF_GLM_RING_CTAS : 2 * INF_GLM_CTAS) * ctx->sm_count) / rows;
     splits = std::max(1, std::min(splits, (past + 255) / 256));
     const int keys_per_split = ((past + splits - 1) / splits + GS_GROUPS - 1) / GS_GROUPS * GS_GROUPS;
     splits = (past + keys_per_split - 1) / keys_per_split;
@@ -290,7 +468,19 @@ int launch_glm_split(inf_ctx* ctx, const float* q, const void* pk, const float* 
     if (rc != INF_OK) return rc;
     float* part_acc = (float*)ctx->workspace;
     float* part_ml = (float*)((char*)ctx->workspace + acc_bytes);
-    {
+    if (use_ring) {
+        constexpr size_t ring_bytes = (size_t)GR_STAGES * GR_KEYS * (KC + VC) * 64 * 2;
+        constexpr uint32_t attr_bit = 1u << (16 + (KC * 4 + VC) % 12);  // (4,4) (3,2) (4,2) (2,2) (1,1): bits 24 18 22 26 21
+        if (!(ctx->func_attr_done & attr_bit)) {
+            INF_CUDA(ctx, cudaFuncSetAttribute(glm_paged_decode_ring_kernel<KC, VC>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes));
+            ctx->func_attr_done |= attr_bit;
+        }
+        inf_prof_scope prof(ctx, "glm_paged_decode_split_kernel");
+        glm_paged_decode_ring_kernel<KC, VC><<<dim3(splits, rows), GR_THREADS, ring_bytes, ctx->stream>>>(
+            q, (const __half*)pk, (const __half*)pv, part_acc, part_ml, batch, heads, past, page_size, keys_per_split, splits,
+            ctx->status);
+    } else {
         inf_prof_scope prof(ctx, "glm_paged_decode_split_kernel");
         glm_paged_decode_split_kernel<KC, VC><<<dim3(splits, rows), GS_THREADS, 0, ctx->stream>>>(
             q, (const __half*)pk, (const __half*)pv, part_acc, part_ml, batch, heads, past, page_size, keys_per_split, splits);

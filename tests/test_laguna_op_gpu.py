@@ -100,11 +100,13 @@ def test_decode_step_matches_nonuniform_cpu_reference(be, sliding, q_heads, toke
 
 
 @pytest.mark.parametrize("B,H,Dk,Dv,P,past", [
-    (2, 64, 256, 256, 128, 300),    # the key-split kernel, two splits
+    (2, 64, 256, 256, 128, 300),    # the key-split kernel (rows through the shared-memory ring), two splits
     (1, 64, 256, 256, 64, 4095),    # the GLM expanded layout at the reference kernel's limit of 4096 keys
     (3, 5, 192, 128, 16, 1000),     # 192 / 128 dims, ragged last split
     (2, 4, 96, 32, 16, 700),        # dims that are not multiples of 64: the one-CTA-per-row kernel
     (1, 8, 256, 256, 128, 100),     # too few keys to split
+    (2, 8, 128, 128, 24, 500),      # pages that do not hold a multiple of 16 keys: the threads load the rows themselves
+    (1, 3, 128, 128, 16, 2000),     # one key per 16-key page tile short of a multiple: ragged last tile of the ring
 ])
 def test_glm_paged_f16_decode_sizes(be, B, H, Dk, Dv, P, past):
     rng = np.random.default_rng(past)
