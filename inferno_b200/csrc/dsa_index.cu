@@ -556,7 +556,7 @@ dsa_topk_kernel(const float* __restrict__ scores, unsigned* __restrict__ out_ids
         const int ca = __popc(above_mask), ct = __popc(tie_mask);
         int ex_a, ex_t, round_above, round_ties;
         scan_counts(ca, ct, ex_a, ex_t, round_above, round_ties);
-        const int ties_open = max(ties_wanted - ties_before, 0);     // ties this round may still take
+        const int ties_open = max(ties_wanted - ties_before, 0);     // ties this pass may still take
         const int quota = max(0, min(ct, ties_open - ex_t));
         unsigned take = tie_mask;
         if (quota < ct) {  // the lowest `quota` ids of this thread's ties

@@ -651,7 +651,14 @@ int inf_gqa_decode_launch(inf_ctx* ctx, const void* q_f16, const inf_kv_pool* po
     p.part_acc = (float*)scratch;
     p.part_ml = p.part_acc + (size_t)table->batch * max_chunks * q_heads * D;
     p.max_chunks = max_chunks;
+    // A CTA streams a run of up to four chunks (2 048 keys), which keeps its ring full across chunk boundaries; a small
+    // batch gets shorter runs, so that the launch still has about two waves of CTAs to spread over the SMs.
     p.chunks_per_cta = MAX_CHUNK / split_chunk;
+    {
+        const long long upper = (long long)table->batch * pool->kv_heads * max_chunks;  // chunks if every sequence were full
+        const long long two_waves = 2LL * 2 * ctx->sm_count;
+        while (p.chunks_per_cta > 1 && upper / p.chunks_per_cta < two_waves) p.chunks_per_cta >>= 1;
+    }
     p.status = ctx->status;
     p.drop_tile = ctx->debug_drop_tile;
     ctx->debug_drop_tile = -1;  // one launch only

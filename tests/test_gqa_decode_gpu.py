@@ -232,7 +232,7 @@ def test_bounded_wait_gives_up_and_the_context_survives(be):
     table = be.page_table(np.arange(12, dtype=np.int32)[None], [180])
     good = be.gqa_decode_paged(q, pool, table, max_len=180, split_chunk=64)
     be.device_flush()
-    be._check(be._lib.inf_debug_drop_next_load(be._ctx, 1))  # the second 64-key tile of CTA (0, 0, 0) never lands
+    be._check(be._lib.inf_debug_drop_next_load(be._ctx, 0))  # the first 64-key tile of CTA (0, 0, 0) never lands
     t0 = time.time()
     be.gqa_decode_paged(q, pool, table, max_len=180, split_chunk=64)
     with pytest.raises(InfernoError) as e:
