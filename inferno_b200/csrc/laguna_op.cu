@@ -252,12 +252,10 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
 #define INF_GLM_RING_STAGES 4
 #define INF_GLM_RING_CTAS 3
 #endif
-// Waves of resident CTAs the grid aims at.  Measured on the 64-head, 4 095-key case (kernel time): four stages, three
-// CTAs per SM, two waves 50.0 us; one wave 48.8 us; three waves 53.6 us; six stages, two CTAs per SM 51.5 us; eight
-// stages, one CTA per SM 65.1 us.
-#ifndef INF_GLM_RING_WAVES
-#define INF_GLM_RING_WAVES 1
-#endif
+// How many CTAs the ring form launches.  Measured on the 64-head, 4 095-key case (kernel time; four stages, up to
+// three CTAs per SM): 2 pieces per head (128 CTAs) 64.4 us, 3 (192) 52.1 us, 4 (256) 46.5-47.1 us, 5 (320) 47.2 us,
+// 6 (384) 48.4 us, 7 for most heads (444, every slot filled) 51.0 us, 13 (832, two waves) 50.0 us; at 4 pieces a ring
+// of three, five or six stages is within 1 us.  The grid therefore aims at seven CTAs per four SMs.
 constexpr int GR_KEYS = 16;
 constexpr int GR_STAGES = INF_GLM_RING_STAGES;
 constexpr int GR_CONSUMERS = 128;
@@ -458,8 +456,8 @@ int launch_glm_split(inf_ctx* ctx, const float* q, const void* pk, const float* 
                      int batch, int heads, int past, int page_size, float* out) {
     const int rows = batch * heads;
     const bool use_ring = page_size % GR_KEYS == 0;
-    // aim at two full waves of the CTAs an SM holds, never more CTAs than that
-    int splits = ((use_ring ? INF_GLM_RING_WAVES * INF_GLM_RING_CTAS : 2 * INF_GLM_CTAS) * ctx->sm_count) / rows;
+    // the form whose threads load the rows themselves aims at two full waves of the CTAs an SM holds
+    int splits = use_ring ? (7 * ctx->sm_count / 4 + rows / 2) / rows : (2 * INF_GLM_CTAS * ctx->sm_count) / rows;
     splits = std::max(1, std::min(splits, (past + 255) / 256));
     const int keys_per_split = ((past + splits - 1) / splits + GS_GROUPS - 1) / GS_GROUPS * GS_GROUPS;
     splits = (past + keys_per_split - 1) / keys_per_split;
