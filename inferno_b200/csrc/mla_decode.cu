@@ -38,6 +38,9 @@ constexpr int NUM_THREADS = 192;
 constexpr float M_INIT = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr uint32_t TMEM_COLS = 512;
+#ifndef INF_MLA_PREFETCH_PAGES
+#define INF_MLA_PREFETCH_PAGES 1  // pages of a CTA's range requested into L2 before the dependent-launch wait
+#endif
 constexpr uint32_t COL_O = 0, COL_S = 256, COL_Q = 320;  // O 256 columns, S 64, Q 144 (each on both lane halves)
 constexpr int STAGES = 3;
 constexpr int GATHER_UNIT = 64;  // the gather form splits the row list in units of 64 rows: one full tile per unit
@@ -107,30 +110,15 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int kp_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
     if (tid == 0 && p.kprof && kp_cta < 256) p.kprof[64 + kp_cta * 2] = kp_t0;
 #endif
-    inf_pdl_wait();  // the appended row and the query come from kernels earlier in the stream
-    inf_pdl_release();
+    // Everything that needs nothing from the kernels before this one comes first, so that under a programmatic
+    // dependent launch it runs while they finish: barriers, TMEM, descriptors -- and a request to bring this CTA's
+    // pages into L2.  The request is a hint computed from the length as it reads now: pages already cached never
+    // change, and a page the append kernel is still writing is coherent in L2, so a wrong guess costs nothing.
     const int split = blockIdx.x;
     const int t = blockIdx.y % p.tokens, hb = blockIdx.y / p.tokens;
     const int b = blockIdx.z;
-    const int seq_rows = p.lens[b] + t + 1;                     // rows visible to this query token
-    int kv_len = GATHER ? p.sel_counts[b] : seq_rows;  // keys this call attends to
-    if (GATHER && kv_len > p.sel_stride) {  // a count beyond the list's row is cut to the row and reported
-        kv_len = p.sel_stride;
-        if (tid == 0 && split == 0) atomicOr(p.status, INF_STATUS_BAD_LEN);
-    }
-    // this CTA's keys: rows [row_begin, row_end) of the sequence (contiguous form: whole pages) or of the list
-    const int unit = GATHER ? GATHER_UNIT : PAGE;
-    int u_begin, u_end;
-    split_range((kv_len + unit - 1) / unit, p.n_splits, split, u_begin, u_end);
-    const int row_begin = u_begin * unit, row_end = min(kv_len, u_end * unit);
-    const int pg_begin = row_begin / PAGE;           // contiguous form only
-    const int n = (row_end - row_begin + PAGE - 1) / PAGE;  // 64-row tiles
-    if (n <= 0) return;
-    if ((smem_u32(smem) & 1023u) != 0) {
-        if (tid == 0) atomicOr(p.status, INF_STATUS_BAD_SMEM);
-        return;
-    }
-    if (tid == 0) {
+    const bool smem_ok = (smem_u32(smem) & 1023u) == 0;
+    if (tid == 0 && smem_ok) {
         mbar_init(q_full, 128);
         mbar_init(q_landed, 1);
         for (int i = 0; i < STAGES; ++i) {
@@ -147,17 +135,51 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
+    if (warp == 4) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_kv);
+        }
+        const int guess_pages = GATHER ? 0 : (p.lens[b] + t + 1 + PAGE - 1) / PAGE;
+        if (guess_pages > 0) {
+            int g_begin, g_end;
+            split_range(guess_pages, p.n_splits, split, g_begin, g_end);
+            for (int slot = g_begin + lane; slot < min(g_end, g_begin + INF_MLA_PREFETCH_PAGES) && slot < p.max_pages; slot += 32) {
+                const int page = p.pages[(long long)b * p.max_pages + slot];
+                if (page >= 0 && page < p.num_pages)
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.rows + (size_t)page * PAGE * ROW),
+                                 "r"((uint32_t)TILE_BYTES)
+                                 : "memory");
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
+    inf_pdl_wait();  // the appended row and the query come from kernels earlier in the stream
+    inf_pdl_release();
+    const int seq_rows = p.lens[b] + t + 1;                     // rows visible to this query token
+    int kv_len = GATHER ? p.sel_counts[b] : seq_rows;  // keys this call attends to
+    if (GATHER && kv_len > p.sel_stride) {  // a count beyond the list's row is cut to the row and reported
+        kv_len = p.sel_stride;
+        if (tid == 0 && split == 0) atomicOr(p.status, INF_STATUS_BAD_LEN);
+    }
+    // this CTA's keys: rows [row_begin, row_end) of the sequence (contiguous form: whole pages) or of the list
+    const int unit = GATHER ? GATHER_UNIT : PAGE;
+    int u_begin, u_end;
+    split_range((kv_len + unit - 1) / unit, p.n_splits, split, u_begin, u_end);
+    const int row_begin = u_begin * unit, row_end = min(kv_len, u_end * unit);
+    const int pg_begin = row_begin / PAGE;           // contiguous form only
+    const int n = (row_end - row_begin + PAGE - 1) / PAGE;  // 64-row tiles
+    if (!smem_ok && tid == 0) atomicOr(p.status, INF_STATUS_BAD_SMEM);
+    const bool active = n > 0 && smem_ok;  // a CTA with nothing to do only gives its TMEM back
     KP_MARK(0);
 
-    if (warp == 4) {
+    if (!active) {
+    } else if (warp == 4) {
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_kv);
             // Q first, into the last ring stage: it is needed before any page and must not queue behind them
             mbar_arrive_expect_tx(q_landed, TILE_BYTES);
 #pragma unroll
