@@ -488,6 +488,39 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             // and the values are bounded by the largest cached latent
             const float inv_l = 1.0f / l;
             __half* dst = p.part_acc + prow * LAT + (lane >> 4) * 256;
+            if (hb * HB + HB <= p.heads) {
+                // A whole block of 64 heads: its partial rows are one contiguous 64 KB run.  Each thread parks its
+                // half row in the first ring stage (every page has been consumed), 16-byte chunks XORed with the row
+                // so that the eight rows of a store phase fall on different banks, and the warp then writes its own
+                // sixteen rows back out as whole 512-byte runs.
+                uint8_t* stage = sKV + (size_t)(warp * 16) * (LAT * 2);
+                const int lr = lane & 15;
+#pragma unroll
+                for (int c = 0; c < 256 / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(tbase + lane_addr + COL_O + c * 32, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                        v.y = pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                        v.z = pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                        v.w = pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                        const int chunk = (lane >> 4) * 32 + c * 4 + (i >> 3);  // 16-byte chunk of the 1 KB row
+                        *reinterpret_cast<uint4*>(stage + lr * (LAT * 2) + ((chunk ^ (lr & 7)) << 4)) = v;
+                    }
+                }
+                __syncwarp();
+                const long long prow_w = ((((long long)b * p.tokens + t) * p.n_splits + split) * p.heads) + hb * HB + warp * 16;
+                uint4* out16 = reinterpret_cast<uint4*>(p.part_acc + prow_w * LAT);
+#pragma unroll 4
+                for (int it = 0; it < 32; ++it) {  // 16 rows x 64 chunks, 32 chunks (half a row) per step
+                    const int r16 = it >> 1, chunk = (it & 1) * 32 + lane;
+                    out16[r16 * 64 + chunk] =
+                        *reinterpret_cast<const uint4*>(stage + r16 * (LAT * 2) + ((chunk ^ (r16 & 7)) << 4));
+                }
+            } else
 #pragma unroll
             for (int c = 0; c < 256 / 32; ++c) {
                 uint32_t o[32];
