@@ -553,12 +553,11 @@ mla_decode_partial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #endif
 }
 
-// Merge of the split partials.  One CTA per (head, token, quarter of the 512 output columns); the split
-// weights are computed once in shared memory, so the accumulation loop is a stream of independent
-// coalesced loads instead of a chain of dependent ones.
+// Merge of the split partials.
 constexpr int MAX_SPLITS = 1024;
 
-// One CTA per (head, query row): 512 threads.  The split weights are computed once; for the weighted sum the
+// One CTA per (head, query row): 512 threads (four CTAs of 128 threads per head, a quarter of the columns each,
+// measured slower: step 30.2 us against 29.3 us).  The split weights are computed once; for the weighted sum the
 // threads form eight groups that walk the splits with stride eight, each thread owning eight adjacent columns
 // (one 16-byte load per split, all of a thread's loads in flight together), and the partial sums meet in shared
 // memory.
