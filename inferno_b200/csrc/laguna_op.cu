@@ -104,13 +104,12 @@ glm_paged_decode_kernel(const float* __restrict__ q, const __half* __restrict__ 
 // whole rows per load instruction and the dot product closes with three shuffles; the 32 lane groups of a CTA keep
 // their own online softmax and merge once at the end.  A second kernel merges the splits and adds the current token,
 // which the reference also takes from its f32 buffers, not from the cache (attention_kernels.metal:374-387).
+// Threads per CTA and resident CTAs per SM.  Measured on the 64-head, 4 095-key case: 256 x 2 53.2 us, 128 x 4 (128
+// registers) 51.1 us, 128 x 3 with every lane group requesting its next key's rows before it works on the current one
+// (163 registers) 52.5 us.
 #ifndef INF_GLM_THREADS
-// Threads per CTA, resident CTAs per SM, and whether a lane group requests its next key's rows before it works on the
-// current one.  Measured on the 64-head, 4 095-key case: 256 x 2 without prefetch 53.2 us, 128 x 3 with prefetch
-// (163 registers) 52.5 us, 128 x 4 without (128 registers) 51.1 us.
 #define INF_GLM_THREADS 128
 #define INF_GLM_CTAS 4
-#define INF_GLM_PREFETCH 0
 #endif
 constexpr int GS_THREADS = INF_GLM_THREADS;
 constexpr int GS_GROUPS = GS_THREADS / 8;
@@ -147,17 +146,8 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
 #pragma unroll
         for (int c = 0; c < VC; ++c) vr[c] = __ldg(reinterpret_cast<const uint4*>(pv + r * vdim + (c * 8 + gl) * 8));
     };
-#if INF_GLM_PREFETCH
-    if (k_begin + group < k_end) request(k_begin + group, kraw, vraw);
-#endif
     for (int key = k_begin + group; key < k_end; key += GS_GROUPS) {
-#if INF_GLM_PREFETCH
-        uint4 knext[KC], vnext[VC];
-        const bool more = key + GS_GROUPS < k_end;
-        if (more) request(key + GS_GROUPS, knext, vnext);
-#else
         request(key, kraw, vraw);
-#endif
         float dot = 0.f;
 #pragma unroll
         for (int c = 0; c < KC; ++c) {
@@ -188,14 +178,6 @@ glm_paged_decode_split_kernel(const float* __restrict__ q, const __half* __restr
                 acc[c][2 * i + 1] = fmaf(acc[c][2 * i + 1], rs, w * f.y);
             }
         }
-#if INF_GLM_PREFETCH
-        if (more) {
-#pragma unroll
-            for (int c = 0; c < KC; ++c) kraw[c] = knext[c];
-#pragma unroll
-            for (int c = 0; c < VC; ++c) vraw[c] = vnext[c];
-        }
-#endif
     }
     // merge the 32 groups of the CTA, 8 at a time through shared memory
     __shared__ float sm[GS_GROUPS], sl[GS_GROUPS];
