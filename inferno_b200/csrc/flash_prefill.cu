@@ -19,7 +19,8 @@
 //                the two streams share; the softmax warpgroup copies its row out at once, which frees the
 //                buffer for the other stream's next QK^T
 //   softmax      row maximum, lazy rescale of O (only when a maximum grew by more than 2^8), exponentials;
-//                the streams take turns at the exponentials, which keeps them in anti-phase; P goes back to
+//                in the dense instantiation the streams take turns at the exponentials, which keeps them in
+//                anti-phase; P goes back to
 //                TMEM as packed fp16, each 64-key half handed to the PV issuer as soon as it is written
 //   O += P V     TS MMA, A = P from TMEM, B = V MN-major straight from its [key][dim] tile
 // TMEM (512 columns): S 128, then per stream P 64 (fp16 pairs) and O 128 (fp32).
@@ -570,7 +571,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 KP_ADD(2);
                 // The two streams take turns at the exponentials (0, 1, 0, 1, ... while both have tiles left): the
                 // special-function unit is shared, and the turn order is the order in which the issuers serve them.
-                if (s == 0 ? (j >= 1 && j - 1 < n_other) : (j < n_other)) {
+                // Only the dense instantiation: for the long MLA prompt turns and no turns measure the same
+                // (19.8-19.9 ms), while the 2 048-token paged prompt runs 2.5 % faster without them (88.9 against
+                // 91.1 us a step).
+                if (!PAGED && (s == 0 ? (j >= 1 && j - 1 < n_other) : (j < n_other))) {
                     if (!mbar_wait(&sm_done[s ^ 1], ((uint32_t)(s == 0 ? j - 1 : j)) & 1u)) {
                         ok = false;
                         break;
