@@ -167,6 +167,15 @@ def test_long_sequence_spans_several_ctas(be):
     _decode_case(be, [5000, 2049, 4096], 48, 8, [64, 512, 2048], SEED0 + 33)
 
 
+def test_mid_sized_batch_takes_runs_of_two_chunks(be):
+    """Ten sequences of up to 9 000 keys: too few for two waves of four-chunk runs, so every CTA streams two 512-key
+    chunks (a single long sequence takes one chunk per CTA, the benchmark's batch of 32 four)."""
+    rng = np.random.RandomState(SEED0 + 35)
+    lens = [int(n) for n in rng.randint(600, 9001, size=10)]
+    lens[3] = 9000
+    _decode_case(be, lens, 48, 8, [512], SEED0 + 36)
+
+
 def test_length_beyond_max_len_is_cut_and_reported(be):
     """lens[b] > max_len with no host mirror (what a replayed graph with stale sizes would do): the kernels cut the
     sequence to what the launch was sized for, never touch another sequence's partials, and inf_flush reports it."""
