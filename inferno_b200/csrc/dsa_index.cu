@@ -171,8 +171,7 @@ __device__ __forceinline__ void tf32_split(const float4& v, uint4& hi, float4& l
 __global__ void __launch_bounds__(TU_THREADS, 1)
 dsa_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_keys, const float* __restrict__ q,
                        const float* __restrict__ weights, const float* __restrict__ current_key,
-                       float* __restrict__ scores, int past, int heads, int nbuf, int tmem_cols, int* status,
-                       const float* __restrict__ past_keys) {
+                       float* __restrict__ scores, int past, int heads, int nbuf, int tmem_cols, int* status) {
     extern __shared__ __align__(1024) uint8_t usm[];
     __shared__ uint64_t k_full[2], a_ready[4], mma_done;
     __shared__ uint32_t tmem_slot;
@@ -194,15 +193,6 @@ dsa_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_keys, const float*
     if (warp == 4) {
         tmem_alloc(&tmem_slot, (uint32_t)tmem_cols);
         tmem_relinquish();
-    }
-    // The cached index keys never change, so this CTA's first tiles are asked into L2 while the kernel before this
-    // one (under a programmatic dependent launch) is still running; the loads proper follow the wait.
-    if (tid < nbuf && (int)(blockIdx.x + tid * gridDim.x) * TU_TOKENS < past) {
-        const int row0 = (int)(blockIdx.x + tid * gridDim.x) * TU_TOKENS;
-        const uint32_t bytes = (uint32_t)min(TU_TOKENS, past - row0) * TU_DIM * 4;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(past_keys + ((size_t)b * past + row0) * TU_DIM),
-                     "r"(bytes)
-                     : "memory");
     }
     inf_pdl_wait();
     inf_pdl_release();
@@ -882,8 +872,7 @@ extern "C" int32_t inf_dsa_scores(inf_ctx* ctx, const float* q, const float* wei
             dim3 grid((tiles + per_cta - 1) / per_cta, batch);
             inf_prof_scope prof(ctx, "dsa_scores_kernel");
             INF_CUDA(ctx, inf_launch_pdl(dsa_scores_umma_kernel, grid, dim3(TU_THREADS), smem_umma, ctx->stream, tm_keys, q,
-                                         weights, current_key, scores, past_tokens, heads, nbuf, tmem_cols, ctx->status,
-                                         past_keys));
+                                         weights, current_key, scores, past_tokens, heads, nbuf, tmem_cols, ctx->status));
             return INF_OK;
         }
     }
